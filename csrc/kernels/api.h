@@ -1,0 +1,61 @@
+// C ABI of the sm_100a kernel library (libnkipy_b200_kernels.so).
+// Every entry point takes raw device pointers and a CUDA stream handle, launches
+// asynchronously and returns 0 or a negative argument error / positive CUDA
+// error code.  Python binds these through ctypes (nkipy_b200/ops/_lib.py).
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace nkb {
+int encode_tmap_bf16_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                        uint32_t box_inner, uint32_t box_outer);
+int encode_tmap_bf16(CUtensorMap* m, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                     const uint32_t* box);
+int* status_word();
+int num_sms();
+}  // namespace nkb
+
+extern "C" {
+int nkb_init();
+// Reads (and optionally clears) the device status word; non-zero = a bounded
+// wait inside a kernel gave up (code in the low byte, CTA index above it).
+int nkb_status(int reset);
+
+int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, int cols, int k, long long lda, long long ldb,
+                  long long ldo, int transpose_out, int out_fp32, int splits, long long split_stride, int gated,
+                  int gate_off, const void* bias, int bias_on_rows, const void* residual, int block_n, int max_ctas,
+                  void* stream);
+int nkb_gemm_effective_splits(int k, int splits);
+
+int nkb_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, float eps, void* stream);
+int nkb_add_rmsnorm(const float* partials, int splits, long long split_stride, const void* x, const void* residual_in,
+                    const void* bias, const void* w, void* residual_out, void* normed_out, int rows, int hidden,
+                    float eps, void* stream);
+int nkb_silu_mul(const void* gate_up, void* out, int rows, int inter, float limit, float alpha, void* stream);
+int nkb_embedding(const int* ids, const void* table, void* out, int n, int hidden, int vocab, void* stream);
+int nkb_rope_kv_append(const void* qkv_bf16, const float* qkv_partials, int splits, long long split_stride,
+                       const void* bias, const int* positions, const int* slots, const float* cos_sin,
+                       const void* q_norm_w, const void* k_norm_w, float norm_eps, void* q_out, void* k_cache,
+                       void* v_cache, int tokens, int nq, int nkv, int head_dim, int max_pos, int block_size,
+                       void* stream);
+int nkb_decode_advance(int* context_lens, const int* block_table, int* positions, int* slots, int batch, int q_len,
+                       int max_blocks, int block_size, void* stream);
+int nkb_argmax(const void* logits, int is_fp32, int* out_ids, float* out_vals, int rows, int vocab, long long ld,
+               void* stream);
+int nkb_sample(const void* logits, int is_fp32, int* out_ids, int rows, int vocab, long long ld, float temperature,
+               int top_k, float top_p, unsigned long long seed, unsigned long long step, void* stream);
+int nkb_router_topk(const void* logits, int is_fp32, float* weights, int* experts, int tokens, int num_experts,
+                    int top_k, int mode, void* stream);
+
+int nkb_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                          const int* context_lens, void* out, float* scratch, int batch, int q_len, int nq, int nkv,
+                          int head_dim, int block_size, int num_blocks, int max_blocks_per_seq, float scale,
+                          int window, const float* sinks, int num_splits, void* stream);
+long long nkb_paged_attn_decode_scratch_floats(int batch, int q_len, int nq, int head_dim, int num_splits);
+
+int nkb_flash_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                           const int* q_start, const int* q_lens, const int* context_lens, void* out, int batch,
+                           int total_q, int max_q_len, int nq, int nkv, int head_dim, int block_size, int num_blocks,
+                           int max_blocks_per_seq, float scale, int causal, int window, const float* sinks,
+                           void* stream);
+}

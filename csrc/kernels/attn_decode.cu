@@ -1,0 +1,407 @@
+// Paged-KV decode attention (flash-decoding) for sm_100a.
+//
+// One CTA per (kv split, kv head, sequence).  The query rows of a CTA are the
+// q_len new tokens x the GQA group of this kv head (at most 16 rows), held as
+// MMA A-fragments in registers for the whole kernel.  Each of the four warps
+// walks its own subset of 32-token KV pages: the page is fetched with TMA
+// (128-byte swizzle, through the per-sequence block table) into a private
+// 3-stage shared-memory ring, scores and P*V run on the tensor cores with
+// m16n8k16 fragments fed by ldmatrix, and the online-softmax state stays in
+// registers.  Warps (and, for long contexts, splits) are merged at the end.
+//
+// This op is bound by HBM traffic (the whole KV cache is read once per step),
+// which is why it uses register-fragment MMAs instead of tcgen05: a 128-row
+// TMEM tile would be 8-32x padded for 4-16 query rows, and the per-row softmax
+// would be serialised on a handful of threads.
+//
+// KV cache layout: [num_blocks, kv_heads, block_size = 32, head_dim] bf16, so a
+// page of one head is one contiguous 32 x head_dim slab.
+//
+// Reference parity: the decode branch of attention_kernel in
+// examples/models/qwen3/kernels/attention.py:104-137 (scores against the whole
+// static cache with an additive mask); sliding window and attention sinks from
+// examples/models/gpt_oss/kernels/attention.py:116-148.  Paging, block tables
+// and prefix sharing are new here.
+#include "common.cuh"
+#include "api.h"
+#include <math.h>
+
+namespace nkb {
+
+constexpr int kPage = 32;
+constexpr int kDecStages = 3;
+constexpr int kDecWarps = 4;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  const int* block_table;
+  const int* context_lens;
+  __nv_bfloat16* out;
+  float* scratch;
+  const float* sinks;
+  int* status;
+  int batch, q_len, nq, nkv, group, max_blocks, num_splits, window;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kDecWarps * 32)
+paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                         const DecodeParams p) {
+  constexpr int NH = D / 64;                 // 128-byte halves per row
+  constexpr int kHalfBytes = kPage * 128;    // one [32 x 64] swizzled slab
+  constexpr int kMatBytes = NH * kHalfBytes; // K (or V) page
+  constexpr int kStageBytes = 2 * kMatBytes;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bars[kDecWarps][kDecStages];
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int ctx = p.context_lens[b];
+  const int rows = p.q_len * p.group;
+
+  if (threadIdx.x == 0) {
+    for (int w = 0; w < kDecWarps; ++w)
+      for (int s = 0; s < kDecStages; ++s) mbar_init(&bars[w][s], 1);
+    abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  __syncthreads();
+
+  // ---- page range of this split
+  int first_tok = 0;
+  if (p.window > 0) first_tok = max(0, ctx - p.q_len - p.window + 1);
+  const int page_lo = first_tok / kPage, page_hi = (ctx + kPage - 1) / kPage;
+  const int npages = max(page_hi - page_lo, 0);
+  const int per_split = (npages + p.num_splits - 1) / p.num_splits;
+  const int p0 = page_lo + split * per_split;
+  const int p1 = min(page_hi, p0 + per_split);
+  const int* table = p.block_table + (long long)b * p.max_blocks;
+
+  // ---- query fragments
+  uint32_t qf[D / 16][4];
+  {
+    const int r0 = g, r1 = g + 8;
+    const __nv_bfloat16* q0 = nullptr;
+    const __nv_bfloat16* q1 = nullptr;
+    if (r0 < rows)
+      q0 = p.q + (((long long)b * p.q_len + r0 / p.group) * p.nq + kvh * p.group + r0 % p.group) * D;
+    if (r1 < rows)
+      q1 = p.q + (((long long)b * p.q_len + r1 / p.group) * p.nq + kvh * p.group + r1 % p.group) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t) : 0u;
+      qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t) : 0u;
+      qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t) : 0u;
+      qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  // last visible kv position (inclusive) and first visible one, per owned row
+  const int lim0 = ctx - p.q_len + (g < rows ? g / p.group : 0);
+  const int lim1 = ctx - p.q_len + (g + 8 < rows ? (g + 8) / p.group : 0);
+  const int low0 = p.window > 0 ? lim0 - p.window + 1 : 0;
+  const int low1 = p.window > 0 ? lim1 - p.window + 1 : 0;
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  uint8_t* my_smem = smem + warp * kDecStages * kStageBytes;
+  auto issue = [&](int page, int stage) {
+    if (lane == 0) {
+      const int blk = table[page];
+      uint8_t* dst = my_smem + stage * kStageBytes;
+      mbar_expect_tx(&bars[warp][stage], kStageBytes);
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        tma_load_4d(dst + h * kHalfBytes, &tmK, &bars[warp][stage], h * 64, 0, kvh, blk);
+        tma_load_4d(dst + kMatBytes + h * kHalfBytes, &tmV, &bars[warp][stage], h * 64, 0, kvh, blk);
+      }
+    }
+  };
+
+  // ---- prologue
+  const int my_first = p0 + warp;
+#pragma unroll
+  for (int s = 0; s < kDecStages; ++s) {
+    const int pg = my_first + s * kDecWarps;
+    if (pg < p1) issue(pg, s);
+  }
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int pg = my_first; pg < p1; pg += kDecWarps) {
+    bool ok = mbar_wait(&bars[warp][stage], phase, &abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+    if (!__all_sync(0xffffffffu, ok)) break;
+    const uint32_t kbase = smem_u32(my_smem + stage * kStageBytes);
+    const uint32_t vbase = kbase + kMatBytes;
+
+    // S = Q K^T for the 32 tokens of the page
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int kp = 0; kp < D / 32; ++kp) {
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int tok = nt * 8 + (lane & 7);
+        const int chunk = 4 * kp + (lane >> 3);
+        const uint32_t addr = kbase + (chunk >> 3) * kHalfBytes + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(addr, b0, b1, b2, b3);
+        mma_16816(s[nt], qf[2 * kp], b0, b1);
+        mma_16816(s[nt], qf[2 * kp + 1], b2, b3);
+      }
+    }
+    // online softmax (base-2 domain)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int tok = pg * kPage + nt * 8 + 2 * t + e;
+        float v0 = s[nt][e] * p.scale_log2, v1 = s[nt][2 + e] * p.scale_log2;
+        if (tok > lim0 || tok < low0) v0 = -INFINITY;
+        if (tok > lim1 || tok < low1) v1 = -INFINITY;
+        s[nt][e] = v0;
+        s[nt][2 + e] = v1;
+        mx0 = fmaxf(mx0, v0);
+        mx1 = fmaxf(mx1, v1);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float base0 = (mn0 == -INFINITY) ? 0.f : mn0, base1 = (mn1 == -INFINITY) ? 0.f : mn1;
+    const float a0 = exp2f(m0 - base0), a1 = exp2f(m1 - base1);
+    m0 = mn0;
+    m1 = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        s[nt][e] = exp2f(s[nt][e] - base0);
+        s[nt][2 + e] = exp2f(s[nt][2 + e] - base1);
+        sum0 += s[nt][e];
+        sum1 += s[nt][2 + e];
+      }
+    }
+    l0 = l0 * a0 + sum0;
+    l1 = l1 * a1 + sum1;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= a0; o[i][1] *= a0;
+      o[i][2] *= a1; o[i][3] *= a1;
+    }
+    // O += P V
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16x2(s[2 * j][0], s[2 * j][1]);
+      pa[1] = pack_bf16x2(s[2 * j][2], s[2 * j][3]);
+      pa[2] = pack_bf16x2(s[2 * j + 1][0], s[2 * j + 1][1]);
+      pa[3] = pack_bf16x2(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < D / 16; ++dp) {
+        const int tok = 16 * j + ((lane >> 3) & 1) * 8 + (lane & 7);
+        const int chunk = 2 * dp + (lane >> 4);
+        const uint32_t addr = vbase + (chunk >> 3) * kHalfBytes + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
+        uint32_t v0, v1, v2, v3;
+        ldsm_x4_t(addr, v0, v1, v2, v3);
+        mma_16816(o[2 * dp], pa, v0, v1);
+        mma_16816(o[2 * dp + 1], pa, v2, v3);
+      }
+    }
+    __syncwarp();
+    const int next = pg + kDecStages * kDecWarps;
+    if (next < p1) issue(next, stage);
+    if (++stage == kDecStages) { stage = 0; phase ^= 1u; }
+  }
+  // quad-reduce the row sums
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  if (abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  __syncthreads();  // every load consumed: the ring can be reused as merge space
+
+  // ---- merge the four warps through shared memory
+  float* mo = reinterpret_cast<float*>(smem);             // [warp][16][D]
+  float* mm = mo + kDecWarps * 16 * D;                    // [warp][16]
+  float* ml = mm + kDecWarps * 16;                        // [warp][16]
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    float* r0 = mo + (warp * 16 + g) * D + i * 8 + 2 * t;
+    float* r1 = mo + (warp * 16 + g + 8) * D + i * 8 + 2 * t;
+    r0[0] = o[i][0]; r0[1] = o[i][1];
+    r1[0] = o[i][2]; r1[1] = o[i][3];
+  }
+  if (t == 0) {
+    mm[warp * 16 + g] = m0; mm[warp * 16 + g + 8] = m1;
+    ml[warp * 16 + g] = l0; ml[warp * 16 + g + 8] = l1;
+  }
+  __syncthreads();
+  float* part = p.scratch
+      ? p.scratch + (((long long)b * p.nkv + kvh) * p.num_splits + split) * (16 * D + 32)
+      : nullptr;
+  for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+    const int r = idx / D, d = idx % D;
+    float mf = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) mf = fmaxf(mf, mm[w * 16 + r]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float mw = mm[w * 16 + r];
+      const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - mf);
+      acc += sc * mo[(w * 16 + r) * D + d];
+      l += sc * ml[w * 16 + r];
+    }
+    if (p.num_splits == 1) {
+      const int head = kvh * p.group + r % p.group;
+      if (p.sinks) {
+        const float sk = p.sinks[head] * 1.4426950408889634f;
+        const float m2 = fmaxf(mf, sk);
+        const float sc = (mf == -INFINITY) ? 0.f : exp2f(mf - m2);
+        acc *= sc;
+        l = l * sc + exp2f(sk - m2);
+      }
+      const float v = l > 0.f ? acc / l : 0.f;
+      p.out[(((long long)b * p.q_len + r / p.group) * p.nq + head) * D + d] = __float2bfloat16(v);
+    } else {
+      part[r * D + d] = acc;
+      if (d == 0) {
+        part[16 * D + r] = mf;
+        part[16 * D + 16 + r] = l;
+      }
+    }
+  }
+}
+
+template <int D>
+__global__ void decode_combine_kernel(const DecodeParams p) {
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int rows = p.q_len * p.group;
+  const float* base = p.scratch + (((long long)b * p.nkv + kvh) * p.num_splits) * (16 * D + 32);
+  for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+    const int r = idx / D, d = idx % D;
+    float mf = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) mf = fmaxf(mf, base[s * (16 * D + 32) + 16 * D + r]);
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float* ps = base + s * (16 * D + 32);
+      const float ms = ps[16 * D + r];
+      const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - mf);
+      acc += sc * ps[r * D + d];
+      l += sc * ps[16 * D + 16 + r];
+    }
+    const int head = kvh * p.group + r % p.group;
+    if (p.sinks) {
+      const float sk = p.sinks[head] * 1.4426950408889634f;
+      const float m2 = fmaxf(mf, sk);
+      const float sc = (mf == -INFINITY) ? 0.f : exp2f(mf - m2);
+      acc *= sc;
+      l = l * sc + exp2f(sk - m2);
+    }
+    const float v = l > 0.f ? acc / l : 0.f;
+    p.out[(((long long)b * p.q_len + r / p.group) * p.nq + head) * D + d] = __float2bfloat16(v);
+  }
+}
+
+template <int D>
+static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t s) {
+  constexpr int kStageBytes = 2 * (D / 64) * kPage * 128;
+  constexpr int smem = kDecWarps * kDecStages * kStageBytes + 1024;
+  static_assert(kDecWarps * kDecStages * kStageBytes >= int((kDecWarps * 16 * D + kDecWarps * 32) * sizeof(float)),
+                "merge space must fit in the KV ring");
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e =
+        cudaFuncSetAttribute(paged_attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return int(e);
+    attr_set = true;
+  }
+  dim3 grid(p.num_splits, p.nkv, p.batch);
+  paged_attn_decode_kernel<D><<<grid, kDecWarps * 32, smem, s>>>(tk, tv, p);
+  if (p.num_splits > 1) {
+    dim3 g2(p.nkv, p.batch);
+    decode_combine_kernel<D><<<g2, 128, 0, s>>>(p);
+  }
+  return int(cudaGetLastError());
+}
+
+}  // namespace nkb
+
+using namespace nkb;
+
+extern "C" long long nkb_paged_attn_decode_scratch_floats(int batch, int q_len, int nq, int head_dim,
+                                                          int num_splits) {
+  (void)q_len;
+  if (num_splits <= 1) return 0;
+  // upper bound: one slot per (sequence, kv head, split); kv heads <= nq
+  return (long long)batch * nq * num_splits * (16 * head_dim + 32);
+}
+
+extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                     const int* context_lens, void* out, float* scratch, int batch, int q_len, int nq,
+                                     int nkv, int head_dim, int block_size, int num_blocks, int max_blocks_per_seq,
+                                     float scale, int window, const float* sinks, int num_splits, void* stream) {
+  if (batch <= 0) return 0;
+  if (block_size != kPage || nq % nkv != 0) return -2;
+  const int group = nq / nkv;
+  if (q_len * group > 16) return -2;
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && !scratch) return -2;
+  if (!status_word() && nkb_init() != 0) return -1;
+  DecodeParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.block_table = block_table;
+  p.context_lens = context_lens;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.scratch = num_splits > 1 ? scratch : nullptr;
+  p.sinks = sinks;
+  p.status = status_word();
+  p.batch = batch; p.q_len = q_len; p.nq = nq; p.nkv = nkv; p.group = group;
+  p.max_blocks = max_blocks_per_seq; p.num_splits = num_splits; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap tk, tv;
+  const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(kPage), uint64_t(nkv), uint64_t(num_blocks)};
+  const uint64_t strides[3] = {uint64_t(head_dim) * 2, uint64_t(head_dim) * kPage * 2,
+                               uint64_t(head_dim) * kPage * nkv * 2};
+  const uint32_t box[4] = {64, uint32_t(kPage), 1, 1};
+  if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
+  if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (head_dim == 128) return launch_decode<128>(tk, tv, p, s);
+  if (head_dim == 64) return launch_decode<64>(tk, tv, p, s);
+  return -2;
+}

@@ -1,0 +1,427 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   D[r, c] = sum_k A[r, k] * B[c, k]          (both operands K-major, bf16)
+//
+// * operands are staged by TMA (128-byte swizzle, 64-wide K slabs) into a
+//   multi-stage shared-memory ring,
+// * one elected thread issues tcgen05.mma (M=128, N=BN, K=16) into a
+//   double-buffered TMEM accumulator,
+// * four epilogue warps read the accumulator back with tcgen05.ld while the MMA
+//   warp already works on the next tile.
+//
+// The same kernel serves both orientations used by the models:
+//   "normal"  A = activations [tokens, K], B = weights [features, K]  (prefill)
+//   "swapped" A = weights [features, K],  B = activations [tokens, K]  (decode:
+//             the 128-row MMA dimension is filled by features, the token count
+//             becomes the narrow N dimension), output written transposed.
+// Optional fusions: split-K partials (fp32), bias, residual add, and the SwiGLU
+// gate (two weight tiles per stage, silu(g)*u in the epilogue).
+//
+// Reference parity: this is the `dot` lowering target of the tracing frontend
+// (nkipy/src/nkipy/core/ops/_hlo_impls.py:633-710 in the reference lowers
+// np.matmul to an HLO dot executed by the Neuron tensor engine).
+#include "common.cuh"
+#include "api.h"
+
+namespace nkb {
+
+constexpr int kBlockK = 64;           // bf16 elements per K slab = one 128B swizzle row
+constexpr int kTileRows = 128;        // UMMA M
+constexpr int kATileBytes = kTileRows * kBlockK * 2;
+constexpr int kMaxStages = 12;
+constexpr int kGemmThreads = 192;     // warp0 TMA, warp1 MMA, warps2-5 epilogue
+
+struct GemmArgs {
+  int rows, cols, k;
+  int splits, kb_per_split, kb_total;
+  int num_row_tiles, num_col_tiles;
+  int gated;        // 0 none, 1 = A operand holds [gate; up], 2 = B operand holds [gate; up]
+  int gate_off;     // row offset of the "up" half inside the gated operand
+  int transpose_out;
+  int out_fp32;
+  int bias_on_rows;
+  int stages;
+  long long ldo;
+  long long split_stride;
+  void* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int* status;
+};
+
+struct GemmCtrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ void decode_tile(const GemmArgs& a, int w, int& row_tile, int& col_tile, int& split) {
+  split = w % a.splits;
+  int t = w / a.splits;
+  constexpr int kGroup = 16;
+  int per_group = kGroup * a.num_col_tiles;
+  int g = t / per_group;
+  int first = g * kGroup;
+  int gsz = min(a.num_row_tiles - first, kGroup);
+  int in = t - g * per_group;
+  row_tile = first + in % gsz;
+  col_tile = in / gsz;
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int a_tiles = (args.gated == 1) ? 2 : 1;
+  const int b_tiles = (args.gated == 2) ? 2 : 1;
+  constexpr int kBTileBytes = BN * kBlockK * 2;
+  const int stage_bytes = a_tiles * kATileBytes + b_tiles * kBTileBytes;
+  const int stages = args.stages;
+  GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(tiles + stages * stage_bytes);
+
+  const int acc_cols = BN * (args.gated ? 2 : 1);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < uint32_t(2 * acc_cols)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&ctrl->full[s], 1);
+      mbar_init(&ctrl->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctrl->tfull[i], 1);
+      mbar_init(&ctrl->tempty[i], 4);
+    }
+    ctrl->abort = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctrl->tmem_base, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  volatile int* abort_flag = &ctrl->abort;
+
+  const int total_work = args.num_row_tiles * args.num_col_tiles * args.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
+      int rt, ct, sp;
+      decode_tile(args, w, rt, ct, sp);
+      const int row0 = rt * kTileRows, col0 = ct * BN;
+      const int kb0 = sp * args.kb_per_split;
+      const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        bool ok = mbar_wait(&ctrl->empty[stage], phase ^ 1u, abort_flag, args.status, ERR_WAIT_SMEM_EMPTY);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        if (lane == 0) {
+          uint8_t* a_ptr = tiles + stage * stage_bytes;
+          uint8_t* b_ptr = a_ptr + a_tiles * kATileBytes;
+          mbar_expect_tx(&ctrl->full[stage], stage_bytes);
+          tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0);
+          if (args.gated == 1)
+            tma_load_2d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0);
+          tma_load_2d(b_ptr, &tmB, &ctrl->full[stage], kb * kBlockK, col0);
+          if (args.gated == 2)
+            tma_load_2d(b_ptr + kBTileBytes, &tmB, &ctrl->full[stage], kb * kBlockK, args.gate_off + col0);
+        }
+        __syncwarp();
+        if (++stage == stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(kTileRows, BN, 0, 0);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool alive = true;
+    for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
+      int rt, ct, sp;
+      decode_tile(args, w, rt, ct, sp);
+      const int kb0 = sp * args.kb_per_split;
+      const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
+      bool ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
+      if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t d0 = tmem_base + uint32_t(acc * acc_cols);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
+          const uint32_t b_addr = a_addr + a_tiles * kATileBytes;
+          const uint64_t da = make_smem_desc_sw128(a_addr, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(b_addr, 0, 1024);
+          const uint64_t da1 = make_smem_desc_sw128(a_addr + kATileBytes, 0, 1024);
+          const uint64_t db1 = make_smem_desc_sw128(b_addr + kBTileBytes, 0, 1024);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = uint64_t(k * 2);  // 16 bf16 = 32 bytes, >>4
+            umma_f16(d0, da + koff, db + koff, idesc, accum);
+            if (args.gated == 1) umma_f16(d0 + BN, da1 + koff, db + koff, idesc, accum);
+            if (args.gated == 2) umma_f16(d0 + BN, da + koff, db1 + koff, idesc, accum);
+          }
+          umma_commit(&ctrl->empty[stage]);
+        }
+        __syncwarp();
+        if (++stage == stages) { stage = 0; phase ^= 1u; }
+      }
+      if (!alive) break;
+      if (lane == 0) umma_commit(&ctrl->tfull[acc]);
+      __syncwarp();
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may touch
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      int rt, ct, sp;
+      decode_tile(args, w, rt, ct, sp);
+      const int row = rt * kTileRows + quad * 32 + lane;
+      const int col0 = ct * BN;
+      bool ok = mbar_wait(&ctrl->tfull[acc], acc_phase, abort_flag, args.status, ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      tc_fence_after();
+      const uint32_t t0 = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * acc_cols);
+      const bool row_ok = row < args.rows;
+      float* out_f = reinterpret_cast<float*>(args.out) + (args.out_fp32 ? sp * args.split_stride : 0);
+      __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(args.out);
+      float bias_r = 0.f;
+      if (args.bias && args.bias_on_rows && row_ok && sp == 0) bias_r = __bfloat162float(args.bias[row]);
+
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t0 + c, v);
+        if (args.gated) {
+          uint32_t u[32];
+          tmem_ld_32x32(t0 + BN + c, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = __float_as_uint(silu_f(__uint_as_float(v[j])) * __uint_as_float(u[j]));
+        } else {
+          tmem_ld_wait();
+        }
+        if (c + 32 >= BN) {
+          // accumulator fully read: hand it back to the MMA warp before the stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctrl->tempty[acc]);
+        }
+        const int cbase = col0 + c;
+        if (cbase >= args.cols) continue;
+        if (args.bias && sp == 0) {
+          if (args.bias_on_rows) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias_r);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cbase + j < args.cols)
+                v[j] = __float_as_uint(__uint_as_float(v[j]) + __bfloat162float(args.bias[cbase + j]));
+          }
+        }
+        if (args.transpose_out) {
+          // out[col * ldo + row]: consecutive lanes hold consecutive rows -> coalesced
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = cbase + j;
+              if (col < args.cols) {
+                const long long idx = (long long)col * args.ldo + row;
+                float x = __uint_as_float(v[j]);
+                if (args.out_fp32) {
+                  out_f[idx] = x;
+                } else {
+                  if (args.residual) x += __bfloat162float(args.residual[idx]);
+                  out_h[idx] = __float2bfloat16(x);
+                }
+              }
+            }
+          }
+        } else if (row_ok) {
+          const long long base = (long long)row * args.ldo + cbase;
+          const bool full = (cbase + 32 <= args.cols);
+          if (args.out_fp32) {
+            if (full && ((base & 3) == 0)) {
+              float4* p = reinterpret_cast<float4*>(out_f + base);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                p[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (cbase + j < args.cols) out_f[base + j] = __uint_as_float(v[j]);
+            }
+          } else {
+            if (full && ((base & 7) == 0)) {
+              uint32_t pk[16];
+              if (args.residual) {
+                const uint4* rp = reinterpret_cast<const uint4*>(args.residual + base);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 rr = rp[q];
+                  uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    float2 f = unpack_bf16x2(rw[e]);
+                    pk[q * 4 + e] = pack_bf16x2(__uint_as_float(v[q * 8 + 2 * e]) + f.x,
+                                                __uint_as_float(v[q * 8 + 2 * e + 1]) + f.y);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  pk[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+              }
+              uint4* p = reinterpret_cast<uint4*>(out_h + base);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) p[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j) {
+                if (cbase + j < args.cols) {
+                  float x = __uint_as_float(v[j]);
+                  if (args.residual) x += __bfloat162float(args.residual[base + j]);
+                  out_h[base + j] = __float2bfloat16(x);
+                }
+              }
+            }
+          }
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  if (*abort_flag) {
+    // let copies / MMAs that were already issued drain before shared memory goes away
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+template <int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
+                       cudaStream_t stream) {
+  const int a_tiles = args.gated == 1 ? 2 : 1, b_tiles = args.gated == 2 ? 2 : 1;
+  const int stage_bytes = a_tiles * kATileBytes + b_tiles * BN * kBlockK * 2;
+  const int budget = 232448 - 1024 - int(sizeof(GemmCtrl)) - 64;
+  int stages = budget / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return -3;
+  args.stages = stages;
+  const int smem = stages * stage_bytes + 1024 + int(sizeof(GemmCtrl)) + 64;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e != cudaSuccess) return int(e);
+    attr_set = true;
+  }
+  int total = args.num_row_tiles * args.num_col_tiles * args.splits;
+  int grid = total < max_ctas ? total : max_ctas;
+  gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(ta, tb, args);
+  return int(cudaGetLastError());
+}
+
+}  // namespace nkb
+
+using namespace nkb;
+
+// D[rows, cols] = A[rows(+gate), k] * B[cols(+gate), k]^T with the fusions described above.
+//   transpose_out: element (r, c) is stored at out[c * ldo + r] instead of out[r * ldo + c]
+//   out_fp32 + splits > 1: partial sums go to out[s * split_stride + ...] as fp32
+extern "C" int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, int cols, int k, long long lda,
+                             long long ldb, long long ldo, int transpose_out, int out_fp32, int splits,
+                             long long split_stride, int gated, int gate_off, const void* bias, int bias_on_rows,
+                             const void* residual, int block_n, int max_ctas, void* stream) {
+  if (!status_word() && nkb_init() != 0) return -1;
+  if (rows <= 0 || cols <= 0 || k <= 0) return -2;
+  if ((k & 7) || (lda & 7) || (ldb & 7)) return -2;
+  if (splits > 1 && !out_fp32) return -2;
+  if (gated && (splits > 1 || out_fp32)) return -2;
+  if (gated && block_n > 128) return -2;
+  GemmArgs args{};
+  args.rows = rows;
+  args.cols = cols;
+  args.k = k;
+  args.kb_total = (k + kBlockK - 1) / kBlockK;
+  if (splits < 1) splits = 1;
+  if (splits > args.kb_total) splits = args.kb_total;
+  args.kb_per_split = (args.kb_total + splits - 1) / splits;
+  args.splits = (args.kb_total + args.kb_per_split - 1) / args.kb_per_split;
+  args.num_row_tiles = (rows + kTileRows - 1) / kTileRows;
+  args.num_col_tiles = (cols + block_n - 1) / block_n;
+  args.gated = gated;
+  args.gate_off = gate_off;
+  args.transpose_out = transpose_out;
+  args.out_fp32 = out_fp32;
+  args.bias_on_rows = bias_on_rows;
+  args.ldo = ldo;
+  args.split_stride = split_stride;
+  args.out = out;
+  args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  args.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  args.status = status_word();
+  if (max_ctas <= 0 || max_ctas > num_sms()) max_ctas = num_sms();
+
+  CUtensorMap ta, tb;
+  const uint64_t a_rows = gated == 1 ? uint64_t(gate_off) + rows : rows;
+  const uint64_t b_rows = gated == 2 ? uint64_t(gate_off) + cols : cols;
+  if (encode_tmap_bf16_2d(&ta, A, k, a_rows, lda, kBlockK, kTileRows)) return -4;
+  if (encode_tmap_bf16_2d(&tb, B, k, b_rows, ldb, kBlockK, block_n)) return -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (block_n) {
+    case 32: return launch_gemm<32>(ta, tb, args, max_ctas, s);
+    case 64: return launch_gemm<64>(ta, tb, args, max_ctas, s);
+    case 128: return launch_gemm<128>(ta, tb, args, max_ctas, s);
+    case 256: return launch_gemm<256>(ta, tb, args, max_ctas, s);
+    default: return -2;
+  }
+}
+
+// Reports the number of split partials the launcher will really produce for a
+// requested split count (k-blocks are distributed in whole 64-wide slabs).
+extern "C" int nkb_gemm_effective_splits(int k, int splits) {
+  int kb_total = (k + kBlockK - 1) / kBlockK;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  int per = (kb_total + splits - 1) / splits;
+  return (kb_total + per - 1) / per;
+}

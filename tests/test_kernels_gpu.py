@@ -1,0 +1,257 @@
+"""Numerics of the hand-written sm_100a kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+from nkipy_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def randn(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1000, 1280, 520), (4096, 6144, 4096)])
+def test_gemm_normal(M, N, K):
+    x, w = randn(M, K), randn(N, K, scale=0.05)
+    y = ops.linear(x, w, swap=False)
+    ref = x.float() @ w.float().T
+    assert rel_err(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (16, 256, 128), (100, 1000, 520), (128, 6144, 4096)])
+def test_gemm_swapped(M, N, K):
+    x, w = randn(M, K), randn(N, K, scale=0.05)
+    y = ops.linear(x, w, swap=True)
+    ref = x.float() @ w.float().T
+    assert rel_err(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("swap,M", [(True, 64), (False, 512)])
+def test_gemm_splitk_bias_residual(swap, M):
+    N, K = 1024, 2048
+    x, w = randn(M, K), randn(N, K, scale=0.05)
+    bias, res = randn(N), randn(M, N)
+    parts = ops.linear(x, w, swap=swap, splits=4, bias=bias)
+    assert parts.dtype == torch.float32 and parts.shape[0] == 4
+    y = ops.reduce_partials(parts, residual=res)
+    ref = x.float() @ w.float().T + bias.float() + res.float()
+    assert rel_err(y, ref) < 1e-2
+    y2 = ops.linear(x, w, swap=swap, bias=bias, residual=res)
+    assert rel_err(y2, ref) < 1e-2
+
+
+@pytest.mark.parametrize("swap,M", [(True, 64), (False, 384)])
+def test_gemm_gated(swap, M):
+    I, K = 768, 512
+    x, w = randn(M, K), randn(2 * I, K, scale=0.05)
+    y = ops.linear(x, w, gated=True, swap=swap)
+    g, u = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    ref = torch.nn.functional.silu(g) * u
+    assert y.shape == (M, I)
+    assert rel_err(y, ref) < 1e-2
+
+
+def test_rmsnorm_and_fused_add():
+    rows, H = 70, 4096
+    x, w, r = randn(rows, H), randn(H), randn(rows, H)
+    y = ops.rmsnorm(x, w, 1e-5)
+    ref = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    assert rel_err(y, ref) < 5e-3
+    parts = torch.randn(3, rows, H, device=DEV)
+    ro, no = ops.add_rmsnorm(None, w, residual_in=r, partials=parts, eps=1e-5)
+    h = (parts.sum(0) + r.float()).to(torch.bfloat16)
+    assert rel_err(ro, h) < 1e-3
+    hf = h.float()
+    ref2 = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    assert rel_err(no, ref2) < 5e-3
+
+
+def test_silu_mul_embedding_argmax():
+    gu = randn(33, 2 * 1536)
+    y = ops.silu_mul(gu)
+    ref = torch.nn.functional.silu(gu[:, :1536].float()) * gu[:, 1536:].float()
+    assert rel_err(y, ref) < 5e-3
+    yc = ops.silu_mul(gu, limit=7.0, alpha=1.702)
+    g, u = gu[:, :1536].float().clamp(max=7.0), gu[:, 1536:].float().clamp(-7.0, 7.0)
+    assert rel_err(yc, (u + 1) * g * torch.sigmoid(1.702 * g)) < 5e-3
+    table = randn(1000, 256)
+    ids = torch.randint(0, 1000, (17,), device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    logits = randn(9, 128256)
+    assert torch.equal(ops.argmax(logits).long(), logits.float().argmax(-1))
+    lf = torch.randn(5, 1003, device=DEV)
+    assert torch.equal(ops.argmax(lf).long(), lf.argmax(-1))
+
+
+def test_router_topk_both_orders():
+    logits = torch.randn(50, 128, device=DEV)
+    w, e = ops.router_topk(logits, 8, "softmax_topk")
+    p = torch.softmax(logits, -1)
+    rw, re = p.topk(8, -1)
+    rw = rw / rw.sum(-1, keepdim=True)
+    assert torch.equal(e.long(), re)
+    assert torch.allclose(w, rw, atol=1e-5)
+    w2, e2 = ops.router_topk(logits.to(torch.bfloat16), 4, "topk_softmax")
+    v, re2 = logits.to(torch.bfloat16).float().topk(4, -1)
+    assert torch.allclose(w2, torch.softmax(v, -1), atol=1e-5)
+
+
+def test_sampling_respects_top_k():
+    logits = torch.randn(8, 5000, device=DEV)
+    top = logits.topk(5, -1).indices
+    for step in range(4):
+        ids = ops.sample(logits, temperature=0.8, top_k=5, top_p=0.95, seed=1, step=step)
+        assert all(int(ids[b]) in top[b].tolist() for b in range(8))
+    greedy = ops.sample(logits, temperature=1.0, top_k=1)
+    assert torch.equal(greedy.long(), logits.argmax(-1))
+
+
+def _make_cache(num_blocks, nkv, D):
+    k = torch.zeros(num_blocks, nkv, 32, D, device=DEV, dtype=torch.bfloat16)
+    return k, torch.zeros_like(k)
+
+
+def _fill_cache(B, ctx_lens, nkv, D, num_blocks):
+    kc, vc = _make_cache(num_blocks, nkv, D)
+    max_blocks = (max(ctx_lens) + 31) // 32
+    perm = torch.randperm(num_blocks)[: B * max_blocks].reshape(B, max_blocks)
+    table = perm.to(torch.int32).to(DEV)
+    ks, vs = [], []
+    for b in range(B):
+        k, v = randn(ctx_lens[b], nkv, D), randn(ctx_lens[b], nkv, D)
+        ks.append(k)
+        vs.append(v)
+        for t in range(ctx_lens[b]):
+            pass
+        nb = (ctx_lens[b] + 31) // 32
+        pad = nb * 32 - ctx_lens[b]
+        kp = torch.cat([k, torch.zeros(pad, nkv, D, device=DEV, dtype=k.dtype)]).reshape(nb, 32, nkv, D)
+        vp = torch.cat([v, torch.zeros(pad, nkv, D, device=DEV, dtype=k.dtype)]).reshape(nb, 32, nkv, D)
+        kc[table[b, :nb].long()] = kp.permute(0, 2, 1, 3)
+        vc[table[b, :nb].long()] = vp.permute(0, 2, 1, 3)
+    return kc, vc, table, ks, vs
+
+
+def _ref_attn(q, k, v, scale, q_pos0, causal=True, window=0, sinks=None):
+    return ops._ref_attention(q.float(), k.float(), v.float(), scale, q_pos0, causal, window, sinks)
+
+
+@pytest.mark.parametrize("nq,nkv,D,q_len,splits", [(32, 8, 128, 1, 1), (32, 8, 128, 1, 4), (8, 2, 128, 3, 2),
+                                                     (8, 8, 64, 1, 1), (4, 1, 128, 2, 0)])
+def test_paged_attn_decode(nq, nkv, D, q_len, splits):
+    B = 5
+    ctx = [1, 33, 700, 1025, 260][:B]
+    ctx = [max(c, q_len) for c in ctx]
+    kc, vc, table, ks, vs = _fill_cache(B, ctx, nkv, D, 256)
+    q = randn(B * q_len, nq * D)
+    lens = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    out = ops.paged_attn_decode(q, kc, vc, table, lens, scale, q_len=q_len, num_splits=splits)
+    for b in range(B):
+        ref = _ref_attn(q[b * q_len:(b + 1) * q_len].reshape(q_len, nq, D), ks[b], vs[b], scale, ctx[b] - q_len)
+        got = out[b * q_len:(b + 1) * q_len].reshape(q_len, nq, D)
+        assert rel_err(got, ref) < 2e-2, (b, ctx[b])
+
+
+def test_paged_attn_decode_window_and_sinks():
+    nq, nkv, D, B = 8, 2, 64, 3
+    ctx = [40, 300, 129]
+    kc, vc, table, ks, vs = _fill_cache(B, ctx, nkv, D, 64)
+    q = randn(B, nq * D)
+    sinks = torch.randn(nq, device=DEV)
+    lens = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    out = ops.paged_attn_decode(q, kc, vc, table, lens, scale, window=128, sinks=sinks, num_splits=2)
+    for b in range(B):
+        ref = _ref_attn(q[b:b + 1].reshape(1, nq, D), ks[b], vs[b], scale, ctx[b] - 1, True, 128, sinks)
+        assert rel_err(out[b].reshape(1, nq, D), ref) < 2e-2
+
+
+@pytest.mark.parametrize("nq,nkv,D", [(8, 2, 128), (4, 4, 64)])
+def test_flash_attn_prefill(nq, nkv, D):
+    ctx = [300, 128, 1000, 77]
+    q_lens = [300, 128, 488, 77]  # third sequence has a cached prefix of 512 tokens
+    B = len(ctx)
+    kc, vc, table, ks, vs = _fill_cache(B, ctx, nkv, D, 128)
+    total = sum(q_lens)
+    q = randn(total, nq * D)
+    starts = [0]
+    for x in q_lens[:-1]:
+        starts.append(starts[-1] + x)
+    t = lambda v: torch.tensor(v, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    out = ops.flash_attn_prefill(q, kc, vc, table, t(starts), t(q_lens), t(ctx), scale, max_q_len=max(q_lens))
+    for b in range(B):
+        qs = q[starts[b]:starts[b] + q_lens[b]].reshape(q_lens[b], nq, D)
+        ref = _ref_attn(qs, ks[b], vs[b], scale, ctx[b] - q_lens[b])
+        got = out[starts[b]:starts[b] + q_lens[b]].reshape(q_lens[b], nq, D)
+        assert rel_err(got, ref) < 2e-2, b
+
+
+def test_flash_attn_prefill_noncausal_window_sinks():
+    nq, nkv, D = 4, 2, 64
+    ctx = [200, 333]
+    B = 2
+    kc, vc, table, ks, vs = _fill_cache(B, ctx, nkv, D, 64)
+    q = randn(sum(ctx), nq * D)
+    t = lambda v: torch.tensor(v, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    sinks = torch.randn(nq, device=DEV)
+    o1 = ops.flash_attn_prefill(q, kc, vc, table, t([0, 200]), t(ctx), t(ctx), scale, max_q_len=333, causal=False)
+    o2 = ops.flash_attn_prefill(q, kc, vc, table, t([0, 200]), t(ctx), t(ctx), scale, max_q_len=333, window=128,
+                                sinks=sinks)
+    s = 0
+    for b in range(B):
+        qs = q[s:s + ctx[b]].reshape(ctx[b], nq, D)
+        assert rel_err(o1[s:s + ctx[b]].reshape(ctx[b], nq, D), _ref_attn(qs, ks[b], vs[b], scale, 0, False)) < 2e-2
+        assert rel_err(o2[s:s + ctx[b]].reshape(ctx[b], nq, D),
+                       _ref_attn(qs, ks[b], vs[b], scale, 0, True, 128, sinks)) < 2e-2
+        s += ctx[b]
+
+
+def test_rope_kv_append_matches_reference():
+    T, nq, nkv, D = 37, 8, 2, 128
+    W = (nq + 2 * nkv) * D
+    qkv = randn(T, W)
+    pos = torch.randint(0, 500, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(20 * 32, device=DEV)[:T].to(torch.int32)
+    tab = ops.rope_table(D, 512, 500000.0, device=DEV)
+    qn, kn = randn(D), randn(D)
+    kc, vc = _make_cache(20, nkv, D)
+    q = ops.rope_kv_append(qkv, pos, slots, tab, kc, vc, nq, nkv, D, q_norm_w=qn, k_norm_w=kn)
+    kc2, vc2 = _make_cache(20, nkv, D)
+    kc2, vc2 = kc2.cpu(), vc2.cpu()
+    q_ref = ops.rope_kv_append(qkv.cpu(), pos.cpu(), slots.cpu(), tab.cpu(), kc2, vc2, nq, nkv, D,
+                               q_norm_w=qn.cpu(), k_norm_w=kn.cpu())
+    assert rel_err(q.cpu(), q_ref) < 1e-2
+    assert rel_err(kc.cpu(), kc2) < 1e-2
+    assert torch.equal(vc.cpu(), vc2)
+    parts = torch.randn(3, T, W, device=DEV)
+    bias = randn(W)
+    kc3, vc3 = _make_cache(20, nkv, D)
+    q3 = ops.rope_kv_append(parts, pos, slots, tab, kc3, vc3, nq, nkv, D, bias=bias)
+    kc4, vc4 = _make_cache(20, nkv, D)
+    kc4, vc4 = kc4.cpu(), vc4.cpu()
+    q4 = ops.rope_kv_append(parts.cpu(), pos.cpu(), slots.cpu(), tab.cpu(), kc4, vc4, nq, nkv, D, bias=bias.cpu())
+    assert rel_err(q3.cpu(), q4) < 1e-2 and rel_err(vc3.cpu(), vc4) < 1e-2
+
+
+def test_decode_advance():
+    B = 4
+    ctx = torch.tensor([5, 31, 32, -1], device=DEV, dtype=torch.int32)
+    table = torch.arange(B * 3, device=DEV, dtype=torch.int32).reshape(B, 3) + 10
+    pos = torch.empty(B, device=DEV, dtype=torch.int32)
+    slots = torch.empty(B, device=DEV, dtype=torch.int32)
+    ops.decode_advance(ctx, table, pos, slots)
+    assert pos.tolist() == [5, 31, 32, 0]
+    assert slots.tolist() == [10 * 32 + 5, 13 * 32 + 31, 17 * 32 + 0, -1]
+    assert ctx.tolist() == [6, 32, 33, -1]
