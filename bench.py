@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Headline benchmark: greedy decode throughput of a Llama-3-8B-shaped model served
+with tensor parallelism over N GPUs of one node (batch 64, 1024-token prompts).
+
+    python bench.py --gpus 1 --steps 64 --warmup 8
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 64 --warmup 8
+
+A "step" is one decode step of the whole batch (one new token per sequence).  The
+device-timed value replays the captured decode graph K times between CUDA events
+(max over ranks); the end-to-end value drives the public ``GenerationEngine.step``
+API with a pinned-host -> device copy of the token ids and a device -> host read of
+the new ids every step.  Weights are random-init bf16, prompts are uniform random
+token ids (seed 0); the per-step working set (weights + KV cache) is far larger than
+L2, so no explicit L2 flush is needed between iterations.
+
+``--impl reference`` reports why the reference cannot run on this hardware;
+``--impl eager`` times the plain PyTorch (cuBLAS + NCCL) implementation of the same
+model as the baseline arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+REFERENCE_UNAVAILABLE = (
+    "reference (aws-neuron/nkipy) cannot be installed or run here: offline pip install fails "
+    "(workspace root has no installable package; the nkipy member needs grpc_tools.protoc) and every "
+    "module imports neuronxcc / needs libnrt and Trainium hardware"
+)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen3-30b-a3b"])
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    import torch
+
+    from nkipy_b200 import ops
+    from nkipy_b200.models import config as C
+    from nkipy_b200.models.engine import GenerationEngine, percentile
+    from nkipy_b200.models.transformer import TransformerLM
+    from nkipy_b200.models.weights import random_weights
+    from nkipy_b200.parallel.comm import TPGroup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    tp = TPGroup.from_env()
+    dev = tp.device
+    if dev.type != "cuda":
+        raise SystemExit("bench.py needs a CUDA device")
+    rank0 = tp.rank == 0
+
+    if args.model == "llama3-8b":
+        cfg = C.llama3_8b()
+        batch, prompt_len = args.batch or 64, args.prompt_len or 1024
+        parallelism = f"tp{world}"
+    else:
+        cfg = C.qwen3_30b_a3b()
+        batch, prompt_len = args.batch or 128, args.prompt_len or 512
+        parallelism = f"tp{world}-ep{world}"
+    debug = False
+    if args.layers:
+        cfg = cfg.scaled(num_layers=args.layers)
+        debug = True
+    K, W = args.steps, max(args.warmup, 3)
+    total_new = 2 * (K + W) + 4
+    max_seq = prompt_len + total_new + 32
+
+    torch.manual_seed(0)
+    t_build = time.perf_counter()
+    weights = random_weights(cfg, tp.rank, world, device=dev, seed=0, std=0.02)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab_size, (batch, prompt_len), generator=g)
+
+    if args.impl == "eager":
+        return run_eager(args, cfg, weights, prompts, tp, K, W, parallelism)
+
+    model = TransformerLM(cfg, weights, tp, device=dev)
+    del weights
+    torch.cuda.empty_cache()
+    engine = GenerationEngine(model, max_batch=batch, max_seq_len=max_seq, use_cuda_graph=not args.no_graph,
+                              enable_prefix_sharing=True)
+    build_s = time.perf_counter() - t_build
+
+    seqs = engine.add_requests(prompts.tolist())
+    tp.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    engine.prefill(seqs)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    ttft_p50 = percentile(engine.stats.ttft_s, 50)
+    ops.raise_on_device_error()
+
+    engine.prepare_decode(total_new)
+    launches_per_step = getattr(engine, "launches_per_step", None)
+
+    # ---------------- device-timed region: K graph replays, ids stay on the device
+    for _ in range(W):
+        engine.decode_step_device()
+    engine.advance_host_state(W)
+    sampler = ClockSampler(dev.index or 0)
+    tp.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(K):
+        engine.decode_step_device()
+    end.record()
+    torch.cuda.synchronize()
+    tp.barrier()
+    clocks = sampler.stop()
+    engine.advance_host_state(K)
+    dev_ms = tp.max_over_ranks(start.elapsed_time(end))
+    ops.raise_on_device_error()
+
+    # ---------------- end-to-end region: public step() API with H2D ids + D2H ids every step
+    host_ids = engine.ids_host
+    host_ids.copy_(engine.ids.cpu())
+    for _ in range(W):
+        host_ids.copy_(engine.step(host_ids))
+    engine.advance_host_state(W)
+    tp.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        host_ids.copy_(engine.step(host_ids))
+    torch.cuda.synchronize()
+    e2e_s = tp.max_over_ranks(time.perf_counter() - t0)
+    tp.barrier()
+    engine.advance_host_state(K)
+    ops.raise_on_device_error()
+
+    ms_per_step = dev_ms / K
+    value = batch * K / (dev_ms / 1e3)
+    e2e_value = batch * K / e2e_s
+    result = {
+        "metric": "decode tokens/s (Llama-3-8B-shaped, TP over N GPUs, batch 64, prompt 1024, greedy)"
+        if args.model == "llama3-8b" else "decode tokens/s (Qwen3-30B-A3B-shaped MoE, batch 128, prompt 512, greedy)",
+        "value": round(value, 2),
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": K,
+        "warmup": W,
+        "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (uniform random token ids seed 0; random-init weights N(0, 0.02))",
+        "impl": "ours",
+        "config": {
+            "model": cfg.name, "global_batch": batch, "seq_len": prompt_len, "parallelism": parallelism,
+            "layers": cfg.num_layers, "new_tokens_timed": K, "kv_cache": "paged, block 32, prefix sharing on",
+            "l2": "per-step working set (weights + KV) exceeds L2; no flush", "cuda_graph": not args.no_graph,
+        },
+        "ttft_p50_s": round(ttft_p50, 4),
+        "prefill_s": round(prefill_s, 4),
+        "prefill_tokens_per_s": round(batch * prompt_len / prefill_s, 1),
+        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": batch * 4,
+                "d2h_bytes_per_step": batch * 4, "ms_per_step": round(e2e_s * 1e3 / K, 4)},
+        "gpu_launches": (launches_per_step or 0) * K,
+        "launches_per_step": launches_per_step,
+        "clocks": clocks,
+        "build_s": round(build_s, 1),
+    }
+    if debug:
+        result["invalid"] = "debug run with a reduced layer count"
+    if rank0:
+        print(json.dumps(result), flush=True)
+    tp.barrier()
+    return 0
+
+
+def run_eager(args, cfg, weights, prompts, tp, K, W, parallelism):
+    """Baseline arm: plain PyTorch (cuBLAS, NCCL) decoder with a dense cache."""
+    import torch
+
+    from nkipy_b200.models.reference import EagerTransformer
+
+    dev = tp.device
+    model = EagerTransformer(cfg, weights, tp, device=dev, dtype=torch.bfloat16)
+    batch, prompt_len = prompts.shape
+    ids = prompts.to(dev)
+    tp.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    h = None
+    chunk = max(1, 16384 // prompt_len)
+    # dense-cache eager prefill has to run the whole batch at once (one cache tensor per layer)
+    h = model.forward(ids, 0)
+    nxt = model.greedy(h[:, -1])
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    pos = prompt_len
+    for _ in range(W):
+        h = model.forward(nxt[:, None], pos)
+        nxt = model.greedy(h[:, -1])
+        pos += 1
+    sampler = ClockSampler(dev.index or 0)
+    tp.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(K):
+        h = model.forward(nxt[:, None], pos)
+        nxt = model.greedy(h[:, -1])
+        pos += 1
+    end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = tp.max_over_ranks(start.elapsed_time(end))
+    if tp.rank == 0:
+        print(json.dumps({
+            "metric": "decode tokens/s", "impl": "eager-pytorch", "value": round(batch * K / (ms / 1e3), 2),
+            "unit": "tokens/s", "n_gpus": tp.world_size, "steps": K, "warmup": W,
+            "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
+            "data": "synthetic", "ttft_p50_s": round(prefill_s, 4),
+            "config": {"model": cfg.name, "global_batch": batch, "seq_len": prompt_len, "parallelism": parallelism},
+            "clocks": clocks}), flush=True)
+    tp.barrier()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,272 @@
+"""Decoder-only transformer on the hand-written sm_100a operators.
+
+The forward pass is the reference's layer structure — RMSNorm -> fused QKV ->
+(QK-norm) -> RoPE -> KV-cache write -> attention -> o_proj -> all-reduce ->
+residual -> RMSNorm -> FFN / MoE -> all-reduce -> residual
+(examples/models/qwen3/kernels/transformer_layer.py:16-120,
+examples/models/qwen3/kernels/attention.py:25-156) — but organised around what a
+B200 wants: a paged KV cache, one packed token batch per prefill, and a decode
+step made of a handful of fused launches per layer that is captured in a CUDA
+graph:
+
+    decode layer (tp = 1):  qkv GEMM (split-K partials) -> [sum + RoPE + cache append]
+        -> paged attention -> o GEMM (split-K) -> [sum + residual + RMSNorm]
+        -> gate_up GEMM with SwiGLU epilogue -> down GEMM (split-K) -> [sum + residual + RMSNorm]
+
+Tensor parallelism follows the reference (column-parallel qkv / gate_up / lm_head,
+row-parallel o / down, two reductions per layer, vocab-parallel argmax gathered
+over ranks, examples/models/qwen3/kernels/sampling.py:127-147).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..parallel.comm import TPGroup
+from .config import ModelConfig, yarn_inv_freq
+from .kv_cache import PagedKVCache
+from .weights import kv_heads_for_rank, to_device_layout
+
+
+def pick_splits(n_out: int, k: int, sms: int = 148) -> int:
+    """Split-K factor for a decode-sized GEMM: enough CTAs to pull HBM bandwidth from
+    every SM while each split still streams at least 512 contraction elements."""
+    tiles = (n_out + 127) // 128
+    if tiles >= sms * 3 // 4:
+        return 1
+    want = max(1, sms // tiles)
+    return max(1, min(want, k // 512, 8))
+
+
+class LayerWeights:
+    __slots__ = ("qkv", "o", "gate_up", "down", "input_norm", "post_norm", "q_norm", "k_norm", "qkv_bias", "o_bias",
+                 "sinks", "router", "router_bias", "gate_up_bias", "down_bias")
+
+    def __init__(self):
+        for s in self.__slots__:
+            setattr(self, s, None)
+
+
+class TransformerLM:
+    """Weights + forward passes of one tensor-parallel rank."""
+
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], tp: Optional[TPGroup] = None,
+                 device=None, moe_parallel: str = "ep"):
+        self.cfg = cfg
+        self.tp = tp or TPGroup.single()
+        self.device = torch.device(device if device is not None else weights["tok_embedding"].device)
+        world, rank = self.tp.world_size, self.tp.rank
+        self.nq = cfg.num_heads // world
+        self.kv0, self.nkv = kv_heads_for_rank(cfg, rank, world)
+        self.d = cfg.head_dim
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.moe_parallel = moe_parallel
+        dev = self.device
+
+        def get(name):
+            return weights[name].to(dev)
+
+        self.tok_embedding = get("tok_embedding").contiguous()
+        self.final_norm = get("norm_weight")
+        self.lm_head = to_device_layout(get("lm_head_weight"))        # [V/tp, H]
+        self.vocab_local = self.lm_head.shape[0]
+        self.layers: List[LayerWeights] = []
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            lw = LayerWeights()
+            lw.qkv = to_device_layout(get(p + "qkv_weight"))
+            lw.o = to_device_layout(get(p + "o_weight"))
+            norm_in = p + ("input_layernorm_weight" if p + "input_layernorm_weight" in weights else "input_weight")
+            norm_post = p + ("post_attention_layernorm_weight" if p + "post_attention_layernorm_weight" in weights
+                             else "post_attention_weight")
+            lw.input_norm = get(norm_in)
+            lw.post_norm = get(norm_post)
+            if cfg.qk_norm:
+                lw.q_norm, lw.k_norm = get(p + "q_norm_weight"), get(p + "k_norm_weight")
+            if cfg.attn_bias:
+                lw.qkv_bias, lw.o_bias = get(p + "qkv_bias"), get(p + "o_bias")
+            if cfg.attention_sinks:
+                lw.sinks = get(p + "sinks").float().contiguous()
+            if cfg.is_moe:
+                lw.router = to_device_layout(get(p + "router_weight"))            # [E, H]
+                lw.router_bias = get(p + "router_bias") if cfg.router_bias else None
+                lw.gate_up = to_device_layout(get(p + "gate_up_weight"))          # [E_l, 2 I_l, H]
+                lw.down = to_device_layout(get(p + "down_weight"))                # [E_l, H, I_l]
+                if cfg.expert_bias:
+                    lw.gate_up_bias, lw.down_bias = get(p + "gate_up_bias"), get(p + "down_bias")
+            else:
+                lw.gate_up = to_device_layout(get(p + "gate_up_weight"))          # [2 I_l, H]
+                lw.down = to_device_layout(get(p + "down_weight"))                # [H, I_l]
+            self.layers.append(lw)
+        inv_freq, rope_scale = yarn_inv_freq(cfg)
+        self.rope = ops.rope_table(cfg.head_dim, cfg.max_position, inv_freq=inv_freq, scaling=rope_scale, device=dev)
+        self._moe = None
+        if cfg.is_moe:
+            from .moe import MoEBlock
+
+            self._moe = MoEBlock(cfg, self.tp, moe_parallel)
+        # decode split-K factors (per GEMM shape)
+        H = cfg.hidden_size
+        self.split_qkv = pick_splits(self.layers[0].qkv.shape[0], H)
+        self.split_o = pick_splits(H, self.layers[0].o.shape[1])
+        self.split_down = 1 if cfg.is_moe else pick_splits(H, self.layers[0].down.shape[1])
+
+    # ------------------------------------------------------------------ cache
+    def new_cache(self, num_blocks: int, max_batch: int, max_seq_len: int,
+                  enable_prefix_sharing: bool = True) -> PagedKVCache:
+        max_blocks = (max_seq_len + self.cfg.block_size - 1) // self.cfg.block_size
+        return PagedKVCache(self.cfg.num_layers, self.nkv, self.d, num_blocks, max_batch, max_blocks, self.device,
+                            enable_prefix_sharing=enable_prefix_sharing)
+
+    def weight_bytes(self) -> int:
+        n = self.tok_embedding.numel() + self.lm_head.numel()
+        for lw in self.layers:
+            for s in ("qkv", "o", "gate_up", "down", "router"):
+                t = getattr(lw, s)
+                if t is not None:
+                    n += t.numel()
+        return n * 2
+
+    # ------------------------------------------------------------------ FFN
+    def _ffn_decode(self, lw: LayerWeights, normed: torch.Tensor, resid: torch.Tensor, next_norm: torch.Tensor):
+        """Returns (new residual, normed for the next block)."""
+        cfg = self.cfg
+        if cfg.is_moe:
+            y = self._moe.forward(lw, normed)                       # [B, H] bf16, already reduced over ranks
+            return ops.add_rmsnorm(y, next_norm, residual_in=resid, eps=cfg.rms_eps)
+        fused_gate = cfg.swiglu_limit <= 0
+        if fused_gate:
+            act = ops.linear(normed, lw.gate_up, gated=True)
+        else:
+            act = ops.silu_mul(ops.linear(normed, lw.gate_up), limit=cfg.swiglu_limit, alpha=cfg.swiglu_alpha)
+        return self._row_parallel_reduce(act, lw.down, self.split_down, resid, next_norm, None)
+
+    def _row_parallel_reduce(self, x, w, splits, resid, next_norm, bias):
+        """Row-parallel GEMM + sum over ranks + residual + next RMSNorm (decode-sized M)."""
+        cfg = self.cfg
+        if self.tp.world_size == 1:
+            if splits > 1:
+                parts = ops.linear(x, w, splits=splits)
+                return ops.add_rmsnorm(None, next_norm, residual_in=resid, partials=parts, bias=bias,
+                                       eps=cfg.rms_eps)
+            y = ops.linear(x, w)
+            return ops.add_rmsnorm(y, next_norm, residual_in=resid, bias=bias, eps=cfg.rms_eps)
+        fused = getattr(self.tp, "fused", None)
+        if fused is not None:
+            return fused.gemm_allreduce_add_rmsnorm(x, w, resid, next_norm, bias, cfg.rms_eps, splits)
+        if splits > 1:
+            y = ops.reduce_partials(ops.linear(x, w, splits=splits))
+        else:
+            y = ops.linear(x, w)
+        self.tp.all_reduce(y)
+        return ops.add_rmsnorm(y, next_norm, residual_in=resid, bias=bias, eps=cfg.rms_eps)
+
+    # ------------------------------------------------------------------ decode
+    def decode_step(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: PagedKVCache,
+                    block_table: torch.Tensor, context_lens: torch.Tensor, q_len: int = 1,
+                    return_hidden: bool = False) -> torch.Tensor:
+        """One decode (or q_len-token verify) step for the batch.  ids [B * q_len] int32;
+        context_lens already count the new tokens.  Returns the final-normed hidden
+        states [B * q_len, H]."""
+        cfg = self.cfg
+        x = ops.embedding(ids, self.tok_embedding)
+        resid = x
+        normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
+        taps = [] if return_hidden else None
+        for i, lw in enumerate(self.layers):
+            if self.split_qkv > 1:
+                qkv = ops.linear(normed, lw.qkv, splits=self.split_qkv)
+            else:
+                qkv = ops.linear(normed, lw.qkv)
+            q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq, self.nkv,
+                                   self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
+                                   norm_eps=cfg.rms_eps)
+            attn = ops.paged_attn_decode(q, cache.k[i], cache.v[i], block_table, context_lens, self.scale,
+                                         q_len=q_len, window=cfg.window_for_layer(i), sinks=lw.sinks)
+            resid, normed = self._row_parallel_reduce(attn, lw.o, self.split_o, resid, lw.post_norm, lw.o_bias)
+            nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
+            resid, normed = self._ffn_decode(lw, normed, resid, nxt)
+            if taps is not None:
+                taps.append(resid)
+        if return_hidden:
+            return normed, taps
+        return normed
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: PagedKVCache,
+                block_table: torch.Tensor, q_start: torch.Tensor, q_lens: torch.Tensor, context_lens: torch.Tensor,
+                max_q_len: int, return_hidden: bool = False):
+        """Packed prefill of several sequences.  ids / positions / slots [T]; returns the
+        final-normed hidden states [T, H] (and the per-layer residual streams when
+        return_hidden is set, for speculative-decoding taps)."""
+        cfg = self.cfg
+        tp1 = self.tp.world_size == 1
+        x = ops.embedding(ids, self.tok_embedding)
+        resid = x
+        normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
+        taps = [] if return_hidden else None
+        for i, lw in enumerate(self.layers):
+            qkv = ops.linear(normed, lw.qkv, swap=False)
+            q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq, self.nkv,
+                                   self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
+                                   norm_eps=cfg.rms_eps)
+            attn = ops.flash_attn_prefill(q, cache.k[i], cache.v[i], block_table, q_start, q_lens, context_lens,
+                                          self.scale, max_q_len=max_q_len, causal=cfg.causal,
+                                          window=cfg.window_for_layer(i), sinks=lw.sinks)
+            if tp1:
+                resid = ops.linear(attn, lw.o, swap=False, residual=resid, bias=lw.o_bias)
+                normed = ops.rmsnorm(resid, lw.post_norm, cfg.rms_eps)
+            else:
+                o = ops.linear(attn, lw.o, swap=False, bias=lw.o_bias)
+                self.tp.all_reduce(o)
+                resid, normed = ops.add_rmsnorm(o, lw.post_norm, residual_in=resid, eps=cfg.rms_eps)
+            nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
+            if cfg.is_moe:
+                y = self._moe.forward(lw, normed)
+                resid, normed = ops.add_rmsnorm(y, nxt, residual_in=resid, eps=cfg.rms_eps)
+            else:
+                if cfg.swiglu_limit <= 0:
+                    act = ops.linear(normed, lw.gate_up, gated=True, swap=False)
+                else:
+                    act = ops.silu_mul(ops.linear(normed, lw.gate_up, swap=False), limit=cfg.swiglu_limit,
+                                       alpha=cfg.swiglu_alpha)
+                if tp1:
+                    resid = ops.linear(act, lw.down, swap=False, residual=resid)
+                    normed = ops.rmsnorm(resid, nxt, cfg.rms_eps)
+                else:
+                    dn = ops.linear(act, lw.down, swap=False)
+                    self.tp.all_reduce(dn)
+                    resid, normed = ops.add_rmsnorm(dn, nxt, residual_in=resid, eps=cfg.rms_eps)
+            if taps is not None:
+                taps.append(resid)
+        if return_hidden:
+            return normed, taps
+        return normed
+
+    # ------------------------------------------------------------------ heads
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Vocab-parallel logits [rows, V / tp] (bf16)."""
+        return ops.linear(hidden, self.lm_head)
+
+    def greedy(self, hidden: torch.Tensor, out_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Greedy next token ids (int32 [rows]) from final-normed hidden states; with tp > 1
+        the per-rank (max, argmax) pairs are gathered and reduced like the reference's
+        vocab-parallel head."""
+        logits = self.logits(hidden)
+        rows = hidden.shape[0]
+        if self.tp.world_size == 1:
+            return ops.argmax(logits, out_ids=out_ids)
+        vals = torch.empty((rows,), dtype=torch.float32, device=hidden.device)
+        ids = ops.argmax(logits, out_vals=vals)
+        packed = torch.stack([vals, (ids + self.tp.rank * self.vocab_local).float()], dim=-1)  # [rows, 2]
+        allp = self.tp.all_gather(packed)                                                       # [tp, rows, 2]
+        best = allp[..., 0].argmax(dim=0)                                                       # first max wins
+        res = allp[..., 1].gather(0, best[None]).squeeze(0).to(torch.int32)
+        if out_ids is not None:
+            out_ids.copy_(res)
+            return out_ids
+        return res
