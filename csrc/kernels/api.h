@@ -13,18 +13,45 @@ int encode_tmap_bf16(CUtensorMap* m, const void* ptr, int rank, const uint64_t* 
                      const uint32_t* box);
 int* status_word();
 int num_sms();
+bool pdl_enabled();
 }  // namespace nkb
+
+#ifdef __CUDACC__
+#include <cuda_runtime.h>
+#include <utility>
+namespace nkb {
+// Launch with the programmatic-stream-serialization attribute (when enabled), so
+// the kernel's prologue overlaps the tail of its predecessor in the stream.
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return int(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+}
+}  // namespace nkb
+#endif
 
 extern "C" {
 int nkb_init();
 // Reads (and optionally clears) the device status word; non-zero = a bounded
 // wait inside a kernel gave up (code in the low byte, CTA index above it).
 int nkb_status(int reset);
+// Enable / disable programmatic dependent launch for all kernels of the library (default on).
+void nkb_set_pdl(int enabled);
 
 int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, int cols, int k, long long lda, long long ldb,
                   long long ldo, int transpose_out, int out_fp32, int splits, long long split_stride, int gated,
                   int gate_off, const void* bias, int bias_on_rows, const void* residual, int block_n, int max_ctas,
-                  void* stream);
+                  int weights_operand, int ctas_per_sm, void* stream);
 int nkb_gemm_effective_splits(int k, int splits);
 
 int nkb_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, float eps, void* stream);

@@ -30,7 +30,6 @@ namespace nkb {
 
 constexpr int kPage = 32;
 constexpr int kDecStages = 3;
-constexpr int kDecWarps = 4;
 
 struct DecodeParams {
   const __nv_bfloat16* q;
@@ -61,7 +60,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int D>
+template <int D, int kDecWarps>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const DecodeParams p) {
@@ -77,7 +76,6 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int ctx = p.context_lens[b];
   const int rows = p.q_len * p.group;
 
   if (threadIdx.x == 0) {
@@ -90,6 +88,9 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     tma_prefetch_desc(&tmV);
   }
   __syncthreads();
+  griddep_wait();   // q, the cache and the tables come from the preceding kernels
+  griddep_launch();
+  const int ctx = p.context_lens[b];
 
   // ---- page range of this split
   int first_tok = 0;
@@ -311,6 +312,8 @@ template <int D>
 __global__ void decode_combine_kernel(const DecodeParams p) {
   const int kvh = blockIdx.x, b = blockIdx.y;
   const int rows = p.q_len * p.group;
+  griddep_wait();
+  griddep_launch();
   const float* base = p.scratch + (((long long)b * p.nkv + kvh) * p.num_splits) * (16 * D + 32);
   for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
     const int r = idx / D, d = idx % D;
@@ -337,7 +340,7 @@ __global__ void decode_combine_kernel(const DecodeParams p) {
   }
 }
 
-template <int D>
+template <int D, int kDecWarps>
 static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t s) {
   constexpr int kStageBytes = 2 * (D / 64) * kPage * 128;
   constexpr int smem = kDecWarps * kDecStages * kStageBytes + 1024;
@@ -346,17 +349,17 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e =
-        cudaFuncSetAttribute(paged_attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(paged_attn_decode_kernel<D, kDecWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
     attr_set = true;
   }
   dim3 grid(p.num_splits, p.nkv, p.batch);
-  paged_attn_decode_kernel<D><<<grid, kDecWarps * 32, smem, s>>>(tk, tv, p);
-  if (p.num_splits > 1) {
+  int rc = launch_pdl(paged_attn_decode_kernel<D, kDecWarps>, grid, dim3(kDecWarps * 32), size_t(smem), s, tk, tv, p);
+  if (rc == 0 && p.num_splits > 1) {
     dim3 g2(p.nkv, p.batch);
-    decode_combine_kernel<D><<<g2, 128, 0, s>>>(p);
+    rc = launch_pdl(decode_combine_kernel<D>, g2, dim3(128), 0, s, p);
   }
-  return int(cudaGetLastError());
+  return rc;
 }
 
 }  // namespace nkb
@@ -401,7 +404,10 @@ extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const v
   if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
   if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (head_dim == 128) return launch_decode<128>(tk, tv, p, s);
-  if (head_dim == 64) return launch_decode<64>(tk, tv, p, s);
+  // Many CTAs: two-warp CTAs (96 KB ring at D = 128) so two of them share an SM and one's
+  // prologue / merge overlaps the other's streaming; few CTAs: four warps each.
+  const bool small = (long long)batch * nkv * num_splits >= 2LL * num_sms();
+  if (head_dim == 128) return small ? launch_decode<128, 2>(tk, tv, p, s) : launch_decode<128, 4>(tk, tv, p, s);
+  if (head_dim == 64) return small ? launch_decode<64, 2>(tk, tv, p, s) : launch_decode<64, 4>(tk, tv, p, s);
   return -2;
 }

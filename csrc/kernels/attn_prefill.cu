@@ -65,6 +65,8 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol = 256;
 
   const int qt = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  griddep_wait();
+  griddep_launch();
   const int q_len = p.q_lens[b];
   if (qt * kQTile >= q_len) return;
   const int ctx = p.context_lens[b];
@@ -377,8 +379,7 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     attr_set = true;
   }
   dim3 grid((max_q_len + kQTile - 1) / kQTile, p.nq, batch);
-  flash_attn_prefill_kernel<D><<<grid, kPfThreads, smem, s>>>(tq, tk, tv, p);
-  return int(cudaGetLastError());
+  return launch_pdl(flash_attn_prefill_kernel<D>, grid, dim3(kPfThreads), size_t(smem), s, tq, tk, tv, p);
 }
 
 }  // namespace nkb

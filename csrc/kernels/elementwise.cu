@@ -38,6 +38,8 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ partials, int split
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int nvec = hidden >> 3;
+  griddep_wait();
+  griddep_launch();
   float h[kNormMaxIters][8];
   float ss = 0.f;
 #pragma unroll
@@ -116,6 +118,8 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ partials, int split
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows,
                                 int inter, float limit, float alpha) {
   const long long nvec = (long long)rows * (inter >> 3);
+  griddep_wait();
+  griddep_launch();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / (inter >> 3);
@@ -145,6 +149,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int n, int hidden, int vocab) {
   const int t = blockIdx.x;
+  griddep_wait();
+  griddep_launch();
   int id = ids[t];
   if (id < 0) id = 0;
   if (id >= vocab) id = vocab - 1;
@@ -172,6 +178,8 @@ __global__ void rope_kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, con
   const int heads = nq + 2 * nkv;
   const long long gw = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  griddep_wait();
+  griddep_launch();
   if (gw >= (long long)tokens * heads) return;
   const int t = int(gw / heads), h = int(gw % heads);
   const int width = heads * D;
@@ -264,11 +272,9 @@ extern "C" int nkb_add_rmsnorm(const float* partials, int splits, long long spli
   if (nvec <= 1024) threads = (nvec + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
   if (!partials) splits = 0;
-  add_rmsnorm_kernel<<<rows, threads, 0, S(stream)>>>(
-      partials, splits, split_stride, (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual_in,
-      (const __nv_bfloat16*)bias, (const __nv_bfloat16*)w, (__nv_bfloat16*)residual_out, (__nv_bfloat16*)normed_out,
-      hidden, eps);
-  return int(cudaGetLastError());
+  return launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(threads), 0, S(stream), partials, splits, split_stride,
+                    (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual_in, (const __nv_bfloat16*)bias,
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)residual_out, (__nv_bfloat16*)normed_out, hidden, eps);
 }
 
 extern "C" int nkb_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, float eps, void* stream) {
@@ -282,17 +288,16 @@ extern "C" int nkb_silu_mul(const void* gate_up, void* out, int rows, int inter,
   long long nvec = (long long)rows * (inter >> 3);
   int blocks = int((nvec + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<<<blocks, 256, 0, S(stream)>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter,
-                                                 limit, alpha);
-  return int(cudaGetLastError());
+  return launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, S(stream), (const __nv_bfloat16*)gate_up,
+                    (__nv_bfloat16*)out, rows, inter, limit, alpha);
 }
 
 extern "C" int nkb_embedding(const int* ids, const void* table, void* out, int n, int hidden, int vocab,
                              void* stream) {
   if (n <= 0) return 0;
   if (hidden & 7) return -2;
-  embedding_kernel<<<n, 128, 0, S(stream)>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, n, hidden, vocab);
-  return int(cudaGetLastError());
+  return launch_pdl(embedding_kernel, dim3(n), dim3(128), 0, S(stream), ids, (const __nv_bfloat16*)table,
+                    (__nv_bfloat16*)out, n, hidden, vocab);
 }
 
 extern "C" int nkb_rope_kv_append(const void* qkv_bf16, const float* qkv_partials, int splits, long long split_stride,
@@ -304,19 +309,19 @@ extern "C" int nkb_rope_kv_append(const void* qkv_bf16, const float* qkv_partial
   const long long warps = (long long)tokens * (nq + 2 * nkv);
   const int threads = 256;
   const long long blocks = (warps * 32 + threads - 1) / threads;
-#define NKB_ROPE(D)                                                                                              \
-  rope_kv_append_kernel<D><<<(unsigned)blocks, threads, 0, S(stream)>>>(                                         \
-      (const __nv_bfloat16*)qkv_bf16, qkv_partials, splits, split_stride, (const __nv_bfloat16*)bias, positions, \
-      slots, cos_sin, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, norm_eps,                  \
-      (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, nq, nkv, max_pos, block_size)
+#define NKB_ROPE(D)                                                                                               \
+  return launch_pdl(rope_kv_append_kernel<D>, dim3((unsigned)blocks), dim3(threads), 0, S(stream),                \
+                    (const __nv_bfloat16*)qkv_bf16, qkv_partials, splits, split_stride,                           \
+                    (const __nv_bfloat16*)bias, positions, slots, cos_sin, (const __nv_bfloat16*)q_norm_w,        \
+                    (const __nv_bfloat16*)k_norm_w, norm_eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,     \
+                    (__nv_bfloat16*)v_cache, tokens, nq, nkv, max_pos, block_size)
   switch (head_dim) {
-    case 64: NKB_ROPE(64); break;
-    case 128: NKB_ROPE(128); break;
-    case 256: NKB_ROPE(256); break;
+    case 64: NKB_ROPE(64);
+    case 128: NKB_ROPE(128);
+    case 256: NKB_ROPE(256);
     default: return -2;
   }
 #undef NKB_ROPE
-  return int(cudaGetLastError());
 }
 
 namespace nkb {
@@ -329,6 +334,8 @@ __global__ void decode_advance_kernel(int* __restrict__ context_lens, const int*
                                       int* __restrict__ positions, int* __restrict__ slots, int batch, int q_len,
                                       int max_blocks, int block_size) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  griddep_wait();
+  griddep_launch();
   if (i >= batch * q_len) return;
   const int b = i / q_len, j = i % q_len;
   const int ctx = context_lens[b];
@@ -344,6 +351,8 @@ __global__ void decode_advance_kernel(int* __restrict__ context_lens, const int*
 }
 __global__ void add_int_kernel(int* __restrict__ v, int n, int delta) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  griddep_wait();
+  griddep_launch();
   if (i < n && v[i] >= 0) v[i] += delta;
 }
 }  // namespace nkb
@@ -352,8 +361,9 @@ extern "C" int nkb_decode_advance(int* context_lens, const int* block_table, int
                                   int q_len, int max_blocks, int block_size, void* stream) {
   if (batch <= 0) return 0;
   const int n = batch * q_len;
-  nkb::decode_advance_kernel<<<(n + 127) / 128, 128, 0, S(stream)>>>(context_lens, block_table, positions, slots,
-                                                                     batch, q_len, max_blocks, block_size);
-  nkb::add_int_kernel<<<(batch + 127) / 128, 128, 0, S(stream)>>>(context_lens, batch, q_len);
-  return int(cudaGetLastError());
+  int rc = launch_pdl(nkb::decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, S(stream), context_lens,
+                      block_table, positions, slots, batch, q_len, max_blocks, block_size);
+  if (rc) return rc;
+  return launch_pdl(nkb::add_int_kernel, dim3((batch + 127) / 128), dim3(128), 0, S(stream), context_lens, batch,
+                    q_len);
 }

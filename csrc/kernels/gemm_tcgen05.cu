@@ -41,6 +41,7 @@ struct GemmArgs {
   int out_fp32;
   int bias_on_rows;
   int stages;
+  int weights_operand;  // 0 = A, 1 = B holds immutable weights (may be fetched before the dependency wait), -1 none
   long long ldo;
   long long split_stride;
   void* out;
@@ -73,8 +74,8 @@ __device__ __forceinline__ void decode_tile(const GemmArgs& a, int w, int& row_t
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, int MINB>
+__global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -120,8 +121,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int total_work = args.num_row_tiles * args.num_col_tiles * args.splits;
 
+  griddep_launch();
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    auto issue = [&](int stage, int kb, int row0, int col0, bool expect, bool do_a, bool do_b) {
+      uint8_t* a_ptr = tiles + stage * stage_bytes;
+      uint8_t* b_ptr = a_ptr + a_tiles * kATileBytes;
+      if (expect) mbar_expect_tx(&ctrl->full[stage], stage_bytes);
+      if (do_a) {
+        tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0);
+        if (args.gated == 1)
+          tma_load_2d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0);
+      }
+      if (do_b) {
+        tma_load_2d(b_ptr, &tmB, &ctrl->full[stage], kb * kBlockK, col0);
+        if (args.gated == 2)
+          tma_load_2d(b_ptr + kBTileBytes, &tmB, &ctrl->full[stage], kb * kBlockK, args.gate_off + col0);
+      }
+    };
+    // Weight tiles do not depend on the preceding kernel: fill the ring with them
+    // before waiting for it, so the HBM stream starts during the predecessor's tail.
+    int pre = 0;
+    const bool w_is_a = args.weights_operand == 0;
+    if (args.weights_operand >= 0 && int(blockIdx.x) < total_work) {
+      int rt, ct, sp;
+      decode_tile(args, blockIdx.x, rt, ct, sp);
+      const int kb0 = sp * args.kb_per_split;
+      const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
+      pre = min(stages, kb1 - kb0);
+      if (lane == 0)
+        for (int i = 0; i < pre; ++i) issue(i, kb0 + i, rt * kTileRows, ct * BN, true, w_is_a, !w_is_a);
+      __syncwarp();
+    }
+    griddep_wait();
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
@@ -135,15 +168,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bool ok = mbar_wait(&ctrl->empty[stage], phase ^ 1u, abort_flag, args.status, ERR_WAIT_SMEM_EMPTY);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
         if (lane == 0) {
-          uint8_t* a_ptr = tiles + stage * stage_bytes;
-          uint8_t* b_ptr = a_ptr + a_tiles * kATileBytes;
-          mbar_expect_tx(&ctrl->full[stage], stage_bytes);
-          tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0);
-          if (args.gated == 1)
-            tma_load_2d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0);
-          tma_load_2d(b_ptr, &tmB, &ctrl->full[stage], kb * kBlockK, col0);
-          if (args.gated == 2)
-            tma_load_2d(b_ptr + kBTileBytes, &tmB, &ctrl->full[stage], kb * kBlockK, args.gate_off + col0);
+          const bool prefetched = (w == int(blockIdx.x)) && (kb - kb0 < pre);
+          if (prefetched) issue(stage, kb, row0, col0, false, !w_is_a, w_is_a);
+          else issue(stage, kb, row0, col0, true, true, true);
         }
         __syncwarp();
         if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -199,6 +226,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may touch
+    griddep_wait();  // residual / output buffers may still be in use by the preceding kernel
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
@@ -337,12 +365,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int BN>
+// ctas_per_sm = 2 caps the ring so that two CTAs (of this or of the next GEMM in
+// the stream, started early by programmatic dependent launch) fit on one SM: the
+// successor then prefetches its weight tiles while this kernel drains.
+template <int BN, int MINB>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
                        cudaStream_t stream) {
   const int a_tiles = args.gated == 1 ? 2 : 1, b_tiles = args.gated == 2 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * BN * kBlockK * 2;
-  const int budget = 232448 - 1024 - int(sizeof(GemmCtrl)) - 64;
+  const int budget = (MINB == 2 ? 113 * 1024 : 232448) - 1024 - int(sizeof(GemmCtrl)) - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return -3;
@@ -350,14 +381,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a
   const int smem = stages * stage_bytes + 1024 + int(sizeof(GemmCtrl)) + 64;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         MINB == 2 ? 113 * 1024 : 232448);
     if (e != cudaSuccess) return int(e);
     attr_set = true;
   }
   int total = args.num_row_tiles * args.num_col_tiles * args.splits;
   int grid = total < max_ctas ? total : max_ctas;
-  gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(ta, tb, args);
-  return int(cudaGetLastError());
+  return launch_pdl(gemm_bf16_kernel<BN, MINB>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb, args);
 }
 
 }  // namespace nkb
@@ -370,7 +401,7 @@ using namespace nkb;
 extern "C" int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, int cols, int k, long long lda,
                              long long ldb, long long ldo, int transpose_out, int out_fp32, int splits,
                              long long split_stride, int gated, int gate_off, const void* bias, int bias_on_rows,
-                             const void* residual, int block_n, int max_ctas, void* stream) {
+                             const void* residual, int block_n, int max_ctas, int weights_operand, int ctas_per_sm, void* stream) {
   if (!status_word() && nkb_init() != 0) return -1;
   if (rows <= 0 || cols <= 0 || k <= 0) return -2;
   if ((k & 7) || (lda & 7) || (ldb & 7)) return -2;
@@ -399,7 +430,9 @@ extern "C" int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, 
   args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   args.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   args.status = status_word();
-  if (max_ctas <= 0 || max_ctas > num_sms()) max_ctas = num_sms();
+  args.weights_operand = weights_operand;
+  const int cap = num_sms() * (ctas_per_sm == 2 ? 2 : 1);
+  if (max_ctas <= 0 || max_ctas > cap) max_ctas = cap;
 
   CUtensorMap ta, tb;
   const uint64_t a_rows = gated == 1 ? uint64_t(gate_off) + rows : rows;
@@ -407,11 +440,20 @@ extern "C" int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, 
   if (encode_tmap_bf16_2d(&ta, A, k, a_rows, lda, kBlockK, kTileRows)) return -4;
   if (encode_tmap_bf16_2d(&tb, B, k, b_rows, ldb, kBlockK, block_n)) return -4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (ctas_per_sm == 2 && block_n <= 128 && !(gated && block_n > 64)) {
+    switch (block_n) {
+      case 32: return launch_gemm<32, 2>(ta, tb, args, max_ctas, s);
+      case 64: return launch_gemm<64, 2>(ta, tb, args, max_ctas, s);
+      case 128: return launch_gemm<128, 2>(ta, tb, args, max_ctas, s);
+      default: return -2;
+    }
+  }
+  if (max_ctas > num_sms()) max_ctas = num_sms();
   switch (block_n) {
-    case 32: return launch_gemm<32>(ta, tb, args, max_ctas, s);
-    case 64: return launch_gemm<64>(ta, tb, args, max_ctas, s);
-    case 128: return launch_gemm<128>(ta, tb, args, max_ctas, s);
-    case 256: return launch_gemm<256>(ta, tb, args, max_ctas, s);
+    case 32: return launch_gemm<32, 1>(ta, tb, args, max_ctas, s);
+    case 64: return launch_gemm<64, 1>(ta, tb, args, max_ctas, s);
+    case 128: return launch_gemm<128, 1>(ta, tb, args, max_ctas, s);
+    case 256: return launch_gemm<256, 1>(ta, tb, args, max_ctas, s);
     default: return -2;
   }
 }

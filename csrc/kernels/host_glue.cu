@@ -4,6 +4,7 @@
 // GPU), the device status word that bounded waits report into, and the SM count.
 #include "api.h"
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 namespace nkb {
 
@@ -53,6 +54,8 @@ int encode_tmap_bf16_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_
 
 static int* g_status = nullptr;
 static int g_num_sms = 0;
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
 int* status_word() { return g_status; }
 int num_sms() { return g_num_sms; }
 
@@ -61,6 +64,7 @@ int num_sms() { return g_num_sms; }
 using namespace nkb;
 
 extern "C" int nkb_init() {
+  if (const char* e = getenv("NKIPY_B200_PDL")) g_pdl = atoi(e) != 0;
   if (!g_status) {
     if (cudaMalloc(&g_status, 64) != cudaSuccess) return -1;
     cudaMemset(g_status, 0, 64);
@@ -70,6 +74,8 @@ extern "C" int nkb_init() {
   cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   return get_encode_fn() ? 0 : -2;
 }
+
+extern "C" void nkb_set_pdl(int enabled) { g_pdl = enabled != 0; }
 
 extern "C" int nkb_status(int reset) {
   if (!g_status) return 0;

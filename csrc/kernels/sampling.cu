@@ -34,6 +34,8 @@ __global__ void argmax_kernel(const void* __restrict__ logits, int is_fp32, int*
   const long long row = blockIdx.x;
   float best = -FLT_MAX;
   int bi = 0x7fffffff;
+  griddep_wait();
+  griddep_launch();
   if (!is_fp32 && (ld % 8 == 0)) {
     const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(logits) + row * ld);
     const int nvec = vocab >> 3;
@@ -113,6 +115,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const void* __restrict__ l
   __shared__ int s_remaining;
   __shared__ float s_red[32];
   const long long row = blockIdx.x;
+  griddep_wait();
+  griddep_launch();
   const int want = (top_k > 0 && top_k < kCand) ? top_k : kCand;
   const int k = want < vocab ? want : vocab;
 
@@ -225,6 +229,8 @@ __global__ void router_topk_kernel(const void* __restrict__ logits, int is_fp32,
                                    int* __restrict__ experts, int tokens, int num_experts, int top_k, int mode) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  griddep_wait();
+  griddep_launch();
   if (warp >= tokens) return;
   constexpr int kPer = 32;
   float v[kPer];
@@ -283,18 +289,16 @@ using namespace nkb;
 extern "C" int nkb_argmax(const void* logits, int is_fp32, int* out_ids, float* out_vals, int rows, int vocab,
                           long long ld, void* stream) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, is_fp32, out_ids, out_vals, vocab,
-                                                                          ld);
-  return int(cudaGetLastError());
+  return launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), logits, is_fp32,
+                    out_ids, out_vals, vocab, ld);
 }
 
 extern "C" int nkb_sample(const void* logits, int is_fp32, int* out_ids, int rows, int vocab, long long ld,
                           float temperature, int top_k, float top_p, unsigned long long seed,
                           unsigned long long step, void* stream) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, is_fp32, out_ids, vocab, ld,
-                                                                          temperature, top_k, top_p, seed, step);
-  return int(cudaGetLastError());
+  return launch_pdl(sample_kernel, dim3(rows), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), logits, is_fp32,
+                    out_ids, vocab, ld, temperature, top_k, top_p, seed, step);
 }
 
 extern "C" int nkb_router_topk(const void* logits, int is_fp32, float* weights, int* experts, int tokens,
@@ -303,8 +307,6 @@ extern "C" int nkb_router_topk(const void* logits, int is_fp32, float* weights, 
   if (num_experts > 1024 || top_k > 32 || top_k > num_experts) return -2;
   const int threads = 128;
   const int blocks = (tokens * 32 + threads - 1) / threads;
-  router_topk_kernel<<<blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, is_fp32, weights,
-                                                                                    experts, tokens, num_experts,
-                                                                                    top_k, mode);
-  return int(cudaGetLastError());
+  return launch_pdl(router_topk_kernel, dim3(blocks), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), logits,
+                    is_fp32, weights, experts, tokens, num_experts, top_k, mode);
 }

@@ -33,12 +33,13 @@ from .weights import kv_heads_for_rank, to_device_layout
 
 
 def pick_splits(n_out: int, k: int, sms: int = 148) -> int:
-    """Split-K factor for a decode-sized GEMM: enough CTAs to pull HBM bandwidth from
-    every SM while each split still streams at least 512 contraction elements."""
+    """Split-K factor for a decode-sized GEMM.  Two CTAs share an SM in that orientation,
+    so aim for about two CTAs per SM while each split still streams at least 512
+    contraction elements."""
     tiles = (n_out + 127) // 128
-    if tiles >= sms * 3 // 4:
+    if tiles >= 2 * sms * 3 // 4:
         return 1
-    want = max(1, sms // tiles)
+    want = max(1, (2 * sms) // tiles)
     return max(1, min(want, k // 512, 8))
 
 

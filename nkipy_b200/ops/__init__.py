@@ -89,6 +89,8 @@ def linear(
     gated: bool = False,
     swap: Optional[bool] = None,
     max_ctas: int = 0,
+    weights_static: bool = True,
+    ctas_per_sm: Optional[int] = None,
 ) -> torch.Tensor:
     """``y = x @ w.T`` with optional fused epilogue.
 
@@ -99,6 +101,11 @@ def linear(
            than requested) for a fused reduction (`add_rmsnorm`, `rope_kv_append`,
            `reduce_partials`).  bias is added to partial 0.
     swap: put the weight on the 128-row MMA side (decode-sized M).  Default: M <= 128.
+    ctas_per_sm: 2 halves the shared-memory ring so two CTAs share an SM (default for the
+           swapped / decode orientation: lets the next kernel's prefetch overlap this one's tail).
+    weights_static: w is not written by the kernels launched just before this one, so its
+           tiles may be fetched before the preceding kernel has finished (set False when w is
+           itself a fresh activation).
     """
     M, K = x.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -159,7 +166,8 @@ def linear(
     rc = L.nkb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out_view.data_ptr(), rows, cols, K, lda, ldb, ldo, transpose_out, out_fp32,
         eff if splits > 1 else 1, split_stride, gate_mode, N if gated else 0, _ptr(bias), bias_on_rows,
-        _ptr(residual), block_n, max_ctas, _stream(),
+        _ptr(residual), block_n, max_ctas, (0 if swap else 1) if weights_static else -1,
+        (2 if (swap and not gated) else 1) if ctas_per_sm is None else ctas_per_sm, _stream(),
     )
     _lib.check(rc, "nkb_gemm_bf16")
     _launches += 1
@@ -528,6 +536,15 @@ def _ref_attention(q, k, v, scale, q_pos0, causal, window, sinks):
     return torch.einsum("hqk,khd->qhd", p, vv)
 
 
+def pick_kv_splits(ctas: int, max_pages: int, sms: int = 148) -> int:
+    """KV split count for decode attention: no split once there are two CTAs per SM;
+    otherwise split until there are, keeping at least 8 pages per split."""
+    if ctas >= 2 * sms:
+        return 1
+    s = min(-(-2 * sms // ctas), max(max_pages // 8, 1), 16)
+    return max(s, 1)
+
+
 def paged_attn_decode(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -565,11 +582,7 @@ def paged_attn_decode(
     _check_bf16(q, k_cache, v_cache)
     L = _lib.lib()
     if num_splits <= 0:
-        ctas = B * nkv
-        num_splits = 1
-        max_pages = block_table.shape[1]
-        while ctas * num_splits < 2 * 148 and num_splits * 8 <= max_pages and num_splits < 16:
-            num_splits *= 2
+        num_splits = pick_kv_splits(B * nkv, block_table.shape[1])
     if num_splits > 1:
         need = L.nkb_paged_attn_decode_scratch_floats(B, q_len, nq, D, num_splits)
         if scratch is None or scratch.numel() < need:

@@ -22,10 +22,11 @@ _P = c_void_p
 _SIGNATURES = {
     "nkb_init": (c_int, []),
     "nkb_status": (c_int, [c_int]),
+    "nkb_set_pdl": (None, [c_int]),
     "nkb_gemm_bf16": (
         c_int,
         [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int, c_longlong,
-         c_int, c_int, _P, c_int, _P, c_int, c_int, _P],
+         c_int, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     ),
     "nkb_gemm_effective_splits": (c_int, [c_int, c_int]),
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),

@@ -74,7 +74,7 @@ def test_block_allocator_refcounts_and_eviction():
 
 
 def test_helpers():
-    assert pick_splits(4096, 4096) == 4 and pick_splits(128256, 4096) == 1 and pick_splits(6144, 4096) == 3
+    assert pick_splits(4096, 4096) == 8 and pick_splits(128256, 4096) == 1 and pick_splits(6144, 4096) == 6
     assert percentile([1, 2, 3, 4], 50) == 2.5
 
 
