@@ -411,3 +411,92 @@ extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const v
   if (head_dim == 64) return small ? launch_decode<64, 2>(tk, tv, p, s) : launch_decode<64, 4>(tk, tv, p, s);
   return -2;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (see no_alloc.h for who needs it and its limits).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+#include <stdio.h>
+
+namespace nkb {
+// Split-KV partial results live here instead of in a caller-provided buffer.
+// In host code this name is only a stand-in for the symbol: the device address
+// is looked up once per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_scratch[NKB_NOALLOC_SCRATCH_FLOATS];
+static __device__ int g_noalloc_status;
+
+struct NoAllocDevice {
+  bool ready;
+  float* scratch;
+  int* status;
+  int sms;
+};
+constexpr int kNoAllocMaxDevices = 64;
+static NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+
+// Once per device, with that device current: resolve the device addresses.
+static int noalloc_setup(NoAllocDevice** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return NKB_NOALLOC_SETUP_FAILED;
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.ready) {
+    void* sp = nullptr;
+    void* st = nullptr;
+    if (cudaGetSymbolAddress(&sp, g_noalloc_scratch) != cudaSuccess || sp == nullptr) return NKB_NOALLOC_SETUP_FAILED;
+    if (cudaGetSymbolAddress(&st, g_noalloc_status) != cudaSuccess || st == nullptr) return NKB_NOALLOC_SETUP_FAILED;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return NKB_NOALLOC_SETUP_FAILED;
+    d.scratch = static_cast<float*>(sp);
+    d.status = static_cast<int*>(st);
+    d.sms = sms;
+    d.ready = true;
+  }
+  *out = &d;
+  return 0;
+}
+}  // namespace nkb
+
+extern "C" int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                             const int* block_table, const int* context_lens, void* out, int batch,
+                                             int q_len, int nq, int nkv, int head_dim, int block_size, int num_blocks,
+                                             int max_blocks_per_seq, float scale, int window, const float* sinks,
+                                             int num_splits, void* stream) {
+  if (batch <= 0) return 0;
+  if (block_size != kPage || nkv <= 0 || nq % nkv != 0) return -2;
+  const int group = nq / nkv;
+  if (q_len * group > 16) return -2;
+  if (head_dim != 64 && head_dim != 128) return -2;
+  if (num_splits < 1) num_splits = 1;
+  const long long need = num_splits > 1 ? (long long)batch * nkv * num_splits * (16 * head_dim + 32) : 0;
+  if (need > NKB_NOALLOC_SCRATCH_FLOATS) {
+    fprintf(stderr,
+            "nkb_paged_attn_decode_noalloc: needs %lld scratch floats (batch %d x kv heads %d x splits %d), the "
+            "built-in array holds %lld; use fewer splits / a smaller batch or the allocating entry point\n",
+            need, batch, nkv, num_splits, (long long)NKB_NOALLOC_SCRATCH_FLOATS);
+    return NKB_NOALLOC_TOO_LARGE;
+  }
+  NoAllocDevice* d = nullptr;
+  if (int rc = noalloc_setup(&d)) return rc;
+  DecodeParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.block_table = block_table;
+  p.context_lens = context_lens;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.scratch = num_splits > 1 ? d->scratch : nullptr;
+  p.sinks = sinks;
+  p.status = d->status;
+  p.batch = batch; p.q_len = q_len; p.nq = nq; p.nkv = nkv; p.group = group;
+  p.max_blocks = max_blocks_per_seq; p.num_splits = num_splits; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap tk, tv;
+  const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(kPage), uint64_t(nkv), uint64_t(num_blocks)};
+  const uint64_t strides[3] = {uint64_t(head_dim) * 2, uint64_t(head_dim) * kPage * 2,
+                               uint64_t(head_dim) * kPage * nkv * 2};
+  const uint32_t box[4] = {64, uint32_t(kPage), 1, 1};
+  if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
+  if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool small = (long long)batch * nkv * num_splits >= 2LL * d->sms;
+  if (head_dim == 128) return small ? launch_decode<128, 2>(tk, tv, p, s) : launch_decode<128, 4>(tk, tv, p, s);
+  return small ? launch_decode<64, 2>(tk, tv, p, s) : launch_decode<64, 4>(tk, tv, p, s);
+}
