@@ -53,6 +53,19 @@ int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, int cols, i
                   int gate_off, const void* bias, int bias_on_rows, const void* residual, int block_n, int max_ctas,
                   int weights_operand, int ctas_per_sm, void* stream);
 int nkb_gemm_effective_splits(int k, int splits);
+int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tokens, int k, long long ldw,
+                       long long ldx, long long ldo, int splits, const void* bias, int block_n, void* const* peer_out,
+                       void* const* peer_flag, int n_peers, int rank, void* done_counter, void* stream);
+
+// symmetric memory over CUDA IPC + consumer of the fused GEMM + all-reduce (comm.cu)
+int nkb_symm_alloc(void** out, long long bytes);
+int nkb_symm_free(void* p);
+int nkb_ipc_get_handle(void* p, void* handle_out64);
+int nkb_ipc_open(const void* handle64, void** out);
+int nkb_ipc_close(void* p);
+int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void* flags, int n_src, void* seen,
+                          void* done_counter, const void* residual_in, const void* w, void* residual_out,
+                          void* normed_out, int rows, int hidden, float eps, void* stream);
 
 int nkb_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, float eps, void* stream);
 int nkb_add_rmsnorm(const float* partials, int splits, long long split_stride, const void* x, const void* residual_in,

@@ -50,6 +50,22 @@ struct GemmArgs {
   int* status;
 };
 
+// Fused collective epilogue ("push" mode, decode orientation only): every finished
+// output tile is stored as a bf16 partial straight into the symmetric buffer of every
+// tensor-parallel peer (plain peer stores over NVLink, 16 bytes per thread, staged
+// through shared memory so that each token row is one contiguous 256-byte run), into
+// slot (rank * splits + split) of the destination's [slots, M, N] partial array.  The
+// last CTA of the grid then bumps this rank's arrival counter on every peer; the
+// consumer (tp_reduce_rmsnorm in comm.cu) waits on those counters with a bounded spin.
+constexpr int kMaxPeers = 8;
+struct PushArgs {
+  int n_peers;
+  int rank;
+  __nv_bfloat16* peer_out[kMaxPeers];
+  unsigned int* peer_flag[kMaxPeers];   // this rank's arrival counter inside each peer's flag array
+  unsigned int* done_counter;           // local: CTAs of this grid that finished their stores
+};
+
 struct GemmCtrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -74,10 +90,10 @@ __device__ __forceinline__ void decode_tile(const GemmArgs& a, int w, int& row_t
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
-template <int BN, int MINB>
+template <int BN, int MINB, bool PUSH>
 __global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs args) {
+                 const GemmArgs args, const PushArgs push) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -89,6 +105,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * kBTileBytes;
   const int stages = args.stages;
   GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(tiles + stages * stage_bytes);
+  // push mode: [BN tokens][128 features] bf16 staging tile behind the control block
+  __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(ctrl) + 512);
 
   const int acc_cols = BN * (args.gated ? 2 : 1);
   uint32_t tmem_cols = 32;
@@ -277,6 +295,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 v[j] = __float_as_uint(__uint_as_float(v[j]) + __bfloat162float(args.bias[cbase + j]));
           }
         }
+        if constexpr (PUSH) {
+          // stage the chunk: token (c + j), feature (quad * 32 + lane)
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            stage_out[(c + j) * kTileRows + quad * 32 + lane] = __float2bfloat16(__uint_as_float(v[j]));
+          continue;
+        }
         if (args.transpose_out) {
           // out[col * ldo + row]: consecutive lanes hold consecutive rows -> coalesced
           if (row_ok) {
@@ -345,8 +370,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      if constexpr (PUSH) {
+        const int et = threadIdx.x - 64;  // 0..127 over the four epilogue warps
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int row0 = rt * kTileRows;
+        const long long slot = (long long)push.rank * args.splits + sp;
+        for (int idx = et; idx < BN * 16; idx += 128) {
+          const int tok = idx >> 4, ch = idx & 15;
+          const int gtok = col0 + tok, gfeat = row0 + ch * 8;
+          if (gtok < args.cols && gfeat < args.rows) {
+            const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
+            const long long off = (slot * args.cols + gtok) * args.ldo + gfeat;
+            for (int pr = 0; pr < push.n_peers; ++pr)
+              *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if constexpr (PUSH) {
+      // all peer stores of this CTA are issued: publish them, count the CTA, and let the
+      // last CTA of the grid signal every peer
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const unsigned int old = atomicAdd(push.done_counter, 1u);
+        if (old == gridDim.x - 1) {
+          *push.done_counter = 0u;
+          __threadfence_system();
+          for (int pr = 0; pr < push.n_peers; ++pr) atomicAdd_system(push.peer_flag[pr], 1u);
+        }
+      }
     }
   }
 
@@ -368,27 +424,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ctas_per_sm = 2 caps the ring so that two CTAs (of this or of the next GEMM in
 // the stream, started early by programmatic dependent launch) fit on one SM: the
 // successor then prefetches its weight tiles while this kernel drains.
-template <int BN, int MINB>
+template <int BN, int MINB, bool PUSH = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const PushArgs* push = nullptr) {
   const int a_tiles = args.gated == 1 ? 2 : 1, b_tiles = args.gated == 2 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * BN * kBlockK * 2;
-  const int budget = (MINB == 2 ? 113 * 1024 : 232448) - 1024 - int(sizeof(GemmCtrl)) - 64;
+  const int extra = 512 + (PUSH ? BN * kTileRows * 2 : 0);   // control block (+ push staging tile)
+  const int budget = (MINB == 2 ? 113 * 1024 : 232448) - 1024 - extra - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return -3;
   args.stages = stages;
-  const int smem = stages * stage_bytes + 1024 + int(sizeof(GemmCtrl)) + 64;
+  static_assert(sizeof(GemmCtrl) <= 512, "control block grew");
+  const int smem = stages * stage_bytes + 1024 + extra + 64;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, MINB, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          MINB == 2 ? 113 * 1024 : 232448);
     if (e != cudaSuccess) return int(e);
     attr_set = true;
   }
   int total = args.num_row_tiles * args.num_col_tiles * args.splits;
   int grid = total < max_ctas ? total : max_ctas;
-  return launch_pdl(gemm_bf16_kernel<BN, MINB>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb, args);
+  PushArgs pa{};
+  if (push) pa = *push;
+  return launch_pdl(gemm_bf16_kernel<BN, MINB, PUSH>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb,
+                    args, pa);
 }
 
 }  // namespace nkb
@@ -466,4 +527,54 @@ extern "C" int nkb_gemm_effective_splits(int k, int splits) {
   if (splits > kb_total) splits = kb_total;
   int per = (kb_total + splits - 1) / splits;
   return (kb_total + per - 1) / per;
+}
+
+
+// Decode-orientation GEMM whose epilogue pushes bf16 partial tiles into every peer's
+// symmetric partial buffer (see PushArgs).  weights [features, k], x [tokens, k]; the
+// destination on every peer is [n_peers * splits, tokens, ldo] bf16.
+extern "C" int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tokens, int k, long long ldw,
+                                  long long ldx, long long ldo, int splits, const void* bias, int block_n,
+                                  void* const* peer_out, void* const* peer_flag, int n_peers, int rank,
+                                  void* done_counter, void* stream) {
+  if (!status_word() && nkb_init() != 0) return -1;
+  if (features <= 0 || tokens <= 0 || k <= 0 || (k & 7) || (ldw & 7) || (ldx & 7) || (ldo & 7) || (features & 7))
+    return -2;
+  if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers || tokens > block_n) return -2;
+  GemmArgs args{};
+  args.rows = features;
+  args.cols = tokens;
+  args.k = k;
+  args.kb_total = (k + kBlockK - 1) / kBlockK;
+  if (splits < 1) splits = 1;
+  if (splits > args.kb_total) splits = args.kb_total;
+  args.kb_per_split = (args.kb_total + splits - 1) / splits;
+  args.splits = (args.kb_total + args.kb_per_split - 1) / args.kb_per_split;
+  args.num_row_tiles = (features + kTileRows - 1) / kTileRows;
+  args.num_col_tiles = 1;
+  args.transpose_out = 1;
+  args.bias_on_rows = 1;
+  args.ldo = ldo;
+  args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  args.status = status_word();
+  args.weights_operand = 0;
+  PushArgs pa{};
+  pa.n_peers = n_peers;
+  pa.rank = rank;
+  for (int i = 0; i < n_peers; ++i) {
+    pa.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(peer_out[i]);
+    pa.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
+  }
+  pa.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  CUtensorMap ta, tb;
+  if (encode_tmap_bf16_2d(&ta, weights, k, features, ldw, kBlockK, kTileRows)) return -4;
+  if (encode_tmap_bf16_2d(&tb, x, k, tokens, ldx, kBlockK, block_n)) return -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int max_ctas = 2 * num_sms();
+  switch (block_n) {
+    case 32: return launch_gemm<32, 2, true>(ta, tb, args, max_ctas, s, &pa);
+    case 64: return launch_gemm<64, 2, true>(ta, tb, args, max_ctas, s, &pa);
+    case 128: return launch_gemm<128, 2, true>(ta, tb, args, max_ctas, s, &pa);
+    default: return -2;
+  }
 }

@@ -12,6 +12,7 @@ vocab-parallel greedy head -> the new ids feed the next replay directly.
 
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -85,6 +86,12 @@ class GenerationEngine:
         self.out_host = torch.zeros((B,), dtype=torch.int32, pin_memory=pin)
         self.active: Dict[int, SequenceState] = {}     # table row -> sequence
         self._graph = None
+        tp = model.tp
+        if (tp.world_size > 1 and dev.type == "cuda" and getattr(tp, "fused", None) is None
+                and os.environ.get("NKIPY_B200_FUSED_TP", "1") == "1"):
+            from ..parallel.symm import FusedTP
+
+            tp.fused = FusedTP(tp, max_batch, model.cfg.hidden_size)
         self.stats = GenerationStats()
 
     # ------------------------------------------------------------------ admission + prefill
@@ -165,6 +172,9 @@ class GenerationEngine:
 
     def _decode_body(self) -> None:
         m = self.model
+        fused = getattr(m.tp, "fused", None)
+        if fused is not None:
+            fused.begin_step()
         ops.decode_advance(self.context_lens, self.cache.block_table, self.positions, self.slots, 1, BLOCK_SIZE)
         hidden = m.decode_step(self.ids, self.positions, self.slots, self.cache, self.cache.block_table,
                                self.context_lens)

@@ -1,0 +1,105 @@
+"""Fused GEMM + all-reduce + RMSNorm over peer memory, 2 ranks on 2 GPUs (child processes)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    from nkipy_b200 import ops
+    from nkipy_b200.parallel.comm import TPGroup
+    from nkipy_b200.parallel.symm import FusedTP
+
+    tp = TPGroup.from_env()
+    dev = tp.device
+    M, N, K = 64, 1024, 1536
+    fused = FusedTP(tp, M, N)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    errs = []
+    resid = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+    dist.broadcast(resid, 0)
+    wn = torch.randn(N, device=dev, generator=g).to(torch.bfloat16)
+    dist.broadcast(wn, 0)
+
+    def reference(x, w, r):
+        y = x.float() @ w.float().T
+        dist.all_reduce(y)
+        h = (y + r.float()).to(torch.bfloat16).float()
+        n = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * wn.float()
+        return h, n
+
+    xs = [torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16) for _ in range(6)]
+    ws = [(torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for _ in range(6)]
+    fused.begin_step()
+    for i in range(6):
+        h, n = fused.gemm_allreduce_add_rmsnorm(xs[i], ws[i], resid, wn, None, 1e-5, splits=1 + (i % 3))
+        rh, rn = reference(xs[i], ws[i], resid)
+        errs.append(((h.float() - rh).norm() / rh.norm()).item())
+        errs.append(((n.float() - rn).norm() / rn.norm()).item())
+    # the same sequence captured in a CUDA graph and replayed: counters must keep working
+    torch.cuda.synchronize()
+    tp.barrier()
+    outs = []
+
+    def body():
+        fused.begin_step()
+        outs.clear()
+        for i in range(6):
+            outs.append(fused.gemm_allreduce_add_rmsnorm(xs[i], ws[i], resid, wn, None, 1e-5, splits=2))
+
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        body()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    for i in range(6):
+        rh, rn = reference(xs[i], ws[i], resid)
+        errs.append(((outs[i][0].float() - rh).norm() / rh.norm()).item())
+    status = ops.device_status()
+    tp.barrier()
+    fused.close()
+    q.put((rank, max(errs), status))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_allreduce_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, status in res:
+        assert status == 0, (rank, status)
+        assert err < 2e-2, (rank, err)
