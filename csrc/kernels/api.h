@@ -72,6 +72,8 @@ int nkb_add_rmsnorm(const float* partials, int splits, long long split_stride, c
                     const void* bias, const void* w, void* residual_out, void* normed_out, int rows, int hidden,
                     float eps, void* stream);
 int nkb_silu_mul(const void* gate_up, void* out, int rows, int inter, float limit, float alpha, void* stream);
+int nkb_silu_mul_partials(const float* partials, int splits, long long stride, const void* bias, void* out, int rows,
+                          int inter, float limit, float alpha, void* stream);
 int nkb_embedding(const int* ids, const void* table, void* out, int n, int hidden, int vocab, void* stream);
 int nkb_rope_kv_append(const void* qkv_bf16, const float* qkv_partials, int splits, long long split_stride,
                        const void* bias, const int* positions, const int* slots, const float* cos_sin,

@@ -146,6 +146,48 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
   }
 }
 
+// Same gate, fed by split-K fp32 partials [S, rows, 2 * inter] of the gate_up GEMM
+// (used when the fused-gate GEMM would have too few tiles to fill the GPU).
+__global__ void silu_mul_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
+                                         const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                         int rows, int inter, float limit, float alpha) {
+  const long long nvec = (long long)rows * (inter >> 2);
+  griddep_wait();
+  griddep_launch();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (inter >> 2);
+    const int c = int(i % (inter >> 2)) * 4;
+    float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < splits; ++s) {
+      const float4 gv = *reinterpret_cast<const float4*>(parts + s * stride + r * 2 * inter + c);
+      const float4 uv = *reinterpret_cast<const float4*>(parts + s * stride + r * 2 * inter + inter + c);
+      g[0] += gv.x; g[1] += gv.y; g[2] += gv.z; g[3] += gv.w;
+      u[0] += uv.x; u[1] += uv.y; u[2] += uv.z; u[3] += uv.w;
+    }
+    float o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float gg = g[e], uu = u[e];
+      if (bias) {
+        gg += __bfloat162float(bias[c + e]);
+        uu += __bfloat162float(bias[inter + c + e]);
+      }
+      if (limit > 0.f) {
+        gg = fminf(gg, limit);
+        uu = fminf(fmaxf(uu, -limit), limit);
+        o[e] = (uu + 1.f) * gg / (1.f + __expf(-alpha * gg));
+      } else {
+        o[e] = gg / (1.f + __expf(-gg)) * uu;
+      }
+    }
+    uint2 pk;
+    pk.x = pack_bf16x2(o[0], o[1]);
+    pk.y = pack_bf16x2(o[2], o[3]);
+    *reinterpret_cast<uint2*>(out + r * inter + c) = pk;
+  }
+}
+
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int n, int hidden, int vocab) {
   const int t = blockIdx.x;
@@ -290,6 +332,17 @@ extern "C" int nkb_silu_mul(const void* gate_up, void* out, int rows, int inter,
   if (blocks > 148 * 16) blocks = 148 * 16;
   return launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, S(stream), (const __nv_bfloat16*)gate_up,
                     (__nv_bfloat16*)out, rows, inter, limit, alpha);
+}
+
+extern "C" int nkb_silu_mul_partials(const float* partials, int splits, long long stride, const void* bias, void* out,
+                                     int rows, int inter, float limit, float alpha, void* stream) {
+  if (rows <= 0) return 0;
+  if (inter & 3) return -2;
+  long long nvec = (long long)rows * (inter >> 2);
+  int blocks = int((nvec + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_pdl(silu_mul_partials_kernel, dim3(blocks), dim3(256), 0, S(stream), partials, splits, stride,
+                    (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, rows, inter, limit, alpha);
 }
 
 extern "C" int nkb_embedding(const int* ids, const void* table, void* out, int n, int hidden, int vocab,

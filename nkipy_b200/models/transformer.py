@@ -115,6 +115,11 @@ class TransformerLM:
         self.split_qkv = pick_splits(self.layers[0].qkv.shape[0], H)
         self.split_o = pick_splits(H, self.layers[0].o.shape[1])
         self.split_down = 1 if cfg.is_moe else pick_splits(H, self.layers[0].down.shape[1])
+        self.split_gate_up = 1
+        if not cfg.is_moe:
+            two_i = self.layers[0].gate_up.shape[0]
+            if two_i // 256 < 100:          # fewer than ~100 fused gate/up tile pairs
+                self.split_gate_up = max(2, pick_splits(two_i, H))
 
     # ------------------------------------------------------------------ cache
     def new_cache(self, num_blocks: int, max_batch: int, max_seq_len: int,
@@ -139,9 +144,12 @@ class TransformerLM:
         if cfg.is_moe:
             y = self._moe.forward(lw, normed)                       # [B, H] bf16, already reduced over ranks
             return ops.add_rmsnorm(y, next_norm, residual_in=resid, eps=cfg.rms_eps)
-        fused_gate = cfg.swiglu_limit <= 0
-        if fused_gate:
+        if cfg.swiglu_limit <= 0 and self.split_gate_up == 1:
             act = ops.linear(normed, lw.gate_up, gated=True)
+        elif self.split_gate_up > 1:
+            # too few gate/up tile pairs to fill the SMs: split-K partials, gate applied by the reducer
+            act = ops.silu_mul(ops.linear(normed, lw.gate_up, splits=self.split_gate_up), limit=cfg.swiglu_limit,
+                               alpha=cfg.swiglu_alpha)
         else:
             act = ops.silu_mul(ops.linear(normed, lw.gate_up), limit=cfg.swiglu_limit, alpha=cfg.swiglu_alpha)
         return self._row_parallel_reduce(act, lw.down, self.split_down, resid, next_norm, None)

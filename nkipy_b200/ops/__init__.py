@@ -264,10 +264,41 @@ def add_rmsnorm(
     return residual_out, normed_out
 
 
+def _silu_mul_partials(parts, out, limit, alpha, bias):
+    """SwiGLU gate over fp32 split-K partials [S, T, 2I] (summed on the fly) -> bf16 [T, I]."""
+    if parts.dim() == 2:
+        parts = parts.unsqueeze(0)
+    S, T, two_i = parts.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((T, inter), dtype=torch.bfloat16, device=parts.device)
+    if not _native(parts):
+        x = parts.sum(0)
+        if bias is not None:
+            x = x + bias.float()
+        g, u = x[:, :inter], x[:, inter:]
+        if limit > 0:
+            g = g.clamp(max=limit)
+            u = u.clamp(-limit, limit)
+            y = (u + 1) * g * torch.sigmoid(alpha * g)
+        else:
+            y = torch.nn.functional.silu(g) * u
+        out.copy_(y.to(torch.bfloat16))
+        return out
+    global _launches
+    rc = _lib.lib().nkb_silu_mul_partials(parts.data_ptr(), S, parts.stride(0), _ptr(bias), out.data_ptr(), T, inter,
+                                          float(limit), float(alpha), _stream())
+    _lib.check(rc, "nkb_silu_mul_partials")
+    _launches += 1
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, limit: float = 0.0,
-             alpha: float = 1.702) -> torch.Tensor:
+             alpha: float = 1.702, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """SwiGLU gate over ``[T, 2I]`` (gate | up) -> ``[T, I]``; limit > 0 selects the
     clamped gpt-oss form ``(up + 1) * gate * sigmoid(alpha * gate)``."""
+    if gate_up.dtype == torch.float32:
+        return _silu_mul_partials(gate_up, out, limit, alpha, bias)
     T, two_i = gate_up.shape
     inter = two_i // 2
     if out is None:

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_add_rmsnorm": (c_int, [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_silu_mul": (c_int, [_P, _P, c_int, c_int, c_float, c_float, _P]),
+    "nkb_silu_mul_partials": (c_int, [_P, c_int, c_longlong, _P, _P, c_int, c_int, c_float, c_float, _P]),
     "nkb_embedding": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
     "nkb_rope_kv_append": (
         c_int,

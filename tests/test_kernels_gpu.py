@@ -255,3 +255,17 @@ def test_decode_advance():
     assert pos.tolist() == [5, 31, 32, 0]
     assert slots.tolist() == [10 * 32 + 5, 13 * 32 + 31, 17 * 32 + 0, -1]
     assert ctx.tolist() == [6, 32, 33, -1]
+
+
+def test_silu_mul_from_split_partials():
+    T, I = 48, 1792
+    parts = torch.randn(3, T, 2 * I, device=DEV)
+    bias = randn(2 * I)
+    y = ops.silu_mul(parts, bias=bias)
+    x = parts.sum(0) + bias.float()
+    ref = torch.nn.functional.silu(x[:, :I]) * x[:, I:]
+    assert rel_err(y, ref) < 5e-3
+    yc = ops.silu_mul(parts, limit=7.0)
+    x = parts.sum(0)
+    g, u = x[:, :I].clamp(max=7.0), x[:, I:].clamp(-7.0, 7.0)
+    assert rel_err(yc, (u + 1) * g * torch.sigmoid(1.702 * g)) < 5e-3
