@@ -1,1 +1,1 @@
-
+from . import collectives  # noqa: F401
