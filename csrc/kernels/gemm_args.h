@@ -1,0 +1,49 @@
+// Argument blocks of the tcgen05 GEMM kernel, shared by the device code, the library
+// launcher and the C++ runtime that launches generated kernels from a plan.
+#pragma once
+#include <cuda_bf16.h>
+
+namespace nkb {
+
+constexpr int kBlockK = 64;           // bf16 elements per K slab = one 128B swizzle row
+constexpr int kTileRows = 128;        // UMMA M
+constexpr int kATileBytes = kTileRows * kBlockK * 2;
+constexpr int kMaxStages = 12;
+constexpr int kGemmThreads = 192;     // warp0 TMA, warp1 MMA, warps2-5 epilogue
+
+struct GemmArgs {
+  int rows, cols, k;
+  int splits, kb_per_split, kb_total;
+  int num_row_tiles, num_col_tiles;
+  int gated;        // 0 none, 1 = A operand holds [gate; up], 2 = B operand holds [gate; up]
+  int gate_off;     // row offset of the "up" half inside the gated operand
+  int transpose_out;
+  int out_fp32;
+  int bias_on_rows;
+  int stages;
+  int weights_operand;  // 0 = A, 1 = B holds immutable weights (may be fetched before the dependency wait), -1 none
+  long long ldo;
+  long long split_stride;
+  void* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int* status;
+};
+
+// Fused collective epilogue ("push" mode, decode orientation only): every finished
+// output tile is stored as a bf16 partial straight into the symmetric buffer of every
+// tensor-parallel peer (plain peer stores over NVLink, 16 bytes per thread, staged
+// through shared memory so that each token row is one contiguous 256-byte run), into
+// slot (rank * splits + split) of the destination's [slots, M, N] partial array.  The
+// last CTA of the grid then bumps this rank's arrival counter on every peer; the
+// consumer (tp_reduce_rmsnorm in comm.cu) waits on those counters with a bounded spin.
+constexpr int kMaxPeers = 8;
+struct PushArgs {
+  int n_peers;
+  int rank;
+  __nv_bfloat16* peer_out[kMaxPeers];
+  unsigned int* peer_flag[kMaxPeers];   // this rank's arrival counter inside each peer's flag array
+  unsigned int* done_counter;           // local: CTAs of this grid that finished their stores
+};
+
+}  // namespace nkb

@@ -1,422 +1,8 @@
-// Persistent, warp-specialised bf16 GEMM for sm_100a.
-//
-//   D[r, c] = sum_k A[r, k] * B[c, k]          (both operands K-major, bf16)
-//
-// * operands are staged by TMA (128-byte swizzle, 64-wide K slabs) into a
-//   multi-stage shared-memory ring,
-// * one elected thread issues tcgen05.mma (M=128, N=BN, K=16) into a
-//   double-buffered TMEM accumulator,
-// * four epilogue warps read the accumulator back with tcgen05.ld while the MMA
-//   warp already works on the next tile.
-//
-// The same kernel serves both orientations used by the models:
-//   "normal"  A = activations [tokens, K], B = weights [features, K]  (prefill)
-//   "swapped" A = weights [features, K],  B = activations [tokens, K]  (decode:
-//             the 128-row MMA dimension is filled by features, the token count
-//             becomes the narrow N dimension), output written transposed.
-// Optional fusions: split-K partials (fp32), bias, residual add, and the SwiGLU
-// gate (two weight tiles per stage, silu(g)*u in the epilogue).
-//
-// Reference parity: this is the `dot` lowering target of the tracing frontend
-// (nkipy/src/nkipy/core/ops/_hlo_impls.py:633-710 in the reference lowers
-// np.matmul to an HLO dot executed by the Neuron tensor engine).
-#include "common.cuh"
+// Host launchers of the tcgen05 GEMM (device code in gemm_tcgen05.cuh).
+#include "gemm_tcgen05.cuh"
 #include "api.h"
 
 namespace nkb {
-
-constexpr int kBlockK = 64;           // bf16 elements per K slab = one 128B swizzle row
-constexpr int kTileRows = 128;        // UMMA M
-constexpr int kATileBytes = kTileRows * kBlockK * 2;
-constexpr int kMaxStages = 12;
-constexpr int kGemmThreads = 192;     // warp0 TMA, warp1 MMA, warps2-5 epilogue
-
-struct GemmArgs {
-  int rows, cols, k;
-  int splits, kb_per_split, kb_total;
-  int num_row_tiles, num_col_tiles;
-  int gated;        // 0 none, 1 = A operand holds [gate; up], 2 = B operand holds [gate; up]
-  int gate_off;     // row offset of the "up" half inside the gated operand
-  int transpose_out;
-  int out_fp32;
-  int bias_on_rows;
-  int stages;
-  int weights_operand;  // 0 = A, 1 = B holds immutable weights (may be fetched before the dependency wait), -1 none
-  long long ldo;
-  long long split_stride;
-  void* out;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* residual;
-  int* status;
-};
-
-// Fused collective epilogue ("push" mode, decode orientation only): every finished
-// output tile is stored as a bf16 partial straight into the symmetric buffer of every
-// tensor-parallel peer (plain peer stores over NVLink, 16 bytes per thread, staged
-// through shared memory so that each token row is one contiguous 256-byte run), into
-// slot (rank * splits + split) of the destination's [slots, M, N] partial array.  The
-// last CTA of the grid then bumps this rank's arrival counter on every peer; the
-// consumer (tp_reduce_rmsnorm in comm.cu) waits on those counters with a bounded spin.
-constexpr int kMaxPeers = 8;
-struct PushArgs {
-  int n_peers;
-  int rank;
-  __nv_bfloat16* peer_out[kMaxPeers];
-  unsigned int* peer_flag[kMaxPeers];   // this rank's arrival counter inside each peer's flag array
-  unsigned int* done_counter;           // local: CTAs of this grid that finished their stores
-};
-
-struct GemmCtrl {
-  uint64_t full[kMaxStages];
-  uint64_t empty[kMaxStages];
-  uint64_t tfull[2];
-  uint64_t tempty[2];
-  uint32_t tmem_base;
-  int abort;
-};
-
-__device__ __forceinline__ void decode_tile(const GemmArgs& a, int w, int& row_tile, int& col_tile, int& split) {
-  split = w % a.splits;
-  int t = w / a.splits;
-  constexpr int kGroup = 16;
-  int per_group = kGroup * a.num_col_tiles;
-  int g = t / per_group;
-  int first = g * kGroup;
-  int gsz = min(a.num_row_tiles - first, kGroup);
-  int in = t - g * per_group;
-  row_tile = first + in % gsz;
-  col_tile = in / gsz;
-}
-
-__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
-
-template <int BN, int MINB, bool PUSH>
-__global__ void __launch_bounds__(kGemmThreads, MINB)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs args, const PushArgs push) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int a_tiles = (args.gated == 1) ? 2 : 1;
-  const int b_tiles = (args.gated == 2) ? 2 : 1;
-  constexpr int kBTileBytes = BN * kBlockK * 2;
-  const int stage_bytes = a_tiles * kATileBytes + b_tiles * kBTileBytes;
-  const int stages = args.stages;
-  GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(tiles + stages * stage_bytes);
-  // push mode: [BN tokens][128 features] bf16 staging tile behind the control block
-  __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(ctrl) + 512);
-
-  const int acc_cols = BN * (args.gated ? 2 : 1);
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < uint32_t(2 * acc_cols)) tmem_cols <<= 1;
-
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&ctrl->full[s], 1);
-      mbar_init(&ctrl->empty[s], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&ctrl->tfull[i], 1);
-      mbar_init(&ctrl->tempty[i], 4);
-    }
-    ctrl->abort = 0;
-    mbar_fence_init();
-    fence_proxy_async();
-  }
-  if (warp == 1) {
-    tmem_alloc(&ctrl->tmem_base, tmem_cols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = ctrl->tmem_base;
-  volatile int* abort_flag = &ctrl->abort;
-
-  const int total_work = args.num_row_tiles * args.num_col_tiles * args.splits;
-
-  griddep_launch();
-
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    auto issue = [&](int stage, int kb, int row0, int col0, bool expect, bool do_a, bool do_b) {
-      uint8_t* a_ptr = tiles + stage * stage_bytes;
-      uint8_t* b_ptr = a_ptr + a_tiles * kATileBytes;
-      if (expect) mbar_expect_tx(&ctrl->full[stage], stage_bytes);
-      if (do_a) {
-        tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0);
-        if (args.gated == 1)
-          tma_load_2d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0);
-      }
-      if (do_b) {
-        tma_load_2d(b_ptr, &tmB, &ctrl->full[stage], kb * kBlockK, col0);
-        if (args.gated == 2)
-          tma_load_2d(b_ptr + kBTileBytes, &tmB, &ctrl->full[stage], kb * kBlockK, args.gate_off + col0);
-      }
-    };
-    // Weight tiles do not depend on the preceding kernel: fill the ring with them
-    // before waiting for it, so the HBM stream starts during the predecessor's tail.
-    int pre = 0;
-    const bool w_is_a = args.weights_operand == 0;
-    if (args.weights_operand >= 0 && int(blockIdx.x) < total_work) {
-      int rt, ct, sp;
-      decode_tile(args, blockIdx.x, rt, ct, sp);
-      const int kb0 = sp * args.kb_per_split;
-      const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
-      pre = min(stages, kb1 - kb0);
-      if (lane == 0)
-        for (int i = 0; i < pre; ++i) issue(i, kb0 + i, rt * kTileRows, ct * BN, true, w_is_a, !w_is_a);
-      __syncwarp();
-    }
-    griddep_wait();
-    int stage = 0;
-    uint32_t phase = 0;
-    bool alive = true;
-    for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
-      int rt, ct, sp;
-      decode_tile(args, w, rt, ct, sp);
-      const int row0 = rt * kTileRows, col0 = ct * BN;
-      const int kb0 = sp * args.kb_per_split;
-      const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        bool ok = mbar_wait(&ctrl->empty[stage], phase ^ 1u, abort_flag, args.status, ERR_WAIT_SMEM_EMPTY);
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        if (lane == 0) {
-          const bool prefetched = (w == int(blockIdx.x)) && (kb - kb0 < pre);
-          if (prefetched) issue(stage, kb, row0, col0, false, !w_is_a, w_is_a);
-          else issue(stage, kb, row0, col0, true, true, true);
-        }
-        __syncwarp();
-        if (++stage == stages) { stage = 0; phase ^= 1u; }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = make_idesc_bf16(kTileRows, BN, 0, 0);
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool alive = true;
-    for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
-      int rt, ct, sp;
-      decode_tile(args, w, rt, ct, sp);
-      const int kb0 = sp * args.kb_per_split;
-      const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
-      bool ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-      tc_fence_after();
-      const uint32_t d0 = tmem_base + uint32_t(acc * acc_cols);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
-          const uint32_t b_addr = a_addr + a_tiles * kATileBytes;
-          const uint64_t da = make_smem_desc_sw128(a_addr, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(b_addr, 0, 1024);
-          const uint64_t da1 = make_smem_desc_sw128(a_addr + kATileBytes, 0, 1024);
-          const uint64_t db1 = make_smem_desc_sw128(b_addr + kBTileBytes, 0, 1024);
-#pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k) {
-            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            const uint64_t koff = uint64_t(k * 2);  // 16 bf16 = 32 bytes, >>4
-            umma_f16(d0, da + koff, db + koff, idesc, accum);
-            if (args.gated == 1) umma_f16(d0 + BN, da1 + koff, db + koff, idesc, accum);
-            if (args.gated == 2) umma_f16(d0 + BN, da + koff, db1 + koff, idesc, accum);
-          }
-          umma_commit(&ctrl->empty[stage]);
-        }
-        __syncwarp();
-        if (++stage == stages) { stage = 0; phase ^= 1u; }
-      }
-      if (!alive) break;
-      if (lane == 0) umma_commit(&ctrl->tfull[acc]);
-      __syncwarp();
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
-    }
-  } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may touch
-    griddep_wait();  // residual / output buffers may still be in use by the preceding kernel
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      int rt, ct, sp;
-      decode_tile(args, w, rt, ct, sp);
-      const int row = rt * kTileRows + quad * 32 + lane;
-      const int col0 = ct * BN;
-      bool ok = mbar_wait(&ctrl->tfull[acc], acc_phase, abort_flag, args.status, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      tc_fence_after();
-      const uint32_t t0 = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * acc_cols);
-      const bool row_ok = row < args.rows;
-      float* out_f = reinterpret_cast<float*>(args.out) + (args.out_fp32 ? sp * args.split_stride : 0);
-      __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(args.out);
-      float bias_r = 0.f;
-      if (args.bias && args.bias_on_rows && row_ok && sp == 0) bias_r = __bfloat162float(args.bias[row]);
-
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t0 + c, v);
-        if (args.gated) {
-          uint32_t u[32];
-          tmem_ld_32x32(t0 + BN + c, u);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = __float_as_uint(silu_f(__uint_as_float(v[j])) * __uint_as_float(u[j]));
-        } else {
-          tmem_ld_wait();
-        }
-        if (c + 32 >= BN) {
-          // accumulator fully read: hand it back to the MMA warp before the stores
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&ctrl->tempty[acc]);
-        }
-        const int cbase = col0 + c;
-        if (cbase >= args.cols) continue;
-        if (args.bias && sp == 0) {
-          if (args.bias_on_rows) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias_r);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cbase + j < args.cols)
-                v[j] = __float_as_uint(__uint_as_float(v[j]) + __bfloat162float(args.bias[cbase + j]));
-          }
-        }
-        if constexpr (PUSH) {
-          // stage the chunk: token (c + j), feature (quad * 32 + lane)
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            stage_out[(c + j) * kTileRows + quad * 32 + lane] = __float2bfloat16(__uint_as_float(v[j]));
-          continue;
-        }
-        if (args.transpose_out) {
-          // out[col * ldo + row]: consecutive lanes hold consecutive rows -> coalesced
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = cbase + j;
-              if (col < args.cols) {
-                const long long idx = (long long)col * args.ldo + row;
-                float x = __uint_as_float(v[j]);
-                if (args.out_fp32) {
-                  out_f[idx] = x;
-                } else {
-                  if (args.residual) x += __bfloat162float(args.residual[idx]);
-                  out_h[idx] = __float2bfloat16(x);
-                }
-              }
-            }
-          }
-        } else if (row_ok) {
-          const long long base = (long long)row * args.ldo + cbase;
-          const bool full = (cbase + 32 <= args.cols);
-          if (args.out_fp32) {
-            if (full && ((base & 3) == 0)) {
-              float4* p = reinterpret_cast<float4*>(out_f + base);
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                p[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (cbase + j < args.cols) out_f[base + j] = __uint_as_float(v[j]);
-            }
-          } else {
-            if (full && ((base & 7) == 0)) {
-              uint32_t pk[16];
-              if (args.residual) {
-                const uint4* rp = reinterpret_cast<const uint4*>(args.residual + base);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint4 rr = rp[q];
-                  uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    float2 f = unpack_bf16x2(rw[e]);
-                    pk[q * 4 + e] = pack_bf16x2(__uint_as_float(v[q * 8 + 2 * e]) + f.x,
-                                                __uint_as_float(v[q * 8 + 2 * e + 1]) + f.y);
-                  }
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  pk[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-              }
-              uint4* p = reinterpret_cast<uint4*>(out_h + base);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) p[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j) {
-                if (cbase + j < args.cols) {
-                  float x = __uint_as_float(v[j]);
-                  if (args.residual) x += __bfloat162float(args.residual[base + j]);
-                  out_h[base + j] = __float2bfloat16(x);
-                }
-              }
-            }
-          }
-        }
-      }
-      if constexpr (PUSH) {
-        const int et = threadIdx.x - 64;  // 0..127 over the four epilogue warps
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int row0 = rt * kTileRows;
-        const long long slot = (long long)push.rank * args.splits + sp;
-        for (int idx = et; idx < BN * 16; idx += 128) {
-          const int tok = idx >> 4, ch = idx & 15;
-          const int gtok = col0 + tok, gfeat = row0 + ch * 8;
-          if (gtok < args.cols && gfeat < args.rows) {
-            const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
-            const long long off = (slot * args.cols + gtok) * args.ldo + gfeat;
-            for (int pr = 0; pr < push.n_peers; ++pr)
-              *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
-    }
-    if constexpr (PUSH) {
-      // all peer stores of this CTA are issued: publish them, count the CTA, and let the
-      // last CTA of the grid signal every peer
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const unsigned int old = atomicAdd(push.done_counter, 1u);
-        if (old == gridDim.x - 1) {
-          *push.done_counter = 0u;
-          __threadfence_system();
-          for (int pr = 0; pr < push.n_peers; ++pr) atomicAdd_system(push.peer_flag[pr], 1u);
-        }
-      }
-    }
-  }
-
-  if (*abort_flag) {
-    // let copies / MMAs that were already issued drain before shared memory goes away
-    for (int i = 0; i < 200; ++i) __nanosleep(1000);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
-}
 
 // ---------------------------------------------------------------------------
 // Host side

@@ -9,3 +9,5 @@ ops), ``utils``.
 """
 
 __version__ = "0.1.0"
+
+from .core.knob import knob  # noqa: E402,F401

@@ -1,0 +1,11 @@
+import logging
+
+
+def get_logger(name: str = "nkipy_b200") -> logging.Logger:
+    logger = logging.getLogger(name)
+    if not logger.handlers:
+        h = logging.StreamHandler()
+        h.setFormatter(logging.Formatter("%(asctime)s %(name)s %(levelname)s: %(message)s"))
+        logger.addHandler(h)
+        logger.setLevel(logging.WARNING)
+    return logger

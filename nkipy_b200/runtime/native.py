@@ -1,0 +1,52 @@
+"""In-tree build of the C++ device runtime (`nkipy_b200/spike/_spike*.so`).
+
+Plain g++ against pybind11 and the CUDA headers; the driver library itself is loaded
+with dlopen at run time, so the module builds and imports without a GPU.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+SRC_DIR = ROOT / "csrc" / "runtime"
+OUT_DIR = ROOT / "nkipy_b200" / "spike"
+BUILD_DIR = ROOT / "build" / "runtime"
+
+
+def module_path() -> Path:
+    return OUT_DIR / f"_spike{sysconfig.get_config_var('EXT_SUFFIX')}"
+
+
+def build(force: bool = False) -> Path:
+    import pybind11
+
+    srcs = sorted(SRC_DIR.glob("*.cpp"))
+    deps = srcs + sorted(SRC_DIR.glob("*.h")) + [ROOT / "csrc" / "kernels" / "gemm_args.h"]
+    h = hashlib.sha256()
+    for d in deps:
+        h.update(d.read_bytes())
+    stamp = h.hexdigest()[:16]
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    stamp_file = BUILD_DIR / "stamp"
+    out = module_path()
+    if not force and out.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
+        return out
+    cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
+           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{cuda_inc}",
+           *[str(s) for s in srcs], "-o", str(out), "-ldl", "-lpthread"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the device runtime failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    stamp_file.write_text(stamp)
+    return out
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))
