@@ -11,11 +11,10 @@ from .spike_tensor import SpikeTensor
 def __getattr__(name):
     # native types are resolved lazily so importing the package never needs the compiled module
     if name in ("SpikeError", "SpikeRuntimeError", "CudaError", "NrtError", "SystemTraceSession", "ModelTensorInfo",
-                "NrtModel", "NrtTensor", "TensorMetadata", "Spike", "_spike"):
+                "NrtModel", "NrtTensor", "TensorMetadata", "Spike"):
         from .spike_singleton import _native
 
-        mod = _native()
-        return mod if name == "_spike" else getattr(mod, name)
+        return getattr(_native(), name)
     raise AttributeError(name)
 
 

@@ -120,9 +120,9 @@ class SpikeModel:
         if outputs is None:
             outputs = self.allocate_output_tensors(self.model_ref.core_id)
         if mode == "device":
-            from . import _spike
+            from .spike_singleton import _native
 
-            with _spike.SystemTraceSession(self.model_ref.core_id) as session:
+            with _native().SystemTraceSession(self.model_ref.core_id) as session:
                 for _ in range(warmup_iterations):
                     self(inputs, outputs)
                 session.drain_events()

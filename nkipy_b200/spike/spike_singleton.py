@@ -22,14 +22,15 @@ _device_ordinal = -1
 
 
 def _native():
+    import importlib
+
     try:
-        from . import _spike
+        return importlib.import_module("nkipy_b200.spike._spike")
     except ImportError:
         from ..runtime.native import build
 
         build()
-        from . import _spike
-    return _spike
+        return importlib.import_module("nkipy_b200.spike._spike")
 
 
 def configure(visible_cores: Optional[Iterable[int]] = None, device_ordinal: Optional[int] = None) -> None:

@@ -153,7 +153,9 @@ def test_runtime_lifecycle_in_subprocess():
 import numpy as np, sys
 sys.path.insert(0, %r)
 from nkipy_b200 import spike
-from nkipy_b200.spike import SpikeTensor, get_spike_singleton, _spike
+from nkipy_b200.spike import SpikeTensor, get_spike_singleton
+from nkipy_b200.spike.spike_singleton import _native
+_spike = _native()
 rt = get_spike_singleton()
 assert rt.sm_count > 0 and 'B200' in rt.device_name or rt.sm_count > 0
 t = SpikeTensor.from_numpy(np.arange(16, dtype=np.float32))
