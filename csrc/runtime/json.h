@@ -1,5 +1,6 @@
 // Minimal JSON reader / writer used for kernel plans and trace events.
 #pragma once
+#include <algorithm>
 #include <cstdint>
 #include <map>
 #include <memory>
@@ -15,6 +16,7 @@ class Json {
   enum Type { Null, Bool, Number, String, Array, Object };
   Type type = Null;
   bool b = false;
+  bool is_int = false;   // number written without fraction / exponent
   double num = 0;
   std::string str;
   std::vector<Json> arr;
@@ -43,6 +45,52 @@ class Json {
     skip_ws(text, pos);
     if (pos != text.size()) throw std::runtime_error("json: trailing characters");
     return j;
+  }
+
+  static Json make_int(long long v) { Json j; j.type = Number; j.num = double(v); j.is_int = true; return j; }
+  static Json make_num(double v) { Json j; j.type = Number; j.num = v; return j; }
+  static Json make_str(const std::string& v) { Json j; j.type = String; j.str = v; return j; }
+  static Json make_bool(bool v) { Json j; j.type = Bool; j.b = v; return j; }
+  static Json make_array() { Json j; j.type = Array; return j; }
+  static Json make_object() { Json j; j.type = Object; return j; }
+  void set(const std::string& k, const Json& v) {
+    type = Object;
+    for (auto& kv : obj)
+      if (kv.first == k) { kv.second = v; return; }
+    obj.emplace_back(k, v);
+  }
+  void erase(const std::string& k) {
+    for (size_t i = 0; i < obj.size(); ++i)
+      if (obj[i].first == k) { obj.erase(obj.begin() + long(i)); return; }
+  }
+  // Same separators as Python's json.dumps(separators=(", ", ": ")); object keys sorted.
+  std::string dump() const {
+    std::ostringstream os;
+    switch (type) {
+      case Null: os << "null"; break;
+      case Bool: os << (b ? "true" : "false"); break;
+      case Number:
+        if (is_int) os << static_cast<long long>(num);
+        else { os.precision(17); os << num; if (os.str().find_first_of(".eE") == std::string::npos) os << ".0"; }
+        break;
+      case String: os << quote(str); break;
+      case Array:
+        os << "[";
+        for (size_t i = 0; i < arr.size(); ++i) os << (i ? ", " : "") << arr[i].dump();
+        os << "]";
+        break;
+      case Object: {
+        std::vector<const std::pair<std::string, Json>*> items;
+        for (auto& kv : obj) items.push_back(&kv);
+        std::sort(items.begin(), items.end(), [](auto* a, auto* b2) { return a->first < b2->first; });
+        os << "{";
+        for (size_t i = 0; i < items.size(); ++i)
+          os << (i ? ", " : "") << quote(items[i]->first) << ": " << items[i]->second.dump();
+        os << "}";
+        break;
+      }
+    }
+    return os.str();
   }
 
   static std::string quote(const std::string& s) {
@@ -112,7 +160,11 @@ class Json {
       ++end;
     if (end == p) throw std::runtime_error("json: unexpected character");
     j.type = Number;
-    j.num = std::stod(t.substr(p, end - p));
+    {
+      const std::string tok = t.substr(p, end - p);
+      j.num = std::stod(tok);
+      j.is_int = tok.find_first_of(".eE") == std::string::npos;
+    }
     p = end;
     return j;
   }

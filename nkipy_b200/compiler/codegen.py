@@ -885,7 +885,25 @@ class Generator:
     lower_all_gather = lower_all_reduce = lower_reduce_scatter = lower_all_to_all = _collective
 
     def lower_custom_call(self, n):
-        raise CodegenError("custom_call kernels are linked by nkipy_b200.core.cuda_op, not generated")
+        """Hand-written kernel: its source is emitted verbatim; arguments are the operand
+        pointers followed by the output pointers.  An output aliased to an operand starts as
+        a copy of that operand (the kernel updates it in place)."""
+        at = n.attrs
+        if at["source"] not in self.kernels:
+            self.kernels.append(at["source"])
+        args = []
+        for x in n.inputs:
+            vw = self.materialize(x)
+            args.append({"buffer": vw.buffer, "offset": 0})
+        aliases = {int(k): int(v) for k, v in (at.get("aliases") or {}).items()}
+        for i, o in enumerate(n.outputs):
+            if i in aliases:
+                ov = self._copy_into_new(n.inputs[aliases[i]], o, n)
+            else:
+                ov = self._out(o)
+            args.append({"buffer": ov.buffer, "offset": 0})
+        self.launches.append(Launch(at["entry"], tuple(at["grid"]), tuple(at["block"]), int(at.get("smem", 0)), args,
+                                    f"{n.loc[0]}:{n.loc[1]}" if n.loc else None))
 
 
 def _int_min(dt) -> str:

@@ -1,0 +1,56 @@
+"""In-tree build of the native compiler: the `_b200c` Python module and the
+`nkipy-b200-opt` command-line driver (plain g++, no external dependencies)."""
+
+from __future__ import annotations
+
+import hashlib
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+SRC_DIR = ROOT / "csrc" / "compiler"
+OUT_DIR = ROOT / "nkipy_b200" / "nkigen"
+BUILD_DIR = ROOT / "build" / "compiler"
+
+
+def module_path() -> Path:
+    return OUT_DIR / f"_b200c{sysconfig.get_config_var('EXT_SUFFIX')}"
+
+
+def opt_path() -> Path:
+    return OUT_DIR / "nkipy-b200-opt"
+
+
+def build(force: bool = False):
+    import pybind11
+
+    deps = sorted(SRC_DIR.glob("*.cpp")) + sorted(SRC_DIR.glob("*.h")) + [ROOT / "csrc" / "runtime" / "json.h"]
+    h = hashlib.sha256()
+    for d in deps:
+        h.update(d.read_bytes())
+    stamp = h.hexdigest()[:16]
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    stamp_file = BUILD_DIR / "stamp"
+    if (not force and module_path().exists() and opt_path().exists() and stamp_file.exists()
+            and stamp_file.read_text() == stamp):
+        return module_path(), opt_path()
+    lib = [str(SRC_DIR / "ir.cpp"), str(SRC_DIR / "passes.cpp")]
+    common = ["g++", "-O2", "-std=c++17", "-Wall", "-fPIC"]
+    cmds = [
+        common + ["-shared", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
+                  f"-I{sysconfig.get_paths()['include']}", *lib, str(SRC_DIR / "bindings.cpp"), "-o",
+                  str(module_path())],
+        common + [*lib, str(SRC_DIR / "opt_main.cpp"), "-o", str(opt_path())],
+    ]
+    for cmd in cmds:
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"building the native compiler failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    stamp_file.write_text(stamp)
+    return module_path(), opt_path()
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

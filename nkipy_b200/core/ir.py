@@ -511,7 +511,7 @@ def _attrs_to_json(attrs: Dict[str, Any]) -> str:
             return {k: enc(x) for k, x in v.items()}
         return v
 
-    return json.dumps({k: enc(v) for k, v in sorted(attrs.items())}, separators=(", ", ": "))
+    return json.dumps({k: enc(v) for k, v in sorted(attrs.items()) if not callable(v)}, separators=(", ", ": "))
 
 
 def _attrs_from_json(s: str) -> Dict[str, Any]:

@@ -88,6 +88,9 @@ class NKIPyKernel:
         graph = Graph(self.func.__name__)
         ctx = HLOTraceContext(graph)
         ctx.backend_name = "hlo"
+        if self.backend == "nkigen":
+            ctx.honours_knobs = True
+            ctx.knobs = {}
         params: List[NKIPyTensorRef] = []
 
         def convert(name: str, arg: Any):
@@ -105,9 +108,21 @@ class NKIPyKernel:
             cargs, ckwargs = _convert_args(sig, bound, convert)
             result = self.func(*cargs, **ckwargs)
             self._finish(graph, params, result)
+        if self.backend == "nkigen":
+            self._apply_nkigen_conventions(graph, ctx)
         self._code = graph
         self._params = params
         return graph
+
+    @staticmethod
+    def _apply_nkigen_conventions(graph: Graph, ctx) -> None:
+        for vid, hint in ctx.knobs.items():
+            for n in graph.nodes:
+                if any(o.id == vid for o in n.outputs):
+                    cur = dict(n.attrs.get("_knob") or {})
+                    cur.update({k: v for k, v in hint.items() if v is not None})
+                    n.attrs["_knob"] = cur
+        _nkigen_names(graph)
 
     def _finish(self, graph: Graph, params: List[NKIPyTensorRef], result) -> None:
         from . import ops
@@ -147,6 +162,19 @@ class NKIPyKernel:
         for a in aliases:
             graph.params[a.param_index].name = f"{a.param_name}.must_alias_input"
         graph.set_results(values, names, aliases)
+
+
+def _nkigen_names(graph: Graph) -> None:
+    """Inputs are called in_tensor_{i}, outputs `output` / `output_{i}` on the native backend
+    (aliased outputs keep the parameter name)."""
+    aliased_out = {a.output_index for a in graph.alias_list}
+    aliased_in = {a.param_index for a in graph.alias_list}
+    for i, p in enumerate(graph.params):
+        if i not in aliased_in:
+            p.name = f"in_tensor_{i}"
+    free = [i for i in range(len(graph.results)) if i not in aliased_out]
+    for k, i in enumerate(free):
+        graph.result_names[i] = "output" if len(free) == 1 else f"output_{k}"
 
 
 def trace(func=None, *, backend: str = "hlo"):

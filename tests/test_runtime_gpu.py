@@ -185,3 +185,28 @@ print('LIFECYCLE_OK')
 """ % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-W", "ignore", "-c", code], capture_output=True, text=True, timeout=120)
     assert "LIFECYCLE_OK" in res.stdout, res.stdout + res.stderr
+
+
+def test_custom_cuda_op_and_native_backend_on_device(tmp_path):
+    from nkipy_b200 import nkigen
+    from nkipy_b200.core.cuda_op import cuda_custom_op
+    from nkipy_b200.nkigen.compile import compile_to_neff
+    from nkipy_b200.runtime import DeviceKernel, DeviceTensor
+
+    src = ('extern "C" __global__ void scale_add_kernel(const float* a, const float* b, float* out) {'
+           ' int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < 4096) out[i] = 2.f * a[i] + b[i]; }')
+    op = cuda_custom_op("scale_add", src, "scale_add_kernel", [((4096,), "f32")], grid=(16,), block=(256,),
+                        reference=lambda a, b: 2 * a + b)
+    a, b = f32(4096), f32(4096)
+    check(lambda x, y: op(x, y) * 0.5 + 1, a, b)
+
+    @nkigen.trace(input_specs=[((64, 128), "f32"), ((96, 128), "f32")])
+    def k(x, w):
+        h = x @ np.transpose(w, (1, 0))
+        return np.tanh(h + np.zeros_like(h)) ** 2
+
+    path = compile_to_neff(k, str(tmp_path), "k.cubin", dump_dir=str(tmp_path / "dump"))
+    model = DeviceKernel.load_from_neff(path)
+    x, w = f32(64, 128), f32(96, 128)
+    out = model({"in_tensor_0": DeviceTensor.from_numpy(x), "in_tensor_1": DeviceTensor.from_numpy(w)})
+    np.testing.assert_allclose(out["output"].numpy(), np.tanh(x @ w.T) ** 2, rtol=1e-3, atol=1e-4)
