@@ -57,6 +57,15 @@ int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tok
                        long long ldx, long long ldo, int splits, const void* bias, int block_n, void* const* peer_out,
                        void* const* peer_flag, int n_peers, int rank, void* done_counter, void* stream);
 
+int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, void* out, const int* group_offsets, int num_groups,
+                          int features, int k, int total_rows, int max_rows_per_group, long long ldx, long long ldo,
+                          int gated, int gate_off, const void* bias, long long bias_group_stride, float act_limit,
+                          float act_alpha, int block_n, void* stream);
+int nkb_moe_dispatch(const int* experts, int tokens, int top_k, int expert_lo, int num_local, const void* x, int hidden,
+                     void* x_sorted, int* counts, int* offsets, int* cursors, int* pair_pos, void* stream);
+int nkb_moe_combine(const void* y_sorted, const int* pair_pos, const float* weights, int tokens, int top_k, int hidden,
+                    void* out, void* stream);
+
 // symmetric memory over CUDA IPC + consumer of the fused GEMM + all-reduce (comm.cu)
 int nkb_symm_alloc(void** out, long long bytes);
 int nkb_symm_free(void* p);

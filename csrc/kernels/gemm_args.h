@@ -22,6 +22,14 @@ struct GemmArgs {
   int bias_on_rows;
   int stages;
   int weights_operand;  // 0 = A, 1 = B holds immutable weights (may be fetched before the dependency wait), -1 none
+  // grouped mode (MoE experts): A is [num_groups, rows(+gate), k] (3-D tensor map), B and the output are
+  // row-sorted by group; group g owns B rows / output columns [group_offsets[g], group_offsets[g + 1])
+  int num_groups;          // 0 = plain GEMM
+  int max_col_tiles;       // upper bound of column tiles per group (work items beyond a group's count are skipped)
+  const int* group_offsets;
+  long long bias_group_stride;
+  float act_limit;         // > 0: clamped SwiGLU (up + 1) * gate * sigmoid(act_alpha * gate)
+  float act_alpha;
   long long ldo;
   long long split_stride;
   void* out;

@@ -164,3 +164,62 @@ extern "C" int nkb_gemm_bf16_push(const void* weights, const void* x, int featur
     default: return -2;
   }
 }
+
+// Grouped (per-expert) GEMM in the decode orientation:
+//   out[r, f] = sum_k x_sorted[r, k] * weights[g(r), f, k]     for the rows r of group g,
+// rows sorted by group, group g = rows [group_offsets[g], group_offsets[g + 1]).
+// gated: weights hold [gate; up] per group (2 * features rows, up half at gate_off) and the
+// epilogue applies the (optionally clamped) SwiGLU.  bias: [groups, bias_group_stride].
+extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, void* out, const int* group_offsets,
+                                     int num_groups, int features, int k, int total_rows, int max_rows_per_group,
+                                     long long ldx, long long ldo, int gated, int gate_off, const void* bias,
+                                     long long bias_group_stride, float act_limit, float act_alpha, int block_n,
+                                     void* stream) {
+  if (!status_word() && nkb_init() != 0) return -1;
+  if (num_groups <= 0 || features <= 0 || k <= 0 || total_rows <= 0) return 0;
+  if ((k & 7) || (ldx & 7)) return -2;
+  if (gated && block_n > 64) return -2;
+  GemmArgs args{};
+  args.rows = features;
+  args.cols = total_rows;
+  args.k = k;
+  args.kb_total = (k + kBlockK - 1) / kBlockK;
+  args.splits = 1;
+  args.kb_per_split = args.kb_total;
+  args.num_row_tiles = (features + kTileRows - 1) / kTileRows;
+  args.num_col_tiles = 1;
+  args.gated = gated ? 1 : 0;
+  args.gate_off = gate_off;
+  args.transpose_out = 1;
+  args.bias_on_rows = 1;
+  args.ldo = ldo;
+  args.out = out;
+  args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  args.bias_group_stride = bias_group_stride;
+  args.status = status_word();
+  args.weights_operand = -1;
+  args.num_groups = num_groups;
+  args.max_col_tiles = (max_rows_per_group + block_n - 1) / block_n;
+  if (args.max_col_tiles < 1) args.max_col_tiles = 1;
+  args.group_offsets = group_offsets;
+  args.act_limit = act_limit;
+  args.act_alpha = act_alpha;
+  const long long rows_per_group = gated ? (long long)gate_off + features : features;
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[3] = {uint64_t(k), uint64_t(rows_per_group), uint64_t(num_groups)};
+    const uint64_t strides[2] = {uint64_t(k) * 2, uint64_t(k) * 2 * uint64_t(rows_per_group)};
+    const uint32_t box[3] = {kBlockK, kTileRows, 1};
+    if (encode_tmap_bf16(&ta, weights, 3, dims, strides, box)) return -4;
+  }
+  if (encode_tmap_bf16_2d(&tb, x_sorted, k, total_rows, ldx, kBlockK, block_n)) return -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int max_ctas = 2 * num_sms();
+  const bool two = !gated || block_n <= 32;
+  switch (block_n) {
+    case 32: return two ? launch_gemm<32, 2>(ta, tb, args, max_ctas, s) : launch_gemm<32, 1>(ta, tb, args, num_sms(), s);
+    case 64: return two ? launch_gemm<64, 2>(ta, tb, args, max_ctas, s) : launch_gemm<64, 1>(ta, tb, args, num_sms(), s);
+    case 128: return launch_gemm<128, 1>(ta, tb, args, num_sms(), s);
+    default: return -2;
+  }
+}

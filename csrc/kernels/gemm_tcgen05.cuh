@@ -50,6 +50,37 @@ __device__ __forceinline__ void decode_tile(const GemmArgs& a, int w, int& row_t
   col_tile = in / gsz;
 }
 
+struct WorkItem {
+  int rt, ct, sp, group;
+  int col0;       // first B row / output column of this tile (global)
+  int cols_end;   // one past the last valid column (global)
+  bool valid;
+};
+
+template <int BN>
+__device__ __forceinline__ WorkItem decode_work(const GemmArgs& a, int w) {
+  WorkItem wi;
+  if (a.num_groups > 0) {
+    const int per_group = a.num_row_tiles * a.max_col_tiles;
+    wi.group = w / per_group;
+    const int rem = w - wi.group * per_group;
+    wi.rt = rem % a.num_row_tiles;
+    wi.ct = rem / a.num_row_tiles;
+    wi.sp = 0;
+    const int off = a.group_offsets[wi.group], end = a.group_offsets[wi.group + 1];
+    wi.col0 = off + wi.ct * BN;
+    wi.cols_end = end;
+    wi.valid = wi.col0 < end;
+  } else {
+    decode_tile(a, w, wi.rt, wi.ct, wi.sp);
+    wi.group = 0;
+    wi.col0 = wi.ct * BN;
+    wi.cols_end = a.cols;
+    wi.valid = true;
+  }
+  return wi;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
 template <int BN, bool PUSH>
@@ -98,20 +129,27 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
   const uint32_t tmem_base = ctrl->tmem_base;
   volatile int* abort_flag = &ctrl->abort;
 
-  const int total_work = args.num_row_tiles * args.num_col_tiles * args.splits;
+  const int total_work = args.num_groups > 0 ? args.num_groups * args.num_row_tiles * args.max_col_tiles
+                                             : args.num_row_tiles * args.num_col_tiles * args.splits;
 
   griddep_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    auto issue = [&](int stage, int kb, int row0, int col0, bool expect, bool do_a, bool do_b) {
+    auto issue = [&](int stage, int kb, int row0, int col0, int group, bool expect, bool do_a, bool do_b) {
       uint8_t* a_ptr = tiles + stage * stage_bytes;
       uint8_t* b_ptr = a_ptr + a_tiles * kATileBytes;
       if (expect) mbar_expect_tx(&ctrl->full[stage], stage_bytes);
       if (do_a) {
-        tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0);
-        if (args.gated == 1)
-          tma_load_2d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0);
+        if (args.num_groups > 0) {
+          tma_load_3d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0, group);
+          if (args.gated == 1)
+            tma_load_3d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0, group);
+        } else {
+          tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0);
+          if (args.gated == 1)
+            tma_load_2d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0);
+        }
       }
       if (do_b) {
         tma_load_2d(b_ptr, &tmB, &ctrl->full[stage], kb * kBlockK, col0);
@@ -123,14 +161,14 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     // before waiting for it, so the HBM stream starts during the predecessor's tail.
     int pre = 0;
     const bool w_is_a = args.weights_operand == 0;
-    if (args.weights_operand >= 0 && int(blockIdx.x) < total_work) {
+    if (args.weights_operand >= 0 && args.num_groups == 0 && int(blockIdx.x) < total_work) {
       int rt, ct, sp;
       decode_tile(args, blockIdx.x, rt, ct, sp);
       const int kb0 = sp * args.kb_per_split;
       const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
       pre = min(stages, kb1 - kb0);
       if (lane == 0)
-        for (int i = 0; i < pre; ++i) issue(i, kb0 + i, rt * kTileRows, ct * BN, true, w_is_a, !w_is_a);
+        for (int i = 0; i < pre; ++i) issue(i, kb0 + i, rt * kTileRows, ct * BN, 0, true, w_is_a, !w_is_a);
       __syncwarp();
     }
     griddep_wait();
@@ -138,9 +176,10 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     uint32_t phase = 0;
     bool alive = true;
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
-      int rt, ct, sp;
-      decode_tile(args, w, rt, ct, sp);
-      const int row0 = rt * kTileRows, col0 = ct * BN;
+      const WorkItem wi = decode_work<BN>(args, w);
+      if (!wi.valid) continue;
+      const int sp = wi.sp;
+      const int row0 = wi.rt * kTileRows, col0 = wi.col0;
       const int kb0 = sp * args.kb_per_split;
       const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
       for (int kb = kb0; kb < kb1; ++kb) {
@@ -148,8 +187,8 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
         if (lane == 0) {
           const bool prefetched = (w == int(blockIdx.x)) && (kb - kb0 < pre);
-          if (prefetched) issue(stage, kb, row0, col0, false, !w_is_a, w_is_a);
-          else issue(stage, kb, row0, col0, true, true, true);
+          if (prefetched) issue(stage, kb, row0, col0, wi.group, false, !w_is_a, w_is_a);
+          else issue(stage, kb, row0, col0, wi.group, true, true, true);
         }
         __syncwarp();
         if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -164,8 +203,9 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     uint32_t acc_phase = 0;
     bool alive = true;
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
-      int rt, ct, sp;
-      decode_tile(args, w, rt, ct, sp);
+      const WorkItem wi = decode_work<BN>(args, w);
+      if (!wi.valid) continue;
+      const int sp = wi.sp;
       const int kb0 = sp * args.kb_per_split;
       const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
       bool ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
@@ -209,10 +249,12 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      int rt, ct, sp;
-      decode_tile(args, w, rt, ct, sp);
+      const WorkItem wi = decode_work<BN>(args, w);
+      if (!wi.valid) continue;
+      const int rt = wi.rt, sp = wi.sp;
+      const int cols_end = wi.cols_end;
       const int row = rt * kTileRows + quad * 32 + lane;
-      const int col0 = ct * BN;
+      const int col0 = wi.col0;
       bool ok = mbar_wait(&ctrl->tfull[acc], acc_phase, abort_flag, args.status, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, ok)) break;
       tc_fence_after();
@@ -221,7 +263,8 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
       float* out_f = reinterpret_cast<float*>(args.out) + (args.out_fp32 ? sp * args.split_stride : 0);
       __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(args.out);
       float bias_r = 0.f;
-      if (args.bias && args.bias_on_rows && row_ok && sp == 0) bias_r = __bfloat162float(args.bias[row]);
+      if (args.bias && args.bias_on_rows && row_ok && sp == 0)
+        bias_r = __bfloat162float(args.bias[wi.group * args.bias_group_stride + row]);
 
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -233,7 +276,20 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            v[j] = __float_as_uint(silu_f(__uint_as_float(v[j])) * __uint_as_float(u[j]));
+          {
+            float gg = __uint_as_float(v[j]), uu = __uint_as_float(u[j]);
+            if (args.bias && args.bias_on_rows && row_ok) {   // gate / up biases before the activation
+              gg += bias_r;
+              uu += __bfloat162float(args.bias[wi.group * args.bias_group_stride + args.gate_off + row]);
+            }
+            if (args.act_limit > 0.f) {
+              gg = fminf(gg, args.act_limit);
+              uu = fminf(fmaxf(uu, -args.act_limit), args.act_limit);
+              v[j] = __float_as_uint((uu + 1.f) * gg / (1.f + __expf(-args.act_alpha * gg)));
+            } else {
+              v[j] = __float_as_uint(silu_f(gg) * uu);
+            }
+          }
         } else {
           tmem_ld_wait();
         }
@@ -244,15 +300,15 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           if (lane == 0) mbar_arrive(&ctrl->tempty[acc]);
         }
         const int cbase = col0 + c;
-        if (cbase >= args.cols) continue;
-        if (args.bias && sp == 0) {
+        if (cbase >= cols_end) continue;
+        if (args.bias && sp == 0 && !args.gated) {
           if (args.bias_on_rows) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias_r);
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (cbase + j < args.cols)
+              if (cbase + j < cols_end)
                 v[j] = __float_as_uint(__uint_as_float(v[j]) + __bfloat162float(args.bias[cbase + j]));
           }
         }
@@ -269,7 +325,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int col = cbase + j;
-              if (col < args.cols) {
+              if (col < cols_end) {
                 const long long idx = (long long)col * args.ldo + row;
                 float x = __uint_as_float(v[j]);
                 if (args.out_fp32) {
@@ -283,7 +339,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
         } else if (row_ok) {
           const long long base = (long long)row * args.ldo + cbase;
-          const bool full = (cbase + 32 <= args.cols);
+          const bool full = (cbase + 32 <= cols_end);
           if (args.out_fp32) {
             if (full && ((base & 3) == 0)) {
               float4* p = reinterpret_cast<float4*>(out_f + base);
@@ -293,7 +349,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
             } else {
               for (int j = 0; j < 32; ++j)
-                if (cbase + j < args.cols) out_f[base + j] = __uint_as_float(v[j]);
+                if (cbase + j < cols_end) out_f[base + j] = __uint_as_float(v[j]);
             }
           } else {
             if (full && ((base & 7) == 0)) {
@@ -321,7 +377,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
               for (int q = 0; q < 4; ++q) p[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
             } else {
               for (int j = 0; j < 32; ++j) {
-                if (cbase + j < args.cols) {
+                if (cbase + j < cols_end) {
                   float x = __uint_as_float(v[j]);
                   if (args.residual) x += __bfloat162float(args.residual[base + j]);
                   out_h[base + j] = __float2bfloat16(x);
@@ -339,7 +395,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
         for (int idx = et; idx < BN * 16; idx += 128) {
           const int tok = idx >> 4, ch = idx & 15;
           const int gtok = col0 + tok, gfeat = row0 + ch * 8;
-          if (gtok < args.cols && gfeat < args.rows) {
+          if (gtok < cols_end && gfeat < args.rows) {
             const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
             const long long off = (slot * args.cols + gtok) * args.ldo + gfeat;
             for (int pr = 0; pr < push.n_peers; ++pr)

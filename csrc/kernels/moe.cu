@@ -1,0 +1,134 @@
+// Mixture-of-experts token routing around the grouped expert GEMM: sort (token, expert)
+// pairs by local expert, gather the token rows into expert-sorted order, and combine the
+// weighted expert outputs per token.
+//
+// Reference parity: the reference evaluates MoE with per-token Python loops unrolled at
+// trace time (examples/models/qwen3/kernels/transformer_layer.py:77-110) or by gathering the
+// top-k expert matrices (examples/models/gpt_oss/kernels/feedforward.py:87-144), with every
+// rank holding all experts.  Here experts are sharded over ranks (expert parallelism): a
+// rank processes the pairs routed to its experts [expert_lo, expert_lo + num_local) and
+// produces the partial sum of its experts' contributions for every token.
+#include "common.cuh"
+#include "api.h"
+
+namespace nkb {
+
+// counts[e] = number of pairs routed to local expert e
+__global__ void moe_count_kernel(const int* __restrict__ experts, int pairs, int expert_lo, int num_local,
+                                 int* __restrict__ counts) {
+  griddep_wait();
+  griddep_launch();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pairs) return;
+  const int e = experts[i] - expert_lo;
+  if (e >= 0 && e < num_local) atomicAdd(&counts[e], 1);
+}
+
+// exclusive scan of counts -> offsets[0..num_local], cursors reset to 0 (one block)
+__global__ void moe_scan_kernel(const int* __restrict__ counts, int num_local, int* __restrict__ offsets,
+                                int* __restrict__ cursors) {
+  griddep_wait();
+  griddep_launch();
+  __shared__ int tmp[1024];
+  const int t = threadIdx.x;
+  tmp[t] = t < num_local ? counts[t] : 0;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int v = t >= o ? tmp[t - o] : 0;
+    __syncthreads();
+    tmp[t] += v;
+    __syncthreads();
+  }
+  if (t < num_local) {
+    offsets[t + 1] = tmp[t];
+    cursors[t] = 0;
+  }
+  if (t == 0) offsets[0] = 0;
+}
+
+// one block per pair: claim a slot in its expert's segment and copy the token row there
+__global__ void moe_scatter_kernel(const int* __restrict__ experts, int pairs, int top_k, int expert_lo,
+                                   int num_local, const int* __restrict__ offsets, int* __restrict__ cursors,
+                                   const __nv_bfloat16* __restrict__ x, int hidden, __nv_bfloat16* __restrict__ x_sorted,
+                                   int* __restrict__ pair_pos) {
+  griddep_wait();
+  griddep_launch();
+  __shared__ int s_pos;
+  const int pair = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = experts[pair] - expert_lo;
+    int pos = -1;
+    if (e >= 0 && e < num_local) pos = offsets[e] + atomicAdd(&cursors[e], 1);
+    pair_pos[pair] = pos;
+    s_pos = pos;
+  }
+  __syncthreads();
+  const int pos = s_pos;
+  if (pos < 0) return;
+  const int token = pair / top_k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)token * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(x_sorted + (long long)pos * hidden);
+  for (int v = threadIdx.x; v < (hidden >> 3); v += blockDim.x) dst[v] = src[v];
+}
+
+// out[t] = sum_j w[t, j] * y_sorted[pair_pos[t * k + j]]   over the pairs handled locally
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y_sorted, const int* __restrict__ pair_pos,
+                                   const float* __restrict__ weights, int top_k, int hidden,
+                                   __nv_bfloat16* __restrict__ out) {
+  griddep_wait();
+  griddep_launch();
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < (hidden >> 3); v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int pos = pair_pos[t * top_k + j];
+      if (pos < 0) continue;
+      const float w = weights[t * top_k + j];
+      const uint4 r = *reinterpret_cast<const uint4*>(y_sorted + (long long)pos * hidden + v * 8);
+      const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(rw[e]);
+        acc[2 * e] += w * f.x;
+        acc[2 * e + 1] += w * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (long long)t * hidden + v * 8) = o;
+  }
+}
+
+}  // namespace nkb
+
+using namespace nkb;
+
+// experts [tokens * top_k] int32 (global expert ids).  Workspace (device, int32): counts[num_local],
+// offsets[num_local + 1], cursors[num_local], pair_pos[tokens * top_k].  x_sorted must hold
+// tokens * top_k rows.  After the call offsets / pair_pos / x_sorted are valid on the stream.
+extern "C" int nkb_moe_dispatch(const int* experts, int tokens, int top_k, int expert_lo, int num_local, const void* x,
+                                int hidden, void* x_sorted, int* counts, int* offsets, int* cursors, int* pair_pos,
+                                void* stream) {
+  if (tokens <= 0) return 0;
+  if (num_local > 1024 || (hidden & 7)) return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int pairs = tokens * top_k;
+  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * num_local, s);
+  if (e != cudaSuccess) return int(e);
+  int rc = launch_pdl(moe_count_kernel, dim3((pairs + 255) / 256), dim3(256), 0, s, experts, pairs, expert_lo,
+                      num_local, counts);
+  if (rc) return rc;
+  rc = launch_pdl(moe_scan_kernel, dim3(1), dim3(1024), 0, s, (const int*)counts, num_local, offsets, cursors);
+  if (rc) return rc;
+  return launch_pdl(moe_scatter_kernel, dim3(pairs), dim3(128), 0, s, experts, pairs, top_k, expert_lo, num_local,
+                    (const int*)offsets, cursors, (const __nv_bfloat16*)x, hidden, (__nv_bfloat16*)x_sorted, pair_pos);
+}
+
+extern "C" int nkb_moe_combine(const void* y_sorted, const int* pair_pos, const float* weights, int tokens, int top_k,
+                               int hidden, void* out, void* stream) {
+  if (tokens <= 0) return 0;
+  if (hidden & 7) return -2;
+  return launch_pdl(moe_combine_kernel, dim3(tokens), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                    (const __nv_bfloat16*)y_sorted, pair_pos, weights, top_k, hidden, (__nv_bfloat16*)out);
+}

@@ -1,0 +1,47 @@
+"""Mixture-of-experts FFN block with expert parallelism.
+
+The reference keeps every expert on every rank and shards the expert intermediate
+dimension (tensor parallelism), evaluating experts with per-token loops or batched
+gathers (examples/models/qwen3/kernels/transformer_layer.py:70-115,
+examples/models/gpt_oss/kernels/feedforward.py:39-206).  Here the default is expert
+parallelism: rank r owns experts [r * E / ep, (r + 1) * E / ep); activations are
+replicated by the preceding tensor-parallel reduction, so *dispatch* is a local
+sort-and-gather of the pairs routed to local experts, the experts run as two grouped
+tcgen05 GEMMs (SwiGLU fused into the first), and *combine* sums the weighted expert
+outputs per token locally and then over ranks.  `moe_parallel="tp"` reproduces the
+reference's sharding with the same code path (all experts local, narrower experts).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..parallel.comm import TPGroup
+from .config import ModelConfig
+
+
+class MoEBlock:
+    def __init__(self, cfg: ModelConfig, tp: TPGroup, moe_parallel: str = "ep"):
+        self.cfg, self.tp, self.mode = cfg, tp, moe_parallel
+        if moe_parallel == "ep" and cfg.num_experts % tp.world_size:
+            raise ValueError("expert parallelism needs num_experts divisible by the number of ranks")
+        self.num_local = cfg.num_experts // tp.world_size if moe_parallel == "ep" else cfg.num_experts
+        self.expert_lo = tp.rank * self.num_local if moe_parallel == "ep" else 0
+
+    def route(self, lw, x: torch.Tensor):
+        logits = ops.linear(x, lw.router, bias=lw.router_bias)
+        return ops.router_topk(logits, self.cfg.top_k, self.cfg.router_mode)
+
+    def forward(self, lw, x: torch.Tensor) -> torch.Tensor:
+        """x [T, H] (normed hidden states, replicated over ranks) -> MoE output [T, H], summed over ranks."""
+        cfg = self.cfg
+        T = x.shape[0]
+        weights, experts = self.route(lw, x)
+        x_sorted, offsets, pair_pos = ops.moe_dispatch(x, experts, self.expert_lo, self.num_local)
+        h = ops.grouped_linear(x_sorted, lw.gate_up, offsets, max_rows_per_group=T, gated=True,
+                               bias=lw.gate_up_bias, act_limit=cfg.swiglu_limit, act_alpha=cfg.swiglu_alpha)
+        y_sorted = ops.grouped_linear(h, lw.down, offsets, max_rows_per_group=T, bias=lw.down_bias)
+        y = ops.moe_combine(y_sorted, pair_pos, weights, T)
+        self.tp.all_reduce(y)
+        return y

@@ -26,7 +26,7 @@ from ._lib import KernelLibraryError, device_status, raise_on_device_error
 
 __all__ = [
     "linear", "reduce_partials", "rmsnorm", "add_rmsnorm", "silu_mul", "embedding", "rope_kv_append",
-    "argmax", "sample", "decode_advance", "router_topk", "paged_attn_decode", "flash_attn_prefill", "rope_table",
+    "argmax", "sample", "decode_advance", "router_topk", "moe_dispatch", "grouped_linear", "moe_combine", "paged_attn_decode", "flash_attn_prefill", "rope_table",
     "KernelLibraryError", "device_status", "raise_on_device_error", "native_available", "launch_count",
     "reset_launch_count",
 ]
@@ -675,5 +675,107 @@ def flash_attn_prefill(
         _stream(),
     )
     _lib.check(rc, "nkb_flash_attn_prefill")
+    _launches += 1
+    return out
+
+
+# --------------------------------------------------------------------------- mixture of experts
+def moe_dispatch(x: torch.Tensor, experts: torch.Tensor, expert_lo: int, num_local: int):
+    """Sort the (token, expert) pairs routed to local experts [expert_lo, expert_lo + num_local) by
+    expert and gather their token rows.  x [T, H] bf16, experts [T, k] int32 (global ids).
+    Returns (x_sorted [T * k, H], offsets int32 [num_local + 1], pair_pos int32 [T * k]); rows past
+    offsets[-1] of x_sorted are unspecified, pair_pos is -1 for pairs of other ranks' experts."""
+    T, H = x.shape
+    k = experts.shape[1]
+    pairs = T * k
+    dev = x.device
+    if not _native(x):
+        flat = experts.reshape(-1).long() - expert_lo
+        local = (flat >= 0) & (flat < num_local)
+        order = torch.argsort(torch.where(local, flat, torch.full_like(flat, num_local)), stable=True)
+        n_local = int(local.sum())
+        pair_pos = torch.full((pairs,), -1, dtype=torch.int32)
+        pair_pos[order[:n_local]] = torch.arange(n_local, dtype=torch.int32)
+        counts = torch.bincount(flat[local], minlength=num_local)
+        offsets = torch.zeros((num_local + 1,), dtype=torch.int32)
+        offsets[1:] = counts.cumsum(0).to(torch.int32)
+        x_sorted = torch.zeros((pairs, H), dtype=x.dtype)
+        x_sorted[:n_local] = x[(order[:n_local] // k)]
+        return x_sorted, offsets, pair_pos
+    global _launches
+    x_sorted = torch.empty((pairs, H), dtype=x.dtype, device=dev)
+    work = torch.empty((3 * num_local + 1 + pairs,), dtype=torch.int32, device=dev)
+    counts, offsets = work[:num_local], work[num_local:2 * num_local + 1]
+    cursors, pair_pos = work[2 * num_local + 1:3 * num_local + 1], work[3 * num_local + 1:]
+    if experts.dtype != torch.int32:
+        experts = experts.to(torch.int32)
+    rc = _lib.lib().nkb_moe_dispatch(experts.data_ptr(), T, k, int(expert_lo), int(num_local), x.data_ptr(), H,
+                                     x_sorted.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursors.data_ptr(),
+                                     pair_pos.data_ptr(), _stream())
+    _lib.check(rc, "nkb_moe_dispatch")
+    _launches += 3
+    return x_sorted, offsets, pair_pos
+
+
+def grouped_linear(x_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, max_rows_per_group: int,
+                   gated: bool = False, bias: Optional[torch.Tensor] = None, act_limit: float = 0.0,
+                   act_alpha: float = 1.702) -> torch.Tensor:
+    """Per-group ``y[r] = x_sorted[r] @ w[g(r)].T`` for rows sorted by group (group g owns rows
+    offsets[g] .. offsets[g + 1]).  w [G, N, K] bf16 (gated: [G, 2 * I, K], gate rows then up
+    rows, output ``act(gate) * up`` of width I).  bias [G, N] is added before the activation."""
+    R, K = x_sorted.shape
+    G = w.shape[0]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    if not _native(x_sorted):
+        out = torch.zeros((R, N), dtype=torch.bfloat16)
+        off = offsets.tolist()
+        for g in range(G):
+            a, b = off[g], off[g + 1]
+            if b <= a:
+                continue
+            y = x_sorted[a:b].float() @ w[g].float().T
+            if bias is not None:
+                y = y + bias[g].float()
+            if gated:
+                gg, uu = y[:, :N], y[:, N:]
+                if act_limit > 0:
+                    gg = gg.clamp(max=act_limit)
+                    uu = uu.clamp(-act_limit, act_limit)
+                    y = (uu + 1) * gg * torch.sigmoid(act_alpha * gg)
+                else:
+                    y = torch.nn.functional.silu(gg) * uu
+            out[a:b] = y.to(torch.bfloat16)
+        return out
+    global _launches
+    _check_bf16(x_sorted, w, bias)
+    out = torch.empty((R, N), dtype=torch.bfloat16, device=x_sorted.device)
+    block_n = 32 if max_rows_per_group <= 32 else 64
+    if not gated and max_rows_per_group > 64:
+        block_n = 128
+    rc = _lib.lib().nkb_gemm_bf16_grouped(
+        w.data_ptr(), x_sorted.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, N, K, R, int(max_rows_per_group),
+        x_sorted.stride(0), N, 1 if gated else 0, N if gated else 0, _ptr(bias),
+        bias.stride(0) if bias is not None else 0, float(act_limit), float(act_alpha), block_n, _stream())
+    _lib.check(rc, "nkb_gemm_bf16_grouped")
+    _launches += 1
+    return out
+
+
+def moe_combine(y_sorted: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tokens: int) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * y_sorted[pair_pos[t * k + j]]`` over local pairs -> bf16 [T, H]."""
+    k = weights.shape[1]
+    H = y_sorted.shape[1]
+    if not _native(y_sorted):
+        pos = pair_pos.reshape(tokens, k).long()
+        valid = pos >= 0
+        rows = y_sorted[pos.clamp(min=0)].float() * (weights.float() * valid)[..., None]
+        return rows.sum(1).to(torch.bfloat16)
+    global _launches
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device=y_sorted.device)
+    if weights.dtype != torch.float32:
+        weights = weights.float()
+    rc = _lib.lib().nkb_moe_combine(y_sorted.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(), tokens, k, H,
+                                    out.data_ptr(), _stream())
+    _lib.check(rc, "nkb_moe_combine")
     _launches += 1
     return out

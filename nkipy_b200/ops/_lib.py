@@ -28,6 +28,13 @@ _SIGNATURES = {
         [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int, c_longlong,
          c_int, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     ),
+    "nkb_gemm_bf16_grouped": (
+        c_int,
+        [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, _P, c_longlong,
+         c_float, c_float, c_int, _P],
+    ),
+    "nkb_moe_dispatch": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P]),
+    "nkb_moe_combine": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P, _P]),
     "nkb_gemm_effective_splits": (c_int, [c_int, c_int]),
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_add_rmsnorm": (c_int, [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),

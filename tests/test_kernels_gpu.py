@@ -269,3 +269,43 @@ def test_silu_mul_from_split_partials():
     x = parts.sum(0)
     g, u = x[:, :I].clamp(max=7.0), x[:, I:].clamp(-7.0, 7.0)
     assert rel_err(yc, (u + 1) * g * torch.sigmoid(1.702 * g)) < 5e-3
+
+
+@pytest.mark.parametrize("T,E,k,H,I,lo,nl", [(128, 16, 4, 512, 256, 0, 16), (37, 8, 2, 256, 128, 4, 4),
+                                              (300, 8, 2, 256, 384, 0, 8)])
+def test_moe_dispatch_grouped_gemm_combine(T, E, k, H, I, lo, nl):
+    x = randn(T, H)
+    logits = torch.randn(T, E, device=DEV)
+    wts, experts = ops.router_topk(logits, k, "softmax_topk")
+    xs, off, pos = ops.moe_dispatch(x, experts, lo, nl)
+    xs_c, off_c, pos_c = ops.moe_dispatch(x.cpu(), experts.cpu(), lo, nl)
+    assert torch.equal(off.cpu(), off_c)
+    n_local = int(off_c[-1])
+    assert ((pos.cpu() >= 0) == (pos_c >= 0)).all() and int((pos >= 0).sum()) == n_local
+    # rows land in the right expert segment and carry the right token
+    flat_e = experts.reshape(-1).cpu() - lo
+    for p in range(T * k):
+        if pos[p] >= 0:
+            e = int(flat_e[p])
+            assert off_c[e] <= int(pos[p]) < off_c[e + 1]
+    sel = (pos >= 0).nonzero().squeeze(-1)
+    assert torch.equal(xs[pos[sel].long()], x[(sel // k)])
+    w_gu = randn(nl, 2 * I, H, scale=0.05)
+    w_dn = randn(nl, H, I, scale=0.05)
+    b_gu, b_dn = randn(nl, 2 * I, scale=0.1), randn(nl, H, scale=0.1)
+    h = ops.grouped_linear(xs, w_gu, off, max_rows_per_group=T, gated=True, bias=b_gu)
+    y = ops.grouped_linear(h, w_dn, off, max_rows_per_group=T, bias=b_dn)
+    out = ops.moe_combine(y, pos, wts, T)
+    # fp32 reference straight from the definition
+    ref = torch.zeros(T, H, device=DEV)
+    for t in range(T):
+        for j in range(k):
+            e = int(experts[t, j]) - lo
+            if 0 <= e < nl:
+                z = x[t].float() @ w_gu[e].float().T + b_gu[e].float()
+                a = torch.nn.functional.silu(z[:I]) * z[I:]
+                ref[t] += wts[t, j] * (a.to(torch.bfloat16).float() @ w_dn[e].float().T + b_dn[e].float())
+    assert rel_err(out, ref) < 2e-2
+    hc = ops.grouped_linear(xs, w_gu, off, max_rows_per_group=T, gated=True, act_limit=7.0, act_alpha=1.702)
+    hc_ref = ops.grouped_linear(xs.cpu(), w_gu.cpu(), off.cpu(), max_rows_per_group=T, gated=True, act_limit=7.0)
+    assert rel_err(hc[:n_local].cpu(), hc_ref[:n_local]) < 2e-2

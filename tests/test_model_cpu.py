@@ -87,3 +87,29 @@ def test_gqa_replicated_kv_and_qknorm_cpu():
     out = eng.generate(p, 3)
     ref = EagerTransformer(cfg, w, dtype=torch.float32).generate(torch.tensor(p), 3)
     assert out[0][0] == ref[0, 0].item()
+
+
+def test_moe_models_match_oracle_cpu():
+    """Qwen3-style (softmax -> top-k -> renorm, QK-norm) and gpt-oss-style (top-k -> softmax, biases,
+    sinks, sliding window, clamped SwiGLU, YaRN) tiny MoE models against the eager oracle."""
+    qwen = C.tiny(name="tiny-qwen3-moe", qk_norm=True, num_experts=8, top_k=2, moe_intermediate_size=128,
+                  intermediate_size=0, rms_eps=1e-6, rope_theta=1e6)
+    oss = C.tiny(name="tiny-gpt-oss", num_experts=4, top_k=2, moe_intermediate_size=128, intermediate_size=0,
+                 attn_bias=True, router_mode="topk_softmax", router_bias=True, expert_bias=True, sliding_window=16,
+                 layer_types=["sliding_attention", "full_attention"], attention_sinks=True, swiglu_limit=7.0,
+                 rope_scaling_factor=4.0, rope_original_max_position=64, rope_theta=150000.0)
+    for cfg in (qwen, oss):
+        w = random_weights(cfg, seed=4, std=0.05)
+        model = TransformerLM(cfg, w, device="cpu")
+        eng = GenerationEngine(model, max_batch=2, max_seq_len=128, use_cuda_graph=False)
+        prompts = [_tokens(45, cfg.vocab_size, 8), _tokens(45, cfg.vocab_size, 9)]
+        seqs = eng.add_requests(prompts)
+        first = eng.prefill(seqs)
+        ref = EagerTransformer(cfg, w, dtype=torch.float32)
+        h = ref.forward(torch.tensor(prompts))
+        logits = (h[:, -1] @ ref.w["lm_head_weight"]).float()
+        for b in range(2):
+            assert logits[b, int(first[b])] >= logits[b].max() - 0.05 * logits[b].std(), cfg.name
+        eng.release(seqs)
+        out = eng.generate(prompts, 4)
+        assert all(len(o) == 4 for o in out)

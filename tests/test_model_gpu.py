@@ -86,3 +86,20 @@ def test_decode_hidden_matches_oracle():
     expect = ref.forward(first.long()[:, None], S)[:, 0]
     err = ((hidden.float() - expect).norm() / expect.norm()).item()
     assert err < 2e-2, err
+
+
+def test_moe_model_prefill_and_decode_match_oracle():
+    cfg = C.tiny(name="tiny-qwen3-moe", hidden_size=512, head_dim=128, num_heads=4, num_kv_heads=2, qk_norm=True,
+                 num_experts=16, top_k=4, moe_intermediate_size=256, intermediate_size=0, vocab_size=2048,
+                 num_layers=2, rms_eps=1e-6)
+    dev = torch.device("cuda")
+    w = random_weights(cfg, device=dev, seed=2, std=0.05)
+    model = TransformerLM(cfg, w, device=dev)
+    eng = GenerationEngine(model, max_batch=4, max_seq_len=256)
+    prompts = _prompts(4, 90, cfg.vocab_size, 3)
+    outs = eng.generate(prompts.tolist(), 6)
+    ref = EagerTransformer(cfg, w, device=dev, dtype=torch.float32)
+    expect = ref.generate(prompts.to(dev), 6).tolist()
+    assert [o[0] for o in outs] == [e[0] for e in expect]
+    agree = sum(int(a == b) for o, e in zip(outs, expect) for a, b in zip(o, e))
+    assert agree >= 18, (outs, expect)
