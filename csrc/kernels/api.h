@@ -60,9 +60,11 @@ int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tok
 int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, void* out, const int* group_offsets, int num_groups,
                           int features, int k, int total_rows, int max_rows_per_group, long long ldx, long long ldo,
                           int gated, int gate_off, const void* bias, long long bias_group_stride, float act_limit,
-                          float act_alpha, int block_n, void* stream);
+                          float act_alpha, int block_n, const int* tile_list, const int* tile_count, int max_tiles,
+                          void* stream);
 int nkb_moe_dispatch(const int* experts, int tokens, int top_k, int expert_lo, int num_local, const void* x, int hidden,
-                     void* x_sorted, int* counts, int* offsets, int* cursors, int* pair_pos, void* stream);
+                     void* x_sorted, int* counts, int* offsets, int* cursors, int* pair_pos, int bn_a, int* tiles_a,
+                     int* ntiles_a, int bn_b, int* tiles_b, int* ntiles_b, void* stream);
 int nkb_moe_combine(const void* y_sorted, const int* pair_pos, const float* weights, int tokens, int top_k, int hidden,
                     void* out, void* stream);
 
@@ -95,8 +97,8 @@ int nkb_argmax(const void* logits, int is_fp32, int* out_ids, float* out_vals, i
                void* stream);
 int nkb_sample(const void* logits, int is_fp32, int* out_ids, int rows, int vocab, long long ld, float temperature,
                int top_k, float top_p, unsigned long long seed, unsigned long long step, void* stream);
-int nkb_router_topk(const void* logits, int is_fp32, float* weights, int* experts, int tokens, int num_experts,
-                    int top_k, int mode, void* stream);
+int nkb_router_topk(const void* logits, int is_fp32, int splits, long long split_stride, const void* bias,
+                    float* weights, int* experts, int tokens, int num_experts, int top_k, int mode, void* stream);
 
 int nkb_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                           const int* context_lens, void* out, float* scratch, int batch, int q_len, int nq, int nkv,

@@ -10,19 +10,25 @@ namespace nkb {
 // ctas_per_sm = 2 caps the ring so that two CTAs (of this or of the next GEMM in
 // the stream, started early by programmatic dependent launch) fit on one SM: the
 // successor then prefetches its weight tiles while this kernel drains.
-template <int BN, int MINB, bool PUSH = false>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
-                       cudaStream_t stream, const PushArgs* push = nullptr) {
+template <int BN, int MINB, bool PUSH, bool GROUPED>
+static int ring_stages(const GemmArgs& args, int& smem) {
   const int a_tiles = args.gated == 1 ? 2 : 1, b_tiles = args.gated == 2 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * BN * kBlockK * 2;
   const int extra = 512 + (PUSH ? BN * kTileRows * 2 : 0);   // control block (+ push staging tile)
   const int budget = (MINB == 2 ? 113 * 1024 : 232448) - 1024 - extra - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) return -3;
-  args.stages = stages;
   static_assert(sizeof(GemmCtrl) <= 512, "control block grew");
-  const int smem = stages * stage_bytes + 1024 + extra + 64;
+  smem = stages * stage_bytes + 1024 + extra + 64;
+  return stages;
+}
+
+template <int BN, int MINB, bool PUSH = false>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
+                       cudaStream_t stream, const PushArgs* push = nullptr) {
+  int smem = 0;
+  args.stages = ring_stages<BN, MINB, PUSH, false>(args, smem);
+  if (args.stages < 2) return -3;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, MINB, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -30,12 +36,31 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a
     if (e != cudaSuccess) return int(e);
     attr_set = true;
   }
-  int total = args.num_row_tiles * args.num_col_tiles * args.splits;
-  int grid = total < max_ctas ? total : max_ctas;
+  const int total = args.num_row_tiles * args.num_col_tiles * args.splits;
+  const int grid = total < max_ctas ? total : max_ctas;
   PushArgs pa{};
   if (push) pa = *push;
   return launch_pdl(gemm_bf16_kernel<BN, MINB, PUSH>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb,
                     args, pa);
+}
+
+template <int BN, int MINB>
+static int launch_grouped(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, const GroupArgs& grp,
+                          int max_ctas, cudaStream_t stream) {
+  int smem = 0;
+  args.stages = ring_stages<BN, MINB, false, true>(args, smem);
+  if (args.stages < 2) return -3;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_grouped_kernel<BN, MINB>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, MINB == 2 ? 113 * 1024 : 232448);
+    if (e != cudaSuccess) return int(e);
+    attr_set = true;
+  }
+  const int total = grp.num_groups * args.num_row_tiles * grp.max_col_tiles;
+  const int grid = total < max_ctas ? total : max_ctas;
+  return launch_pdl(gemm_bf16_grouped_kernel<BN, MINB>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb,
+                    args, grp);
 }
 
 }  // namespace nkb
@@ -174,7 +199,7 @@ extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, 
                                      int num_groups, int features, int k, int total_rows, int max_rows_per_group,
                                      long long ldx, long long ldo, int gated, int gate_off, const void* bias,
                                      long long bias_group_stride, float act_limit, float act_alpha, int block_n,
-                                     void* stream) {
+                                     const int* tile_list, const int* tile_count, int max_tiles, void* stream) {
   if (!status_word() && nkb_init() != 0) return -1;
   if (num_groups <= 0 || features <= 0 || k <= 0 || total_rows <= 0) return 0;
   if ((k & 7) || (ldx & 7)) return -2;
@@ -195,15 +220,22 @@ extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, 
   args.ldo = ldo;
   args.out = out;
   args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  args.bias_group_stride = bias_group_stride;
+  GroupArgs grp{};
+  grp.bias_group_stride = bias_group_stride;
   args.status = status_word();
   args.weights_operand = -1;
-  args.num_groups = num_groups;
-  args.max_col_tiles = (max_rows_per_group + block_n - 1) / block_n;
-  if (args.max_col_tiles < 1) args.max_col_tiles = 1;
-  args.group_offsets = group_offsets;
-  args.act_limit = act_limit;
-  args.act_alpha = act_alpha;
+  grp.num_groups = num_groups;
+  grp.max_col_tiles = (max_rows_per_group + block_n - 1) / block_n;
+  if (grp.max_col_tiles < 1) grp.max_col_tiles = 1;
+  grp.group_offsets = group_offsets;
+  if (tile_list && tile_count && max_tiles > 0) {
+    grp.tile_list = tile_list;
+    grp.tile_count = tile_count;
+    // work items = tiles x row tiles; express the bound through max_col_tiles for the grid size
+    grp.max_col_tiles = (max_tiles + num_groups - 1) / num_groups;
+  }
+  grp.act_limit = act_limit;
+  grp.act_alpha = act_alpha;
   const long long rows_per_group = gated ? (long long)gate_off + features : features;
   CUtensorMap ta, tb;
   {
@@ -217,9 +249,11 @@ extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, 
   const int max_ctas = 2 * num_sms();
   const bool two = !gated || block_n <= 32;
   switch (block_n) {
-    case 32: return two ? launch_gemm<32, 2>(ta, tb, args, max_ctas, s) : launch_gemm<32, 1>(ta, tb, args, num_sms(), s);
-    case 64: return two ? launch_gemm<64, 2>(ta, tb, args, max_ctas, s) : launch_gemm<64, 1>(ta, tb, args, num_sms(), s);
-    case 128: return launch_gemm<128, 1>(ta, tb, args, num_sms(), s);
+    case 32:
+      return two ? launch_grouped<32, 2>(ta, tb, args, grp, max_ctas, s) : launch_grouped<32, 1>(ta, tb, args, grp, num_sms(), s);
+    case 64:
+      return two ? launch_grouped<64, 2>(ta, tb, args, grp, max_ctas, s) : launch_grouped<64, 1>(ta, tb, args, grp, num_sms(), s);
+    case 128: return launch_grouped<128, 1>(ta, tb, args, grp, num_sms(), s);
     default: return -2;
   }
 }

@@ -57,35 +57,56 @@ struct WorkItem {
   bool valid;
 };
 
-template <int BN>
-__device__ __forceinline__ WorkItem decode_work(const GemmArgs& a, int w) {
+template <int BN, bool GROUPED>
+__device__ __forceinline__ WorkItem decode_work(const GemmArgs& a, const GroupArgs& g, int w) {
   WorkItem wi;
-  if (a.num_groups > 0) {
-    const int per_group = a.num_row_tiles * a.max_col_tiles;
-    wi.group = w / per_group;
-    const int rem = w - wi.group * per_group;
-    wi.rt = rem % a.num_row_tiles;
-    wi.ct = rem / a.num_row_tiles;
-    wi.sp = 0;
-    const int off = a.group_offsets[wi.group], end = a.group_offsets[wi.group + 1];
-    wi.col0 = off + wi.ct * BN;
-    wi.cols_end = end;
-    wi.valid = wi.col0 < end;
-  } else {
+  if constexpr (!GROUPED) {
     decode_tile(a, w, wi.rt, wi.ct, wi.sp);
     wi.group = 0;
     wi.col0 = wi.ct * BN;
     wi.cols_end = a.cols;
     wi.valid = true;
+    return wi;
+  }
+  if (g.tile_list) {
+    const int t = w / a.num_row_tiles;
+    wi.rt = w - t * a.num_row_tiles;
+    wi.sp = 0;
+    if (t >= *g.tile_count) {
+      wi.valid = false;
+      wi.group = wi.ct = wi.col0 = wi.cols_end = 0;
+      return wi;
+    }
+    wi.group = g.tile_list[2 * t];
+    wi.ct = g.tile_list[2 * t + 1];
+    wi.col0 = g.group_offsets[wi.group] + wi.ct * BN;
+    wi.cols_end = g.group_offsets[wi.group + 1];
+    wi.valid = true;
+  } else if (g.num_groups > 0) {
+    const int per_group = a.num_row_tiles * g.max_col_tiles;
+    wi.group = w / per_group;
+    const int rem = w - wi.group * per_group;
+    wi.rt = rem % a.num_row_tiles;
+    wi.ct = rem / a.num_row_tiles;
+    wi.sp = 0;
+    const int off = g.group_offsets[wi.group], end = g.group_offsets[wi.group + 1];
+    wi.col0 = off + wi.ct * BN;
+    wi.cols_end = end;
+    wi.valid = wi.col0 < end;
+  } else {
+    wi.valid = false;
+    wi.rt = wi.ct = wi.sp = wi.group = wi.col0 = wi.cols_end = 0;
   }
   return wi;
 }
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
-template <int BN, bool PUSH>
+// GROUPED selects the per-expert variant (3-D weight map, group offsets / tile list, expert
+// biases and the clamped activation); the plain variant compiles none of that.
+template <int BN, bool PUSH, bool GROUPED>
 __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
-                                               const PushArgs& push) {
+                                               const PushArgs& push, const GroupArgs& grp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -129,8 +150,8 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
   const uint32_t tmem_base = ctrl->tmem_base;
   volatile int* abort_flag = &ctrl->abort;
 
-  const int total_work = args.num_groups > 0 ? args.num_groups * args.num_row_tiles * args.max_col_tiles
-                                             : args.num_row_tiles * args.num_col_tiles * args.splits;
+  const int total_work = GROUPED ? grp.num_groups * args.num_row_tiles * grp.max_col_tiles
+                                 : args.num_row_tiles * args.num_col_tiles * args.splits;
 
   griddep_launch();
 
@@ -141,7 +162,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
       uint8_t* b_ptr = a_ptr + a_tiles * kATileBytes;
       if (expect) mbar_expect_tx(&ctrl->full[stage], stage_bytes);
       if (do_a) {
-        if (args.num_groups > 0) {
+        if constexpr (GROUPED) {
           tma_load_3d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, row0, group);
           if (args.gated == 1)
             tma_load_3d(a_ptr + kATileBytes, &tmA, &ctrl->full[stage], kb * kBlockK, args.gate_off + row0, group);
@@ -161,7 +182,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     // before waiting for it, so the HBM stream starts during the predecessor's tail.
     int pre = 0;
     const bool w_is_a = args.weights_operand == 0;
-    if (args.weights_operand >= 0 && args.num_groups == 0 && int(blockIdx.x) < total_work) {
+    if (!GROUPED && args.weights_operand >= 0 && int(blockIdx.x) < total_work) {
       int rt, ct, sp;
       decode_tile(args, blockIdx.x, rt, ct, sp);
       const int kb0 = sp * args.kb_per_split;
@@ -176,7 +197,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     uint32_t phase = 0;
     bool alive = true;
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
-      const WorkItem wi = decode_work<BN>(args, w);
+      const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
       if (!wi.valid) continue;
       const int sp = wi.sp;
       const int row0 = wi.rt * kTileRows, col0 = wi.col0;
@@ -203,7 +224,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     uint32_t acc_phase = 0;
     bool alive = true;
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
-      const WorkItem wi = decode_work<BN>(args, w);
+      const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
       if (!wi.valid) continue;
       const int sp = wi.sp;
       const int kb0 = sp * args.kb_per_split;
@@ -249,7 +270,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const WorkItem wi = decode_work<BN>(args, w);
+      const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
       if (!wi.valid) continue;
       const int rt = wi.rt, sp = wi.sp;
       const int cols_end = wi.cols_end;
@@ -262,9 +283,12 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
       const bool row_ok = row < args.rows;
       float* out_f = reinterpret_cast<float*>(args.out) + (args.out_fp32 ? sp * args.split_stride : 0);
       __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(args.out);
-      float bias_r = 0.f;
-      if (args.bias && args.bias_on_rows && row_ok && sp == 0)
-        bias_r = __bfloat162float(args.bias[wi.group * args.bias_group_stride + row]);
+      float bias_r = 0.f, bias_u = 0.f;
+      if (args.bias && args.bias_on_rows && row_ok && sp == 0) {
+        const __nv_bfloat16* bp = args.bias + (GROUPED ? wi.group * grp.bias_group_stride : 0) + row;
+        bias_r = __bfloat162float(bp[0]);
+        if (GROUPED && args.gated) bias_u = __bfloat162float(bp[args.gate_off]);   // up-projection bias
+      }
 
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -274,21 +298,23 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           uint32_t u[32];
           tmem_ld_32x32(t0 + BN + c, u);
           tmem_ld_wait();
+          if (GROUPED && grp.act_limit > 0.f) {
+            // clamped variant: (up + 1) * gate * sigmoid(alpha * gate), biases before the activation
+            const float lim = grp.act_limit, alpha = grp.act_alpha;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-          {
-            float gg = __uint_as_float(v[j]), uu = __uint_as_float(u[j]);
-            if (args.bias && args.bias_on_rows && row_ok) {   // gate / up biases before the activation
-              gg += bias_r;
-              uu += __bfloat162float(args.bias[wi.group * args.bias_group_stride + args.gate_off + row]);
+            for (int j = 0; j < 32; ++j) {
+              const float gg = fminf(__uint_as_float(v[j]) + bias_r, lim);
+              const float uu = fminf(fmaxf(__uint_as_float(u[j]) + bias_u, -lim), lim);
+              v[j] = __float_as_uint((uu + 1.f) * gg / (1.f + __expf(-alpha * gg)));
             }
-            if (args.act_limit > 0.f) {
-              gg = fminf(gg, args.act_limit);
-              uu = fminf(fmaxf(uu, -args.act_limit), args.act_limit);
-              v[j] = __float_as_uint((uu + 1.f) * gg / (1.f + __expf(-args.act_alpha * gg)));
-            } else {
-              v[j] = __float_as_uint(silu_f(gg) * uu);
-            }
+          } else if (GROUPED) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __float_as_uint(silu_f(__uint_as_float(v[j]) + bias_r) * (__uint_as_float(u[j]) + bias_u));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __float_as_uint(silu_f(__uint_as_float(v[j])) * __uint_as_float(u[j]));
           }
         } else {
           tmem_ld_wait();
@@ -439,7 +465,14 @@ template <int BN, int MINB, bool PUSH>
 __global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs args, const PushArgs push) {
-  gemm_bf16_body<BN, PUSH>(tmA, tmB, args, push);
+  gemm_bf16_body<BN, PUSH, false>(tmA, tmB, args, push, GroupArgs{});
+}
+
+template <int BN, int MINB>
+__global__ void __launch_bounds__(kGemmThreads, MINB)
+gemm_bf16_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmArgs args, const GroupArgs grp) {
+  gemm_bf16_body<BN, false, true>(tmA, tmB, args, PushArgs{}, grp);
 }
 
 }  // namespace nkb

@@ -46,6 +46,99 @@ __global__ void moe_scan_kernel(const int* __restrict__ counts, int num_local, i
   if (t == 0) offsets[0] = 0;
 }
 
+// compact tile schedules for the grouped GEMMs: for tile width bn, group g contributes
+// ceil(count_g / bn) tiles (one block; runs after the scan)
+__global__ void moe_tiles_kernel(const int* __restrict__ offsets, int num_local, int bn_a, int* __restrict__ tiles_a,
+                                 int* __restrict__ ntiles_a, int bn_b, int* __restrict__ tiles_b,
+                                 int* __restrict__ ntiles_b) {
+  griddep_wait();
+  griddep_launch();
+  __shared__ int sa[1024], sb[1024];
+  const int t = threadIdx.x;
+  const int n = t < num_local ? offsets[t + 1] - offsets[t] : 0;
+  const int ca = (n + bn_a - 1) / bn_a, cb = (n + bn_b - 1) / bn_b;
+  sa[t] = ca;
+  sb[t] = cb;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int va = t >= o ? sa[t - o] : 0, vb = t >= o ? sb[t - o] : 0;
+    __syncthreads();
+    sa[t] += va;
+    sb[t] += vb;
+    __syncthreads();
+  }
+  if (t < num_local) {
+    int base = sa[t] - ca;
+    for (int i = 0; i < ca; ++i) { tiles_a[2 * (base + i)] = t; tiles_a[2 * (base + i) + 1] = i; }
+    base = sb[t] - cb;
+    for (int i = 0; i < cb; ++i) { tiles_b[2 * (base + i)] = t; tiles_b[2 * (base + i) + 1] = i; }
+  }
+  if (t == 1023) { *ntiles_a = sa[1023]; *ntiles_b = sb[1023]; }
+}
+
+// Small batches (decode): one block counts, scans, assigns every pair its sorted position and
+// builds both tile schedules, replacing the count / scan / tile kernels and the memset.
+__global__ void moe_plan_small_kernel(const int* __restrict__ experts, int pairs, int expert_lo, int num_local,
+                                      int* __restrict__ offsets, int* __restrict__ pair_pos, int bn_a,
+                                      int* __restrict__ tiles_a, int* __restrict__ ntiles_a, int bn_b,
+                                      int* __restrict__ tiles_b, int* __restrict__ ntiles_b) {
+  griddep_wait();
+  griddep_launch();
+  __shared__ int cnt[1024], off[1025], sa[1024], sb[1024];
+  const int t = threadIdx.x;
+  cnt[t] = 0;
+  __syncthreads();
+  for (int i = t; i < pairs; i += 1024) {
+    const int e = experts[i] - expert_lo;
+    if (e >= 0 && e < num_local) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  const int n = t < num_local ? cnt[t] : 0;
+  const int ca = (n + bn_a - 1) / bn_a, cb = (n + bn_b - 1) / bn_b;
+  off[t + 1] = n;
+  sa[t] = ca;
+  sb[t] = cb;
+  if (t == 0) off[0] = 0;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int v = t >= o ? off[t + 1 - o] : 0, va = t >= o ? sa[t - o] : 0, vb = t >= o ? sb[t - o] : 0;
+    __syncthreads();
+    off[t + 1] += v;
+    sa[t] += va;
+    sb[t] += vb;
+    __syncthreads();
+  }
+  if (t <= num_local) offsets[t] = off[t];
+  if (t < num_local) {
+    int base = sa[t] - ca;
+    for (int i = 0; i < ca; ++i) { tiles_a[2 * (base + i)] = t; tiles_a[2 * (base + i) + 1] = i; }
+    base = sb[t] - cb;
+    for (int i = 0; i < cb; ++i) { tiles_b[2 * (base + i)] = t; tiles_b[2 * (base + i) + 1] = i; }
+  }
+  if (t == 1023) { *ntiles_a = sa[1023]; *ntiles_b = sb[1023]; }
+  cnt[t] = 0;      // reused as per-expert cursors
+  __syncthreads();
+  // deterministic order inside an expert is not needed: every pair's output row is independent
+  for (int i = t; i < pairs; i += 1024) {
+    const int e = experts[i] - expert_lo;
+    pair_pos[i] = (e >= 0 && e < num_local) ? off[e] + atomicAdd(&cnt[e], 1) : -1;
+  }
+}
+
+// one block per pair: copy the token row to its sorted position
+__global__ void moe_gather_kernel(const int* __restrict__ pair_pos, int top_k, const __nv_bfloat16* __restrict__ x,
+                                  int hidden, __nv_bfloat16* __restrict__ x_sorted) {
+  griddep_wait();
+  griddep_launch();
+  const int pair = blockIdx.x;
+  const int pos = pair_pos[pair];
+  if (pos < 0) return;
+  const int token = pair / top_k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)token * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(x_sorted + (long long)pos * hidden);
+  for (int v = threadIdx.x; v < (hidden >> 3); v += blockDim.x) dst[v] = src[v];
+}
+
 // one block per pair: claim a slot in its expert's segment and copy the token row there
 __global__ void moe_scatter_kernel(const int* __restrict__ experts, int pairs, int top_k, int expert_lo,
                                    int num_local, const int* __restrict__ offsets, int* __restrict__ cursors,
@@ -109,17 +202,28 @@ using namespace nkb;
 // tokens * top_k rows.  After the call offsets / pair_pos / x_sorted are valid on the stream.
 extern "C" int nkb_moe_dispatch(const int* experts, int tokens, int top_k, int expert_lo, int num_local, const void* x,
                                 int hidden, void* x_sorted, int* counts, int* offsets, int* cursors, int* pair_pos,
+                                int bn_a, int* tiles_a, int* ntiles_a, int bn_b, int* tiles_b, int* ntiles_b,
                                 void* stream) {
   if (tokens <= 0) return 0;
-  if (num_local > 1024 || (hidden & 7)) return -2;
+  if (num_local > 1024 || (hidden & 7) || bn_a <= 0 || bn_b <= 0) return -2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int pairs = tokens * top_k;
+  if (pairs <= 8192) {
+    int rc = launch_pdl(moe_plan_small_kernel, dim3(1), dim3(1024), 0, s, experts, pairs, expert_lo, num_local, offsets,
+                        pair_pos, bn_a, tiles_a, ntiles_a, bn_b, tiles_b, ntiles_b);
+    if (rc) return rc;
+    return launch_pdl(moe_gather_kernel, dim3(pairs), dim3(128), 0, s, (const int*)pair_pos, top_k,
+                      (const __nv_bfloat16*)x, hidden, (__nv_bfloat16*)x_sorted);
+  }
   cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * num_local, s);
   if (e != cudaSuccess) return int(e);
   int rc = launch_pdl(moe_count_kernel, dim3((pairs + 255) / 256), dim3(256), 0, s, experts, pairs, expert_lo,
                       num_local, counts);
   if (rc) return rc;
   rc = launch_pdl(moe_scan_kernel, dim3(1), dim3(1024), 0, s, (const int*)counts, num_local, offsets, cursors);
+  if (rc) return rc;
+  rc = launch_pdl(moe_tiles_kernel, dim3(1), dim3(1024), 0, s, (const int*)offsets, num_local, bn_a, tiles_a, ntiles_a,
+                  bn_b, tiles_b, ntiles_b);
   if (rc) return rc;
   return launch_pdl(moe_scatter_kernel, dim3(pairs), dim3(128), 0, s, experts, pairs, top_k, expert_lo, num_local,
                     (const int*)offsets, cursors, (const __nv_bfloat16*)x, hidden, (__nv_bfloat16*)x_sorted, pair_pos);

@@ -225,7 +225,9 @@ __global__ void __launch_bounds__(1024) sample_kernel(const void* __restrict__ l
 //   mode 0: softmax over all experts -> top-k -> divide by the selected sum
 //   mode 1: top-k on raw logits -> softmax over the selected
 // ---------------------------------------------------------------------------
-__global__ void router_topk_kernel(const void* __restrict__ logits, int is_fp32, float* __restrict__ weights,
+// logits may be bf16 / fp32 [tokens, E] or fp32 split-K partials [splits, tokens, E] (summed here, plus bias)
+__global__ void router_topk_kernel(const void* __restrict__ logits, int is_fp32, int splits, long long split_stride,
+                                   const __nv_bfloat16* __restrict__ bias, float* __restrict__ weights,
                                    int* __restrict__ experts, int tokens, int num_experts, int top_k, int mode) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -239,7 +241,15 @@ __global__ void router_topk_kernel(const void* __restrict__ logits, int is_fp32,
 #pragma unroll
   for (int j = 0; j < kPer; ++j) {
     const int e = j * 32 + lane;
-    v[j] = (j < per && e < num_experts) ? load_logit(logits, is_fp32, (long long)warp * num_experts + e) : -FLT_MAX;
+    if (j < per && e < num_experts) {
+      float a = load_logit(logits, is_fp32, (long long)warp * num_experts + e);
+      for (int s = 1; s < splits; ++s)
+        a += reinterpret_cast<const float*>(logits)[s * split_stride + (long long)warp * num_experts + e];
+      if (bias) a += __bfloat162float(bias[e]);
+      v[j] = a;
+    } else {
+      v[j] = -FLT_MAX;
+    }
     mx = fmaxf(mx, v[j]);
   }
   mx = warp_max(mx);
@@ -301,12 +311,16 @@ extern "C" int nkb_sample(const void* logits, int is_fp32, int* out_ids, int row
                     out_ids, vocab, ld, temperature, top_k, top_p, seed, step);
 }
 
-extern "C" int nkb_router_topk(const void* logits, int is_fp32, float* weights, int* experts, int tokens,
-                               int num_experts, int top_k, int mode, void* stream) {
+extern "C" int nkb_router_topk(const void* logits, int is_fp32, int splits, long long split_stride, const void* bias,
+                               float* weights, int* experts, int tokens, int num_experts, int top_k, int mode,
+                               void* stream) {
   if (tokens <= 0) return 0;
   if (num_experts > 1024 || top_k > 32 || top_k > num_experts) return -2;
   const int threads = 128;
   const int blocks = (tokens * 32 + threads - 1) / threads;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && !is_fp32) return -2;
   return launch_pdl(router_topk_kernel, dim3(blocks), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), logits,
-                    is_fp32, weights, experts, tokens, num_experts, top_k, mode);
+                    is_fp32, splits, split_stride, (const __nv_bfloat16*)bias, weights, experts, tokens, num_experts,
+                    top_k, mode);
 }

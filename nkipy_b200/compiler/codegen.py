@@ -655,7 +655,7 @@ class Generator:
         bn_tile = 256 if N >= 256 else (128 if N > 64 else 64 if N > 32 else 32)
         self.kernels.append(f"""extern "C" __global__ void __launch_bounds__(nkb::kGemmThreads, 1)
 {name}(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const nkb::GemmArgs args) {{
-  nkb::gemm_bf16_body<{bn_tile}, false>(tmA, tmB, args, nkb::PushArgs{{}});
+  nkb::gemm_bf16_body<{bn_tile}, false, false>(tmA, tmB, args, nkb::PushArgs{{}}, nkb::GroupArgs{{}});
 }}
 """)
         stage_bytes = 128 * 64 * 2 + bn_tile * 64 * 2

@@ -30,18 +30,21 @@ class MoEBlock:
         self.expert_lo = tp.rank * self.num_local if moe_parallel == "ep" else 0
 
     def route(self, lw, x: torch.Tensor):
-        logits = ops.linear(x, lw.router, bias=lw.router_bias)
-        return ops.router_topk(logits, self.cfg.top_k, self.cfg.router_mode)
+        # one 128-row weight tile: split the contraction so several SMs share the work
+        logits = ops.linear(x, lw.router, splits=max(2, min(16, x.shape[1] // 256)))
+        return ops.router_topk(logits, self.cfg.top_k, self.cfg.router_mode, bias=lw.router_bias)
 
     def forward(self, lw, x: torch.Tensor) -> torch.Tensor:
         """x [T, H] (normed hidden states, replicated over ranks) -> MoE output [T, H], summed over ranks."""
         cfg = self.cfg
         T = x.shape[0]
         weights, experts = self.route(lw, x)
-        x_sorted, offsets, pair_pos = ops.moe_dispatch(x, experts, self.expert_lo, self.num_local)
-        h = ops.grouped_linear(x_sorted, lw.gate_up, offsets, max_rows_per_group=T, gated=True,
-                               bias=lw.gate_up_bias, act_limit=cfg.swiglu_limit, act_alpha=cfg.swiglu_alpha)
-        y_sorted = ops.grouped_linear(h, lw.down, offsets, max_rows_per_group=T, bias=lw.down_bias)
-        y = ops.moe_combine(y_sorted, pair_pos, weights, T)
+        plan = ops.moe_dispatch(x, experts, self.expert_lo, self.num_local)
+        h = ops.grouped_linear(plan.x_sorted, lw.gate_up, plan.offsets, max_rows_per_group=T, gated=True,
+                               bias=lw.gate_up_bias, act_limit=cfg.swiglu_limit, act_alpha=cfg.swiglu_alpha,
+                               tiles=plan.tiles)
+        y_sorted = ops.grouped_linear(h, lw.down, plan.offsets, max_rows_per_group=T, bias=lw.down_bias,
+                                      tiles=plan.tiles)
+        y = ops.moe_combine(y_sorted, plan.pair_pos, weights, T)
         self.tp.all_reduce(y)
         return y

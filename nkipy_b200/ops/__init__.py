@@ -505,13 +505,18 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p
     return out_ids
 
 
-def router_topk(logits: torch.Tensor, top_k: int, mode: str = "softmax_topk") -> Tuple[torch.Tensor, torch.Tensor]:
+def router_topk(logits: torch.Tensor, top_k: int, mode: str = "softmax_topk",
+                bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """MoE routing.  mode "softmax_topk": softmax over all experts, top-k, renormalise
-    (Qwen3); "topk_softmax": top-k raw logits, softmax over them (gpt-oss).
+    (Qwen3); "topk_softmax": top-k raw logits, softmax over them (gpt-oss).  logits are bf16 /
+    fp32 ``[T, E]`` or fp32 split-K partials ``[S, T, E]`` (summed here); bias [E] is added first.
     Returns (weights fp32 [T, k], experts int32 [T, k])."""
-    T, E = logits.shape
+    partial = logits.dim() == 3
+    T, E = logits.shape[-2], logits.shape[-1]
     if not _native(logits):
-        lf = logits.float()
+        lf = logits.float().sum(0) if partial else logits.float()
+        if bias is not None:
+            lf = lf + bias.float()
         if mode == "softmax_topk":
             p = torch.softmax(lf, dim=-1)
             w, e = p.topk(top_k, dim=-1)
@@ -526,8 +531,10 @@ def router_topk(logits: torch.Tensor, top_k: int, mode: str = "softmax_topk") ->
     is_fp32 = 1 if logits.dtype == torch.float32 else 0
     if not logits.is_contiguous():
         logits = logits.contiguous()
-    rc = _lib.lib().nkb_router_topk(logits.data_ptr(), is_fp32, w.data_ptr(), e.data_ptr(), T, E, top_k,
-                                    0 if mode == "softmax_topk" else 1, _stream())
+    splits = logits.shape[0] if partial else 1
+    rc = _lib.lib().nkb_router_topk(logits.data_ptr(), is_fp32, splits, logits.stride(0) if partial else 0, _ptr(bias),
+                                    w.data_ptr(), e.data_ptr(), T, E, top_k, 0 if mode == "softmax_topk" else 1,
+                                    _stream())
     _lib.check(rc, "nkb_router_topk")
     _launches += 1
     return w, e
@@ -680,11 +687,30 @@ def flash_attn_prefill(
 
 
 # --------------------------------------------------------------------------- mixture of experts
-def moe_dispatch(x: torch.Tensor, experts: torch.Tensor, expert_lo: int, num_local: int):
+class MoEPlan:
+    """Result of `moe_dispatch`: expert-sorted rows plus the device-side schedules of the grouped GEMMs."""
+    __slots__ = ("x_sorted", "offsets", "pair_pos", "tiles", "max_rows")
+
+    def __init__(self, x_sorted, offsets, pair_pos, tiles, max_rows):
+        self.x_sorted, self.offsets, self.pair_pos, self.tiles, self.max_rows = x_sorted, offsets, pair_pos, tiles, max_rows
+
+    def __iter__(self):          # (x_sorted, offsets, pair_pos) unpacking
+        return iter((self.x_sorted, self.offsets, self.pair_pos))
+
+
+def moe_tile_widths(tokens: int):
+    """(gated GEMM tile width, down GEMM tile width) in tokens for a batch of `tokens`."""
+    if tokens <= 512:
+        return 32, 32
+    return 64, 128
+
+
+def moe_dispatch(x: torch.Tensor, experts: torch.Tensor, expert_lo: int, num_local: int) -> MoEPlan:
     """Sort the (token, expert) pairs routed to local experts [expert_lo, expert_lo + num_local) by
     expert and gather their token rows.  x [T, H] bf16, experts [T, k] int32 (global ids).
-    Returns (x_sorted [T * k, H], offsets int32 [num_local + 1], pair_pos int32 [T * k]); rows past
-    offsets[-1] of x_sorted are unspecified, pair_pos is -1 for pairs of other ranks' experts."""
+    Returns a `MoEPlan` (unpacks to x_sorted [T * k, H], offsets int32 [num_local + 1], pair_pos int32
+    [T * k]); rows past offsets[-1] of x_sorted are unspecified, pair_pos is -1 for pairs of other
+    ranks' experts."""
     T, H = x.shape
     k = experts.shape[1]
     pairs = T * k
@@ -701,25 +727,36 @@ def moe_dispatch(x: torch.Tensor, experts: torch.Tensor, expert_lo: int, num_loc
         offsets[1:] = counts.cumsum(0).to(torch.int32)
         x_sorted = torch.zeros((pairs, H), dtype=x.dtype)
         x_sorted[:n_local] = x[(order[:n_local] // k)]
-        return x_sorted, offsets, pair_pos
+        return MoEPlan(x_sorted, offsets, pair_pos, None, T)
     global _launches
+    bn_a, bn_b = moe_tile_widths(T)
+    cap_a, cap_b = num_local + pairs // bn_a + 1, num_local + pairs // bn_b + 1
     x_sorted = torch.empty((pairs, H), dtype=x.dtype, device=dev)
-    work = torch.empty((3 * num_local + 1 + pairs,), dtype=torch.int32, device=dev)
-    counts, offsets = work[:num_local], work[num_local:2 * num_local + 1]
-    cursors, pair_pos = work[2 * num_local + 1:3 * num_local + 1], work[3 * num_local + 1:]
+    work = torch.empty((3 * num_local + 1 + pairs + 2 * cap_a + 2 * cap_b + 2,), dtype=torch.int32, device=dev)
+    o = 0
+    counts = work[o:o + num_local]; o += num_local
+    offsets = work[o:o + num_local + 1]; o += num_local + 1
+    cursors = work[o:o + num_local]; o += num_local
+    pair_pos = work[o:o + pairs]; o += pairs
+    tiles_a = work[o:o + 2 * cap_a]; o += 2 * cap_a
+    tiles_b = work[o:o + 2 * cap_b]; o += 2 * cap_b
+    ntiles = work[o:o + 2]
     if experts.dtype != torch.int32:
         experts = experts.to(torch.int32)
     rc = _lib.lib().nkb_moe_dispatch(experts.data_ptr(), T, k, int(expert_lo), int(num_local), x.data_ptr(), H,
                                      x_sorted.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursors.data_ptr(),
-                                     pair_pos.data_ptr(), _stream())
+                                     pair_pos.data_ptr(), bn_a, tiles_a.data_ptr(), ntiles.data_ptr(), bn_b,
+                                     tiles_b.data_ptr(), ntiles.data_ptr() + 4, _stream())
     _lib.check(rc, "nkb_moe_dispatch")
-    _launches += 3
-    return x_sorted, offsets, pair_pos
+    _launches += 2 if pairs <= 8192 else 5
+    tiles = {bn_a: (tiles_a, ntiles[0:1], cap_a)}
+    tiles.setdefault(bn_b, (tiles_b, ntiles[1:2], cap_b))
+    return MoEPlan(x_sorted, offsets, pair_pos, tiles, T)
 
 
 def grouped_linear(x_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, max_rows_per_group: int,
                    gated: bool = False, bias: Optional[torch.Tensor] = None, act_limit: float = 0.0,
-                   act_alpha: float = 1.702) -> torch.Tensor:
+                   act_alpha: float = 1.702, tiles=None) -> torch.Tensor:
     """Per-group ``y[r] = x_sorted[r] @ w[g(r)].T`` for rows sorted by group (group g owns rows
     offsets[g] .. offsets[g + 1]).  w [G, N, K] bf16 (gated: [G, 2 * I, K], gate rows then up
     rows, output ``act(gate) * up`` of width I).  bias [G, N] is added before the activation."""
@@ -749,13 +786,22 @@ def grouped_linear(x_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tenso
     global _launches
     _check_bf16(x_sorted, w, bias)
     out = torch.empty((R, N), dtype=torch.bfloat16, device=x_sorted.device)
-    block_n = 32 if max_rows_per_group <= 32 else 64
-    if not gated and max_rows_per_group > 64:
-        block_n = 128
+    tl = tc = None
+    max_tiles = 0
+    if tiles is not None:
+        bn_a, bn_b = moe_tile_widths(max_rows_per_group)
+        block_n = bn_a if gated else bn_b
+        tl_t, tc_t, max_tiles = tiles[block_n]
+        tl, tc = tl_t.data_ptr(), tc_t.data_ptr()
+    else:
+        block_n = 32 if max_rows_per_group <= 32 else 64
+        if not gated and max_rows_per_group > 64:
+            block_n = 128
     rc = _lib.lib().nkb_gemm_bf16_grouped(
         w.data_ptr(), x_sorted.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, N, K, R, int(max_rows_per_group),
         x_sorted.stride(0), N, 1 if gated else 0, N if gated else 0, _ptr(bias),
-        bias.stride(0) if bias is not None else 0, float(act_limit), float(act_alpha), block_n, _stream())
+        bias.stride(0) if bias is not None else 0, float(act_limit), float(act_alpha), block_n, tl, tc,
+        int(max_tiles), _stream())
     _lib.check(rc, "nkb_gemm_bf16_grouped")
     _launches += 1
     return out

@@ -31,9 +31,10 @@ _SIGNATURES = {
     "nkb_gemm_bf16_grouped": (
         c_int,
         [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, _P, c_longlong,
-         c_float, c_float, c_int, _P],
+         c_float, c_float, c_int, _P, _P, c_int, _P],
     ),
-    "nkb_moe_dispatch": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P]),
+    "nkb_moe_dispatch": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
+                                 _P, _P, _P]),
     "nkb_moe_combine": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P, _P]),
     "nkb_gemm_effective_splits": (c_int, [c_int, c_int]),
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
@@ -50,7 +51,7 @@ _SIGNATURES = {
     "nkb_argmax": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_longlong, _P]),
     "nkb_sample": (c_int, [_P, c_int, _P, c_int, c_int, c_longlong, c_float, c_int, c_float, c_ulonglong,
                            c_ulonglong, _P]),
-    "nkb_router_topk": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "nkb_router_topk": (c_int, [_P, c_int, c_int, c_longlong, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "nkb_paged_attn_decode": (
         c_int,
         [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P,

@@ -103,6 +103,12 @@ def test_router_topk_both_orders():
     w2, e2 = ops.router_topk(logits.to(torch.bfloat16), 4, "topk_softmax")
     v, re2 = logits.to(torch.bfloat16).float().topk(4, -1)
     assert torch.allclose(w2, torch.softmax(v, -1), atol=1e-5)
+    parts = torch.randn(3, 50, 128, device=DEV)
+    bias = randn(128)
+    w3, e3 = ops.router_topk(parts, 8, "softmax_topk", bias=bias)
+    p3 = torch.softmax(parts.sum(0) + bias.float(), -1)
+    rw3, re3 = p3.topk(8, -1)
+    assert torch.equal(e3.long(), re3) and torch.allclose(w3, rw3 / rw3.sum(-1, keepdim=True), atol=1e-5)
 
 
 def test_sampling_respects_top_k():
@@ -293,8 +299,13 @@ def test_moe_dispatch_grouped_gemm_combine(T, E, k, H, I, lo, nl):
     w_gu = randn(nl, 2 * I, H, scale=0.05)
     w_dn = randn(nl, H, I, scale=0.05)
     b_gu, b_dn = randn(nl, 2 * I, scale=0.1), randn(nl, H, scale=0.1)
-    h = ops.grouped_linear(xs, w_gu, off, max_rows_per_group=T, gated=True, bias=b_gu)
-    y = ops.grouped_linear(h, w_dn, off, max_rows_per_group=T, bias=b_dn)
+    plan = ops.moe_dispatch(x, experts, lo, nl)
+    h = ops.grouped_linear(plan.x_sorted, w_gu, plan.offsets, max_rows_per_group=T, gated=True, bias=b_gu,
+                           tiles=plan.tiles)
+    y = ops.grouped_linear(h, w_dn, plan.offsets, max_rows_per_group=T, bias=b_dn, tiles=plan.tiles)
+    pos, off = plan.pair_pos, plan.offsets
+    h2 = ops.grouped_linear(plan.x_sorted, w_gu, off, max_rows_per_group=T, gated=True, bias=b_gu)   # enumerated schedule
+    assert rel_err(h2[:n_local], h[:n_local]) < 1e-3
     out = ops.moe_combine(y, pos, wts, T)
     # fp32 reference straight from the definition
     ref = torch.zeros(T, H, device=DEV)
