@@ -1,0 +1,216 @@
+"""Single-kernel micro-benchmarks of the sm_100a kernel library.
+
+    python -m nkipy_b200.ops.microbench <case> [--iters N] [--sets S]
+
+Each case launches one kernel of the library at a serving shape, rotating over several
+operand sets so that every launch reads data that is not in L2 (the sets together exceed
+the 126 MB cache), times the launches with CUDA events after warm-up and prints one JSON
+line: microseconds per launch, algorithmic bytes and FLOPs, achieved TB/s and TFLOP/s and
+their fraction of the measured peaks (``MEASURED_PEAKS.json`` beside the package when it
+exists, otherwise 6.65 TB/s and 1590 TFLOP/s).  The same command line is what the profiler
+is pointed at (``--iters 1 --warmup 1`` keeps a capture short).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from . import (add_rmsnorm, flash_attn_prefill, grouped_linear, linear, moe_combine, moe_dispatch, paged_attn_decode,
+               router_topk)
+
+_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return dict(_FALLBACK, source="fallback")
+
+
+def _bf16(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _time(fns, iters, warmup, graph=True):
+    """fns: list of callables (one per operand set); returns us per launch.  With graph=True one
+    pass over all sets is captured into a CUDA graph and replayed, so that host launch cost does
+    not hide the device time of kernels that run for a few microseconds."""
+    n = len(fns)
+    for i in range(max(warmup, 1)):
+        fns[i % n]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for f in fns:
+                f()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        reps = max(1, iters // n)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * n)
+    e0.record()
+    for i in range(iters):
+        fns[i % n]()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def _sets_for(bytes_per_set, want):
+    # enough sets that a rotation touches > 2x L2 between two uses of the same set
+    need = int(2 * 126e6 / max(bytes_per_set, 1)) + 1
+    return max(2, min(max(need, 2), want))
+
+
+# --------------------------------------------------------------------------- cases
+def case_gemm_decode(name, features, k, tokens, splits, gated, args):
+    wrows = features * (2 if gated else 1)
+    nbytes = wrows * k * 2
+    sets = _sets_for(nbytes, args.sets)
+    ws = [_bf16(wrows, k, scale=0.02) for _ in range(sets)]
+    x = _bf16(tokens, k)
+    fns = [lambda w=w: linear(x, w, splits=splits, gated=gated) for w in ws]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case=name, us=us, bytes=nbytes + tokens * k * 2 + tokens * features * (4 * splits if splits > 1 else 2),
+                flops=2.0 * tokens * wrows * k, shape=dict(features=features, k=k, tokens=tokens, splits=splits,
+                                                           gated=gated, sets=sets))
+
+
+def case_gemm_prefill(args):
+    M, K, N = 8192, 4096, 14336
+    x = _bf16(M, K)
+    ws = [_bf16(N, K, scale=0.02) for _ in range(2)]
+    fns = [lambda w=w: linear(x, w) for w in ws]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case="gemm-prefill", us=us, bytes=(M * K + N * K + M * N) * 2, flops=2.0 * M * N * K,
+                shape=dict(M=M, K=K, N=N))
+
+
+def case_attn_decode(args):
+    B, ctx, nkv, nq, D = 64, 1056, 8, 32, 128
+    pages = (ctx + 31) // 32
+    nb = B * pages
+    per_set = 2 * nb * nkv * 32 * D * 2
+    sets = _sets_for(per_set, args.sets)
+    caches = [(_bf16(nb, nkv, 32, D), _bf16(nb, nkv, 32, D)) for _ in range(sets)]
+    table = torch.arange(nb, device="cuda", dtype=torch.int32).reshape(B, pages)
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    q = _bf16(B, nq * D)
+    fns = [lambda kc=kc, vc=vc: paged_attn_decode(q, kc, vc, table, lens, D ** -0.5) for kc, vc in caches]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case="attn-decode", us=us, bytes=B * ctx * nkv * D * 2 * 2, flops=4.0 * B * nq * ctx * D,
+                shape=dict(batch=B, context=ctx, nq=nq, nkv=nkv, head_dim=D, sets=sets))
+
+
+def case_attn_prefill(args):
+    B, S, nq, nkv, D = 8, 2048, 32, 8, 128
+    pages = S // 32
+    nb = B * pages
+    kc, vc = _bf16(nb, nkv, 32, D), _bf16(nb, nkv, 32, D)
+    table = torch.arange(nb, device="cuda", dtype=torch.int32).reshape(B, pages)
+    q = _bf16(B * S, nq * D)
+    q_start = torch.arange(B, device="cuda", dtype=torch.int32) * S
+    q_lens = torch.full((B,), S, device="cuda", dtype=torch.int32)
+    fns = [lambda: flash_attn_prefill(q, kc, vc, table, q_start, q_lens, q_lens, D ** -0.5, max_q_len=S, causal=True)]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case="attn-prefill", us=us, bytes=(2 * q.numel() + kc.numel() + vc.numel()) * 2,
+                flops=4.0 * B * nq * S * S * D / 2, shape=dict(batch=B, seq=S, nq=nq, nkv=nkv, head_dim=D, causal=True))
+
+
+def case_moe(args):
+    """The grouped expert GEMMs of one Qwen3-30B-A3B decode layer (128 tokens, top-8 of 128 experts)."""
+    T, H, E, I, topk = 128, 2048, 128, 768, 8
+    sets = max(2, min(args.sets, 4))
+    w13 = [_bf16(E, 2 * I, H, scale=0.02) for _ in range(sets)]
+    w2 = [_bf16(E, H, I, scale=0.02) for _ in range(sets)]
+    x = _bf16(T, H)
+    logits = torch.randn(T, E, device="cuda")
+    wts, experts = router_topk(logits, topk)
+
+    def layer(a, b):
+        plan = moe_dispatch(x, experts, 0, E)
+        h = grouped_linear(plan.x_sorted, a, plan.offsets, max_rows_per_group=T, gated=True, tiles=plan.tiles)
+        y = grouped_linear(h, b, plan.offsets, max_rows_per_group=T, tiles=plan.tiles)
+        return moe_combine(y, plan.pair_pos, wts, T)
+
+    fns = [lambda a=a, b=b: layer(a, b) for a, b in zip(w13, w2)]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case="moe-decode-layer", us=us, bytes=E * 3 * I * H * 2, flops=2.0 * T * topk * 3 * I * H,
+                shape=dict(tokens=T, hidden=H, experts=E, inter=I, top_k=topk, sets=sets,
+                           note="dispatch + gated grouped GEMM + down grouped GEMM + combine; bytes = all expert weights"))
+
+
+def case_addnorm(args):
+    T, H, S = 64, 4096, 8
+    parts = [torch.randn(S, T, H, device="cuda") for _ in range(4)]
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    r = _bf16(T, H)
+    fns = [lambda p=p: add_rmsnorm(None, w, residual_in=r, partials=p, eps=1e-5) for p in parts]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case="add-rmsnorm", us=us, bytes=S * T * H * 4 + 3 * T * H * 2, flops=0.0,
+                shape=dict(tokens=T, hidden=H, splits=S))
+
+
+CASES = {
+    "gemm-decode-qkv": lambda a: case_gemm_decode("gemm-decode-qkv", 6144, 4096, 64, 6, False, a),
+    "gemm-decode-o": lambda a: case_gemm_decode("gemm-decode-o", 4096, 4096, 64, 8, False, a),
+    "gemm-decode-gate-up": lambda a: case_gemm_decode("gemm-decode-gate-up", 14336, 4096, 64, 1, True, a),
+    "gemm-decode-down": lambda a: case_gemm_decode("gemm-decode-down", 4096, 14336, 64, 8, False, a),
+    "gemm-decode-lmhead": lambda a: case_gemm_decode("gemm-decode-lmhead", 128256, 4096, 64, 1, False, a),
+    "gemm-prefill": case_gemm_prefill,
+    "attn-decode": case_attn_decode,
+    "attn-prefill": case_attn_prefill,
+    "moe-decode-layer": case_moe,
+    "add-rmsnorm": case_addnorm,
+}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("case", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--sets", type=int, default=8, help="upper bound of rotating operand sets")
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a GPU", file=sys.stderr)
+        return 2
+    pk = peaks()
+    names = sorted(CASES) if args.case == "all" else [args.case]
+    for nm in names:
+        torch.manual_seed(0)
+        r = CASES[nm](args)
+        tbs = r["bytes"] / r["us"] / 1e6
+        tfl = r["flops"] / r["us"] / 1e6
+        r.update(us=round(r["us"], 2), tb_per_s=round(tbs, 3), tflops=round(tfl, 1),
+                 frac_hbm=round(tbs * 1e3 / pk["hbm_gbs"], 3), frac_bf16=round(tfl / pk["bf16_tflops"], 3),
+                 peaks=pk["source"])
+        print(json.dumps(r), flush=True)
+        torch.cuda.empty_cache()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
