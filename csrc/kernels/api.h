@@ -77,6 +77,13 @@ int nkb_ipc_close(void* p);
 int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void* flags, int n_src, void* seen,
                           void* done_counter, const void* residual_in, const void* w, void* residual_out,
                           void* normed_out, int rows, int hidden, float eps, void* stream);
+// tensor-parallel GEMMs fused with reduce-scatter / all-gather over symmetric memory (gemm_comm.cu)
+int nkb_gemm_rs(const void* x, const void* w, void* out, int m, int n, int k, long long ldx, long long ldw,
+                long long ldo, void* const* peer_stage, void* const* peer_flags, int flag_stride, int tp, int rank,
+                unsigned int epoch, void* stream);
+int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m, int n, int k, long long ldx, long long ldw,
+                long long ldo, void* const* peer_gather, void* const* peer_flags, int flag_stride, int tp, int rank,
+                unsigned int epoch, int comm_ctas, void* stream);
 
 int nkb_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, float eps, void* stream);
 int nkb_add_rmsnorm(const float* partials, int splits, long long split_stride, const void* x, const void* residual_in,

@@ -277,7 +277,12 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
       const int row = rt * kTileRows + quad * 32 + lane;
       const int col0 = wi.col0;
       bool ok = mbar_wait(&ctrl->tfull[acc], acc_phase, abort_flag, args.status, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, ok)) break;
+      if constexpr (PUSH) {
+        // the four epilogue warps leave together: a warp left alone at the tile barrier below would hang
+        if (!bar_red_and(2, 128, __all_sync(0xffffffffu, ok))) break;
+      } else {
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
       tc_fence_after();
       const uint32_t t0 = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * acc_cols);
       const bool row_ok = row < args.rows;

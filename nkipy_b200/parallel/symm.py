@@ -163,3 +163,102 @@ class FusedTP:
 
     def close(self) -> None:
         self.mem.close()
+
+
+class _FusedGemmCollective:
+    """Shared plumbing of `GemmReduceScatter` and `AllGatherGemm`: two alternating symmetric buffers
+    plus one array of arrival counters per rank, and the call counter the kernels compare against."""
+
+    FLAG_BYTES = 8192
+
+    def __init__(self, tp: TPGroup, buf_bytes: int, rows_per_rank: int):
+        if tp.world_size > 8:
+            raise ValueError("fused GEMM collectives support up to 8 ranks (one NVSwitch domain)")
+        self.tp = tp
+        self.flag_stride = (rows_per_rank + 127) // 128
+        if tp.world_size * self.flag_stride * 4 > self.FLAG_BYTES:
+            raise ValueError("too many row tiles per rank for the counter array")
+        self.buf_bytes = (int(buf_bytes) + 255) // 256 * 256
+        self.mem = SymmetricMemory(tp, self.FLAG_BYTES + 2 * self.buf_bytes)
+        P = ctypes.c_void_p
+        n = tp.world_size
+        self._bufs = [(P * n)(*[p + self.FLAG_BYTES + b * self.buf_bytes for p in self.mem.ptrs]) for b in range(2)]
+        self._flags = (P * n)(*self.mem.ptrs)
+        self.epoch = 0
+        self._lib = _lib.lib()
+
+    def _next(self):
+        self.epoch += 1
+        return self.epoch, self._bufs[self.epoch & 1]
+
+    def close(self) -> None:
+        self.mem.close()
+
+
+class GemmReduceScatter(_FusedGemmCollective):
+    """``out[M/tp, N] = reduce_scatter_rows(x[M, K/tp] @ w[N, K/tp].T)`` as one kernel per rank
+    (csrc/kernels/gemm_comm.cu): finished tiles are stored into the owner rank's staging buffer over
+    NVLink while later tiles are computed; the owner's CTAs sum the tp partials at the end."""
+
+    def __init__(self, tp: TPGroup, m: int, n: int):
+        if m % tp.world_size:
+            raise ValueError("m must be divisible by the number of ranks")
+        self.m, self.n = m, n
+        super().__init__(tp, m * n * 2, m // tp.world_size)
+        I, LL, P, U = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_uint
+        self._lib.nkb_gemm_rs.restype = I
+        self._lib.nkb_gemm_rs.argtypes = [P, P, P, I, I, I, LL, LL, LL, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I,
+                                          U, P]
+
+    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .. import ops
+
+        m, k = x.shape
+        n = w.shape[0]
+        if (m, n) != (self.m, self.n) or w.shape[1] != k:
+            raise ValueError(f"GemmReduceScatter sized for [{self.m}, {self.n}], got x {tuple(x.shape)} w {tuple(w.shape)}")
+        tp = self.tp
+        if out is None:
+            out = torch.empty((m // tp.world_size, n), dtype=torch.bfloat16, device=x.device)
+        epoch, bufs = self._next()
+        rc = self._lib.nkb_gemm_rs(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+                                   out.stride(0), bufs, self._flags, self.flag_stride, tp.world_size, tp.rank, epoch,
+                                   torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "nkb_gemm_rs")
+        ops._launches += 1
+        return out
+
+
+class AllGatherGemm(_FusedGemmCollective):
+    """``out[M, N/tp] = all_gather_rows(x_local[M/tp, K]) @ w[N/tp, K].T`` as one kernel per rank
+    (csrc/kernels/gemm_comm.cu): a few CTAs push this rank's slab chunk by chunk into every peer's
+    gather buffer while the others multiply the slabs in arrival order."""
+
+    def __init__(self, tp: TPGroup, m: int, k: int, comm_ctas: int = 0):
+        if m % tp.world_size:
+            raise ValueError("m must be divisible by the number of ranks")
+        self.m, self.k, self.comm_ctas = m, k, comm_ctas
+        super().__init__(tp, m * k * 2, m // tp.world_size)
+        I, LL, P, U = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_uint
+        self._lib.nkb_ag_gemm.restype = I
+        self._lib.nkb_ag_gemm.argtypes = [P, P, P, I, I, I, LL, LL, LL, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I,
+                                          U, I, P]
+
+    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .. import ops
+
+        rows, k = x_local.shape
+        n = w.shape[0]
+        tp = self.tp
+        if rows * tp.world_size != self.m or k != self.k or w.shape[1] != k:
+            raise ValueError(f"AllGatherGemm sized for [{self.m}, {self.k}], got x {tuple(x_local.shape)} "
+                             f"w {tuple(w.shape)}")
+        if out is None:
+            out = torch.empty((self.m, n), dtype=torch.bfloat16, device=x_local.device)
+        epoch, bufs = self._next()
+        rc = self._lib.nkb_ag_gemm(x_local.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, n, k, x_local.stride(0),
+                                   w.stride(0), out.stride(0), bufs, self._flags, self.flag_stride, tp.world_size,
+                                   tp.rank, epoch, self.comm_ctas, torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "nkb_ag_gemm")
+        ops._launches += 1
+        return out
