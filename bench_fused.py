@@ -11,8 +11,8 @@ for M = 16 ... 16384.  "fused" is one kernel per rank (csrc/kernels/gemm_comm.cu
 over NVLink + arrival counters); "baseline" is torch.matmul (cuBLAS) with NCCL reduce_scatter_tensor /
 all_gather_into_tensor.  Every iteration is timed on the device with CUDA events after an L2 flush (a 256 MB
 memset) and a barrier; the reported time is the median over iterations of the max over ranks.  The roofline is
-the slower of FLOPs / measured cuBLAS bf16 throughput and bytes leaving this GPU / 770 GB/s (measured peer copy
-per direction); `frac_roofline` = roofline time / achieved time.  Rank 0 prints one JSON line per (op, M).
+the slowest of FLOPs / measured cuBLAS bf16 throughput, bytes leaving this GPU / 770 GB/s (measured peer copy
+per direction) and operand + result bytes / measured HBM copy bandwidth; `frac_roofline` = roofline time / achieved time.  Rank 0 prints one JSON line per (op, M).
 """
 from __future__ import annotations
 
@@ -145,15 +145,17 @@ def main():
             rel = ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
             t_f = timed(tp, run, args.iters + (args.iters + args.warmup) % 2, args.warmup, flush)
             t_b = timed(tp, base, args.iters, args.warmup, flush)
-            roof = max(flops / (pk["bf16_tflops"] * 1e6), link_bytes / (NVLINK_GBS * 1e3))
+            t_c = flops / (pk["bf16_tflops"] * 1e6)
+            t_l = link_bytes / (NVLINK_GBS * 1e3)
+            t_h = (x.numel() + w.numel() + m * n // (n_r if op == "rs" else 1)) * 2 / (pk["hbm_gbs"] * 1e3)
+            roof = max(t_c, t_l, t_h)
             status = ops.device_status()
             if tp.rank == 0:
                 print(json.dumps({
                     "op": {"rs": "gemm_rs", "ag": "ag_gemm", "ar": "gemm_ar_norm"}[op], "tp": n_r, "m": m, "n": n, "k": k,
                     "fused_us": round(t_f, 1), "nccl_cublas_us": round(t_b, 1), "speedup": round(t_b / t_f, 2),
                     "roofline_us": round(roof, 1), "frac_roofline": round(roof / t_f, 3),
-                    "bound": "compute" if flops / (pk["bf16_tflops"] * 1e6) >= link_bytes / (NVLINK_GBS * 1e3)
-                    else "nvlink", "tflops": round(flops / t_f / 1e6, 1), "rel_err_vs_baseline": round(rel, 5),
+                    "bound": "compute" if roof == t_c else ("nvlink" if roof == t_l else "hbm"), "tflops": round(flops / t_f / 1e6, 1), "rel_err_vs_baseline": round(rel, 5),
                     "status": status, "peaks": pk["source"]}), flush=True)
             torch.cuda.synchronize()
             tp.barrier()

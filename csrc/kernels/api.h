@@ -77,6 +77,12 @@ int nkb_ipc_close(void* p);
 int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void* flags, int n_src, void* seen,
                           void* done_counter, const void* residual_in, const void* w, void* residual_out,
                           void* normed_out, int rows, int hidden, float eps, void* stream);
+int nkb_moe_combine_push(const void* y_sorted, const int* pair_pos, const float* weights, int tokens, int top_k,
+                         int hidden, void* const* peer_out, void* const* peer_flag, int n_peers, int rank,
+                         void* done_counter, void* stream);
+int nkb_argmax_exchange(const float* vals, const int* ids, int rows, int max_rows, int id_offset,
+                        void* const* peer_pairs, void* const* peer_flag, int n_peers, int rank, const void* local_pairs,
+                        const void* local_flags, void* seen, int* out_ids, void* stream);
 // tensor-parallel GEMMs fused with reduce-scatter / all-gather over symmetric memory (gemm_comm.cu)
 int nkb_gemm_rs(const void* x, const void* w, void* out, int m, int n, int k, long long ldx, long long ldw,
                 long long ldo, void* const* peer_stage, void* const* peer_flags, int flag_stride, int tp, int rank,

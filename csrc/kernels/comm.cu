@@ -24,6 +24,7 @@
 // Neuron runtime (examples/models/qwen3/kernels/attention.py:150-154,
 // examples/models/qwen3/kernels/transformer_layer.py:112-115).
 #include "common.cuh"
+#include "gemm_args.h"
 #include "api.h"
 #include <string.h>
 
@@ -153,6 +154,112 @@ __global__ void tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ parti
   }
 }
 
+// MoE combine fused with the push half of the all-reduce: out[t] = sum_j w[t, j] * y_sorted[pair_pos[t, j]]
+// over the pairs handled by this rank's experts, stored as a bf16 partial row into slot [rank] of every
+// peer's partial array (rows without local pairs are stored as zeros: the consumer sums all slots).
+// The last CTA signals every peer exactly like the GEMM push epilogue does.
+__global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ y_sorted, const int* __restrict__ pair_pos,
+                                        const float* __restrict__ weights, int tokens, int top_k, int hidden,
+                                        const PushArgs push) {
+  griddep_wait();
+  griddep_launch();
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < (hidden >> 3); v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int pos = pair_pos[t * top_k + j];
+      if (pos < 0) continue;
+      const float w = weights[t * top_k + j];
+      const uint4 r = *reinterpret_cast<const uint4*>(y_sorted + (long long)pos * hidden + v * 8);
+      const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(rw[e]);
+        acc[2 * e] += w * f.x;
+        acc[2 * e + 1] += w * f.y;
+      }
+    }
+    const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                               pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    const long long off = ((long long)push.rank * tokens + t) * hidden + v * 8;
+    for (int pr = 0; pr < push.n_peers; ++pr) *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int old = atomicAdd(push.done_counter, 1u);
+    if (old == gridDim.x - 1) {
+      *push.done_counter = 0u;
+      __threadfence_system();
+      for (int pr = 0; pr < push.n_peers; ++pr) atomicAdd_system(push.peer_flag[pr], 1u);
+    }
+  }
+}
+
+// Cross-rank arg-max of a vocabulary-parallel head in one launch of one CTA: every rank stores its
+// (value, global id) pair per row into all peers' pair arrays [2][n_peers][max_rows] (the half is chosen
+// by the parity of `seen`, which all ranks advance in step), bumps its arrival counter on every peer,
+// waits (bounded) for all counters and picks the best pair per row (the lowest rank wins ties, i.e. the
+// lowest vocabulary index).  Replaces an all-gather plus a handful of tiny kernels
+// (examples/models/qwen3/kernels/sampling.py:130-135 in the reference gathers values and ids).
+struct ArgmaxPeers {
+  float2* pairs[kMaxPeers];
+  unsigned int* flag[kMaxPeers];   // this rank's counter inside each peer's flag array
+};
+__global__ void argmax_exchange_kernel(const float* __restrict__ vals, const int* __restrict__ ids, int rows,
+                                       int max_rows, int id_offset, int rank, int n_peers, const ArgmaxPeers peers,
+                                       const float2* __restrict__ local_pairs, const unsigned int* __restrict__ flags,
+                                       unsigned int* __restrict__ seen, int* __restrict__ out_ids,
+                                       int* __restrict__ status) {
+  __shared__ int ok_flag;
+  griddep_wait();
+  griddep_launch();
+  const unsigned int use = *reinterpret_cast<volatile unsigned int*>(seen);
+  const long long half = (long long)(use & 1u) * n_peers * max_rows;
+  for (int i = threadIdx.x; i < rows * n_peers; i += blockDim.x) {
+    const int pr = i / rows, r = i - pr * rows;
+    peers.pairs[pr][half + (long long)rank * max_rows + r] = make_float2(vals[r], __int_as_float(ids[r] + id_offset));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int pr = 0; pr < n_peers; ++pr) atomicAdd_system(peers.flag[pr], 1u);
+    int ok = 1;
+    const unsigned long long t0 = globaltimer_ns();
+    for (int s = 0; s < n_peers && ok; ++s) {
+      unsigned int spins = 0;
+      while (int(ld_acquire_sys(flags + s) - (use + 1u)) < 0) {
+        if ((++spins & 255u) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+          atomicCAS(status, 0, ERR_WAIT_PEER_FLAG | (s << 8));
+          ok = 0;
+          break;
+        }
+      }
+    }
+    ok_flag = ok;
+  }
+  __syncthreads();
+  if (ok_flag) {
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+      float best = -INFINITY;
+      int best_id = 0;
+      for (int s = 0; s < n_peers; ++s) {
+        const float2 p = __ldcg(local_pairs + half + (long long)s * max_rows + r);
+        if (s == 0 || p.x > best) {
+          best = p.x;
+          best_id = __float_as_int(p.y);
+        }
+      }
+      out_ids[r] = best_id;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && ok_flag) {
+    __threadfence();
+    *seen = use + 1u;
+  }
+}
+
 }  // namespace nkb
 
 using namespace nkb;
@@ -198,4 +305,45 @@ extern "C" int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void
                     (const __nv_bfloat16*)partials, slots, (const unsigned int*)flags, n_src, (unsigned int*)seen,
                     (unsigned int*)done_counter, (const __nv_bfloat16*)residual_in, (const __nv_bfloat16*)w,
                     (__nv_bfloat16*)residual_out, (__nv_bfloat16*)normed_out, rows, hidden, eps, status_word());
+}
+
+// y_sorted [pairs, hidden] bf16, pair_pos [tokens * top_k], weights [tokens, top_k] fp32.  peer_out[r] is
+// rank r's partial array [n_peers, tokens, hidden] bf16, peer_flag[r] this rank's counter on rank r.
+extern "C" int nkb_moe_combine_push(const void* y_sorted, const int* pair_pos, const float* weights, int tokens,
+                                    int top_k, int hidden, void* const* peer_out, void* const* peer_flag, int n_peers,
+                                    int rank, void* done_counter, void* stream) {
+  if (tokens <= 0) return 0;
+  if ((hidden & 7) || n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return -2;
+  if (!status_word() && nkb_init() != 0) return -1;
+  PushArgs pa{};
+  pa.n_peers = n_peers;
+  pa.rank = rank;
+  for (int i = 0; i < n_peers; ++i) {
+    pa.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(peer_out[i]);
+    pa.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
+  }
+  pa.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  return launch_pdl(moe_combine_push_kernel, dim3(tokens), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                    (const __nv_bfloat16*)y_sorted, pair_pos, weights, tokens, top_k, hidden, pa);
+}
+
+// vals / ids [rows]: this rank's per-row maximum and local index; id_offset is added to make the index
+// global.  peer_pairs[r]: rank r's pair array (2 * n_peers * max_rows float2), peer_flag[r]: this rank's
+// counter on rank r; local_pairs / local_flags: this rank's own arrays; seen: device counter of completed
+// exchanges (selects the half of the pair array).
+extern "C" int nkb_argmax_exchange(const float* vals, const int* ids, int rows, int max_rows, int id_offset,
+                                   void* const* peer_pairs, void* const* peer_flag, int n_peers, int rank,
+                                   const void* local_pairs, const void* local_flags, void* seen, int* out_ids,
+                                   void* stream) {
+  if (rows <= 0) return 0;
+  if (rows > max_rows || n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return -2;
+  if (!status_word() && nkb_init() != 0) return -1;
+  ArgmaxPeers ap{};
+  for (int i = 0; i < n_peers; ++i) {
+    ap.pairs[i] = reinterpret_cast<float2*>(peer_pairs[i]);
+    ap.flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
+  }
+  return launch_pdl(argmax_exchange_kernel, dim3(1), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), vals, ids,
+                    rows, max_rows, id_offset, rank, n_peers, ap, (const float2*)local_pairs,
+                    (const unsigned int*)local_flags, (unsigned int*)seen, out_ids, status_word());
 }

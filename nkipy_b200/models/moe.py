@@ -34,8 +34,8 @@ class MoEBlock:
         logits = ops.linear(x, lw.router, splits=max(2, min(16, x.shape[1] // 256)))
         return ops.router_topk(logits, self.cfg.top_k, self.cfg.router_mode, bias=lw.router_bias)
 
-    def forward(self, lw, x: torch.Tensor) -> torch.Tensor:
-        """x [T, H] (normed hidden states, replicated over ranks) -> MoE output [T, H], summed over ranks."""
+    def _experts(self, lw, x: torch.Tensor):
+        """Route, dispatch and run the local experts; returns (y_sorted, plan, routing weights)."""
         cfg = self.cfg
         T = x.shape[0]
         weights, experts = self.route(lw, x)
@@ -45,6 +45,25 @@ class MoEBlock:
                                tiles=plan.tiles)
         y_sorted = ops.grouped_linear(h, lw.down, plan.offsets, max_rows_per_group=T, bias=lw.down_bias,
                                       tiles=plan.tiles)
-        y = ops.moe_combine(y_sorted, plan.pair_pos, weights, T)
+        return y_sorted, plan, weights
+
+    def forward(self, lw, x: torch.Tensor) -> torch.Tensor:
+        """x [T, H] (normed hidden states, replicated over ranks) -> MoE output [T, H], summed over ranks."""
+        y_sorted, plan, weights = self._experts(lw, x)
+        y = ops.moe_combine(y_sorted, plan.pair_pos, weights, x.shape[0])
         self.tp.all_reduce(y)
         return y
+
+    def forward_add_rmsnorm(self, lw, x: torch.Tensor, resid: torch.Tensor, next_norm: torch.Tensor):
+        """MoE block + residual + next RMSNorm; returns (new residual, normed).  With the fused
+        tensor-parallel runtime the combine kernel pushes its partial rows straight into the peers'
+        buffers and the reducing norm kernel sums them (no library collective)."""
+        cfg = self.cfg
+        fused = getattr(self.tp, "fused", None)
+        T = x.shape[0]
+        if fused is not None and T <= fused.max_tokens:
+            y_sorted, plan, weights = self._experts(lw, x)
+            return fused.moe_combine_allreduce_add_rmsnorm(y_sorted, plan.pair_pos, weights, T, resid, next_norm,
+                                                           cfg.rms_eps)
+        y = self.forward(lw, x)
+        return ops.add_rmsnorm(y, next_norm, residual_in=resid, eps=cfg.rms_eps)

@@ -142,8 +142,7 @@ class TransformerLM:
         """Returns (new residual, normed for the next block)."""
         cfg = self.cfg
         if cfg.is_moe:
-            y = self._moe.forward(lw, normed)                       # [B, H] bf16, already reduced over ranks
-            return ops.add_rmsnorm(y, next_norm, residual_in=resid, eps=cfg.rms_eps)
+            return self._moe.forward_add_rmsnorm(lw, normed, resid, next_norm)
         if cfg.swiglu_limit <= 0 and self.split_gate_up == 1:
             act = ops.linear(normed, lw.gate_up, gated=True)
         elif self.split_gate_up > 1:
@@ -214,6 +213,10 @@ class TransformerLM:
         return_hidden is set, for speculative-decoding taps)."""
         cfg = self.cfg
         tp1 = self.tp.world_size == 1
+        if (not tp1 and not return_hidden and getattr(self.tp, "fused", None) is not None
+                and ids.shape[0] % self.tp.world_size == 0 and ids.shape[0] >= 128 * self.tp.world_size):
+            return self._prefill_sequence_parallel(ids, positions, slots, cache, block_table, q_start, q_lens,
+                                                   context_lens, max_q_len)
         x = ops.embedding(ids, self.tok_embedding)
         resid = x
         normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
@@ -256,6 +259,53 @@ class TransformerLM:
             return normed, taps
         return normed
 
+    def _prefill_sequence_parallel(self, ids, positions, slots, cache, block_table, q_start, q_lens, context_lens,
+                                   max_q_len):
+        """Prefill for tp > 1 in the sequence-parallel layout: the residual stream lives as one row slab
+        [T / tp, H] per rank, the column-parallel projections gather the slabs inside the GEMM kernel
+        (`AllGatherGemm`) and the row-parallel projections reduce-scatter inside theirs
+        (`GemmReduceScatter`), so no library collective sits between the GEMMs of a layer."""
+        from ..parallel.symm import AllGatherGemm, GemmReduceScatter
+
+        cfg, tp = self.cfg, self.tp
+        T = ids.shape[0]
+        n, r = tp.world_size, tp.rank
+        rows = T // n
+        if not hasattr(self, "_sp_ops"):
+            self._sp_ops = {}
+        if T not in self._sp_ops:
+            self._sp_ops[T] = (GemmReduceScatter(tp, T, cfg.hidden_size), AllGatherGemm(tp, T, cfg.hidden_size))
+        rs, ag = self._sp_ops[T]
+        if not hasattr(self, "_o_bias_full"):
+            # the row-parallel bias is stored on rank 0 only (zeros elsewhere); every slab needs it
+            self._o_bias_full = [None if lw.o_bias is None else tp.all_reduce(lw.o_bias.clone())
+                                 for lw in self.layers]
+        resid = ops.embedding(ids[r * rows:(r + 1) * rows], self.tok_embedding)
+        normed = ops.rmsnorm(resid, self.layers[0].input_norm, cfg.rms_eps)
+        for i, lw in enumerate(self.layers):
+            qkv = ag(normed, lw.qkv)
+            q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq, self.nkv,
+                                   self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
+                                   norm_eps=cfg.rms_eps)
+            attn = ops.flash_attn_prefill(q, cache.k[i], cache.v[i], block_table, q_start, q_lens, context_lens,
+                                          self.scale, max_q_len=max_q_len, causal=cfg.causal,
+                                          window=cfg.window_for_layer(i), sinks=lw.sinks)
+            o = rs(attn, lw.o)
+            resid, normed = ops.add_rmsnorm(o, lw.post_norm, residual_in=resid, bias=self._o_bias_full[i],
+                                            eps=cfg.rms_eps)
+            nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
+            if cfg.is_moe:
+                full = tp.all_gather(normed).reshape(T, cfg.hidden_size)
+                y_sorted, plan, weights = self._moe._experts(lw, full)
+                y = ops.moe_combine(y_sorted, plan.pair_pos, weights, T)
+                dn = tp.reduce_scatter(y)
+            else:
+                gu = ag(normed, lw.gate_up)
+                act = ops.silu_mul(gu, limit=cfg.swiglu_limit, alpha=cfg.swiglu_alpha)
+                dn = rs(act, lw.down)
+            resid, normed = ops.add_rmsnorm(dn, nxt, residual_in=resid, eps=cfg.rms_eps)
+        return tp.all_gather(normed).reshape(T, cfg.hidden_size)
+
     # ------------------------------------------------------------------ heads
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Vocab-parallel logits [rows, V / tp] (bf16)."""
@@ -271,6 +321,10 @@ class TransformerLM:
             return ops.argmax(logits, out_ids=out_ids)
         vals = torch.empty((rows,), dtype=torch.float32, device=hidden.device)
         ids = ops.argmax(logits, out_vals=vals)
+        fused = getattr(self.tp, "fused", None)
+        if fused is not None and rows <= fused.max_tokens:
+            # (value, id) pairs exchanged over peer memory by one kernel
+            return fused.argmax_exchange(vals, ids, self.tp.rank * self.vocab_local, out_ids)
         packed = torch.stack([vals, (ids + self.tp.rank * self.vocab_local).float()], dim=-1)  # [rows, 2]
         allp = self.tp.all_gather(packed)                                                       # [tp, rows, 2]
         best = allp[..., 0].argmax(dim=0)                                                       # first max wins

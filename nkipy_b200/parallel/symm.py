@@ -92,6 +92,7 @@ class FusedTP:
     """Fused row-parallel GEMM + all-reduce + residual + RMSNorm for decode-sized batches."""
 
     FLAG_BYTES = 4096
+    ARGMAX_FLAG_OFFSET = 1024      # byte offset of the argmax arrival counters inside the flag page
 
     def __init__(self, tp: TPGroup, max_tokens: int, hidden: int, max_splits: int = 8):
         if tp.world_size < 2:
@@ -100,26 +101,35 @@ class FusedTP:
             raise ValueError("FusedTP supports up to 8 ranks (one NVSwitch domain)")
         self.tp = tp
         self.max_tokens, self.hidden, self.max_splits = max_tokens, hidden, max_splits
-        self.buf_bytes = tp.world_size * max_splits * max_tokens * hidden * 2
+        n = tp.world_size
+        self.buf_bytes = n * max_splits * max_tokens * hidden * 2
         self.buf_bytes = (self.buf_bytes + 255) // 256 * 256
-        self.mem = SymmetricMemory(tp, self.FLAG_BYTES + 2 * self.buf_bytes)
+        self.pair_bytes = (2 * n * max_tokens * 8 + 255) // 256 * 256
+        self.mem = SymmetricMemory(tp, self.FLAG_BYTES + 2 * self.buf_bytes + self.pair_bytes)
         dev = tp.device
-        self.seen = torch.zeros((2,), dtype=torch.int32, device=dev)
-        self.done = torch.zeros((4,), dtype=torch.int32, device=dev)   # [gemm, reduce0, reduce1, spare]
+        self.seen = torch.zeros((4,), dtype=torch.int32, device=dev)   # [buffer 0, buffer 1, argmax, spare]
+        self.done = torch.zeros((4,), dtype=torch.int32, device=dev)   # [producer, reduce0, reduce1, spare]
         self._parity = 0
         self.ops_issued = 0
         lib = _lib.lib()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        PP = ctypes.POINTER(P)
         lib.nkb_gemm_bf16_push.restype = I
-        lib.nkb_gemm_bf16_push.argtypes = [P, P, I, I, I, LL, LL, LL, I, P, I, ctypes.POINTER(P), ctypes.POINTER(P),
-                                           I, I, P, P]
+        lib.nkb_gemm_bf16_push.argtypes = [P, P, I, I, I, LL, LL, LL, I, P, I, PP, PP, I, I, P, P]
         lib.nkb_tp_reduce_rmsnorm.restype = I
         lib.nkb_tp_reduce_rmsnorm.argtypes = [P, I, P, I, P, P, P, P, P, P, I, I, ctypes.c_float, P]
+        lib.nkb_moe_combine_push.restype = I
+        lib.nkb_moe_combine_push.argtypes = [P, P, P, I, I, I, PP, PP, I, I, P, P]
+        lib.nkb_argmax_exchange.restype = I
+        lib.nkb_argmax_exchange.argtypes = [P, P, I, I, I, PP, PP, I, I, P, P, P, P, P]
         self._lib = lib
-        n = tp.world_size
         self._peer_out = [(P * n)(*[p + self.FLAG_BYTES + b * self.buf_bytes for p in self.mem.ptrs])
                           for b in range(2)]
         self._peer_flag = [(P * n)(*[p + (b * n + tp.rank) * 4 for p in self.mem.ptrs]) for b in range(2)]
+        pair_off = self.FLAG_BYTES + 2 * self.buf_bytes
+        self._pair_off = pair_off
+        self._peer_pairs = (P * n)(*[p + pair_off for p in self.mem.ptrs])
+        self._peer_aflag = (P * n)(*[p + self.ARGMAX_FLAG_OFFSET + tp.rank * 4 for p in self.mem.ptrs])
 
     def begin_step(self) -> None:
         """Call at the start of every decode body: buffers alternate per operation and a
@@ -150,16 +160,68 @@ class FusedTP:
                                     None if bias is None else bias.data_ptr(), block_n, self._peer_out[b],
                                     self._peer_flag[b], n, self.tp.rank, self.done.data_ptr(), stream)
         _lib.check(rc, "nkb_gemm_bf16_push")
-        resid_out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        normed = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if next_norm is not None else None
-        rc = lib.nkb_tp_reduce_rmsnorm(
-            self.mem.local_ptr + self.FLAG_BYTES + b * self.buf_bytes, n * eff, self.mem.local_ptr + b * n * 4, n,
+        ops._launches += 1
+        return self._reduce(b, n * eff, M, resid, next_norm, eps, x.device)
+
+    def _reduce(self, b: int, slots: int, M: int, resid, next_norm, eps: float, device):
+        """Consumer of buffer b: wait for all ranks, sum the slots, add the residual, RMSNorm."""
+        from .. import ops
+
+        n, N = self.tp.world_size, self.hidden
+        resid_out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        normed = torch.empty((M, N), dtype=torch.bfloat16, device=device) if next_norm is not None else None
+        rc = self._lib.nkb_tp_reduce_rmsnorm(
+            self.mem.local_ptr + self.FLAG_BYTES + b * self.buf_bytes, slots, self.mem.local_ptr + b * n * 4, n,
             self.seen.data_ptr() + 4 * b, self.done.data_ptr() + 4 * (1 + b),
             None if resid is None else resid.data_ptr(), None if next_norm is None else next_norm.data_ptr(),
-            resid_out.data_ptr(), None if normed is None else normed.data_ptr(), M, N, float(eps), stream)
+            resid_out.data_ptr(), None if normed is None else normed.data_ptr(), M, N, float(eps),
+            torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "nkb_tp_reduce_rmsnorm")
-        ops._launches += 2
+        ops._launches += 1
         return resid_out, normed
+
+    def moe_combine_allreduce_add_rmsnorm(self, y_sorted: torch.Tensor, pair_pos: torch.Tensor,
+                                          weights: torch.Tensor, tokens: int, resid: Optional[torch.Tensor],
+                                          next_norm: Optional[torch.Tensor], eps: float):
+        """Expert-parallel combine: the weighted sum of this rank's expert outputs per token is pushed into
+        every peer's partial buffer by the combine kernel itself; the consumer sums over ranks, adds the
+        residual and applies the next RMSNorm.  Returns (new residual, normed)."""
+        from .. import ops
+
+        if tokens > self.max_tokens or y_sorted.shape[1] != self.hidden:
+            raise ValueError(f"FusedTP sized for [{self.max_tokens}, {self.hidden}]")
+        b = self._parity
+        self._parity ^= 1
+        self.ops_issued += 1
+        n = self.tp.world_size
+        rc = self._lib.nkb_moe_combine_push(y_sorted.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(), tokens,
+                                            weights.shape[1], self.hidden, self._peer_out[b], self._peer_flag[b], n,
+                                            self.tp.rank, self.done.data_ptr(),
+                                            torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "nkb_moe_combine_push")
+        ops._launches += 1
+        return self._reduce(b, n, tokens, resid, next_norm, eps, y_sorted.device)
+
+    def argmax_exchange(self, vals: torch.Tensor, ids: torch.Tensor, id_offset: int,
+                        out_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Global arg-max of a vocabulary-parallel head: vals / ids are this rank's per-row maximum (fp32)
+        and local index (int32); returns the global ids (int32 [rows]) on every rank."""
+        from .. import ops
+
+        rows = vals.shape[0]
+        if rows > self.max_tokens:
+            raise ValueError(f"FusedTP sized for {self.max_tokens} rows, got {rows}")
+        if out_ids is None:
+            out_ids = torch.empty((rows,), dtype=torch.int32, device=vals.device)
+        rc = self._lib.nkb_argmax_exchange(vals.data_ptr(), ids.data_ptr(), rows, self.max_tokens, int(id_offset),
+                                           self._peer_pairs, self._peer_aflag, self.tp.world_size, self.tp.rank,
+                                           self.mem.local_ptr + self._pair_off,
+                                           self.mem.local_ptr + self.ARGMAX_FLAG_OFFSET,
+                                           self.seen.data_ptr() + 8, out_ids.data_ptr(),
+                                           torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "nkb_argmax_exchange")
+        ops._launches += 1
+        return out_ids
 
     def close(self) -> None:
         self.mem.close()
