@@ -85,14 +85,20 @@ struct CommShared {
   GemmCtrl ctrl;                               // <= 512 bytes
   __nv_bfloat16* peer_buf[kCommMaxPeers];
   unsigned int* peer_flags[kCommMaxPeers];
+  uint64_t pub_full[2];                        // gemm_rs: a tile's peer stores are issued (4 epilogue warps arrive)
+  uint64_t pub_empty[2];                       // gemm_rs: the publisher has counted that tile
 };
+
+// warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warp 6 publisher (gemm_rs: system fence + arrival counters,
+// kept off the epilogue's critical path)
+constexpr int kCommThreads = kGemmThreads + 32;
 
 constexpr int kCommCtrlBytes = 1024;
 constexpr int kStageOutBytes = 4 * 32 * 128 * 2;   // per epilogue warp: 32 rows x 128 columns bf16
 
 // MODE 0 = gemm_rs, 1 = ag_gemm
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kCommThreads, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                  const __grid_constant__ CUtensorMap tmB, const CommArgs args, const CommPeers peers) {
   // shared memory: [control block 1 KB][gemm_rs: epilogue staging 32 KB][ring of stages], 1024-aligned
@@ -205,6 +211,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctrl->tfull[i], 1);
       mbar_init(&ctrl->tempty[i], 4);
+      mbar_init(&sh->pub_full[i], 4);
+      mbar_init(&sh->pub_empty[i], 1);
     }
     ctrl->abort = 0;
     mbar_fence_init();
@@ -312,11 +320,60 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ publisher (gemm_rs)
+    // A system fence waits for every peer store this SM has in flight, which under a saturated link is
+    // tens of microseconds: the counters of the tiles of one owner phase are therefore published in
+    // batches (one fence per batch).  A tile that also holds rows of this rank is published at once,
+    // because the same CTA then waits for its peers, who may be waiting for exactly this tile.
+    if (MODE == 0 && args.tp > 1) {
+      constexpr int kBatch = 8;
+      const int rpr = args.rows_per_rank;
+      const int own0 = args.rank * rpr, own1 = own0 + rpr;
+      unsigned int* pend[kBatch];
+      int npend = 0, pend_phase = -1;
+      int u = 0;
+      bool alive = true;
+      auto flush = [&]() {
+        if (lane == 0 && npend > 0) {
+          // the epilogue warps' stores happen-before this point (mbarrier acquire); the fence is cumulative
+          __threadfence_system();
+          for (int i = 0; i < npend; ++i) atomicAdd_system(pend[i], 1u);
+        }
+        npend = 0;
+      };
+      for (int w = cta; w < total_work && alive; w += ncta) {
+        const int ro = w / args.num_col_tiles;
+        int rt = args.first_tile + ro;
+        if (rt >= args.num_row_tiles) rt -= args.num_row_tiles;
+        const int r0 = rt * kTileRows, r1 = min(args.m, r0 + kTileRows);
+        const int phase_id = r0 / rpr;
+        if (npend > 0 && phase_id != pend_phase) flush();
+        if (!(r0 < own0 || r1 > own1)) continue;   // no peer rows in this tile
+        const int slot = u & 1;
+        bool ok = mbar_wait(&sh->pub_full[slot], (uint32_t(u) >> 1) & 1u, abort_flag, args.status, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        if (lane == 0) mbar_arrive(&sh->pub_empty[slot]);
+        ++u;
+        for (int o = r0 / rpr; o <= (r1 - 1) / rpr; ++o) {
+          if (o == args.rank) continue;
+          const int lo = max(r0, o * rpr) - o * rpr, hi = min(r1, (o + 1) * rpr) - o * rpr;
+          for (int t = lo / 128; t <= (hi - 1) / 128; ++t) {
+            if (npend == kBatch) flush();
+            pend[npend++] = sh->peer_flags[o] + args.rank * args.flag_stride + t;
+          }
+        }
+        pend_phase = phase_id;
+        if (r0 < own1 && r1 > own0) flush();       // this CTA is about to wait for its peers
+        __syncwarp();
+      }
+      flush();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;
-    const int et = threadIdx.x - 64;   // 0..127
     griddep_wait();
+    int published = 0;   // gemm_rs: tiles of this CTA handed to the publisher so far
     int acc = 0;
     uint32_t acc_phase = 0;
     bool alive = true;
@@ -447,20 +504,15 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __syncwarp();
           }
         };
-        // once all 128 epilogue threads have issued their peer stores, one thread makes them visible
-        // system-wide (the fence is cumulative over the barrier) and counts the tile on every peer that
-        // owns rows of it
+        // hand the tile to the publisher warp: it fences and counts while these warps go on.  The slot
+        // of two tiles ago must have been published first (bounded wait; first uses pass at once).
         auto publish = [&]() {
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et == 0) {
-            __threadfence_system();
-            for (int o = r0 / rpr; o <= (r1 - 1) / rpr; ++o) {
-              if (o == args.rank) continue;
-              const int lo = max(r0, o * rpr) - o * rpr, hi = min(r1, (o + 1) * rpr) - o * rpr;
-              for (int t = lo / 128; t <= (hi - 1) / 128; ++t)
-                atomicAdd_system(sh->peer_flags[o] + args.rank * args.flag_stride + t, 1u);
-            }
-          }
+          const int slot = published & 1;
+          const bool ok2 = mbar_wait(&sh->pub_empty[slot], ((uint32_t(published) >> 1) & 1u) ^ 1u, abort_flag,
+                                     args.status, ERR_WAIT_PEER_FLAG);
+          __syncwarp();
+          if (lane == 0 && ok2) mbar_arrive(&sh->pub_full[slot]);
+          ++published;
         };
         // bounded wait (per warp) until every peer has delivered its partials of this warp's own rows
         auto wait_peers = [&]() -> bool {
@@ -531,7 +583,7 @@ static int launch_comm(const CUtensorMap& ta, const CUtensorMap& ta2, const CUte
   // every CTA must be resident at once: reducers and consumers wait on work of other CTAs' peers only,
   // but the pushers of ag_gemm must run beside the consumers
   const int grid = num_sms();
-  return launch_pdl(gemm_comm_kernel<BN, MODE>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, ta2, tb, args,
+  return launch_pdl(gemm_comm_kernel<BN, MODE>, dim3(grid), dim3(kCommThreads), size_t(smem), stream, ta, ta2, tb, args,
                     peers);
 }
 
