@@ -169,6 +169,69 @@ class EagerTransformer:
         out = _rms(x, w["norm_weight"], cfg.rms_eps)
         return (out, taps) if return_hidden else out
 
+    # ------------------------------------------------------------------ timed baseline path
+    def alloc_static_cache(self, batch: int, max_len: int) -> None:
+        """Preallocated dense KV cache [B, kv_heads, max_len, d] per layer for `forward_sdpa`."""
+        shape = (batch, self.nkv, max_len, self.cfg.head_dim)
+        self.k_static = [torch.empty(shape, dtype=self.dtype, device=self.device) for _ in range(self.cfg.num_layers)]
+        self.v_static = [torch.empty(shape, dtype=self.dtype, device=self.device) for _ in range(self.cfg.num_layers)]
+
+    def forward_sdpa(self, ids: torch.Tensor, start_pos: int = 0) -> torch.Tensor:
+        """The same decoder the way a PyTorch user would write it for speed: bf16 matmuls (cuBLAS),
+        `scaled_dot_product_attention` with grouped-query heads over a preallocated dense cache, NCCL
+        all-reduces.  Causal models without sliding windows or attention sinks only (Llama, Qwen3)."""
+        cfg, w = self.cfg, self.w
+        if cfg.attention_sinks or any(cfg.window_for_layer(i) > 0 for i in range(cfg.num_layers)):
+            return self.forward(ids, start_pos)
+        B, S = ids.shape
+        d = cfg.head_dim
+        x = w["tok_embedding"][ids.long()]
+        pos = torch.arange(start_pos, start_pos + S, device=self.device)[None, :].expand(B, S)
+        end = start_pos + S
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            in_name = p + ("input_layernorm_weight" if p + "input_layernorm_weight" in w else "input_weight")
+            post_name = p + ("post_attention_layernorm_weight" if p + "post_attention_layernorm_weight" in w
+                             else "post_attention_weight")
+            h = _rms(x, w[in_name], cfg.rms_eps)
+            qkv = h @ w[p + "qkv_weight"]
+            if cfg.attn_bias:
+                qkv = qkv + w[p + "qkv_bias"]
+            q, k, v = qkv.split([self.nq * d, self.nkv * d, self.nkv * d], dim=-1)
+            q, k, v = q.reshape(B, S, self.nq, d), k.reshape(B, S, self.nkv, d), v.reshape(B, S, self.nkv, d)
+            if cfg.qk_norm:
+                q, k = _rms(q, w[p + "q_norm_weight"], cfg.rms_eps), _rms(k, w[p + "k_norm_weight"], cfg.rms_eps)
+            q, k = self._rope(q, pos), self._rope(k, pos)
+            self.k_static[i][:, :, start_pos:end] = k.transpose(1, 2)
+            self.v_static[i][:, :, start_pos:end] = v.transpose(1, 2)
+            if S == 1:
+                # decode: the g query heads of a kv head act as g query rows, so the fused attention
+                # kernels apply without materialising repeated K / V
+                g = self.nq // self.nkv
+                a = F.scaled_dot_product_attention(q.reshape(B, self.nkv, g, d), self.k_static[i][:, :, :end],
+                                                   self.v_static[i][:, :, :end])
+                a = a.reshape(B, 1, self.nq * d)
+            else:
+                a = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_static[i][:, :, :end],
+                                                   self.v_static[i][:, :, :end],
+                                                   is_causal=(S > 1 and start_pos == 0), enable_gqa=True)
+                a = a.transpose(1, 2).reshape(B, S, self.nq * d)
+            o = a @ w[p + "o_weight"]
+            if cfg.attn_bias:
+                o = o + w[p + "o_bias"]
+            self.tp.all_reduce(o)
+            x = x + o
+            h = _rms(x, w[post_name], cfg.rms_eps)
+            if cfg.is_moe:
+                y = self._moe(p, h.reshape(B * S, -1)).reshape(B, S, -1)
+            else:
+                gu = h @ w[p + "gate_up_weight"]
+                i_l = gu.shape[-1] // 2
+                y = (F.silu(gu[..., :i_l]) * gu[..., i_l:]) @ w[p + "down_weight"]
+                self.tp.all_reduce(y)
+            x = x + y
+        return _rms(x, w["norm_weight"], cfg.rms_eps)
+
     def greedy(self, hidden_last: torch.Tensor) -> torch.Tensor:
         """hidden_last [B, H] -> global greedy ids (vocab-parallel aware)."""
         logits = (hidden_last @ self.w["lm_head_weight"]).float()
