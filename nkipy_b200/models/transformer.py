@@ -176,14 +176,19 @@ class TransformerLM:
     # ------------------------------------------------------------------ decode
     def decode_step(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: PagedKVCache,
                     block_table: torch.Tensor, context_lens: torch.Tensor, q_len: int = 1,
-                    return_hidden: bool = False) -> torch.Tensor:
+                    return_hidden: bool = False, inputs=None) -> torch.Tensor:
         """One decode (or q_len-token verify) step for the batch.  ids [B * q_len] int32;
         context_lens already count the new tokens.  Returns the final-normed hidden
-        states [B * q_len, H]."""
+        states [B * q_len, H] (with return_hidden also the residual stream after every layer).
+        inputs = (residual [T, H], first-layer input [T, K0]) replaces the embedding lookup and the
+        first norm (used by models whose first layer consumes something else than token embeddings)."""
         cfg = self.cfg
-        x = ops.embedding(ids, self.tok_embedding)
-        resid = x
-        normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
+        if inputs is None:
+            x = ops.embedding(ids, self.tok_embedding)
+            resid = x
+            normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
+        else:
+            resid, normed = inputs
         taps = [] if return_hidden else None
         for i, lw in enumerate(self.layers):
             if self.split_qkv > 1:
@@ -207,19 +212,22 @@ class TransformerLM:
     # ------------------------------------------------------------------ prefill
     def prefill(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: PagedKVCache,
                 block_table: torch.Tensor, q_start: torch.Tensor, q_lens: torch.Tensor, context_lens: torch.Tensor,
-                max_q_len: int, return_hidden: bool = False):
+                max_q_len: int, return_hidden: bool = False, inputs=None):
         """Packed prefill of several sequences.  ids / positions / slots [T]; returns the
         final-normed hidden states [T, H] (and the per-layer residual streams when
-        return_hidden is set, for speculative-decoding taps)."""
+        return_hidden is set, for speculative-decoding taps).  inputs: see `decode_step`."""
         cfg = self.cfg
         tp1 = self.tp.world_size == 1
-        if (not tp1 and not return_hidden and getattr(self.tp, "fused", None) is not None
+        if (not tp1 and not return_hidden and inputs is None and getattr(self.tp, "fused", None) is not None
                 and ids.shape[0] % self.tp.world_size == 0 and ids.shape[0] >= 128 * self.tp.world_size):
             return self._prefill_sequence_parallel(ids, positions, slots, cache, block_table, q_start, q_lens,
                                                    context_lens, max_q_len)
-        x = ops.embedding(ids, self.tok_embedding)
-        resid = x
-        normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
+        if inputs is None:
+            x = ops.embedding(ids, self.tok_embedding)
+            resid = x
+            normed = ops.rmsnorm(x, self.layers[0].input_norm, cfg.rms_eps)
+        else:
+            resid, normed = inputs
         taps = [] if return_hidden else None
         for i, lw in enumerate(self.layers):
             qkv = ops.linear(normed, lw.qkv, swap=False)

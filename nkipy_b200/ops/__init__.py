@@ -618,6 +618,13 @@ def paged_attn_decode(
         return out
     global _launches
     _check_bf16(q, k_cache, v_cache)
+    if q_len * (nq // nkv) > 16:
+        # more query rows per kv head than the decode kernel's 16-row fragment: the blockwise prefill
+        # kernel handles any window (query i of a sequence sits at position context_len - q_len + i)
+        q_start = torch.arange(B, device=q.device, dtype=torch.int32) * q_len
+        q_lens = torch.full((B,), q_len, device=q.device, dtype=torch.int32)
+        return flash_attn_prefill(q, k_cache, v_cache, block_table, q_start, q_lens, context_lens, scale,
+                                  max_q_len=q_len, causal=True, window=window, sinks=sinks, out=out)
     L = _lib.lib()
     if num_splits <= 0:
         num_splits = pick_kv_splits(B * nkv, block_table.shape[1])

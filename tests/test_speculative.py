@@ -1,0 +1,109 @@
+"""Speculative decoding: whatever the drafter proposes, greedy output must equal plain decoding."""
+import pytest
+import torch
+
+from nkipy_b200.models import config as C
+from nkipy_b200.models.engine import GenerationEngine
+from nkipy_b200.models.speculative import (DrafterLM, EagleConfig, SpeculativeEngine, random_drafter_weights,
+                                           tap_layers)
+from nkipy_b200.models.transformer import TransformerLM
+from nkipy_b200.models.weights import random_weights
+
+
+def _build(device, k):
+    cfg = C.tiny(num_heads=4, num_kv_heads=2, num_layers=4)
+    w = random_weights(cfg, 0, 1, seed=5, std=0.05)
+    target = TransformerLM(cfg, w, device=device)
+    ecfg = EagleConfig(hidden_size=cfg.hidden_size, target_hidden_size=cfg.hidden_size, num_heads=4, num_kv_heads=4,
+                       head_dim=64, intermediate_size=256, draft_vocab_size=cfg.vocab_size, vocab_size=cfg.vocab_size,
+                       num_draft_tokens=k, ptd_token_id=3)
+    drafter = DrafterLM(ecfg, random_drafter_weights(ecfg, seed=9, std=0.05), device)
+    return cfg, w, target, drafter
+
+
+def _run(device, k=3, new_tokens=12):
+    cfg, w, target, drafter = _build(device, k)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (19, 33, 26)]
+    spec = SpeculativeEngine(target, drafter, max_batch=4, max_seq_len=96)
+    out = spec.generate(prompts, new_tokens)
+    eng = GenerationEngine(target, max_batch=4, max_seq_len=96, use_cuda_graph=False)
+    ref = eng.generate(prompts, new_tokens)
+    return cfg, w, prompts, out, ref, spec.stats
+
+
+def _check_against_oracle(cfg, w, prompts, out):
+    from nkipy_b200.models.reference import EagerTransformer
+
+    oracle = EagerTransformer(cfg, w, dtype=torch.float32)
+    for b, p in enumerate(prompts):
+        seq = list(p)
+        for tok in out[b]:
+            oracle.reset()
+            h = oracle.forward(torch.tensor([seq]))[:, -1]
+            logits = (h @ oracle.w["lm_head_weight"]).float()[0]
+            assert logits[tok] >= logits.max() - 0.05 * logits.std(), (b, tok)
+            seq.append(tok)
+
+
+def test_tap_layers():
+    assert tap_layers(24) == (1, 11, 20)
+    assert tap_layers(4) == (1, 1, 0)
+
+
+@pytest.mark.parametrize("k", [1, 3])
+def test_speculative_matches_plain_decoding_cpu(k):
+    cfg, w, prompts, out, ref, stats = _run("cpu", k)
+    assert all(len(o) == 12 for o in out)
+    assert out == ref
+    assert stats.mean_acceptance >= 1.0
+
+
+@pytest.mark.gpu
+def test_speculative_on_gpu_is_lossless():
+    cfg, w, prompts, out, ref, stats = _run("cuda", 3)
+    assert all(len(o) == 12 for o in out)
+    # (K + 1)-row verify and 1-row decode round differently in bf16: every token must be (near-)best
+    # under the fp32 oracle, and almost all tokens must agree with plain decoding
+    _check_against_oracle(cfg, w, prompts, out)
+    agree = sum(a == b for o, r in zip(out, ref) for a, b in zip(o, r))
+    assert agree >= 0.8 * sum(len(o) for o in out)
+    from nkipy_b200 import ops
+    assert ops.device_status() == 0
+
+
+def test_perfect_drafter_accepts_everything_cpu():
+    """A drafter that always proposes what the target would say is accepted K times per step."""
+    cfg, w, target, drafter = _build("cpu", 3)
+    spec = SpeculativeEngine(target, drafter, max_batch=2, max_seq_len=96)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (21,), generator=g).tolist()]
+    eng = GenerationEngine(target, max_batch=2, max_seq_len=96, use_cuda_graph=False)
+    ref = eng.generate(prompts, 13)[0]
+    full = prompts[0] + ref
+
+    class Oracle:
+        """Stands in for the drafter: reads the known continuation."""
+        ecfg = drafter.ecfg
+        d2t = drafter.d2t
+        lm = drafter.lm
+
+        def new_cache(self, like):
+            return drafter.new_cache(like)
+
+        def prefill(self, *a, **k):
+            return None
+
+        def step(self, token_ids, hidden3, is_mask, positions, slots, cache, block_table, context_lens, q_len):
+            # row at position p must predict token p + 2 of the sequence (its input is token p + 1)
+            V = cfg.vocab_size
+            logits = torch.zeros((positions.numel(), V))
+            for i, p in enumerate(positions.tolist()):
+                t = full[p + 2] if p + 2 < len(full) else 0
+                logits[i, t] = 1.0
+            return logits.to(torch.bfloat16)
+
+    spec.drafter = Oracle()
+    out = spec.generate(prompts, 13)[0]
+    assert out == ref
+    assert spec.stats.mean_acceptance > 3.0
