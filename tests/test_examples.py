@@ -1,0 +1,69 @@
+"""The example scripts run end to end (CPU here; the GPU variants are marked)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script, *args, timeout=600):
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, script), *args], capture_output=True, text=True,
+                         timeout=timeout, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    return res.stdout
+
+
+def test_deltanet_cpu():
+    assert "max |err|" in _run("examples/linear_attention/deltanet.py", "--cpu", "--L", "16")
+
+
+def test_playground_cpu_paths():
+    env_has_gpu = torch.cuda.is_available()
+    out = _run("examples/playground/simple_cuda_kernel.py")
+    assert ("gpu" if env_has_gpu else "cpu reference") in out
+
+
+def test_qwen3_example_cpu():
+    out = _run("examples/models/qwen3/qwen3.py", "--layers", "1", "--batch", "2", "--prompt-len", "12", "-n", "3",
+               "--max-seq-len", "96")
+    assert "Decode tokens/sec" in out
+
+
+def test_embedding_example_cpu():
+    out = _run("examples/models/qwen3_embedding/example_retrieval.py", "--layers", "1", "--device", "cpu")
+    cos = float(out.strip().splitlines()[-1].split()[-1])
+    assert cos > 0.999
+
+
+def test_speculate_example_cpu():
+    out = _run("examples/models/gpt_oss/peagle/speculate.py", "--layers", "1", "--batch", "1", "--prompt-len", "12",
+               "-n", "4", "-k", "2")
+    assert "Token agreement with plain decoding: 1.000" in out
+
+
+@pytest.mark.gpu
+def test_deltanet_and_playground_gpu():
+    assert "on gpu" in _run("examples/linear_attention/deltanet.py", "--L", "16")
+    assert "baremetal_jit" in _run("examples/playground/simple_nkipy_kernel.py")
+    assert "on gpu" in _run("examples/playground/simple_cuda_kernel.py")
+
+
+@pytest.mark.gpu
+def test_embedding_matches_eager_gpu():
+    out = _run("examples/models/qwen3_embedding/example_retrieval.py", "--layers", "4")
+    cos = float(out.strip().splitlines()[-1].split()[-1])
+    assert cos > 0.99
+
+
+@pytest.mark.gpu
+def test_gpt_oss_and_speculate_gpu():
+    out = _run("examples/models/gpt_oss/gpt_oss.py", "--layers", "2", "--batch", "2", "--prompt-len", "64", "-n", "8")
+    assert "Decode tokens/sec" in out
+    out = _run("examples/models/gpt_oss/peagle/speculate.py", "--layers", "2", "--batch", "2", "--prompt-len", "48",
+               "-n", "8", "-k", "3")
+    agree = float(out.strip().splitlines()[-1].split()[-1])
+    assert agree >= 0.75
