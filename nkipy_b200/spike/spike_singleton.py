@@ -22,8 +22,18 @@ _device_ordinal = -1
 
 
 def _native():
+    """The C++ runtime module; rebuilt first when its sources (or the argument-block header it shares
+    with the kernels) changed since the in-tree binary was made and a compiler is available."""
     import importlib
+    import shutil
 
+    if "nkipy_b200.spike._spike" not in __import__("sys").modules and shutil.which("g++"):
+        try:
+            from ..runtime.native import build
+
+            build()            # no-op when the stamp matches
+        except Exception:      # fall back to the binary that is there
+            pass
     try:
         return importlib.import_module("nkipy_b200.spike._spike")
     except ImportError:

@@ -10,8 +10,12 @@ from nkipy_b200.models.transformer import TransformerLM
 from nkipy_b200.models.weights import random_weights
 
 
-def _build(device, k):
-    cfg = C.tiny(num_heads=4, num_kv_heads=2, num_layers=4)
+def _build(device, k, kind="llama"):
+    if kind == "gpt_oss":      # sinks, sliding window, biases; 8 query heads per kv head -> wide verify windows
+        cfg = C.tiny(num_heads=8, num_kv_heads=1, head_dim=64, num_layers=4, attn_bias=True, attention_sinks=True,
+                     sliding_window=16)
+    else:
+        cfg = C.tiny(num_heads=4, num_kv_heads=2, num_layers=4)
     w = random_weights(cfg, 0, 1, seed=5, std=0.05)
     target = TransformerLM(cfg, w, device=device)
     ecfg = EagleConfig(hidden_size=cfg.hidden_size, target_hidden_size=cfg.hidden_size, num_heads=4, num_kv_heads=4,
@@ -21,8 +25,8 @@ def _build(device, k):
     return cfg, w, target, drafter
 
 
-def _run(device, k=3, new_tokens=12):
-    cfg, w, target, drafter = _build(device, k)
+def _run(device, k=3, new_tokens=12, kind="llama"):
+    cfg, w, target, drafter = _build(device, k, kind)
     g = torch.Generator().manual_seed(2)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (19, 33, 26)]
     spec = SpeculativeEngine(target, drafter, max_batch=4, max_seq_len=96)
@@ -51,17 +55,23 @@ def test_tap_layers():
     assert tap_layers(4) == (1, 1, 0)
 
 
-@pytest.mark.parametrize("k", [1, 3])
-def test_speculative_matches_plain_decoding_cpu(k):
-    cfg, w, prompts, out, ref, stats = _run("cpu", k)
+@pytest.mark.parametrize("k,kind", [(1, "llama"), (3, "llama"), (3, "gpt_oss")])
+def test_speculative_matches_plain_decoding_cpu(k, kind):
+    cfg, w, prompts, out, ref, stats = _run("cpu", k, kind=kind)
     assert all(len(o) == 12 for o in out)
-    assert out == ref
+    if kind == "llama":
+        assert out == ref
+    else:
+        # bf16 rounding of a 4-row and a 1-row pass can differ: near-tied logits may flip, after which the
+        # two runs legitimately diverge.  Every token must still be (near-)best under the fp32 oracle.
+        _check_against_oracle(cfg, w, prompts, out)
     assert stats.mean_acceptance >= 1.0
 
 
 @pytest.mark.gpu
-def test_speculative_on_gpu_is_lossless():
-    cfg, w, prompts, out, ref, stats = _run("cuda", 3)
+@pytest.mark.parametrize("kind", ["llama", "gpt_oss"])
+def test_speculative_on_gpu_is_lossless(kind):
+    cfg, w, prompts, out, ref, stats = _run("cuda", 3, kind=kind)
     assert all(len(o) == 12 for o in out)
     # (K + 1)-row verify and 1-row decode round differently in bf16: every token must be (near-)best
     # under the fp32 oracle, and almost all tokens must agree with plain decoding
