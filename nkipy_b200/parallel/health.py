@@ -1,0 +1,256 @@
+"""Failure detection for the multi-GPU runtime: device wait time-outs, a host watchdog, rank heartbeats,
+host-side fault injection and a thread model of the arrival-counter protocol.
+
+The reference has no failure handling: a hung collective simply hangs, and errors of the runtime surface
+as typed exceptions with the runtime's status code (spike/src/error.h:24-43, nrt_wrapper.cpp:12-43).
+Here every device-side wait is bounded (one second) and reports through a status word; this module turns
+that word into exceptions, adds a per-step host deadline and rank liveness, and lets tests provoke the
+failure paths from the host only (a rank that sleeps, skips its signal or leaves between steps) — nothing
+here makes a GPU fault, trap or spin without bound.
+
+Recovery is a restart of the communication layer, not of the GPU: close the symmetric buffers
+(`FusedTP.close`), re-create the process group without the dead rank, reload that rank's weight shards,
+rebuild `FusedTP`; KV caches are lost and requests are re-prefilled.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import os
+import threading
+import time
+from typing import Callable, Dict, List, Optional
+
+ERR_NAMES = {1: "producer waited for a free shared-memory stage", 2: "MMA warp waited for TMA data",
+             3: "MMA warp waited for the epilogue", 4: "epilogue waited for the MMA",
+             5: "a peer / producer flag never arrived", 6: "bad argument", 7: "softmax hand-off"}
+
+
+class CommTimeoutError(RuntimeError):
+    """A bounded device-side wait expired; `code` / `detail` decode the status word."""
+
+    def __init__(self, status: int):
+        self.status = status
+        self.code = status & 0xFF
+        self.detail = status >> 8
+        super().__init__(f"device wait timed out: {ERR_NAMES.get(self.code, 'unknown')} "
+                         f"(code {self.code}, detail 0x{self.detail:x})")
+
+
+def check_device_status(reset: bool = True) -> None:
+    """Raise `CommTimeoutError` if a kernel of the library recorded an expired wait."""
+    from .. import ops
+
+    st = ops.device_status(reset=reset) if _accepts_reset(ops.device_status) else ops.device_status()
+    if st:
+        raise CommTimeoutError(st)
+
+
+def _accepts_reset(fn) -> bool:
+    import inspect
+
+    try:
+        return "reset" in inspect.signature(fn).parameters
+    except (TypeError, ValueError):
+        return False
+
+
+# ----------------------------------------------------------------------------- watchdog
+class Watchdog:
+    """Host thread that fires `on_timeout(step_name, elapsed)` when a guarded step overruns its deadline.
+
+        wd = Watchdog(on_timeout=lambda name, t: log.error(...))
+        with wd.step("decode", deadline_s=2.0):
+            engine.step()
+    """
+
+    def __init__(self, on_timeout: Optional[Callable[[str, float], None]] = None, poll_s: float = 0.02):
+        self.on_timeout = on_timeout
+        self.poll_s = poll_s
+        self.timeouts: List[str] = []
+        self._lock = threading.Lock()
+        self._active: Optional[tuple] = None      # (name, start, deadline, fired)
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        while not self._stop.wait(self.poll_s):
+            with self._lock:
+                a = self._active
+                if a and not a[3] and time.monotonic() - a[1] > a[2]:
+                    self._active = (a[0], a[1], a[2], True)
+                    self.timeouts.append(a[0])
+                    cb, name, el = self.on_timeout, a[0], time.monotonic() - a[1]
+                else:
+                    cb = None
+            if cb:
+                cb(name, el)
+
+    class _Step:
+        def __init__(self, wd, name, deadline_s):
+            self.wd, self.name, self.deadline_s = wd, name, deadline_s
+
+        def __enter__(self):
+            with self.wd._lock:
+                self.wd._active = (self.name, time.monotonic(), self.deadline_s, False)
+            return self
+
+        def __exit__(self, *exc):
+            with self.wd._lock:
+                self.wd._active = None
+            return False
+
+    def step(self, name: str, deadline_s: float) -> "_Step":
+        return Watchdog._Step(self, name, deadline_s)
+
+    def close(self):
+        self._stop.set()
+        self._thread.join(timeout=1.0)
+
+
+# ----------------------------------------------------------------------------- heartbeat
+class Heartbeat:
+    """Rank liveness through a key-value store (a `torch.distributed.TCPStore` or anything with
+    `set(key, value)` / `get(key)`): every rank publishes a timestamp from a thread; `dead_ranks`
+    lists the ranks whose last beat is older than `timeout_s`."""
+
+    def __init__(self, store, rank: int, world_size: int, interval_s: float = 0.1):
+        self.store, self.rank, self.world_size, self.interval_s = store, rank, world_size, interval_s
+        self._stop = threading.Event()
+        self._beat()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _beat(self):
+        self.store.set(f"hb/{self.rank}", repr(time.time()))
+
+    def _run(self):
+        while not self._stop.wait(self.interval_s):
+            try:
+                self._beat()
+            except Exception:
+                return
+
+    def last_seen(self, rank: int) -> Optional[float]:
+        try:
+            v = self.store.get(f"hb/{rank}")
+        except Exception:
+            return None
+        return float(v.decode() if isinstance(v, (bytes, bytearray)) else v)
+
+    def dead_ranks(self, timeout_s: float = 1.0) -> List[int]:
+        now = time.time()
+        dead = []
+        for r in range(self.world_size):
+            if r == self.rank:
+                continue
+            t = self.last_seen(r)
+            if t is None or now - t > timeout_s:
+                dead.append(r)
+        return dead
+
+    def stop(self):
+        """Stop beating (what a leaving rank does between steps)."""
+        self._stop.set()
+        self._thread.join(timeout=1.0)
+
+
+# ----------------------------------------------------------------------------- fault injection (host only)
+class InjectedRankExit(SystemExit):
+    """Raised on the rank chosen by a `kill_rank` fault, between steps (no kernel in flight)."""
+
+
+@dataclasses.dataclass
+class FaultPlan:
+    """Parsed `B200_FAULT` specification: ``drop_flag:<rank>:<step>``, ``delay_ms:<rank>:<ms>[:<step>]`` or
+    ``kill_rank:<rank>:<step>``; several faults separated by commas."""
+    drop_flag: Dict[int, int] = dataclasses.field(default_factory=dict)     # rank -> step
+    delay_ms: Dict[int, tuple] = dataclasses.field(default_factory=dict)    # rank -> (ms, step or None)
+    kill_rank: Dict[int, int] = dataclasses.field(default_factory=dict)     # rank -> step
+
+    @classmethod
+    def from_env(cls, value: Optional[str] = None) -> "FaultPlan":
+        spec = os.environ.get("B200_FAULT", "") if value is None else value
+        plan = cls()
+        for item in filter(None, (s.strip() for s in spec.split(","))):
+            parts = item.split(":")
+            kind = parts[0]
+            if kind == "drop_flag" and len(parts) == 3:
+                plan.drop_flag[int(parts[1])] = int(parts[2])
+            elif kind == "delay_ms" and len(parts) in (3, 4):
+                plan.delay_ms[int(parts[1])] = (int(parts[2]), int(parts[3]) if len(parts) == 4 else None)
+            elif kind == "kill_rank" and len(parts) == 3:
+                plan.kill_rank[int(parts[1])] = int(parts[2])
+            else:
+                raise ValueError(f"bad B200_FAULT item '{item}'")
+        return plan
+
+    def before_step(self, rank: int, step: int) -> None:
+        """Call between steps (nothing of this rank in flight): sleeps or leaves as planned."""
+        if rank in self.delay_ms:
+            ms, at = self.delay_ms[rank]
+            if at is None or at == step:
+                time.sleep(ms / 1e3)
+        if self.kill_rank.get(rank) == step:
+            raise InjectedRankExit(f"rank {rank} leaves before step {step} (injected)")
+
+    def drops_signal(self, rank: int, step: int) -> bool:
+        """True when `rank` must skip signalling its peers in `step` (they then run into their bounded wait)."""
+        return self.drop_flag.get(rank) == step
+
+
+# ----------------------------------------------------------------------------- protocol model (CPU threads)
+class CounterProtocolSim:
+    """Thread model of the push / arrival-counter protocol of `FusedTP`: `n` ranks, two alternating buffers,
+    counters that only grow.  `run(ops, drop=(rank, op))` executes `ops` fused operations on `n` threads and
+    returns per-rank results (sums seen) or the string "timeout" for a rank whose wait expired.  It checks
+    the invariant the kernels rely on: a buffer is never overwritten while a peer still reads it."""
+
+    def __init__(self, n: int, wait_limit_s: float = 0.2):
+        self.n, self.wait_limit_s = n, wait_limit_s
+        self.lock = threading.Lock()
+        self.flags = [[[0] * n for _ in range(2)] for _ in range(n)]          # [dest][buffer][src]
+        self.slots = [[[None] * n for _ in range(2)] for _ in range(n)]       # [dest][buffer][src] -> (op, value)
+        self.reading = [[-1, -1] for _ in range(n)]                           # op a rank is reading, per buffer
+        self.violations: List[str] = []
+
+    def _rank(self, r: int, ops: int, drop, out: list):
+        seen = [0, 0]
+        for op in range(ops):
+            b = op & 1
+            for d in range(self.n):                                           # push partial + signal
+                with self.lock:
+                    if self.reading[d][b] not in (-1, op):
+                        self.violations.append(f"rank {r} overwrote buffer {b} of rank {d} during op "
+                                               f"{self.reading[d][b]}")
+                    self.slots[d][b][r] = (op, r + 1 + op)
+                    if drop != (r, op):
+                        self.flags[d][b][r] += 1
+            t0 = time.monotonic()                                             # bounded wait for all sources
+            while True:
+                with self.lock:
+                    ready = all(self.flags[r][b][s] >= seen[b] + 1 for s in range(self.n))
+                    if ready:
+                        self.reading[r][b] = op
+                        break
+                if time.monotonic() - t0 > self.wait_limit_s:
+                    out[r] = "timeout"
+                    return
+                time.sleep(0.0005)
+            with self.lock:
+                vals = [self.slots[r][b][s] for s in range(self.n)]
+                self.reading[r][b] = -1
+            if any(v is None or v[0] != op for v in vals):
+                self.violations.append(f"rank {r} read a stale slot in op {op}")
+            out[r].append(sum(v[1] for v in vals))
+            seen[b] += 1
+
+    def run(self, ops: int, drop=None):
+        out: list = [[] for _ in range(self.n)]
+        threads = [threading.Thread(target=self._rank, args=(r, ops, drop, out)) for r in range(self.n)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        return out
