@@ -880,7 +880,8 @@ class Generator:
             self._simple("conv", n, params, lines, o.size)
 
     def _collective(self, n):
-        raise CodegenError(f"collective '{n.opcode}' runs through the distributed runtime, not a generated kernel")
+        raise CodegenError(f"collective '{n.opcode}' cannot be part of one generated module: compile the kernel with "
+                           "nkipy_b200.runtime.segmented.SegmentedKernel, which cuts the graph at its collectives")
 
     lower_all_gather = lower_all_reduce = lower_reduce_scatter = lower_all_to_all = _collective
 
