@@ -96,3 +96,5 @@ def cuda_custom_op(name: str, source: str, entry: str, output_specs: Sequence[Tu
 nki_custom_op = cuda_custom_op
 NKICustomOp = CudaCustomOp
 wrap_nki_kernel = cuda_custom_op
+NKICustomOpHandle = CudaCustomOp     # what a wrapped kernel call returns in the reference is the op object itself here
+NKIOp = CudaCustomOp
