@@ -53,6 +53,8 @@ int nkb_gemm_bf16(const void* A, const void* B, void* out, int rows, int cols, i
                   int gate_off, const void* bias, int bias_on_rows, const void* residual, int block_n, int max_ctas,
                   int weights_operand, int ctas_per_sm, void* stream);
 int nkb_gemm_effective_splits(int k, int splits);
+int nkb_gemm_bf16_2cta(const void* A, const void* B, void* out, int m, int n, int k, long long lda, long long ldb,
+                       long long ldo, const void* bias, const void* residual, int gated, int gate_off, void* stream);
 int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tokens, int k, long long ldw,
                        long long ldx, long long ldo, int splits, const void* bias, int block_n, void* const* peer_out,
                        void* const* peer_flag, int n_peers, int rank, void* done_counter, void* stream);

@@ -47,7 +47,10 @@ def main():
     tp = TPGroup.from_env()
     cfg = get_config(args.model)
     target = build_model(cfg, args, tp)
+    cfg = target.cfg
     ecfg = peagle_config.get_eagle_config(cfg, args.num_draft_tokens)
+    if args.tiny:
+        ecfg.intermediate_size, ecfg.draft_vocab_size = 512, min(ecfg.draft_vocab_size, cfg.vocab_size)
     dw = (load_shard(args.draft_checkpoint, 0, device=tp.device) if args.draft_checkpoint
           else random_drafter_weights(ecfg, device=tp.device, seed=args.seed + 1))
     drafter = DrafterLM(ecfg, dw, tp.device)

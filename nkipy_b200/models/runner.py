@@ -30,6 +30,8 @@ def add_common_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--moe-parallel", choices=["ep", "tp"], default="ep")
     ap.add_argument("--no-graph", action="store_true", help="do not capture the decode step in a CUDA graph")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--tiny", action="store_true",
+                    help="shrink the model (hidden 256, vocabulary 2048, <= 8 experts) for quick functional runs")
 
 
 def load_tokenizer(path: Optional[str]):
@@ -48,9 +50,27 @@ def build_prompts(args, cfg: ModelConfig, tokenizer) -> List[List[int]]:
     return torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist()
 
 
+def shrink(cfg: ModelConfig) -> ModelConfig:
+    """Same architecture features, toy sizes."""
+    over = dict(vocab_size=2048, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=512,
+                max_position=min(cfg.max_position, 4096))
+    if cfg.is_moe:
+        over.update(num_experts=min(cfg.num_experts, 8), top_k=min(cfg.top_k, 2), moe_intermediate_size=128,
+                    intermediate_size=0)
+    if cfg.layer_types is not None:
+        over["layer_types"] = cfg.layer_types[: max(cfg.num_layers, 1)]
+    if cfg.sliding_window:
+        over["sliding_window"] = min(cfg.sliding_window, 16)
+    return cfg.scaled(**over)
+
+
 def build_model(cfg: ModelConfig, args, tp: TPGroup) -> TransformerLM:
     if args.layers:
         cfg.num_layers = args.layers
+        if cfg.layer_types is not None:
+            cfg.layer_types = cfg.layer_types[: args.layers]
+    if getattr(args, "tiny", False):
+        cfg = shrink(cfg)
     if args.checkpoint:
         weights = load_shard(args.checkpoint, tp.rank, device=tp.device)
     else:

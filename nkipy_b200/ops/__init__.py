@@ -16,6 +16,8 @@ is transposed once at load time.
 
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Optional, Tuple
 
@@ -70,6 +72,9 @@ def _check_bf16(*tensors):
 
 
 # --------------------------------------------------------------------------- GEMM
+_USE_2CTA = os.environ.get("NKIPY_B200_GEMM_2CTA", "1") == "1"
+
+
 def _pick_block_n(cols: int, gated: bool) -> int:
     cap = 128 if gated else 256
     for bn in (32, 64, 128, 256):
@@ -151,6 +156,15 @@ def linear(
         out_view = out
         out_fp32, split_stride = 0, 0
     ldo = out_view.stride(-2) if out_view.dim() >= 2 else N
+    if (not swap and splits <= 1 and M >= 512 and N >= 256 and _USE_2CTA and (ldo & 7) == 0
+            and not (gated and (bias is not None or residual is not None))):
+        # prefill-sized: CTA pairs on 256 x 256 tiles (csrc/kernels/gemm_2cta.cu)
+        rc = L.nkb_gemm_bf16_2cta(x.data_ptr(), w.data_ptr(), out_view.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+                                  ldo, _ptr(bias), _ptr(residual), 1 if gated else 0, N if gated else 0, _stream())
+        if rc != -5:
+            _lib.check(rc, "nkb_gemm_bf16_2cta")
+            _launches += 1
+            return out_view
     if swap:
         a, b, rows, cols = w, x, N, M
         lda, ldb = w.stride(0), x.stride(0)

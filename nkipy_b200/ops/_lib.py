@@ -28,6 +28,8 @@ _SIGNATURES = {
         [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int, c_longlong,
          c_int, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     ),
+    "nkb_gemm_bf16_2cta": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, _P, _P, c_int,
+                                   c_int, _P]),
     "nkb_gemm_bf16_grouped": (
         c_int,
         [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, _P, c_longlong,

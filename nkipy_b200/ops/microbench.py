@@ -107,6 +107,40 @@ def case_gemm_prefill(args):
                 shape=dict(M=M, K=K, N=N))
 
 
+def case_gemm_prefill_gated(args):
+    M, K, I = 8192, 4096, 14336
+    x = _bf16(M, K)
+    ws = [_bf16(2 * I, K, scale=0.02) for _ in range(2)]
+    fns = [lambda w=w: linear(x, w, gated=True, swap=False) for w in ws]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    return dict(case="gemm-prefill-gated", us=us, bytes=(M * K + 2 * I * K + M * I) * 2, flops=4.0 * M * I * K,
+                shape=dict(M=M, K=K, I=I, note="gate/up GEMM with the SwiGLU epilogue on CTA pairs"))
+
+
+def case_gemm_comm(mode, args):
+    """The fused GEMM + collective kernels with a single rank: same tcgen05 pipeline, staging / pusher paths
+    included, no NVLink traffic (multi-GPU numbers come from bench_fused.py)."""
+    from ..parallel.comm import TPGroup
+    from ..parallel.symm import AllGatherGemm, GemmReduceScatter
+
+    tp = TPGroup.single(torch.device("cuda"))
+    if mode == "rs":
+        M, K, N = 8192, 4096, 8192
+        op = GemmReduceScatter(tp, M, N)
+    else:
+        M, K, N = 8192 + 64, 8192, 3584          # rows per rank not a multiple of 128: the pusher CTA runs
+        op = AllGatherGemm(tp, M, K)
+    x = _bf16(M, K)
+    ws = [_bf16(N, K, scale=0.02) for _ in range(2)]
+    fns = [lambda w=w: op(x, w) for w in ws]
+    us = _time(fns, args.iters, args.warmup, False)
+    r = dict(case=f"gemm-{mode}-tp1" if mode == "rs" else "ag-gemm-tp1", us=us, bytes=(M * K + N * K + M * N) * 2,
+             flops=2.0 * M * N * K, shape=dict(M=M, K=K, N=N, ranks=1))
+    torch.cuda.synchronize()
+    op.close()
+    return r
+
+
 def case_attn_decode(args):
     B, ctx, nkv, nq, D = 64, 1056, 8, 32, 128
     pages = (ctx + 31) // 32
@@ -179,6 +213,9 @@ CASES = {
     "gemm-decode-down": lambda a: case_gemm_decode("gemm-decode-down", 4096, 14336, 64, 8, False, a),
     "gemm-decode-lmhead": lambda a: case_gemm_decode("gemm-decode-lmhead", 128256, 4096, 64, 1, False, a),
     "gemm-prefill": case_gemm_prefill,
+    "gemm-prefill-gated": case_gemm_prefill_gated,
+    "gemm-rs-tp1": lambda a: case_gemm_comm("rs", a),
+    "ag-gemm-tp1": lambda a: case_gemm_comm("ag", a),
     "attn-decode": case_attn_decode,
     "attn-prefill": case_attn_prefill,
     "moe-decode-layer": case_moe,

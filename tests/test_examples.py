@@ -28,8 +28,8 @@ def test_playground_cpu_paths():
 
 
 def test_qwen3_example_cpu():
-    out = _run("examples/models/qwen3/qwen3.py", "--layers", "1", "--batch", "2", "--prompt-len", "12", "-n", "3",
-               "--max-seq-len", "96")
+    out = _run("examples/models/qwen3/qwen3.py", "--tiny", "--layers", "2", "--batch", "2", "--prompt-len", "12", "-n",
+               "3", "--max-seq-len", "96")
     assert "Decode tokens/sec" in out
 
 
@@ -40,8 +40,8 @@ def test_embedding_example_cpu():
 
 
 def test_speculate_example_cpu():
-    out = _run("examples/models/gpt_oss/peagle/speculate.py", "--layers", "1", "--batch", "1", "--prompt-len", "12",
-               "-n", "4", "-k", "2")
+    out = _run("examples/models/gpt_oss/peagle/speculate.py", "--tiny", "--layers", "2", "--batch", "1",
+               "--prompt-len", "12", "-n", "4", "-k", "2")
     assert "Token agreement with plain decoding: 1.000" in out
 
 

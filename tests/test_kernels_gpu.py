@@ -320,3 +320,44 @@ def test_moe_dispatch_grouped_gemm_combine(T, E, k, H, I, lo, nl):
     hc = ops.grouped_linear(xs, w_gu, off, max_rows_per_group=T, gated=True, act_limit=7.0, act_alpha=1.702)
     hc_ref = ops.grouped_linear(xs.cpu(), w_gu.cpu(), off.cpu(), max_rows_per_group=T, gated=True, act_limit=7.0)
     assert rel_err(hc[:n_local].cpu(), hc_ref[:n_local]) < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K,bias,resid", [(512, 256, 64, False, False), (1024, 768, 512, True, True),
+                                              (640, 392, 192, True, False), (2048, 1024, 1024, False, True)])
+def test_linear_cta_pair_kernel(M, N, K, bias, resid):
+    """Prefill-sized GEMMs take the cta_group::2 kernel (256 x 256 tiles on CTA pairs); ragged edges included."""
+    import nkipy_b200.ops as O
+
+    assert O._USE_2CTA
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(M + N)
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, device=dev, generator=g).to(torch.bfloat16) if bias else None
+    r = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16) if resid else None
+    y = O.linear(x, w, bias=b, residual=r, swap=False)
+    assert O._lib.lib().nkb_gemm_2cta_pairs() > 0          # the pair kernel really ran
+    ref = x.float() @ w.float().T
+    if b is not None:
+        ref += b.float()
+    if r is not None:
+        ref += r.float()
+    rel = ((y.float() - ref).norm() / ref.norm()).item()
+    assert rel < 5e-3, rel
+    assert O.device_status() == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(512, 256, 128), (1024, 1408, 512), (640, 392, 192)])
+def test_linear_cta_pair_kernel_gated(M, I, K):
+    """SwiGLU on CTA pairs: the first CTA of a pair loads gate rows, the second up rows."""
+    import nkipy_b200.ops as O
+
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(M + I)
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    y = O.linear(x, w, gated=True, swap=False)
+    ref = torch.nn.functional.silu(x.float() @ w[:I].float().T) * (x.float() @ w[I:].float().T)
+    rel = ((y.float() - ref).norm() / ref.norm()).item()
+    assert y.shape == (M, I) and rel < 1e-2, rel
+    assert O.device_status() == 0
