@@ -32,6 +32,7 @@
 // counterpart for token counts where reduce-scatter / all-gather (sequence-parallel layout) pay off.
 #include "gemm_tcgen05.cuh"
 #include "api.h"
+#include <stdlib.h>
 
 namespace nkb {
 
@@ -96,8 +97,12 @@ constexpr int kCommThreads = kGemmThreads + 32;
 constexpr int kCommCtrlBytes = 1024;
 constexpr int kStageOutBytes = 4 * 32 * 128 * 2;   // per epilogue warp: 32 rows x 128 columns bf16
 
-// MODE 0 = gemm_rs, 1 = ag_gemm
-template <int BN, int MODE>
+// MODE 0 = gemm_rs, 1 = ag_gemm.  PAIR: two CTAs of a cluster share one 256 x BN tile through
+// `tcgen05.mma.cta_group::2` (CTA r of the pair holds rows 128 r .. 128 r + 127 of the A tile and of the
+// B tile); everything below that is keyed on 128-row tiles (owners, counters, staging, chunk waits) then
+// simply applies to this CTA's half.  The first CTA of a pair issues the MMAs and owns the `full` and
+// `tempty` barriers; see gemm_2cta.cu for the barrier scheme.
+template <int BN, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kCommThreads, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                  const __grid_constant__ CUtensorMap tmB, const CommArgs args, const CommPeers peers) {
@@ -194,8 +199,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     return;
   }
 
-  constexpr int kBTileBytes = BN * kBlockK * 2;
+  constexpr int kBTileBytes = (PAIR ? BN / 2 : BN) * kBlockK * 2;      // this CTA's rows of the B tile
   constexpr int stage_bytes = kATileBytes + kBTileBytes;
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;                // 0 issues the MMAs
   const int stages = args.stages;
   GemmCtrl* ctrl = &sh->ctrl;
   constexpr uint32_t tmem_cols = 2 * BN;                                  // 256 or 512
@@ -210,7 +216,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctrl->tfull[i], 1);
-      mbar_init(&ctrl->tempty[i], 4);
+      mbar_init(&ctrl->tempty[i], PAIR ? 8 : 4);
       mbar_init(&sh->pub_full[i], 4);
       mbar_init(&sh->pub_empty[i], 1);
     }
@@ -219,18 +225,36 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     fence_proxy_async();
   }
   if (warp == 1) {
-    tmem_alloc(&ctrl->tmem_base, tmem_cols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(&ctrl->tmem_base, tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&ctrl->tmem_base, tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();          // both CTAs' barriers exist before anything remote arrives
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
   volatile int* abort_flag = &ctrl->abort;
 
-  const int cta = int(blockIdx.x) - (MODE == 1 ? args.comm_ctas : 0);
-  const int ncta = int(gridDim.x) - (MODE == 1 ? args.comm_ctas : 0);
-  const int total_work = args.num_row_tiles * args.num_col_tiles;
+  // work items: (row tile or pair of row tiles in rotated order) x column tile
+  const int units = PAIR ? 2 : 1;
+  const int cta = (int(blockIdx.x) - (MODE == 1 ? args.comm_ctas : 0)) / units;
+  const int ncta = (int(gridDim.x) - (MODE == 1 ? args.comm_ctas : 0)) / units;
+  const int row_groups = PAIR ? (args.num_row_tiles + 1) / 2 : args.num_row_tiles;
+  const int total_work = row_groups * args.num_col_tiles;
+  // this CTA's 128-row tile and the column tile of work item w (the row tile may lie past the last row
+  // for the second CTA of the last pair: it then loads zeros and skips its epilogue)
+  auto decode = [&](int w, int& rt, int& ct) {
+    const int ro = w / args.num_col_tiles;
+    ct = w - ro * args.num_col_tiles;
+    int g = args.first_tile + ro;
+    if (g >= row_groups) g -= row_groups;
+    rt = PAIR ? 2 * g + int(crank) : g;
+  };
   griddep_launch();
 
   if (warp == 0) {
@@ -240,17 +264,16 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t phase = 0;
     bool alive = true;
     for (int w = cta; w < total_work && alive; w += ncta) {
-      const int ro = w / args.num_col_tiles, ct = w - ro * args.num_col_tiles;
-      int rt = args.first_tile + ro;
-      if (rt >= args.num_row_tiles) rt -= args.num_row_tiles;
+      int rt, ct;
+      decode(w, rt, ct);
       const int r0 = rt * kTileRows, r1 = min(args.m, r0 + kTileRows);
       bool from_local = false;
       int a_row = r0;
       if (MODE == 1) {
         // rows [r0, r1) of the gathered activations: wait for the chunks that hold them
         const int rpr = args.rows_per_rank;
-        const int s0 = r0 / rpr, s1 = (r1 - 1) / rpr;
-        if (args.local_direct && s0 == args.rank) {
+        const int s0 = r0 / rpr, s1 = r1 > r0 ? (r1 - 1) / rpr : s0 - 1;
+        if (args.local_direct && s0 == args.rank && r1 > r0) {
           from_local = true;
           a_row = r0 - args.rank * rpr;
         } else {
@@ -276,18 +299,26 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
         if (lane == 0) {
           uint8_t* a_ptr = tiles + stage * stage_bytes;
-          mbar_expect_tx(&ctrl->full[stage], stage_bytes);
-          if (MODE == 1 && !from_local) tma_load_2d(a_ptr, &tmA2, &ctrl->full[stage], kb * kBlockK, a_row);
-          else tma_load_2d(a_ptr, &tmA, &ctrl->full[stage], kb * kBlockK, a_row);
-          tma_load_2d(a_ptr + kATileBytes, &tmB, &ctrl->full[stage], kb * kBlockK, ct * BN);
+          const CUtensorMap* ma = (MODE == 1 && !from_local) ? &tmA2 : &tmA;
+          if (PAIR) {
+            // the first CTA announces the bytes of both; both CTAs' loads complete on its barrier
+            const uint32_t full0 = map_to_cta(&ctrl->full[stage], 0);
+            if (crank == 0) mbar_expect_tx(&ctrl->full[stage], 2 * stage_bytes);
+            tma_load_2d_pair(a_ptr, ma, full0, kb * kBlockK, a_row);
+            tma_load_2d_pair(a_ptr + kATileBytes, &tmB, full0, kb * kBlockK, ct * BN + int(crank) * (BN / 2));
+          } else {
+            mbar_expect_tx(&ctrl->full[stage], stage_bytes);
+            tma_load_2d(a_ptr, ma, &ctrl->full[stage], kb * kBlockK, a_row);
+            tma_load_2d(a_ptr + kATileBytes, &tmB, &ctrl->full[stage], kb * kBlockK, ct * BN);
+          }
         }
         __syncwarp();
         if (++stage == stages) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = make_idesc_bf16(kTileRows, BN, 0, 0);
+  } else if (warp == 1 && crank == 0) {
+    // ------------------------------------------------------------------ MMA issuer (first CTA of a pair)
+    constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 2 * kTileRows : kTileRows, BN, 0, 0);
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -307,19 +338,35 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint64_t da = make_smem_desc_sw128(a_addr, 0, 1024);
           const uint64_t db = make_smem_desc_sw128(a_addr + kATileBytes, 0, 1024);
 #pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k)
-            umma_f16(d0, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&ctrl->empty[stage]);
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            if (PAIR) umma_f16_pair(d0, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16(d0, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          if (PAIR) {
+            umma_commit_pair(map_to_cta(&ctrl->empty[stage], 0));
+            umma_commit_pair(map_to_cta(&ctrl->empty[stage], 1));
+          } else {
+            umma_commit(&ctrl->empty[stage]);
+          }
         }
         __syncwarp();
         if (++stage == stages) { stage = 0; phase ^= 1u; }
       }
       if (!alive) break;
-      if (lane == 0) umma_commit(&ctrl->tfull[acc]);
+      if (lane == 0) {
+        if (PAIR) {
+          umma_commit_pair(map_to_cta(&ctrl->tfull[acc], 0));
+          umma_commit_pair(map_to_cta(&ctrl->tfull[acc], 1));
+        } else {
+          umma_commit(&ctrl->tfull[acc]);
+        }
+      }
       __syncwarp();
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+  } else if (warp == 1) {
+    // second CTA of a pair: the MMAs of both CTAs are issued by the first
   } else if (warp == 6) {
     // ------------------------------------------------------------------ publisher (gemm_rs)
     // A system fence waits for every peer store this SM has in flight, which under a saturated link is
@@ -343,10 +390,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         npend = 0;
       };
       for (int w = cta; w < total_work && alive; w += ncta) {
-        const int ro = w / args.num_col_tiles;
-        int rt = args.first_tile + ro;
-        if (rt >= args.num_row_tiles) rt -= args.num_row_tiles;
+        int rt, ct_unused;
+        decode(w, rt, ct_unused);
         const int r0 = rt * kTileRows, r1 = min(args.m, r0 + kTileRows);
+        if (r0 >= args.m) continue;                // the second CTA of the last pair may have no rows
         const int phase_id = r0 / rpr;
         if (npend > 0 && phase_id != pend_phase) flush();
         if (!(r0 < own0 || r1 > own1)) continue;   // no peer rows in this tile
@@ -377,16 +424,30 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool alive = true;
+    // hands an accumulator back to the MMA warp (of the pair's first CTA)
+    auto release_acc = [&](int a) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(map_to_cta(&ctrl->tempty[a], 0));
+        else mbar_arrive(&ctrl->tempty[a]);
+      }
+    };
     for (int w = cta; w < total_work; w += ncta) {
-      const int ro = w / args.num_col_tiles, ct = w - ro * args.num_col_tiles;
-      int rt = args.first_tile + ro;
-      if (rt >= args.num_row_tiles) rt -= args.num_row_tiles;
+      int rt, ct;
+      decode(w, rt, ct);
       const int col0 = ct * BN;
       bool ok = mbar_wait(&ctrl->tfull[acc], acc_phase, abort_flag, args.status, ERR_WAIT_TMEM_FULL);
       // the four epilogue warps leave together: a warp left alone at the tile barrier below would hang
       if (!bar_red_and(2, 128, __all_sync(0xffffffffu, ok))) { alive = false; break; }
       tc_fence_after();
       const uint32_t t0 = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN);
+      if (rt * kTileRows >= args.m) {              // no rows in this CTA's half: nothing to write or publish
+        release_acc(acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        continue;
+      }
       if (MODE == 1) {
         // local output rows, 64 contiguous bytes per lane and chunk
         const int row = rt * kTileRows + quad * 32 + lane;
@@ -396,11 +457,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t v[32];
           tmem_ld_32x32(t0 + c, v);
           tmem_ld_wait();
-          if (c + 32 >= BN) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctrl->tempty[acc]);
-          }
+          if (c + 32 >= BN) release_acc(acc);
           const int cbase = col0 + c;
           if (row < args.m && cbase < args.n) {
             const long long base = (long long)row * args.ldo + cbase;
@@ -443,11 +500,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               uint32_t v[32];
               tmem_ld_32x32(t0 + half * 128 + c, v);
               tmem_ld_wait();
-              if (release && half * 128 + c + 32 >= BN) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&ctrl->tempty[acc]);
-              }
+              if (release && half * 128 + c + 32 >= BN) release_acc(acc);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const int chunk = (c >> 3) + q;   // 16-byte chunk index inside the 256-byte staged row
@@ -537,10 +590,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           pass(true, false, !warp_own);
           publish();
           if (wait_peers()) { if (warp_own) pass(false, true, true); }
-          else if (warp_own) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(&ctrl->tempty[acc]); }
+          else if (warp_own) release_acc(acc);
         } else if (tile_own) {
           if (wait_peers()) pass(false, true, true);
-          else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(&ctrl->tempty[acc]); }
+          else release_acc(acc);
         } else {
           pass(true, false, true);
           publish();
@@ -556,16 +609,18 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA frees shared / tensor memory while its peer still works
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, tmem_cols);
+    else tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool PAIR>
 static int launch_comm(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb, CommArgs& args,
                        const CommPeers& peers, cudaStream_t stream) {
-  constexpr int stage_bytes = kATileBytes + BN * kBlockK * 2;
+  constexpr int stage_bytes = kATileBytes + (PAIR ? BN / 2 : BN) * kBlockK * 2;
   const int extra = kCommCtrlBytes + (MODE == 0 ? kStageOutBytes : 0);
   int stages = (232448 - 1024 - extra) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -576,15 +631,47 @@ static int launch_comm(const CUtensorMap& ta, const CUtensorMap& ta2, const CUte
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e =
-        cudaFuncSetAttribute(gemm_comm_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        cudaFuncSetAttribute(gemm_comm_kernel<BN, MODE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     if (e != cudaSuccess) return int(e);
     attr_set = true;
   }
-  // every CTA must be resident at once: reducers and consumers wait on work of other CTAs' peers only,
-  // but the pushers of ag_gemm must run beside the consumers
-  const int grid = num_sms();
-  return launch_pdl(gemm_comm_kernel<BN, MODE>, dim3(grid), dim3(kCommThreads), size_t(smem), stream, ta, ta2, tb, args,
-                    peers);
+  // The work loops stride by the grid (or the number of pairs), so every CTA must be resident at once; the
+  // pushers of ag_gemm must run beside the consumers in any case.
+  if (!PAIR)
+    return launch_pdl(gemm_comm_kernel<BN, MODE, PAIR>, dim3(num_sms()), dim3(kCommThreads), size_t(smem), stream, ta,
+                      ta2, tb, args, peers);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (num_sms() / 2));
+  cfg.blockDim = dim3(kCommThreads);
+  cfg.dynamicSmemBytes = size_t(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  static int max_pairs = 0;      // pairs need two SMs of one GPC; not every SM can be paired
+  if (max_pairs == 0) {
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_comm_kernel<BN, MODE, PAIR>, &cfg);
+    max_pairs = (e == cudaSuccess && n > 0) ? n : num_sms() / 4;
+  }
+  cfg.gridDim = dim3(2 * max_pairs);
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return int(cudaLaunchKernelEx(&cfg, gemm_comm_kernel<BN, MODE, PAIR>, ta, ta2, tb, args, peers));
+}
+
+static bool comm_pair_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("NKIPY_B200_COMM_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 }  // namespace nkb
@@ -621,12 +708,19 @@ extern "C" int nkb_gemm_rs(const void* x, const void* w, void* out, int m, int n
     p.flags[i] = reinterpret_cast<unsigned int*>(peer_flags[i]);
   }
   const int bn = n >= 256 ? 256 : 128;
+  const bool pair = bn == 256 && m >= 256 && comm_pair_enabled();
   a.num_col_tiles = (n + bn - 1) / bn;
+  if (pair) {
+    // rotation in units of 256-row pairs: start with the pair after the one that holds this rank's last row
+    const int groups = (a.num_row_tiles + 1) / 2;
+    a.first_tile = ((((rank + 1) * rpr + 2 * kTileRows - 1) / (2 * kTileRows))) % groups;
+  }
   CUtensorMap ta, tb;
   if (encode_tmap_bf16_2d(&ta, x, k, m, ldx, kBlockK, kTileRows)) return -4;
-  if (encode_tmap_bf16_2d(&tb, w, k, n, ldw, kBlockK, bn)) return -4;
+  if (encode_tmap_bf16_2d(&tb, w, k, n, ldw, kBlockK, pair ? bn / 2 : bn)) return -4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return bn == 256 ? launch_comm<256, 0>(ta, ta, tb, a, p, s) : launch_comm<128, 0>(ta, ta, tb, a, p, s);
+  if (pair) return launch_comm<256, 0, true>(ta, ta, tb, a, p, s);
+  return bn == 256 ? launch_comm<256, 0, false>(ta, ta, tb, a, p, s) : launch_comm<128, 0, false>(ta, ta, tb, a, p, s);
 }
 
 // All-gather + column-parallel GEMM.  x_local [m / tp, k] (this rank's row slab), w [n, k] (this rank's
@@ -667,11 +761,17 @@ extern "C" int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m,
     p.flags[i] = reinterpret_cast<unsigned int*>(peer_flags[i]);
   }
   const int bn = n >= 256 ? 256 : 128;
+  const bool pair = bn == 256 && m >= 256 && comm_pair_enabled();
   a.num_col_tiles = (n + bn - 1) / bn;
+  if (pair) {
+    a.first_tile = (rank * rpr) / (2 * kTileRows);
+    a.comm_ctas = (a.comm_ctas + 1) & ~1;          // whole pairs push
+  }
   CUtensorMap ta, tg, tb;
   if (encode_tmap_bf16_2d(&ta, x_local, k, rpr, ldx, kBlockK, kTileRows)) return -4;
   if (encode_tmap_bf16_2d(&tg, peer_gather[rank], k, m, k, kBlockK, kTileRows)) return -4;
-  if (encode_tmap_bf16_2d(&tb, w, k, n, ldw, kBlockK, bn)) return -4;
+  if (encode_tmap_bf16_2d(&tb, w, k, n, ldw, kBlockK, pair ? bn / 2 : bn)) return -4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return bn == 256 ? launch_comm<256, 1>(ta, tg, tb, a, p, s) : launch_comm<128, 1>(ta, tg, tb, a, p, s);
+  if (pair) return launch_comm<256, 1, true>(ta, tg, tb, a, p, s);
+  return bn == 256 ? launch_comm<256, 1, false>(ta, tg, tb, a, p, s) : launch_comm<128, 1, false>(ta, tg, tb, a, p, s);
 }
