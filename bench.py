@@ -90,7 +90,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager"])
-    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen3-30b-a3b"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen3-30b-a3b", "gpt-oss-20b"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
@@ -126,9 +126,15 @@ def main():
         cfg = C.llama3_8b()
         batch, prompt_len = args.batch or 64, args.prompt_len or 1024
         parallelism = f"tp{world}"
-    else:
+    elif args.model == "qwen3-30b-a3b":
         cfg = C.qwen3_30b_a3b()
         batch, prompt_len = args.batch or 128, args.prompt_len or 512
+        parallelism = f"tp{world}-ep{world}"
+    else:
+        # the only configuration the reference publishes numbers for: gpt-oss-20b, batch 1, greedy
+        # (examples/models/gpt_oss/peagle/README.md:101-102: 31.5 / 34.7 tok/s base decode on trn2 at TP = 4)
+        cfg = C.gpt_oss_20b()
+        batch, prompt_len = args.batch or 1, args.prompt_len or 128
         parallelism = f"tp{world}-ep{world}"
     debug = False
     if args.layers:
@@ -208,8 +214,9 @@ def main():
     value = batch * K / (dev_ms / 1e3)
     e2e_value = batch * K / e2e_s
     result = {
-        "metric": "decode tokens/s (Llama-3-8B-shaped, TP over N GPUs, batch 64, prompt 1024, greedy)"
-        if args.model == "llama3-8b" else "decode tokens/s (Qwen3-30B-A3B-shaped MoE, batch 128, prompt 512, greedy)",
+        "metric": {"llama3-8b": "decode tokens/s (Llama-3-8B-shaped, TP over N GPUs, batch 64, prompt 1024, greedy)",
+                   "qwen3-30b-a3b": "decode tokens/s (Qwen3-30B-A3B-shaped MoE, batch 128, prompt 512, greedy)",
+                   "gpt-oss-20b": "decode tokens/s (gpt-oss-20b-shaped MoE, batch 1, greedy)"}[args.model],
         "value": round(value, 2),
         "unit": "tokens/s",
         "n_gpus": world,
@@ -218,7 +225,8 @@ def main():
         "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True,
         "scaling": "strong",
-        "vs_baseline": None,
+        # published reference number exists only for gpt-oss-20b at batch 1 (34.7 tok/s, best base decode on trn2)
+        "vs_baseline": round(value / 34.7, 2) if (args.model == "gpt-oss-20b" and batch == 1) else None,
         "dtype": "bf16",
         "data": "synthetic (uniform random token ids seed 0; random-init weights N(0, 0.02))",
         "impl": "ours",
