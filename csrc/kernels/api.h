@@ -91,7 +91,7 @@ int nkb_gemm_rs(const void* x, const void* w, void* out, int m, int n, int k, lo
                 unsigned int epoch, void* stream);
 int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m, int n, int k, long long ldx, long long ldw,
                 long long ldo, void* const* peer_gather, void* const* peer_flags, int flag_stride, int tp, int rank,
-                unsigned int epoch, int comm_ctas, void* stream);
+                unsigned int epoch, int comm_ctas, int gated, void* stream);
 
 int nkb_rmsnorm(const void* x, const void* w, void* out, int rows, int hidden, float eps, void* stream);
 int nkb_add_rmsnorm(const float* partials, int splits, long long split_stride, const void* x, const void* residual_in,

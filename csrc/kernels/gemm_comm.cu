@@ -48,6 +48,8 @@ struct CommArgs {               // <= 128 bytes (see GemmArgs)
   unsigned int epoch;           // 1, 2, 3, ... per call on these buffers
   int flag_stride;              // counters per source rank
   int ldx;                      // ag_gemm: row stride of x_local in elements
+  int gated;                    // ag_gemm on CTA pairs: B holds [gate; up], out = silu(gate) * up
+  int gate_off;                 // row offset of the up half in B
   long long ldo;
   void* out;
   const __nv_bfloat16* x_local; // ag_gemm: this rank's slab [rows_per_rank, k]
@@ -122,10 +124,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // ------------------------------------------------------------------ ag_gemm: slab pusher CTAs
   // One thread per pusher CTA streams the slab through a ring of 16 KB shared-memory buffers with bulk
-  // copies (global -> shared, shared -> peer global): 64 KB of loads and up to 64 KB of peer stores in
+  // copies (global -> shared, shared -> peer global): 128 KB of loads and up to 64 KB of peer stores in
   // flight per CTA without spending registers or issue slots on the data.
   if (MODE == 1 && int(blockIdx.x) < args.comm_ctas) {
-    constexpr int kSlots = 8, kAhead = 4, kPiece = 16384;
+    constexpr int kSlots = 12, kAhead = 8, kPiece = 16384;
     uint8_t* ring = base + kCommCtrlBytes;
     uint64_t* full = sh->ctrl.full;
     if (threadIdx.x == 0) {
@@ -305,7 +307,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t full0 = map_to_cta(&ctrl->full[stage], 0);
             if (crank == 0) mbar_expect_tx(&ctrl->full[stage], 2 * stage_bytes);
             tma_load_2d_pair(a_ptr, ma, full0, kb * kBlockK, a_row);
-            tma_load_2d_pair(a_ptr + kATileBytes, &tmB, full0, kb * kBlockK, ct * BN + int(crank) * (BN / 2));
+            const int b_row = (MODE == 1 && args.gated) ? int(crank) * args.gate_off + ct * (BN / 2)
+                                                        : ct * BN + int(crank) * (BN / 2);
+            tma_load_2d_pair(a_ptr + kATileBytes, &tmB, full0, kb * kBlockK, b_row);
           } else {
             mbar_expect_tx(&ctrl->full[stage], stage_bytes);
             tma_load_2d(a_ptr, ma, &ctrl->full[stage], kb * kBlockK, a_row);
@@ -448,7 +452,40 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_phase ^= 1u;
         continue;
       }
-      if (MODE == 1) {
+      if (MODE == 1 && PAIR && args.gated) {
+        // accumulator columns [0, BN/2) = gate, [BN/2, BN) = up (the pair's first CTA loaded gate rows, the
+        // second up rows): out[:, ct * BN/2 + j] = silu(gate_j) * up_j
+        const int row = rt * kTileRows + quad * 32 + lane;
+        __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(args.out);
+        const int gcol0 = ct * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t v[32], u[32];
+          tmem_ld_32x32(t0 + c, v);
+          tmem_ld_32x32(t0 + BN / 2 + c, u);
+          tmem_ld_wait();
+          if (c + 32 >= BN / 2) release_acc(acc);
+          const int cbase = gcol0 + c;
+          if (row < args.m && cbase < args.n) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __float_as_uint(silu_f(__uint_as_float(v[j])) * __uint_as_float(u[j]));
+            const long long base = (long long)row * args.ldo + cbase;
+            if (cbase + 32 <= args.n && ((base & 7) == 0)) {
+              uint4* p = reinterpret_cast<uint4*>(out_h + base);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                p[q] = make_uint4(pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
+                                  pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
+                                  pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
+                                  pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (cbase + j < args.n) out_h[base + j] = __float2bfloat16(__uint_as_float(v[j]));
+            }
+          }
+        }
+      } else if (MODE == 1) {
         // local output rows, 64 contiguous bytes per lane and chunk
         const int row = rt * kTileRows + quad * 32 + lane;
         __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(args.out);
@@ -728,7 +765,7 @@ extern "C" int nkb_gemm_rs(const void* x, const void* w, void* out, int m, int n
 // peer_flags[r]: its counter array (tp * flag_stride u32, flag_stride >= ceil(m / tp / 128)).
 extern "C" int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m, int n, int k, long long ldx,
                            long long ldw, long long ldo, void* const* peer_gather, void* const* peer_flags,
-                           int flag_stride, int tp, int rank, unsigned int epoch, int comm_ctas, void* stream) {
+                           int flag_stride, int tp, int rank, unsigned int epoch, int comm_ctas, int gated, void* stream) {
   if (!status_word() && nkb_init() != 0) return -1;
   if (m <= 0 || n <= 0 || k <= 0 || tp < 1 || tp > kCommMaxPeers || rank < 0 || rank >= tp) return -2;
   if ((m % tp) || (k & 7) || (ldx & 7) || (ldw & 7) || (ldo & 7)) return -2;
@@ -742,7 +779,17 @@ extern "C" int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m,
   a.tp = tp; a.rank = rank; a.rows_per_rank = rpr;
   a.local_direct = (rpr % kTileRows) == 0 ? 1 : 0;
   a.first_tile = (rank * rpr) / kTileRows;
-  if (comm_ctas < 1) comm_ctas = 2 * tp;   // egress time / GEMM time grows with tp - 1
+  if (comm_ctas < 1) {
+    // enough pusher CTAs (about 45 GB/s each) to deliver the peers' slabs well inside the time the GEMM
+    // spends on the slabs it already has; every pusher costs 1/148 of the GEMM's throughput
+    const double gemm_us = 2.0 * m * double(n) * k / 1.3e9;
+    const double push_bytes = double(tp - 1) * rpr * double(k) * 2.0;
+    const double window_us = gemm_us * (tp - 1) / tp * 0.6 + 1.0;
+    const double want = push_bytes / window_us / 1e3 / 45.0;
+    comm_ctas = int(want) + 1;
+    if (comm_ctas < 2) comm_ctas = 2;
+    if (comm_ctas > 32) comm_ctas = 32;
+  }
   if (tp == 1) comm_ctas = a.local_direct ? 0 : 1;
   if (comm_ctas > num_sms() / 2) comm_ctas = num_sms() / 2;
   a.comm_ctas = comm_ctas;
@@ -760,9 +807,12 @@ extern "C" int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m,
     p.buf[i] = reinterpret_cast<__nv_bfloat16*>(peer_gather[i]);
     p.flags[i] = reinterpret_cast<unsigned int*>(peer_flags[i]);
   }
-  const int bn = n >= 256 ? 256 : 128;
+  const int bn = (gated || n >= 256) ? 256 : 128;
   const bool pair = bn == 256 && m >= 256 && comm_pair_enabled();
-  a.num_col_tiles = (n + bn - 1) / bn;
+  if (gated && !pair) return -5;       // SwiGLU epilogue exists on CTA pairs only: callers gate separately
+  a.gated = gated ? 1 : 0;
+  a.gate_off = n;                      // w holds n gate rows followed by n up rows
+  a.num_col_tiles = gated ? (n + 127) / 128 : (n + bn - 1) / bn;
   if (pair) {
     a.first_tile = (rank * rpr) / (2 * kTileRows);
     a.comm_ctas = (a.comm_ctas + 1) & ~1;          // whole pairs push
@@ -770,7 +820,8 @@ extern "C" int nkb_ag_gemm(const void* x_local, const void* w, void* out, int m,
   CUtensorMap ta, tg, tb;
   if (encode_tmap_bf16_2d(&ta, x_local, k, rpr, ldx, kBlockK, kTileRows)) return -4;
   if (encode_tmap_bf16_2d(&tg, peer_gather[rank], k, m, k, kBlockK, kTileRows)) return -4;
-  if (encode_tmap_bf16_2d(&tb, w, k, n, ldw, kBlockK, pair ? bn / 2 : bn)) return -4;
+  if (encode_tmap_bf16_2d(&tb, w, k, gated ? 2 * uint64_t(n) : uint64_t(n), ldw, kBlockK, pair ? bn / 2 : bn))
+    return -4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (pair) return launch_comm<256, 1, true>(ta, tg, tb, a, p, s);
   return bn == 256 ? launch_comm<256, 1, false>(ta, tg, tb, a, p, s) : launch_comm<128, 1, false>(ta, tg, tb, a, p, s);

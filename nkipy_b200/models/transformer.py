@@ -308,8 +308,10 @@ class TransformerLM:
                 y = ops.moe_combine(y_sorted, plan.pair_pos, weights, T)
                 dn = tp.reduce_scatter(y)
             else:
-                gu = ag(normed, lw.gate_up)
-                act = ops.silu_mul(gu, limit=cfg.swiglu_limit, alpha=cfg.swiglu_alpha)
+                if cfg.swiglu_limit <= 0:
+                    act = ag(normed, lw.gate_up, gated=True)           # SwiGLU in the GEMM epilogue
+                else:
+                    act = ops.silu_mul(ag(normed, lw.gate_up), limit=cfg.swiglu_limit, alpha=cfg.swiglu_alpha)
                 dn = rs(act, lw.down)
             resid, normed = ops.add_rmsnorm(dn, nxt, residual_in=resid, eps=cfg.rms_eps)
         return tp.all_gather(normed).reshape(T, cfg.hidden_size)

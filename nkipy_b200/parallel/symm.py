@@ -304,23 +304,42 @@ class AllGatherGemm(_FusedGemmCollective):
         I, LL, P, U = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_uint
         self._lib.nkb_ag_gemm.restype = I
         self._lib.nkb_ag_gemm.argtypes = [P, P, P, I, I, I, LL, LL, LL, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I,
-                                          U, I, P]
+                                          U, I, I, P]
 
-    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    @staticmethod
+    def _swiglu(gu: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+
+        i = gu.shape[1] // 2
+        if i % 8 == 0:
+            return ops.silu_mul(gu)
+        return (torch.nn.functional.silu(gu[:, :i].float()) * gu[:, i:].float()).to(gu.dtype)
+
+    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 gated: bool = False) -> torch.Tensor:
+        """gated: w holds [gate; up] rows (2 * I) and the result is ``silu(x @ gate.T) * (x @ up.T)`` [M, I]
+        (SwiGLU in the epilogue; falls back to a separate activation kernel when the shape does not take the
+        CTA-pair kernel)."""
         from .. import ops
 
         rows, k = x_local.shape
-        n = w.shape[0]
+        n = w.shape[0] // 2 if gated else w.shape[0]
         tp = self.tp
         if rows * tp.world_size != self.m or k != self.k or w.shape[1] != k:
             raise ValueError(f"AllGatherGemm sized for [{self.m}, {self.k}], got x {tuple(x_local.shape)} "
                              f"w {tuple(w.shape)}")
         if out is None:
             out = torch.empty((self.m, n), dtype=torch.bfloat16, device=x_local.device)
+        if gated and (self.m < 256 or n < 128 or n % 8):
+            return self._swiglu(self(x_local, w))
         epoch, bufs = self._next()
         rc = self._lib.nkb_ag_gemm(x_local.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, n, k, x_local.stride(0),
                                    w.stride(0), out.stride(0), bufs, self._flags, self.flag_stride, tp.world_size,
-                                   tp.rank, epoch, self.comm_ctas, torch.cuda.current_stream().cuda_stream)
+                                   tp.rank, epoch, self.comm_ctas, 1 if gated else 0,
+                                   torch.cuda.current_stream().cuda_stream)
+        if rc == -5 and gated:
+            self.epoch -= 1
+            return self._swiglu(self(x_local, w))
         _lib.check(rc, "nkb_ag_gemm")
         ops._launches += 1
         return out

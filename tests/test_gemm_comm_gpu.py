@@ -66,7 +66,35 @@ def test_ag_gemm_single_rank(m, n, k):
     op.close()
 
 
+@pytest.mark.parametrize("m,i,k", [(1024, 384, 512), (512, 200, 256)])
+def test_ag_gemm_gated_single_rank(m, i, k):
+    from nkipy_b200 import ops
+    from nkipy_b200.parallel.comm import TPGroup
+    from nkipy_b200.parallel.symm import AllGatherGemm
+
+    dev = torch.device("cuda:0")
+    op = AllGatherGemm(TPGroup.single(dev), m, k)
+    torch.manual_seed(2)
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    w = (torch.randn(2 * i, k, device=dev) * 0.1).to(torch.bfloat16)
+    out = op(x, w, gated=True)
+    ref = torch.nn.functional.silu(x.float() @ w[:i].float().T) * (x.float() @ w[i:].float().T)
+    assert out.shape == (m, i) and _rel(out, ref) < 1e-2
+    assert ops.device_status() == 0
+    op.close()
+
+
 def _worker(rank, world, port, q):
+    try:
+        _worker_body(rank, world, port, q)
+    except BaseException:       # make a failing rank visible instead of letting its peer wait for it
+        import traceback
+
+        q.put((rank, float("inf"), -1, {"exception": traceback.format_exc()[-1500:]}))
+        raise
+
+
+def _worker_body(rank, world, port, q):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -104,6 +132,12 @@ def _worker(rank, world, port, q):
             dist.all_gather(xs, xl)
             ref = torch.cat(xs).float() @ w.float().T
             errs[("ag", m, n, k, it)] = _rel(out, ref)
+            if n // 2 >= 128:
+                out = ag(xl, w, gated=True)                  # w read as [gate; up]
+                full = torch.cat(xs).float()
+                h = n // 2
+                ref = torch.nn.functional.silu(full @ w[:h].float().T) * (full @ w[h:].float().T)
+                errs[("ag-gated", m, n, k, it)] = _rel(out, ref)
         torch.cuda.synchronize()
         tp.barrier()
         ag.close()
