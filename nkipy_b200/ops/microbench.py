@@ -141,6 +141,28 @@ def case_gemm_comm(mode, args):
     return r
 
 
+def case_gemm_ar(args):
+    """Decode-form row-parallel GEMM whose epilogue stores its partial tiles into the symmetric buffers, followed
+    by the consumer (wait on the arrival counters, sum, residual, RMSNorm); one rank, so no NVLink traffic."""
+    from ..parallel.comm import TPGroup
+    from ..parallel.symm import FusedTP
+
+    M, K, N = 64, 14336, 4096                     # Llama-3-8B down projection at batch 64
+    fused = FusedTP(TPGroup.single(torch.device("cuda")), M, N)
+    x = _bf16(M, K)
+    resid, wn = _bf16(M, N), _bf16(N)
+    sets = _sets_for(N * K * 2, args.sets)
+    sets += sets % 2                              # the two partial buffers alternate per call
+    ws = [_bf16(N, K, scale=0.02) for _ in range(sets)]
+    fns = [lambda w=w: fused.gemm_allreduce_add_rmsnorm(x, w, resid, wn, None, 1e-5, splits=8) for w in ws]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    r = dict(case="gemm-ar-tp1", us=us, bytes=(M * K + N * K + 3 * M * N) * 2, flops=2.0 * M * N * K,
+             shape=dict(M=M, K=K, N=N, ranks=1, sets=sets, launches_per_call=2))
+    torch.cuda.synchronize()
+    fused.close()
+    return r
+
+
 def case_attn_decode(args):
     B, ctx, nkv, nq, D = 64, 1056, 8, 32, 128
     pages = (ctx + 31) // 32
@@ -216,6 +238,7 @@ CASES = {
     "gemm-prefill-gated": case_gemm_prefill_gated,
     "gemm-rs-tp1": lambda a: case_gemm_comm("rs", a),
     "ag-gemm-tp1": lambda a: case_gemm_comm("ag", a),
+    "gemm-ar-tp1": case_gemm_ar,
     "attn-decode": case_attn_decode,
     "attn-prefill": case_attn_prefill,
     "moe-decode-layer": case_moe,

@@ -89,14 +89,13 @@ class SymmetricMemory:
 
 
 class FusedTP:
-    """Fused row-parallel GEMM + all-reduce + residual + RMSNorm for decode-sized batches."""
+    """Fused row-parallel GEMM + all-reduce + residual + RMSNorm for decode-sized batches.  One rank is allowed
+    (the same two kernels, the only "peer" being this GPU): single-GPU tests and profiles use it."""
 
     FLAG_BYTES = 4096
     ARGMAX_FLAG_OFFSET = 1024      # byte offset of the argmax arrival counters inside the flag page
 
     def __init__(self, tp: TPGroup, max_tokens: int, hidden: int, max_splits: int = 8):
-        if tp.world_size < 2:
-            raise ValueError("FusedTP needs at least two ranks")
         if tp.world_size > 8:
             raise ValueError("FusedTP supports up to 8 ranks (one NVSwitch domain)")
         self.tp = tp

@@ -103,3 +103,61 @@ def test_fused_gemm_allreduce_two_ranks():
     for rank, err, status in res:
         assert status == 0, (rank, status)
         assert err < 2e-2, (rank, err)
+
+
+def test_fused_gemm_allreduce_single_rank():
+    """The push epilogue, the arrival counters and the consumer with this GPU as the only peer (eager calls and
+    graph replays), including the argmax exchange used by the vocabulary-parallel head."""
+    from nkipy_b200 import ops
+    from nkipy_b200.parallel.comm import TPGroup
+    from nkipy_b200.parallel.symm import FusedTP
+
+    dev = torch.device("cuda:0")
+    M, N, K = 48, 1024, 1536
+    fused = FusedTP(TPGroup.single(dev), 64, N)
+    g = torch.Generator(device=dev).manual_seed(5)
+    resid = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+    wn = torch.randn(N, device=dev, generator=g).to(torch.bfloat16)
+    xs = [torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+    ws = [(torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for _ in range(4)]
+
+    def reference(x, w):
+        h = (x.float() @ w.float().T + resid.float()).to(torch.bfloat16).float()
+        return h, h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * wn.float()
+
+    outs = []
+
+    def body():
+        fused.begin_step()
+        outs.clear()
+        for i in range(4):
+            outs.append(fused.gemm_allreduce_add_rmsnorm(xs[i], ws[i], resid, wn, None, 1e-5, splits=1 + i % 3))
+
+    body()
+    torch.cuda.synchronize()
+    for i in range(4):
+        rh, rn = reference(xs[i], ws[i])
+        assert ((outs[i][0].float() - rh).norm() / rh.norm()).item() < 2e-2
+        assert ((outs[i][1].float() - rn).norm() / rn.norm()).item() < 2e-2
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        body()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for i in range(4):
+        rh, _ = reference(xs[i], ws[i])
+        assert ((outs[i][0].float() - rh).norm() / rh.norm()).item() < 2e-2
+    vals = torch.randn(M, device=dev, generator=g)
+    ids = torch.randint(0, 1000, (M,), device=dev, generator=g, dtype=torch.int32)
+    got = fused.argmax_exchange(vals, ids, 7)
+    torch.cuda.synchronize()
+    assert torch.equal(got, ids + 7)
+    assert ops.device_status() == 0
+    fused.close()
