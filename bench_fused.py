@@ -7,6 +7,11 @@ Shapes (per rank, bf16):
   ag: all-gather(X[M/tp, 8192]) @ W[8192, 28672/tp]                      (column-parallel gate_up)
   ar: X[M, 8192/tp] @ W[8192/tp, 8192] -> all-reduce + residual + RMSNorm, M <= 128 (the decode form of rs:
       weights on the 128-row MMA side, split-K, partial tiles pushed to every peer, reducing norm kernel)
+  moe: one Qwen3-30B-A3B-shaped expert-parallel MoE block (hidden 2048, 128 experts / tp per rank, top-8, expert
+      FFN 768) on M replicated tokens, M <= 256: router, device-built dispatch, two grouped tcgen05 GEMMs, then the
+      combine whose kernel stores every token's weighted partial sum into all peers' buffers (the all-to-all of
+      this layout) followed by the summing residual + RMSNorm kernel.  Baseline: the same experts with a local
+      combine, NCCL all-reduce and a separate residual + RMSNorm.  `combine_*` fields time the exchange alone.
 for M = 16 ... 16384.  "fused" is one kernel per rank (csrc/kernels/gemm_comm.cu: tcgen05 tiles + peer stores
 over NVLink + arrival counters); "baseline" is torch.matmul (cuBLAS) with NCCL reduce_scatter_tensor /
 all_gather_into_tensor.  Every iteration is timed on the device with CUDA events after an L2 flush (a 256 MB
@@ -52,10 +57,93 @@ def timed(tp, fn, iters, warmup, flush):
     return ts[len(ts) // 2]
 
 
+def bench_moe(tp, m, args, pk, flush, g):
+    from nkipy_b200.models import config as C
+    from nkipy_b200.models.moe import MoEBlock
+
+    n_r, dev = tp.world_size, tp.device
+    cfg = C.qwen3_30b_a3b()
+    H, E, I, K = cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size, cfg.top_k
+    e_l = E // n_r
+
+    class LW:
+        pass
+
+    lw = LW()
+    gs = torch.Generator(device=dev).manual_seed(3)          # replicated tensors: same seed on every rank
+    lw.router = (torch.randn(E, H, device=dev, generator=gs) * 0.02).to(torch.bfloat16)
+    lw.router_bias = lw.gate_up_bias = lw.down_bias = None
+    lw.gate_up = (torch.randn(e_l, 2 * I, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    lw.down = (torch.randn(e_l, H, I, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(m, H, device=dev, generator=gs).to(torch.bfloat16)
+    resid = torch.randn(m, H, device=dev, generator=gs).to(torch.bfloat16)
+    wn = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    blk = MoEBlock(cfg, tp, "ep")
+    fused = FusedTP(tp, m, H) if n_r > 1 else None
+    state = {"i": 0}
+
+    def tick():
+        if state["i"] % 2 == 0:
+            fused.begin_step()
+        state["i"] += 1
+
+    def run():
+        if fused is None:
+            return base()
+        tick()
+        y_sorted, plan, weights = blk._experts(lw, x)
+        return fused.moe_combine_allreduce_add_rmsnorm(y_sorted, plan.pair_pos, weights, m, resid, wn, cfg.rms_eps)[1]
+
+    def base():
+        y = blk.forward(lw, x)                               # local combine + NCCL all-reduce
+        return ops.add_rmsnorm(y, wn, residual_in=resid, eps=cfg.rms_eps)[1]
+
+    y_sorted, plan, weights = blk._experts(lw, x)
+
+    def run_c():
+        if fused is None:
+            return base_c()
+        tick()
+        return fused.moe_combine_allreduce_add_rmsnorm(y_sorted, plan.pair_pos, weights, m, resid, wn, cfg.rms_eps)[1]
+
+    def base_c():
+        y = ops.moe_combine(y_sorted, plan.pair_pos, weights, m)
+        tp.all_reduce(y)
+        return ops.add_rmsnorm(y, wn, residual_in=resid, eps=cfg.rms_eps)[1]
+
+    a, b = run().float(), base().float()
+    if fused is not None:
+        run()
+    rel = ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
+    even = args.iters + (args.iters + args.warmup) % 2
+    t_f, t_b = timed(tp, run, even, args.warmup, flush), timed(tp, base, args.iters, args.warmup, flush)
+    t_fc, t_bc = timed(tp, run_c, even, args.warmup, flush), timed(tp, base_c, args.iters, args.warmup, flush)
+    pairs_local = m * K / n_r
+    active = e_l * (1.0 - (1.0 - 1.0 / E) ** (m * K))        # expected number of local experts with a token
+    t_h = (active * 3 * H * I + E * H) * 2 / (pk["hbm_gbs"] * 1e3)
+    t_c = 2.0 * pairs_local * 3 * H * I / (pk["bf16_tflops"] * 1e6)
+    link_bytes = (n_r - 1) * m * H * 2                       # every rank's partial rows go to every peer
+    t_l = link_bytes / (NVLINK_GBS * 1e3)
+    roof = max(t_h, t_c, t_l)
+    status = ops.device_status()
+    if tp.rank == 0:
+        print(json.dumps({
+            "op": "moe_ep_block", "tp": n_r, "m": m, "experts_per_rank": e_l, "fused_us": round(t_f, 1),
+            "nccl_us": round(t_b, 1), "speedup": round(t_b / t_f, 2), "roofline_us": round(roof, 1),
+            "frac_roofline": round(roof / t_f, 3), "bound": "hbm" if roof == t_h else ("nvlink" if roof == t_l else "compute"),
+            "combine_fused_us": round(t_fc, 1), "combine_nccl_us": round(t_bc, 1),
+            "combine_link_us": round(t_l, 2), "combine_frac_link": round(t_l / t_fc, 3),
+            "rel_err_vs_baseline": round(rel, 5), "status": status, "peaks": pk["source"]}), flush=True)
+    torch.cuda.synchronize()
+    tp.barrier()
+    if fused is not None:
+        fused.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ms", type=str, default="16,64,256,1024,4096,16384")
-    ap.add_argument("--ops", type=str, default="ar,rs,ag")
+    ap.add_argument("--ops", type=str, default="ar,rs,ag,moe")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--hidden", type=int, default=8192)
@@ -72,6 +160,10 @@ def main():
     for op in args.ops.split(","):
         for m in [int(v) for v in args.ms.split(",")]:
             if m % n_r:
+                continue
+            if op == "moe":
+                if m <= 256:
+                    bench_moe(tp, m, args, pk, flush, g)
                 continue
             if op == "ar":
                 if m > 128 or n_r < 2:
