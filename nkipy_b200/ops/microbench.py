@@ -85,6 +85,10 @@ def _sets_for(bytes_per_set, want):
 
 # --------------------------------------------------------------------------- cases
 def case_gemm_decode(name, features, k, tokens, splits, gated, args):
+    if args.splits > 0 and not gated:
+        splits = args.splits
+    if args.tokens > 0:
+        tokens = args.tokens
     wrows = features * (2 if gated else 1)
     nbytes = wrows * k * 2
     sets = _sets_for(nbytes, args.sets)
@@ -253,6 +257,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--sets", type=int, default=8, help="upper bound of rotating operand sets")
+    ap.add_argument("--splits", type=int, default=0, help="override the split-K factor of the gemm-decode-* cases")
+    ap.add_argument("--tokens", type=int, default=0, help="override the token count of the gemm-decode-* cases")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a GPU", file=sys.stderr)

@@ -1,4 +1,4 @@
-"""Tensor-parallel sharding and collectives on CPU ranks (gloo, world_size 2)."""
+"""Tensor-parallel sharding and collectives on CPU ranks (gloo, world_size 2 and 4)."""
 import os
 import socket
 import sys
@@ -40,18 +40,20 @@ def _worker(rank, world, port, q):
     gathered = tp.all_gather_object(out)
     assert all(o == gathered[0] for o in gathered)
     t = torch.full((4,), float(rank + 1))
-    assert tp.all_reduce(t.clone()).tolist() == [3.0] * 4
-    assert tp.all_gather(t).shape == (2, 4)
-    assert tp.reduce_scatter(torch.arange(8.0)).tolist() == [(2 * v) for v in range(rank * 4, rank * 4 + 4)]
+    assert tp.all_reduce(t.clone()).tolist() == [world * (world + 1) / 2.0] * 4
+    assert tp.all_gather(t).shape == (world, 4)
+    per = 8 // world
+    assert tp.reduce_scatter(torch.arange(8.0)).tolist() == [(world * v) for v in range(rank * per, (rank + 1) * per)]
     assert tp.broadcast_object({"a": rank}, src=0) == {"a": 0}
-    assert tp.max_over_ranks(float(rank)) == 1.0
+    assert tp.max_over_ranks(float(rank)) == world - 1.0
     if rank == 0:
         q.put(out)
     tp.barrier()
     torch.distributed.destroy_process_group()
 
 
-def test_tp2_matches_tp1_on_cpu():
+@pytest.mark.parametrize("world", [2, 4])       # 4 ranks over 2 KV heads: KV heads are replicated in pairs
+def test_tp_matches_tp1_on_cpu(world):
     from nkipy_b200.models import config as C
     from nkipy_b200.models.engine import GenerationEngine
     from nkipy_b200.models.transformer import TransformerLM
@@ -60,7 +62,7 @@ def test_tp2_matches_tp1_on_cpu():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     out_tp2 = q.get(timeout=180)
