@@ -221,6 +221,46 @@ def case_moe(args):
                            note="dispatch + gated grouped GEMM + down grouped GEMM + combine; bytes = all expert weights"))
 
 
+def case_moe_push(args):
+    """The expert-parallel MoE block as a rank runs it (router, dispatch, two grouped GEMMs, the combine kernel
+    that stores every token's weighted partial sum into the peers' buffers, the summing residual + RMSNorm
+    kernel) with one rank, i.e. without NVLink traffic."""
+    from ..models import config as C
+    from ..models.moe import MoEBlock
+    from ..parallel.comm import TPGroup
+    from ..parallel.symm import FusedTP
+
+    cfg = C.qwen3_30b_a3b()
+    T, H, E, I = 128, cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size
+    tp = TPGroup.single(torch.device("cuda"))
+    fused = FusedTP(tp, T, H)
+    blk = MoEBlock(cfg, tp, "ep")
+    sets = max(2, min(args.sets, 4))
+    sets += sets % 2
+
+    class LW:
+        router_bias = gate_up_bias = down_bias = None
+
+    lws = []
+    for _ in range(sets):
+        lw = LW()
+        lw.router, lw.gate_up, lw.down = _bf16(E, H, scale=0.02), _bf16(E, 2 * I, H, scale=0.02), _bf16(E, H, I, scale=0.02)
+        lws.append(lw)
+    x, resid, wn = _bf16(T, H), _bf16(T, H), _bf16(H)
+
+    def layer(lw):
+        y_sorted, plan, weights = blk._experts(lw, x)
+        return fused.moe_combine_allreduce_add_rmsnorm(y_sorted, plan.pair_pos, weights, T, resid, wn, cfg.rms_eps)
+
+    fns = [lambda lw=lw: layer(lw) for lw in lws]
+    us = _time(fns, args.iters, args.warmup, not args.no_graph)
+    r = dict(case="moe-ep-block-tp1", us=us, bytes=E * 3 * I * H * 2, flops=2.0 * T * cfg.top_k * 3 * I * H,
+             shape=dict(tokens=T, hidden=H, experts=E, inter=I, top_k=cfg.top_k, ranks=1, sets=sets))
+    torch.cuda.synchronize()
+    fused.close()
+    return r
+
+
 def case_addnorm(args):
     T, H, S = 64, 4096, 8
     parts = [torch.randn(S, T, H, device="cuda") for _ in range(4)]
@@ -246,6 +286,7 @@ CASES = {
     "attn-decode": case_attn_decode,
     "attn-prefill": case_attn_prefill,
     "moe-decode-layer": case_moe,
+    "moe-ep-block-tp1": case_moe_push,
     "add-rmsnorm": case_addnorm,
 }
 
