@@ -186,7 +186,9 @@ __global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ y_sort
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    // release at GPU scope into the grid counter; the last CTA has observed every other CTA's release and
+    // publishes all of them with one system-scope fence before it bumps the peers' flags
+    __threadfence();
     const unsigned int old = atomicAdd(push.done_counter, 1u);
     if (old == gridDim.x - 1) {
       *push.done_counter = 0u;

@@ -14,7 +14,7 @@ template <int BN, int MINB, bool PUSH, bool GROUPED>
 static int ring_stages(const GemmArgs& args, int& smem) {
   const int a_tiles = args.gated == 1 ? 2 : 1, b_tiles = args.gated == 2 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * BN * kBlockK * 2;
-  const int extra = 512 + (PUSH ? BN * kTileRows * 2 : 0);   // control block (+ push staging tile)
+  const int extra = 512 + (PUSH ? 32 * kTileRows * 2 : 0);   // control block (+ push staging tile: 32 tokens)
   const int budget = (MINB == 2 ? 113 * 1024 : 232448) - 1024 - extra - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;

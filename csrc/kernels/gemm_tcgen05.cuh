@@ -118,7 +118,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * kBTileBytes;
   const int stages = args.stages;
   GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(tiles + stages * stage_bytes);
-  // push mode: [BN tokens][128 features] bf16 staging tile behind the control block
+  // push mode: [32 tokens][128 features] bf16 staging tile (one accumulator chunk) behind the control block
   __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(ctrl) + 512);
 
   const int acc_cols = BN * (args.gated ? 2 : 1);
@@ -344,10 +344,28 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
         }
         if constexpr (PUSH) {
-          // stage the chunk: token (c + j), feature (quad * 32 + lane)
+          // stage the chunk (token j, feature quad * 32 + lane), then the four warps store it to every rank as
+          // 16-byte pieces, 256 contiguous bytes per token.  cbase and cols_end are CTA-uniform, so the four
+          // warps reach the two barriers together.
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            stage_out[(c + j) * kTileRows + quad * 32 + lane] = __float2bfloat16(__uint_as_float(v[j]));
+            stage_out[j * kTileRows + quad * 32 + lane] = __float2bfloat16(__uint_as_float(v[j]));
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int et = threadIdx.x - 64;  // 0..127 over the four epilogue warps
+          const int row0 = rt * kTileRows;
+          const long long slot = (long long)push.rank * args.splits + sp;
+#pragma unroll
+          for (int idx = et; idx < 32 * 16; idx += 128) {
+            const int tok = idx >> 4, ch = idx & 15;
+            const int gtok = cbase + tok, gfeat = row0 + ch * 8;
+            if (gtok < cols_end && gfeat < args.rows) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
+              const long long off = (slot * args.cols + gtok) * args.ldo + gfeat;
+              for (int pr = 0; pr < push.n_peers; ++pr)
+                *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
           continue;
         }
         if (args.transpose_out) {
@@ -418,32 +436,18 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
         }
       }
-      if constexpr (PUSH) {
-        const int et = threadIdx.x - 64;  // 0..127 over the four epilogue warps
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int row0 = rt * kTileRows;
-        const long long slot = (long long)push.rank * args.splits + sp;
-        for (int idx = et; idx < BN * 16; idx += 128) {
-          const int tok = idx >> 4, ch = idx & 15;
-          const int gtok = col0 + tok, gfeat = row0 + ch * 8;
-          if (gtok < cols_end && gfeat < args.rows) {
-            const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
-            const long long off = (slot * args.cols + gtok) * args.ldo + gfeat;
-            for (int pr = 0; pr < push.n_peers; ++pr)
-              *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
     if constexpr (PUSH) {
       // all peer stores of this CTA are issued: publish them, count the CTA, and let the
       // last CTA of the grid signal every peer
-      __threadfence_system();
+      // The barrier orders the four warps' stores before the publishing thread's fence.  Every CTA releases at
+      // GPU scope into the grid counter; the last CTA, which has observed all of them, releases at system scope
+      // into the peers' flags (causality order is transitive across the two scopes).
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
+        __threadfence();
         const unsigned int old = atomicAdd(push.done_counter, 1u);
         if (old == gridDim.x - 1) {
           *push.done_counter = 0u;
