@@ -80,15 +80,26 @@ __global__ void tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ parti
       float a[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) a[j] = 0.f;
-      for (int s = 0; s < slots; ++s) {
-        // remote ranks wrote these lines: read them from L2, never from a stale L1 line
-        const uint4 r = __ldcg(reinterpret_cast<const uint4*>(partials + (long long)s * rows * hidden + off));
-        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+      // remote ranks wrote these lines: read them from L2, never from a stale L1 line.  Eight slots are
+      // fetched per batch so that a thread keeps 128 bytes in flight (one row per CTA leaves most SMs idle,
+      // and with 8 ranks x 3 splits a slot-by-slot loop was a chain of 24 L2 round trips).
+      constexpr int kBatch = 8;
+      const long long slot_stride = (long long)rows * hidden;
+      for (int s0 = 0; s0 < slots; s0 += kBatch) {
+        uint4 r[kBatch];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = unpack_bf16x2(rw[e]);
-          a[2 * e] += f.x;
-          a[2 * e + 1] += f.y;
+        for (int u = 0; u < kBatch; ++u)
+          r[u] = (s0 + u < slots) ? __ldcg(reinterpret_cast<const uint4*>(partials + (s0 + u) * slot_stride + off))
+                                  : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const uint32_t rw[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16x2(rw[e]);
+            a[2 * e] += f.x;
+            a[2 * e + 1] += f.y;
+          }
         }
       }
       if (residual_in) {
