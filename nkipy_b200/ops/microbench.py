@@ -177,10 +177,11 @@ def case_attn_decode(args):
     table = torch.arange(nb, device="cuda", dtype=torch.int32).reshape(B, pages)
     lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
     q = _bf16(B, nq * D)
-    fns = [lambda kc=kc, vc=vc: paged_attn_decode(q, kc, vc, table, lens, D ** -0.5) for kc, vc in caches]
+    fns = [lambda kc=kc, vc=vc: paged_attn_decode(q, kc, vc, table, lens, D ** -0.5, num_splits=args.kv_splits)
+           for kc, vc in caches]
     us = _time(fns, args.iters, args.warmup, not args.no_graph)
     return dict(case="attn-decode", us=us, bytes=B * ctx * nkv * D * 2 * 2, flops=4.0 * B * nq * ctx * D,
-                shape=dict(batch=B, context=ctx, nq=nq, nkv=nkv, head_dim=D, sets=sets))
+                shape=dict(batch=B, context=ctx, nq=nq, nkv=nkv, head_dim=D, sets=sets, kv_splits=args.kv_splits))
 
 
 def case_attn_prefill(args):
@@ -299,6 +300,7 @@ def main(argv=None):
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--sets", type=int, default=8, help="upper bound of rotating operand sets")
     ap.add_argument("--splits", type=int, default=0, help="override the split-K factor of the gemm-decode-* cases")
+    ap.add_argument("--kv-splits", type=int, default=0, help="split-KV factor of attn-decode (0 = heuristic)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count of the gemm-decode-* cases")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
