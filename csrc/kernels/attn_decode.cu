@@ -7,7 +7,10 @@
 // (128-byte swizzle, through the per-sequence block table) into a private
 // 3-stage shared-memory ring, scores and P*V run on the tensor cores with
 // m16n8k16 fragments fed by ldmatrix, and the online-softmax state stays in
-// registers.  Warps (and, for long contexts, splits) are merged at the end.
+// registers.  Warps are merged through shared memory; for long contexts the KV
+// range is split over several CTAs, each writes its partial (accumulator, running
+// maximum, denominator) to a scratch buffer and the CTA that arrives last at a
+// per-(sequence, kv head) counter merges them, so the whole op is one launch.
 //
 // This op is bound by HBM traffic (the whole KV cache is read once per step),
 // which is why it uses register-fragment MMAs instead of tcgen05: a 128-row
@@ -30,13 +33,17 @@ namespace nkb {
 
 constexpr int kPage = 32;
 constexpr int kDecStages = 3;
+// The scratch buffer starts with the arrival counters (one per sequence x kv head, at most this many), the
+// split partials follow.  Counters must be zero before the first call and are reset by the merging CTA.
+constexpr int kDecCounters = 16384;
 
 struct DecodeParams {
   const __nv_bfloat16* q;
   const int* block_table;
   const int* context_lens;
   __nv_bfloat16* out;
-  float* scratch;
+  float* scratch;            // partials (behind the counters); nullptr when num_splits == 1
+  unsigned int* counters;    // arrival counters of the split merge
   const float* sinks;
   int* status;
   int batch, q_len, nq, nkv, group, max_blocks, num_splits, window;
@@ -306,26 +313,34 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       }
     }
   }
-}
+  if (p.num_splits == 1) return;
 
-template <int D>
-__global__ void decode_combine_kernel(const DecodeParams p) {
-  const int kvh = blockIdx.x, b = blockIdx.y;
-  const int rows = p.q_len * p.group;
-  griddep_wait();
-  griddep_launch();
+  // ---- split merge by the CTA that arrives last at this (sequence, kv head)'s counter
+  __shared__ int is_last;
+  __threadfence();                 // this CTA's partial is visible device-wide before it is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* ctr = p.counters + (long long)b * p.nkv + kvh;
+    const unsigned int old = atomicAdd(ctr, 1u);
+    const int last = old == unsigned(p.num_splits - 1);
+    if (last) *ctr = 0u;           // ready for the next call (the next kernel starts after this grid)
+    is_last = last;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   const float* base = p.scratch + (((long long)b * p.nkv + kvh) * p.num_splits) * (16 * D + 32);
   for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
     const int r = idx / D, d = idx % D;
     float mf = -INFINITY;
-    for (int s = 0; s < p.num_splits; ++s) mf = fmaxf(mf, base[s * (16 * D + 32) + 16 * D + r]);
+    for (int s = 0; s < p.num_splits; ++s) mf = fmaxf(mf, __ldcg(base + s * (16 * D + 32) + 16 * D + r));
     float acc = 0.f, l = 0.f;
     for (int s = 0; s < p.num_splits; ++s) {
       const float* ps = base + s * (16 * D + 32);
-      const float ms = ps[16 * D + r];
+      const float ms = __ldcg(ps + 16 * D + r);
       const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - mf);
-      acc += sc * ps[r * D + d];
-      l += sc * ps[16 * D + 16 + r];
+      acc += sc * __ldcg(ps + r * D + d);
+      l += sc * __ldcg(ps + 16 * D + 16 + r);
     }
     const int head = kvh * p.group + r % p.group;
     if (p.sinks) {
@@ -346,20 +361,18 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   constexpr int smem = kDecWarps * kDecStages * kStageBytes + 1024;
   static_assert(kDecWarps * kDecStages * kStageBytes >= int((kDecWarps * 16 * D + kDecWarps * 32) * sizeof(float)),
                 "merge space must fit in the KV ring");
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the attribute is per device: remember which devices of this process have it
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!attr_set[dev]) {
     cudaError_t e =
         cudaFuncSetAttribute(paged_attn_decode_kernel<D, kDecWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
-    attr_set = true;
+    attr_set[dev] = true;
   }
   dim3 grid(p.num_splits, p.nkv, p.batch);
-  int rc = launch_pdl(paged_attn_decode_kernel<D, kDecWarps>, grid, dim3(kDecWarps * 32), size_t(smem), s, tk, tv, p);
-  if (rc == 0 && p.num_splits > 1) {
-    dim3 g2(p.nkv, p.batch);
-    rc = launch_pdl(decode_combine_kernel<D>, g2, dim3(128), 0, s, p);
-  }
-  return rc;
+  return launch_pdl(paged_attn_decode_kernel<D, kDecWarps>, grid, dim3(kDecWarps * 32), size_t(smem), s, tk, tv, p);
 }
 
 }  // namespace nkb
@@ -370,8 +383,8 @@ extern "C" long long nkb_paged_attn_decode_scratch_floats(int batch, int q_len, 
                                                           int num_splits) {
   (void)q_len;
   if (num_splits <= 1) return 0;
-  // upper bound: one slot per (sequence, kv head, split); kv heads <= nq
-  return (long long)batch * nq * num_splits * (16 * head_dim + 32);
+  // arrival counters first, then (upper bound) one partial per (sequence, kv head, split); kv heads <= nq
+  return kDecCounters + (long long)batch * nq * num_splits * (16 * head_dim + 32);
 }
 
 extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
@@ -383,14 +396,15 @@ extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const v
   const int group = nq / nkv;
   if (q_len * group > 16) return -2;
   if (num_splits < 1) num_splits = 1;
-  if (num_splits > 1 && !scratch) return -2;
+  if (num_splits > 1 && (!scratch || (long long)batch * nkv > kDecCounters)) return -2;
   if (!status_word() && nkb_init() != 0) return -1;
   DecodeParams p{};
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.block_table = block_table;
   p.context_lens = context_lens;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  p.scratch = num_splits > 1 ? scratch : nullptr;
+  p.scratch = num_splits > 1 ? scratch + kDecCounters : nullptr;
+  p.counters = reinterpret_cast<unsigned int*>(scratch);
   p.sinks = sinks;
   p.status = status_word();
   p.batch = batch; p.q_len = q_len; p.nq = nq; p.nkv = nkv; p.group = group;
@@ -416,10 +430,11 @@ extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const v
 // Allocation-free variant (see no_alloc.h for who needs it and its limits).
 // ---------------------------------------------------------------------------
 #include "no_alloc.h"
+#include <mutex>
 #include <stdio.h>
 
 namespace nkb {
-// Split-KV partial results live here instead of in a caller-provided buffer.
+// Arrival counters and split-KV partial results live here instead of in a caller-provided buffer.
 // In host code this name is only a stand-in for the symbol: the device address
 // is looked up once per device with cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_noalloc_scratch[NKB_NOALLOC_SCRATCH_FLOATS];
@@ -433,11 +448,13 @@ struct NoAllocDevice {
 };
 constexpr int kNoAllocMaxDevices = 64;
 static NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+static std::mutex g_noalloc_mutex;   // the first calls of two host threads may meet in the set-up
 
 // Once per device, with that device current: resolve the device addresses.
 static int noalloc_setup(NoAllocDevice** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return NKB_NOALLOC_SETUP_FAILED;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   NoAllocDevice& d = g_noalloc_dev[dev];
   if (!d.ready) {
     void* sp = nullptr;
@@ -456,6 +473,18 @@ static int noalloc_setup(NoAllocDevice** out) {
 }
 }  // namespace nkb
 
+extern "C" int nkb_noalloc_status(int reset) {
+  NoAllocDevice* d = nullptr;
+  if (int rc = noalloc_setup(&d)) return rc;
+  int v = 0;
+  if (cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return NKB_NOALLOC_SETUP_FAILED;
+  if (reset && v) {
+    const int zero = 0;
+    cudaMemcpy(d->status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}
+
 extern "C" int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
                                              const int* block_table, const int* context_lens, void* out, int batch,
                                              int q_len, int nq, int nkv, int head_dim, int block_size, int num_blocks,
@@ -467,8 +496,10 @@ extern "C" int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache,
   if (q_len * group > 16) return -2;
   if (head_dim != 64 && head_dim != 128) return -2;
   if (num_splits < 1) num_splits = 1;
-  const long long need = num_splits > 1 ? (long long)batch * nkv * num_splits * (16 * head_dim + 32) : 0;
-  if (need > NKB_NOALLOC_SCRATCH_FLOATS) {
+  const long long counters = (long long)batch * nkv;
+  const long long need =
+      num_splits > 1 ? kDecCounters + (long long)batch * nkv * num_splits * (16 * head_dim + 32) : 0;
+  if (need > NKB_NOALLOC_SCRATCH_FLOATS || (num_splits > 1 && counters > kDecCounters)) {
     fprintf(stderr,
             "nkb_paged_attn_decode_noalloc: needs %lld scratch floats (batch %d x kv heads %d x splits %d), the "
             "built-in array holds %lld; use fewer splits / a smaller batch or the allocating entry point\n",
@@ -477,12 +508,20 @@ extern "C" int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache,
   }
   NoAllocDevice* d = nullptr;
   if (int rc = noalloc_setup(&d)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (num_splits > 1) {
+    // The merge counts arrivals from zero.  A finished call leaves its counters at zero, but a call that gave
+    // up in a bounded wait may not have: clear the ones this call uses (a memset, not an allocation).
+    cudaError_t e = cudaMemsetAsync(d->scratch, 0, size_t(counters) * sizeof(unsigned int), s);
+    if (e != cudaSuccess) return int(e);
+  }
   DecodeParams p{};
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.block_table = block_table;
   p.context_lens = context_lens;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  p.scratch = num_splits > 1 ? d->scratch : nullptr;
+  p.scratch = num_splits > 1 ? d->scratch + kDecCounters : nullptr;
+  p.counters = reinterpret_cast<unsigned int*>(d->scratch);
   p.sinks = sinks;
   p.status = d->status;
   p.batch = batch; p.q_len = q_len; p.nq = nq; p.nkv = nkv; p.group = group;
@@ -495,7 +534,6 @@ extern "C" int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache,
   const uint32_t box[4] = {64, uint32_t(kPage), 1, 1};
   if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
   if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool small = (long long)batch * nkv * num_splits >= 2LL * d->sms;
   if (head_dim == 128) return small ? launch_decode<128, 2>(tk, tv, p, s) : launch_decode<128, 4>(tk, tv, p, s);
   return small ? launch_decode<64, 2>(tk, tv, p, s) : launch_decode<64, 4>(tk, tv, p, s);

@@ -14,16 +14,24 @@
 //   * Inputs and outputs are still the caller's buffers; only the scratch is ours.
 //   * The call rejects (returns NKB_NOALLOC_TOO_LARGE and prints one line to
 //     stderr) any problem whose scratch need
-//         batch * nkv * num_splits * (16 * head_dim + 32) floats
-//     exceeds NKB_NOALLOC_SCRATCH_FLOATS.  num_splits == 1 needs no scratch.
+//         16384 + batch * nkv * num_splits * (16 * head_dim + 32) floats
+//     exceeds NKB_NOALLOC_SCRATCH_FLOATS, or that has more than 16384
+//     (sequence, kv head) pairs.  num_splits == 1 needs no scratch.
 //   * The first call on each device looks up the device address of the array
 //     (and of a private status word).  Make that first call before starting any
-//     stream capture on that device.
+//     stream capture on that device.  The look-up is guarded by a mutex, so two
+//     host threads may both make "the first call".
 //   * All calls share the one array, and it keeps whatever the previous call
-//     left in it.  Nothing in it has to start at zero: every slot that the merge
-//     step reads is written earlier in the same call.  Two calls that may run at
-//     the same time on the GPU (different streams) would overwrite each other's
-//     partial results: serialise them.
+//     left in it.  The array begins with the arrival counters of the split
+//     merge, which must count from zero: each call clears the counters it uses
+//     with a memset on its stream before the kernel (the partial results behind
+//     them need no clearing, every slot that the merge reads is written earlier
+//     in the same call).  Two calls that may run at the same time on the GPU
+//     (different streams) would overwrite each other's counters and partial
+//     results: serialise them.
+//   * A wait inside the kernel that gives up (after one second) reports into a
+//     status word of this entry point's own, read with nkb_noalloc_status();
+//     nkb_status() covers the other entry points only.
 //   * The function calls no cudaMalloc, cudaFree or allocating library routine.
 #pragma once
 
@@ -42,6 +50,11 @@ int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache, const void
                                   const int* context_lens, void* out, int batch, int q_len, int nq, int nkv,
                                   int head_dim, int block_size, int num_blocks, int max_blocks_per_seq, float scale,
                                   int window, const float* sinks, int num_splits, void* stream);
+
+// Reads (reset != 0: and clears) the status word of the allocation-free entry point on the current
+// device: 0, or the code of a bounded wait that gave up (low byte) with the CTA index above it.
+// Synchronises the device.  Negative: the set-up failed.
+int nkb_noalloc_status(int reset);
 
 #ifdef __cplusplus
 }

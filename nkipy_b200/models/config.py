@@ -72,6 +72,19 @@ class ModelConfig:
     def scaled(self, **overrides) -> "ModelConfig":
         return replace(self, **overrides)
 
+    def shard_shapes(self, n: int) -> "ModelConfig":
+        """The configuration whose full model has the per-rank shapes of this one under n-way tensor
+        (and expert) parallelism: 1/n of the heads, of the FFN width, of the experts and of the
+        vocabulary.  Used to time the kernels of one rank of an n-GPU job on a single GPU."""
+        if n <= 1:
+            return self
+        return replace(
+            self, name=f"{self.name}-shard{n}", num_heads=max(1, self.num_heads // n),
+            num_kv_heads=max(1, self.num_kv_heads // n), intermediate_size=self.intermediate_size // n,
+            num_experts=self.num_experts // n if self.is_moe else 0,
+            top_k=max(1, self.top_k // n) if self.is_moe else 0,      # same (token, expert) pairs per rank
+            vocab_size=self.vocab_size // n)
+
     def param_count(self) -> int:
         h = self.hidden_size
         attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h

@@ -87,7 +87,8 @@ class GenerationEngine:
         self.active: Dict[int, SequenceState] = {}     # table row -> sequence
         self._graph = None
         tp = model.tp
-        if (tp.world_size > 1 and dev.type == "cuda" and getattr(tp, "fused", None) is None
+        if ((tp.world_size > 1 or getattr(model, "force_fused", False)) and dev.type == "cuda"
+                and getattr(tp, "fused", None) is None
                 and os.environ.get("NKIPY_B200_FUSED_TP", "1") == "1"):
             from ..parallel.symm import FusedTP
 

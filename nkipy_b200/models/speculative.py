@@ -224,7 +224,11 @@ class SpeculativeEngine:
         ptd = dr.ecfg.ptd_token_id
         tH3 = commit_aux[0].shape[-1]
 
-        while min(len(o) for o in out) < max_new_tokens:
+        # A sequence that has its max_new_tokens is frozen: it stays in the batch (static shapes), but its
+        # committed length, pending commit and output no longer advance, so its speculative rows keep
+        # landing on the same reserved cache slots however long the slowest sequence still needs.
+        done = [len(o) >= max_new_tokens for o in out]
+        while not all(done):
             # ---- draft: window of W rows per sequence starting at base = L - C + ... (position of commit_0)
             t1 = time.perf_counter()
             tok_rows = torch.full((B, W), ptd, dtype=torch.int32)
@@ -268,6 +272,8 @@ class SpeculativeEngine:
             self.stats.verify_s += time.perf_counter() - t2
 
             for b in range(B):
+                if done[b]:
+                    continue
                 j = n_acc_h[b]
                 emitted = pred_h[b][:j + 1]                # j matched drafts (== pred) + the target's next token
                 out[b].extend(emitted)
@@ -275,7 +281,8 @@ class SpeculativeEngine:
                 commit_aux[b] = aux_all[b, :j + 1]
                 L[b] += j + 1
                 self.stats.emitted += j + 1
-            self.stats.steps += B
+                self.stats.steps += 1
+                done[b] = len(out[b]) >= max_new_tokens
         self.stats.decode_s = time.perf_counter() - t_dec
         for s in seqs:
             cache.free_sequence(s)

@@ -21,6 +21,7 @@ over ranks, examples/models/qwen3/kernels/sampling.py:127-147).
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -43,6 +44,18 @@ def pick_splits(n_out: int, k: int, sms: int = 148) -> int:
     return max(1, min(want, k // 512, 8))
 
 
+def pick_cluster_splits(tiles: int, k: int, tokens: int, sms: int = 148) -> int:
+    """Cluster size (= split-K factor: 1, 2, 4 or 8) of the decode GEMM whose split-K sum happens inside the
+    kernel (`ops.decode_linear`): double it while the grid still fits the resident CTA slots (two CTAs per SM
+    up to 64 tokens, one above) and every split keeps at least two 64-wide k-blocks."""
+    slots = sms * (2 if tokens <= 64 else 1)
+    kb = max(1, k // 64)
+    s = 1
+    while s < 8 and tiles * s * 2 <= slots and kb // (s * 2) >= 2:
+        s *= 2
+    return s
+
+
 class LayerWeights:
     __slots__ = ("qkv", "o", "gate_up", "down", "input_norm", "post_norm", "q_norm", "k_norm", "qkv_bias", "o_bias",
                  "sinks", "router", "router_bias", "gate_up_bias", "down_bias")
@@ -56,8 +69,11 @@ class TransformerLM:
     """Weights + forward passes of one tensor-parallel rank."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], tp: Optional[TPGroup] = None,
-                 device=None, moe_parallel: str = "ep"):
+                 device=None, moe_parallel: str = "ep", force_fused: bool = False):
         self.cfg = cfg
+        # force_fused: take the peer-memory (push + reduce) kernels even with one rank, whose only peer is
+        # then this GPU itself (single-GPU profiles of the multi-GPU decode path)
+        self.force_fused = force_fused
         self.tp = tp or TPGroup.single()
         self.device = torch.device(device if device is not None else weights["tok_embedding"].device)
         world, rank = self.tp.world_size, self.tp.rank
@@ -115,6 +131,8 @@ class TransformerLM:
         self.split_qkv = pick_splits(self.layers[0].qkv.shape[0], H)
         self.split_o = pick_splits(H, self.layers[0].o.shape[1])
         self.split_down = 1 if cfg.is_moe else pick_splits(H, self.layers[0].down.shape[1])
+        # NKIPY_B200_DECODE_GEMM=legacy: persistent split-K GEMMs that leave fp32 partials to the next kernel
+        self.cluster_gemm = os.environ.get("NKIPY_B200_DECODE_GEMM", "cluster") != "legacy"
         self.split_gate_up = 1
         if not cfg.is_moe:
             two_i = self.layers[0].gate_up.shape[0]
@@ -138,11 +156,26 @@ class TransformerLM:
         return n * 2
 
     # ------------------------------------------------------------------ FFN
+    def _csplits(self, w: torch.Tensor, tokens: int, gated: bool = False) -> int:
+        """Cluster split factor for a decode GEMM with this weight and token count (cached per shape)."""
+        key = (w.shape[0], w.shape[1], tokens, gated)
+        cache = self.__dict__.setdefault("_csplit_cache", {})
+        if key not in cache:
+            tiles = (w.shape[0] // 2 + 63) // 64 if gated else (w.shape[0] + 127) // 128
+            cache[key] = pick_cluster_splits(tiles, w.shape[1], tokens)
+        return cache[key]
+
     def _ffn_decode(self, lw: LayerWeights, normed: torch.Tensor, resid: torch.Tensor, next_norm: torch.Tensor):
         """Returns (new residual, normed for the next block)."""
         cfg = self.cfg
         if cfg.is_moe:
             return self._moe.forward_add_rmsnorm(lw, normed, resid, next_norm)
+        T = normed.shape[0]
+        if self.cluster_gemm and T <= 128 and normed.is_cuda:
+            # gate / up with the split-K sum and SwiGLU inside one kernel
+            act = ops.decode_linear(normed, lw.gate_up, gated=True, splits=self._csplits(lw.gate_up, T, True),
+                                    act_limit=cfg.swiglu_limit, act_alpha=cfg.swiglu_alpha)
+            return self._row_parallel_reduce(act, lw.down, self._csplits(lw.down, T), resid, next_norm, None)
         if cfg.swiglu_limit <= 0 and self.split_gate_up == 1:
             act = ops.linear(normed, lw.gate_up, gated=True)
         elif self.split_gate_up > 1:
@@ -156,7 +189,10 @@ class TransformerLM:
     def _row_parallel_reduce(self, x, w, splits, resid, next_norm, bias):
         """Row-parallel GEMM + sum over ranks + residual + next RMSNorm (decode-sized M)."""
         cfg = self.cfg
-        if self.tp.world_size == 1:
+        if self.tp.world_size == 1 and not (self.force_fused and getattr(self.tp, "fused", None) is not None):
+            if self.cluster_gemm and x.shape[0] <= 128 and x.is_cuda:
+                h = ops.decode_linear(x, w, splits=splits, bias=bias, residual=resid)
+                return h, ops.rmsnorm(h, next_norm, cfg.rms_eps)
             if splits > 1:
                 parts = ops.linear(x, w, splits=splits)
                 return ops.add_rmsnorm(None, next_norm, residual_in=resid, partials=parts, bias=bias,
@@ -190,17 +226,26 @@ class TransformerLM:
         else:
             resid, normed = inputs
         taps = [] if return_hidden else None
+        T = normed.shape[0]
+        cluster = self.cluster_gemm and T <= 128 and normed.is_cuda and self.d in (64, 128)
         for i, lw in enumerate(self.layers):
-            if self.split_qkv > 1:
-                qkv = ops.linear(normed, lw.qkv, splits=self.split_qkv)
+            if cluster:
+                # QKV projection, QK-norm, RoPE and the cache append in one launch
+                q = ops.qkv_rope_append(normed, lw.qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq,
+                                        self.nkv, self.d, splits=self._csplits(lw.qkv, T), bias=lw.qkv_bias,
+                                        q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_eps)
             else:
-                qkv = ops.linear(normed, lw.qkv)
-            q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq, self.nkv,
-                                   self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
-                                   norm_eps=cfg.rms_eps)
+                if self.split_qkv > 1:
+                    qkv = ops.linear(normed, lw.qkv, splits=self.split_qkv)
+                else:
+                    qkv = ops.linear(normed, lw.qkv)
+                q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq, self.nkv,
+                                       self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
+                                       norm_eps=cfg.rms_eps)
             attn = ops.paged_attn_decode(q, cache.k[i], cache.v[i], block_table, context_lens, self.scale,
                                          q_len=q_len, window=cfg.window_for_layer(i), sinks=lw.sinks)
-            resid, normed = self._row_parallel_reduce(attn, lw.o, self.split_o, resid, lw.post_norm, lw.o_bias)
+            split_o = self._csplits(lw.o, T) if cluster else self.split_o
+            resid, normed = self._row_parallel_reduce(attn, lw.o, split_o, resid, lw.post_norm, lw.o_bias)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
             resid, normed = self._ffn_decode(lw, normed, resid, nxt)
             if taps is not None:

@@ -27,7 +27,7 @@ from . import _lib
 from ._lib import KernelLibraryError, device_status, raise_on_device_error
 
 __all__ = [
-    "linear", "reduce_partials", "rmsnorm", "add_rmsnorm", "silu_mul", "embedding", "rope_kv_append",
+    "linear", "decode_linear", "qkv_rope_append", "reduce_partials", "rmsnorm", "add_rmsnorm", "silu_mul", "embedding", "rope_kv_append",
     "argmax", "sample", "decode_advance", "router_topk", "moe_dispatch", "grouped_linear", "moe_combine", "paged_attn_decode", "flash_attn_prefill", "rope_table",
     "KernelLibraryError", "device_status", "raise_on_device_error", "native_available", "launch_count",
     "reset_launch_count",
@@ -186,6 +186,91 @@ def linear(
     _lib.check(rc, "nkb_gemm_bf16")
     _launches += 1
     return out_view
+
+
+def decode_linear(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    *,
+    splits: int = 1,
+    gated: bool = False,
+    bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    ctas_per_sm: int = 2,
+    act_limit: float = 0.0,
+    act_alpha: float = 1.702,
+) -> torch.Tensor:
+    """``y = x @ w.T`` for a decode-sized batch (at most 128 rows) with the split-K reduction inside the
+    kernel: the `splits` CTAs of one 128-feature tile form a cluster and exchange their partial sums
+    through distributed shared memory, so the result is final bf16 (csrc/kernels/gemm_decode.cu).
+    gated: w holds [gate; up] rows and the result is ``silu(x @ gate.T) * (x @ up.T)`` (act_limit > 0:
+    the clamped form ``(up + 1) * gate * sigmoid(act_alpha * gate)``); bias then is [gate bias; up bias].
+    splits is rounded down to a power of two (at most 8)."""
+    M, K = x.shape
+    N = w.shape[0] // 2 if gated else w.shape[0]
+    if not _native(x) or M > 128:
+        if gated and (act_limit > 0 or bias is not None):
+            return silu_mul(linear(x, w, bias=bias), limit=act_limit, alpha=act_alpha, out=out)
+        return linear(x, w, bias=bias, residual=residual, out=out, gated=gated)
+    global _launches
+    _check_bf16(x, w, bias, residual)
+    if x.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError("decode_linear needs K-contiguous operands")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    block_n = 32 if M <= 32 else (64 if M <= 64 else 128)
+    rc = _lib.lib().nkb_decode_gemm(w.data_ptr(), x.data_ptr(), out.data_ptr(), N, M, K, w.stride(0), x.stride(0),
+                                    out.stride(0), int(splits), 1 if gated else 0, N if gated else 0, _ptr(bias),
+                                    _ptr(residual), float(act_limit), float(act_alpha), block_n, int(ctas_per_sm),
+                                    _stream())
+    _lib.check(rc, "nkb_decode_gemm")
+    _launches += 1
+    return out
+
+
+def qkv_rope_append(
+    x: torch.Tensor,
+    w_qkv: torch.Tensor,
+    positions: torch.Tensor,
+    slots: Optional[torch.Tensor],
+    cos_sin: Optional[torch.Tensor],
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    nq: int,
+    nkv: int,
+    head_dim: int,
+    *,
+    splits: int = 1,
+    bias: Optional[torch.Tensor] = None,
+    q_norm_w: Optional[torch.Tensor] = None,
+    k_norm_w: Optional[torch.Tensor] = None,
+    norm_eps: float = 1e-6,
+    q_out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """The fused QKV projection of a decode step in one launch: ``x @ w_qkv.T`` (+ bias), per-head
+    QK-norm, RoPE, K / V written to their cache slots; returns the rotated queries [T, nq * head_dim].
+    Equivalent to `linear` followed by `rope_kv_append`."""
+    T, K = x.shape
+    if not _native(x) or T > 128 or head_dim not in (64, 128):
+        qkv = linear(x, w_qkv, swap=True) if _native(x) else linear(x, w_qkv)
+        return rope_kv_append(qkv, positions, slots, cos_sin, k_cache, v_cache, nq, nkv, head_dim, bias=bias,
+                              q_norm_w=q_norm_w, k_norm_w=k_norm_w, norm_eps=norm_eps, q_out=q_out)
+    global _launches
+    _check_bf16(x, w_qkv, bias, q_norm_w, k_norm_w)
+    if w_qkv.shape[0] != (nq + 2 * nkv) * head_dim:
+        raise ValueError("w_qkv rows must be (nq + 2 * nkv) * head_dim")
+    if q_out is None:
+        q_out = torch.empty((T, nq * head_dim), dtype=torch.bfloat16, device=x.device)
+    block_n = 32 if T <= 32 else (64 if T <= 64 else 128)
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    rc = _lib.lib().nkb_decode_gemm_rope(
+        w_qkv.data_ptr(), x.data_ptr(), T, K, w_qkv.stride(0), x.stride(0), int(splits), _ptr(bias), _ptr(positions),
+        _ptr(slots), _ptr(cos_sin), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), q_out.data_ptr(),
+        k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv, head_dim, max_pos, k_cache.shape[2], block_n, _stream())
+    _lib.check(rc, "nkb_decode_gemm_rope")
+    _launches += 1
+    return q_out
 
 
 def reduce_partials(partials: torch.Tensor, residual: Optional[torch.Tensor] = None,
@@ -597,6 +682,21 @@ def pick_kv_splits(ctas: int, max_pages: int, sms: int = 148) -> int:
     return max(s, 1)
 
 
+_DECODE_SCRATCH = {}
+
+
+def _decode_scratch(device: torch.device, floats: int) -> torch.Tensor:
+    """Split-KV scratch of the decode attention, one per (device, stream): it starts with the arrival
+    counters of the split merge, which must be zero before the first call (the merging CTA resets them),
+    so the buffer is zero-filled once and then reused by every call on that stream."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _DECODE_SCRATCH.get(key)
+    if buf is None or buf.numel() < floats:
+        buf = torch.zeros((int(floats),), dtype=torch.float32, device=device)
+        _DECODE_SCRATCH[key] = buf
+    return buf
+
+
 def paged_attn_decode(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -645,14 +745,14 @@ def paged_attn_decode(
     if num_splits > 1:
         need = L.nkb_paged_attn_decode_scratch_floats(B, q_len, nq, D, num_splits)
         if scratch is None or scratch.numel() < need:
-            scratch = torch.empty((need,), dtype=torch.float32, device=q.device)
+            scratch = _decode_scratch(q.device, need)
     rc = L.nkb_paged_attn_decode(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), context_lens.data_ptr(),
         out.data_ptr(), _ptr(scratch), B, q_len, nq, nkv, D, bs, k_cache.shape[0], block_table.stride(0),
         float(scale), int(window), _ptr(sinks), num_splits, _stream(),
     )
     _lib.check(rc, "nkb_paged_attn_decode")
-    _launches += 2 if num_splits > 1 else 1
+    _launches += 1
     return out
 
 

@@ -39,6 +39,14 @@ _SIGNATURES = {
                                  _P, _P, _P]),
     "nkb_moe_combine": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P, _P]),
     "nkb_gemm_effective_splits": (c_int, [c_int, c_int]),
+    "nkb_decode_gemm_splits": (c_int, [c_int, c_int, c_int]),
+    "nkb_decode_gemm": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
+                                c_int, _P, _P, c_float, c_float, c_int, c_int, _P]),
+    "nkb_decode_gemm_push": (c_int, [_P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P, c_int,
+                                     ctypes.POINTER(_P), ctypes.POINTER(_P), c_int, c_int, _P, _P]),
+    "nkb_decode_gemm_rope": (c_int, [_P, _P, c_int, c_int, c_longlong, c_longlong, c_int, _P, _P, _P, _P, _P, _P,
+                                     c_float, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
+    "nkb_noalloc_status": (c_int, [c_int]),
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_add_rmsnorm": (c_int, [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_silu_mul": (c_int, [_P, _P, c_int, c_int, c_float, c_float, _P]),
@@ -81,14 +89,20 @@ def lib():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
-        if os.environ.get("NKIPY_B200_AUTOBUILD", "1") == "1":
-            from ._build import build
+    from . import _build
 
-            build()
-        if not LIB_PATH.exists():
+    # The signatures below are declared from the sources in the tree, so the binary must have been built
+    # from exactly those sources: a stale library would be handed shifted arguments.
+    if _build.is_stale():
+        if os.environ.get("NKIPY_B200_AUTOBUILD", "1") == "1":
+            try:
+                _build.build()          # takes an inter-process lock; other ranks wait and then find it fresh
+            except RuntimeError as e:
+                raise KernelLibraryError(f"the kernel library is missing or stale and could not be rebuilt: {e}")
+        if _build.is_stale():
             raise KernelLibraryError(
-                f"{LIB_PATH} not found: run `python -m nkipy_b200.ops._build` (needs nvcc) first"
+                f"{LIB_PATH} is missing or was built from other sources than csrc/kernels: "
+                "run `python -m nkipy_b200.ops._build` (needs nvcc) first"
             )
     handle = ctypes.CDLL(str(LIB_PATH))
     for name, (res, args) in _SIGNATURES.items():

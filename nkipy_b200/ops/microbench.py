@@ -19,8 +19,8 @@ import sys
 
 import torch
 
-from . import (add_rmsnorm, flash_attn_prefill, grouped_linear, linear, moe_combine, moe_dispatch, paged_attn_decode,
-               router_topk)
+from . import (add_rmsnorm, decode_linear, flash_attn_prefill, grouped_linear, linear, moe_combine, moe_dispatch,
+               paged_attn_decode, router_topk)
 
 _FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -84,21 +84,65 @@ def _sets_for(bytes_per_set, want):
 
 
 # --------------------------------------------------------------------------- cases
-def case_gemm_decode(name, features, k, tokens, splits, gated, args):
-    if args.splits > 0 and not gated:
+def case_gemm_decode(name, features, k, tokens, splits, gated, args, row_parallel=False):
+    """One decode projection.  --impl splitk: the persistent GEMM (fp32 split-K partials left to the next
+    kernel); --impl cluster: the cluster GEMM that sums the splits through distributed shared memory and
+    applies the epilogue itself.  --tp N takes the per-rank shard of an N-way tensor-parallel layer."""
+    if args.splits > 0 and (not gated or args.impl == "cluster"):
         splits = args.splits
     if args.tokens > 0:
         tokens = args.tokens
+    if args.tp > 1:
+        if row_parallel:
+            k //= args.tp
+        else:
+            features //= args.tp
     wrows = features * (2 if gated else 1)
     nbytes = wrows * k * 2
-    sets = _sets_for(nbytes, args.sets)
+    sets = _sets_for(nbytes, max(args.sets, 2))
     ws = [_bf16(wrows, k, scale=0.02) for _ in range(sets)]
     x = _bf16(tokens, k)
-    fns = [lambda w=w: linear(x, w, splits=splits, gated=gated) for w in ws]
+    if args.impl == "cluster":
+        fns = [lambda w=w: decode_linear(x, w, splits=splits, gated=gated) for w in ws]
+        out_bytes = tokens * features * 2
+    else:
+        fns = [lambda w=w: linear(x, w, splits=splits, gated=gated) for w in ws]
+        out_bytes = tokens * features * (4 * splits if splits > 1 else 2)
     us = _time(fns, args.iters, args.warmup, not args.no_graph)
-    return dict(case=name, us=us, bytes=nbytes + tokens * k * 2 + tokens * features * (4 * splits if splits > 1 else 2),
+    return dict(case=name, us=us, bytes=nbytes + tokens * k * 2 + out_bytes,
                 flops=2.0 * tokens * wrows * k, shape=dict(features=features, k=k, tokens=tokens, splits=splits,
-                                                           gated=gated, sets=sets))
+                                                           gated=gated, sets=sets, impl=args.impl, tp=args.tp))
+
+
+def case_gemm_decode_sweep(args):
+    """Both implementations of the four decode projections of Llama-3-8B at tp = 1 and tp = 8 over a range of
+    split factors; prints one compact line per point (us per launch and fraction of the measured copy
+    bandwidth) and returns the last point."""
+    import copy
+
+    pk = peaks()
+    last = None
+    shapes = [("qkv", 6144, 4096, False, False), ("o", 4096, 4096, False, True),
+              ("gate-up", 14336, 4096, True, False), ("down", 4096, 14336, False, True)]
+    for tp in (1, 8):
+        for nm, feat, k, gated, rowp in shapes:
+            for impl in ("splitk", "cluster"):
+                cands = (1, 2, 4, 8) if impl == "cluster" else ((1,) if gated else (1, 4, 6, 8))
+                for sp in cands:
+                    a = copy.copy(args)
+                    a.impl, a.tp, a.splits, a.tokens = impl, tp, sp, 64
+                    torch.manual_seed(0)
+                    try:
+                        r = case_gemm_decode(f"gemm-decode-{nm}", feat, k, 64, sp, gated, a, rowp)
+                    except Exception as e:  # noqa: BLE001 - a rejected configuration is reported, not fatal
+                        print(json.dumps(dict(case=nm, tp=tp, impl=impl, splits=sp, error=str(e)[:120])), flush=True)
+                        continue
+                    frac = r["bytes"] / r["us"] / 1e6 * 1e3 / pk["hbm_gbs"]
+                    print(json.dumps(dict(case=nm, tp=tp, impl=impl, splits=sp, us=round(r["us"], 2),
+                                          frac_hbm=round(frac, 3))), flush=True)
+                    last = r
+                    torch.cuda.empty_cache()
+    return last
 
 
 def case_gemm_prefill(args):
@@ -275,9 +319,10 @@ def case_addnorm(args):
 
 CASES = {
     "gemm-decode-qkv": lambda a: case_gemm_decode("gemm-decode-qkv", 6144, 4096, 64, 6, False, a),
-    "gemm-decode-o": lambda a: case_gemm_decode("gemm-decode-o", 4096, 4096, 64, 8, False, a),
+    "gemm-decode-o": lambda a: case_gemm_decode("gemm-decode-o", 4096, 4096, 64, 8, False, a, True),
     "gemm-decode-gate-up": lambda a: case_gemm_decode("gemm-decode-gate-up", 14336, 4096, 64, 1, True, a),
-    "gemm-decode-down": lambda a: case_gemm_decode("gemm-decode-down", 4096, 14336, 64, 8, False, a),
+    "gemm-decode-down": lambda a: case_gemm_decode("gemm-decode-down", 4096, 14336, 64, 8, False, a, True),
+    "gemm-decode-sweep": case_gemm_decode_sweep,
     "gemm-decode-lmhead": lambda a: case_gemm_decode("gemm-decode-lmhead", 128256, 4096, 64, 1, False, a),
     "gemm-prefill": case_gemm_prefill,
     "gemm-prefill-gated": case_gemm_prefill_gated,
@@ -302,12 +347,15 @@ def main(argv=None):
     ap.add_argument("--splits", type=int, default=0, help="override the split-K factor of the gemm-decode-* cases")
     ap.add_argument("--kv-splits", type=int, default=0, help="split-KV factor of attn-decode (0 = heuristic)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count of the gemm-decode-* cases")
+    ap.add_argument("--impl", default="cluster", choices=["cluster", "splitk"],
+                    help="gemm-decode-*: cluster = split-K summed inside the kernel, splitk = fp32 partials")
+    ap.add_argument("--tp", type=int, default=1, help="gemm-decode-*: per-rank shard of an N-way tensor-parallel layer")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a GPU", file=sys.stderr)
         return 2
     pk = peaks()
-    names = sorted(CASES) if args.case == "all" else [args.case]
+    names = sorted(c for c in CASES if c != "gemm-decode-sweep") if args.case == "all" else [args.case]
     for nm in names:
         torch.manual_seed(0)
         r = CASES[nm](args)

@@ -110,6 +110,10 @@ class FusedTP:
         self.done = torch.zeros((4,), dtype=torch.int32, device=dev)   # [producer, reduce0, reduce1, spare]
         self._parity = 0
         self.ops_issued = 0
+        # NKIPY_B200_DECODE_GEMM=legacy keeps the persistent split-K producer that pushes one partial per split
+        import os
+
+        self.cluster_splitk = os.environ.get("NKIPY_B200_DECODE_GEMM", "cluster") != "legacy"
         lib = _lib.lib()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         PP = ctypes.POINTER(P)
@@ -148,13 +152,25 @@ class FusedTP:
         if M > self.max_tokens or N != self.hidden:
             raise ValueError(f"FusedTP sized for [{self.max_tokens}, {self.hidden}], got [{M}, {N}]")
         lib = self._lib
+        block_n = 32 if M <= 32 else (64 if M <= 64 else 128)
+        stream = torch.cuda.current_stream().cuda_stream
+        n = self.tp.world_size
+        if self.cluster_splitk and M <= 128:
+            # split-K summed inside the producer (CTA clusters): exactly one bf16 partial leaves this rank
+            b = self._parity
+            self._parity ^= 1
+            self.ops_issued += 1
+            rc = lib.nkb_decode_gemm_push(w.data_ptr(), x.data_ptr(), N, M, K, w.stride(0), x.stride(0), N,
+                                          max(1, int(splits)), None if bias is None else bias.data_ptr(), block_n,
+                                          self._peer_out[b], self._peer_flag[b], n, self.tp.rank,
+                                          self.done.data_ptr(), stream)
+            _lib.check(rc, "nkb_decode_gemm_push")
+            ops._launches += 1
+            return self._reduce(b, n, M, resid, next_norm, eps, x.device)
         eff = lib.nkb_gemm_effective_splits(K, max(1, min(splits, self.max_splits)))
         b = self._parity
         self._parity ^= 1
         self.ops_issued += 1
-        n = self.tp.world_size
-        block_n = 32 if M <= 32 else (64 if M <= 64 else 128)
-        stream = torch.cuda.current_stream().cuda_stream
         rc = lib.nkb_gemm_bf16_push(w.data_ptr(), x.data_ptr(), N, M, K, w.stride(0), x.stride(0), N, eff,
                                     None if bias is None else bias.data_ptr(), block_n, self._peer_out[b],
                                     self._peer_flag[b], n, self.tp.rank, self.done.data_ptr(), stream)

@@ -117,3 +117,53 @@ def test_perfect_drafter_accepts_everything_cpu():
     out = spec.generate(prompts, 13)[0]
     assert out == ref
     assert spec.stats.mean_acceptance > 3.0
+
+
+def test_uneven_acceptance_does_not_outrun_reserved_blocks_cpu():
+    """Batch of two: one sequence accepts every draft, the other none.  The fast one finishes many steps
+    before the slow one and must stop advancing; before the fix its committed length kept growing by
+    K + 1 per step and ran past the cache blocks reserved for it."""
+    K, new_tokens = 4, 40
+    cfg, w, target, drafter = _build("cpu", K)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab_size, (17,), generator=g).tolist() for _ in range(2)]
+    max_seq = 17 + new_tokens + 8
+    # the oracle must stay right for sequence 0 for as long as the slow sequence keeps the loop alive
+    long_new = new_tokens * (K + 1) + 2 * K
+    eng = GenerationEngine(target, max_batch=2, max_seq_len=17 + long_new + 8, use_cuda_graph=False)
+    ref_long = eng.generate(prompts, long_new)
+    ref = [r[:new_tokens] for r in ref_long]
+    full = [prompts[b] + ref_long[b] for b in range(2)]
+    spec = SpeculativeEngine(target, drafter, max_batch=2, max_seq_len=max_seq)
+    W = spec.W
+
+    class HalfOracle:
+        """Knows the continuation of sequence 0 only; proposes a never-matching token for sequence 1."""
+        ecfg = drafter.ecfg
+        d2t = torch.zeros_like(drafter.d2t)
+        lm = drafter.lm
+
+        def new_cache(self, like):
+            return drafter.new_cache(like)
+
+        def prefill(self, *a, **k):
+            return None
+
+        def step(self, token_ids, hidden3, is_mask, positions, slots, cache, block_table, context_lens, q_len):
+            V = cfg.vocab_size
+            logits = torch.zeros((positions.numel(), V))
+            for i, p in enumerate(positions.tolist()):
+                b = i // W
+                if b == 0:
+                    t = full[0][p + 2] if p + 2 < len(full[0]) else 0
+                else:
+                    nxt = full[1][p + 2] if p + 2 < len(full[1]) else 0
+                    t = (nxt + 1) % V            # always wrong
+                logits[i, t] = 1.0
+            return logits.to(torch.bfloat16)
+
+    spec.drafter = HalfOracle()
+    out = spec.generate(prompts, new_tokens)
+    assert out == ref
+    # sequence 0 needs about new_tokens / (K + 1) steps, sequence 1 new_tokens: counted per live sequence
+    assert new_tokens - 1 <= spec.stats.steps <= new_tokens + new_tokens // (K + 1) + 1
