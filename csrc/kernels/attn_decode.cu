@@ -375,6 +375,26 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   return launch_pdl(paged_attn_decode_kernel<D, kDecWarps>, grid, dim3(kDecWarps * 32), size_t(smem), s, tk, tv, p);
 }
 
+// Warps per CTA: every warp streams its own pages through a private 3-stage ring (48 KB at D = 128), so an SM
+// holds four warps' rings whatever the CTA size.  The grid should fit the resident slots in one wave (a second,
+// partly filled wave costs as much as a full one): four-warp CTAs while there is at most one CTA per SM, two-warp
+// CTAs up to two per SM, one-warp CTAs (four per SM) beyond.
+static int dispatch_decode(int head_dim, long long ctas, int sms, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const DecodeParams& p, cudaStream_t s) {
+  const int warps = ctas <= sms ? 4 : (ctas <= 2LL * sms ? 2 : 1);
+  if (head_dim == 128) {
+    if (warps == 4) return launch_decode<128, 4>(tk, tv, p, s);
+    if (warps == 2) return launch_decode<128, 2>(tk, tv, p, s);
+    return launch_decode<128, 1>(tk, tv, p, s);
+  }
+  if (head_dim == 64) {
+    if (warps == 4) return launch_decode<64, 4>(tk, tv, p, s);
+    if (warps == 2) return launch_decode<64, 2>(tk, tv, p, s);
+    return launch_decode<64, 1>(tk, tv, p, s);
+  }
+  return -2;
+}
+
 }  // namespace nkb
 
 using namespace nkb;
@@ -418,12 +438,7 @@ extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const v
   if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
   if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // Many CTAs: two-warp CTAs (96 KB ring at D = 128) so two of them share an SM and one's
-  // prologue / merge overlaps the other's streaming; few CTAs: four warps each.
-  const bool small = (long long)batch * nkv * num_splits >= 2LL * num_sms();
-  if (head_dim == 128) return small ? launch_decode<128, 2>(tk, tv, p, s) : launch_decode<128, 4>(tk, tv, p, s);
-  if (head_dim == 64) return small ? launch_decode<64, 2>(tk, tv, p, s) : launch_decode<64, 4>(tk, tv, p, s);
-  return -2;
+  return dispatch_decode(head_dim, (long long)batch * nkv * num_splits, num_sms(), tk, tv, p, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -534,7 +549,5 @@ extern "C" int nkb_paged_attn_decode_noalloc(const void* q, const void* k_cache,
   const uint32_t box[4] = {64, uint32_t(kPage), 1, 1};
   if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
   if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
-  const bool small = (long long)batch * nkv * num_splits >= 2LL * d->sms;
-  if (head_dim == 128) return small ? launch_decode<128, 2>(tk, tv, p, s) : launch_decode<128, 4>(tk, tv, p, s);
-  return small ? launch_decode<64, 2>(tk, tv, p, s) : launch_decode<64, 4>(tk, tv, p, s);
+  return dispatch_decode(head_dim, (long long)batch * nkv * num_splits, d->sms, tk, tv, p, s);
 }

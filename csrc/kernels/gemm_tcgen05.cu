@@ -44,6 +44,75 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a
                     args, pa);
 }
 
+// Split-K with the fix-up epilogue (splitk_fix.cuh), decode orientation, two CTAs per SM.
+template <int BN, class Fix>
+static int launch_fix(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, const typename Fix::Args& fix,
+                      cudaStream_t stream) {
+  const int stage_bytes = kATileBytes + BN * kBlockK * 2;
+  const int extra = 1024 + (Fix::kind == FIX_PUSH ? 32 * kTileRows * 2 : 0);   // control + reduction scratch (+ staging)
+  const int budget = 113 * 1024 - 1024 - extra - 64;
+  int stages = budget / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return -3;
+  args.stages = stages;
+  const int smem = stages * stage_bytes + 1024 + extra + 64;
+  auto kernel = gemm_bf16_fix_kernel<BN, 2, Fix>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
+    if (e != cudaSuccess) return int(e);
+    attr_set[dev] = true;
+  }
+  const int total = args.num_row_tiles * args.splits;
+  const int cap = 2 * num_sms();
+  const int grid = total < cap ? total : cap;
+  return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb, args, fix);
+}
+
+// Common argument set-up of the fix-up launches: weights [rows, k] on the MMA row side, x [tokens, k].
+static int fix_setup(GemmArgs& args, FixCommon& c, CUtensorMap& ta, CUtensorMap& tb, const void* w, const void* x,
+                     int rows, int tokens, int k, long long ldw, long long ldx, int splits, int block_n,
+                     float* partials, unsigned int* counters, const void* bias) {
+  if (!status_word() && nkb_init() != 0) return -1;
+  if (rows <= 0 || tokens <= 0 || k <= 0 || (k & 7) || (ldw & 7) || (ldx & 7)) return -2;
+  if (tokens > block_n || !partials || !counters) return -2;
+  if (block_n != 32 && block_n != 64 && block_n != 128) return -2;
+  args = GemmArgs{};
+  args.rows = rows;
+  args.cols = tokens;
+  args.k = k;
+  args.kb_total = (k + kBlockK - 1) / kBlockK;
+  if (splits < 1) splits = 1;
+  if (splits > args.kb_total) splits = args.kb_total;
+  args.kb_per_split = (args.kb_total + splits - 1) / splits;
+  args.splits = (args.kb_total + args.kb_per_split - 1) / args.kb_per_split;
+  args.num_row_tiles = (rows + kTileRows - 1) / kTileRows;
+  args.num_col_tiles = 1;
+  args.transpose_out = 1;
+  args.out_fp32 = 1;
+  args.ldo = rows;
+  args.split_stride = (long long)tokens * rows;
+  args.out = partials;
+  args.status = status_word();
+  args.weights_operand = 0;
+  c.partials = partials;
+  c.tile_counters = counters;
+  c.ld = rows;
+  c.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  if (encode_tmap_bf16_2d(&ta, w, k, rows, ldw, kBlockK, kTileRows)) return -4;
+  if (encode_tmap_bf16_2d(&tb, x, k, tokens, ldx, kBlockK, block_n)) return -4;
+  return 0;
+}
+
+#define NKB_FIX_DISPATCH(FixT, fixargs)                                                   \
+  switch (block_n) {                                                                      \
+    case 32: return launch_fix<32, FixT>(ta, tb, args, fixargs, s);                       \
+    case 64: return launch_fix<64, FixT>(ta, tb, args, fixargs, s);                       \
+    default: return launch_fix<128, FixT>(ta, tb, args, fixargs, s);                      \
+  }
+
 template <int BN, int MINB>
 static int launch_grouped(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, const GroupArgs& grp,
                           int max_ctas, cudaStream_t stream) {
@@ -256,4 +325,104 @@ extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, 
     case 128: return launch_grouped<128, 1>(ta, tb, args, grp, num_sms(), s);
     default: return -2;
   }
+}
+
+
+// ---------------------------------------------------------------------------
+// Decode projections whose split-K sum and epilogue run inside the GEMM kernel (splitk_fix.cuh).
+// partials: fp32 scratch with room for splits * tokens * rows floats; counters: one zero-initialised
+// unsigned int per 128-row tile (they are left at zero).  Both may be shared by consecutive launches
+// of one stream.
+// ---------------------------------------------------------------------------
+extern "C" long long nkb_gemm_fix_scratch_floats(int rows, int tokens, int k, int splits) {
+  return (long long)nkb_gemm_effective_splits(k, splits) * tokens * rows;
+}
+
+// out[tokens, rows] = x @ w^T (+ bias) (+ residual)
+extern "C" int nkb_gemm_fix_store(const void* w, const void* x, void* out, int rows, int tokens, int k, long long ldw,
+                                  long long ldx, long long ldo, int splits, const void* bias, const void* residual,
+                                  float* partials, unsigned int* counters, int block_n, void* stream) {
+  GemmArgs args;
+  StoreFix::Args fx{};
+  CUtensorMap ta, tb;
+  if (int rc = fix_setup(args, fx.c, ta, tb, w, x, rows, tokens, k, ldw, ldx, splits, block_n, partials, counters, bias))
+    return rc;
+  fx.out = reinterpret_cast<__nv_bfloat16*>(out);
+  fx.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  fx.ldo = ldo;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  NKB_FIX_DISPATCH(StoreFix, fx)
+}
+
+// out[tokens, inter] = silu(x @ gate^T) * (x @ up^T), w = [gate; up] with inter rows each (inter % 128 == 0);
+// act_limit > 0 selects the clamped form; bias = [gate bias; up bias] or null.
+extern "C" int nkb_gemm_fix_swiglu(const void* w, const void* x, void* out, int inter, int tokens, int k,
+                                   long long ldw, long long ldx, long long ldo, int splits, const void* bias,
+                                   float act_limit, float act_alpha, float* partials, unsigned int* counters,
+                                   int block_n, void* stream) {
+  if (inter <= 0 || (inter % kTileRows)) return -2;
+  GemmArgs args;
+  SwigluFix::Args fx{};
+  CUtensorMap ta, tb;
+  if (int rc = fix_setup(args, fx.c, ta, tb, w, x, 2 * inter, tokens, k, ldw, ldx, splits, block_n, partials, counters,
+                         bias))
+    return rc;
+  fx.out = reinterpret_cast<__nv_bfloat16*>(out);
+  fx.ldo = ldo;
+  fx.inter = inter;
+  fx.act_limit = act_limit;
+  fx.act_alpha = act_alpha;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  NKB_FIX_DISPATCH(SwigluFix, fx)
+}
+
+// Fused QKV projection of a decode step: w [(nq + 2 nkv) * head_dim, k], head_dim 64 or 128.
+extern "C" int nkb_gemm_fix_rope(const void* w, const void* x, int tokens, int k, long long ldw, long long ldx,
+                                 int splits, const void* bias, const int* positions, const int* slots,
+                                 const float* cos_sin, const void* q_norm_w, const void* k_norm_w, float norm_eps,
+                                 void* q_out, void* k_cache, void* v_cache, int nq, int nkv, int head_dim, int max_pos,
+                                 int block_size, float* partials, unsigned int* counters, int block_n, void* stream) {
+  if (head_dim != 64 && head_dim != 128) return -2;
+  if (cos_sin && !positions) return -2;
+  GemmArgs args;
+  RopeFix::Args fx{};
+  CUtensorMap ta, tb;
+  if (int rc = fix_setup(args, fx.c, ta, tb, w, x, (nq + 2 * nkv) * head_dim, tokens, k, ldw, ldx, splits, block_n,
+                         partials, counters, bias))
+    return rc;
+  fx.positions = positions;
+  fx.slots = slots;
+  fx.cos_sin = cos_sin;
+  fx.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(q_norm_w);
+  fx.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(k_norm_w);
+  fx.q_out = reinterpret_cast<__nv_bfloat16*>(q_out);
+  fx.k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache);
+  fx.v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache);
+  fx.norm_eps = norm_eps;
+  fx.nq = nq; fx.nkv = nkv; fx.head_dim = head_dim; fx.max_pos = max_pos; fx.block_size = block_size;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  NKB_FIX_DISPATCH(RopeFix, fx)
+}
+
+// Row-parallel projection: the finished bf16 partial [tokens, rows] of this rank goes into slot [rank] of every
+// peer's partial array [n_peers, tokens, rows]; the last CTA bumps this rank's arrival counter on every peer.
+extern "C" int nkb_gemm_fix_push(const void* w, const void* x, int rows, int tokens, int k, long long ldw,
+                                 long long ldx, int splits, const void* bias, void* const* peer_out,
+                                 void* const* peer_flag, int n_peers, int rank, void* done_counter, float* partials,
+                                 unsigned int* counters, int block_n, void* stream) {
+  if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers || (rows & 7)) return -2;
+  GemmArgs args;
+  PushFix::Args fx{};
+  CUtensorMap ta, tb;
+  if (int rc = fix_setup(args, fx.c, ta, tb, w, x, rows, tokens, k, ldw, ldx, splits, block_n, partials, counters, bias))
+    return rc;
+  fx.push.n_peers = n_peers;
+  fx.push.rank = rank;
+  for (int i = 0; i < n_peers; ++i) {
+    fx.push.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(peer_out[i]);
+    fx.push.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
+  }
+  fx.push.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  NKB_FIX_DISPATCH(PushFix, fx)
 }

@@ -24,6 +24,7 @@
 #pragma once
 #include "common.cuh"
 #include "gemm_args.h"
+#include "splitk_fix.cuh"
 
 namespace nkb {
 
@@ -35,6 +36,7 @@ struct GemmCtrl {
   uint64_t tempty[2];
   uint32_t tmem_base;
   int abort;
+  int fix_last;   // split-K fix-up: this CTA arrived last at the tile's counter
 };
 
 __device__ __forceinline__ void decode_tile(const GemmArgs& a, int w, int& row_tile, int& col_tile, int& split) {
@@ -104,9 +106,12 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 
 // GROUPED selects the per-expert variant (3-D weight map, group offsets / tile list, expert
 // biases and the clamped activation); the plain variant compiles none of that.
-template <int BN, bool PUSH, bool GROUPED>
+// Fix selects a split-K fix-up epilogue (splitk_fix.cuh): the partial tiles go to fix.c.partials (the
+// launcher points args.out there) and the CTA that completes a tile's arrival counter finishes the tile.
+template <int BN, bool PUSH, bool GROUPED, class Fix = NoFix>
 __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
-                                               const PushArgs& push, const GroupArgs& grp) {
+                                               const PushArgs& push, const GroupArgs& grp,
+                                               const typename Fix::Args& fix = typename Fix::Args{}) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -118,8 +123,11 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * kBTileBytes;
   const int stages = args.stages;
   GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(tiles + stages * stage_bytes);
-  // push mode: [32 tokens][128 features] bf16 staging tile (one accumulator chunk) behind the control block
-  __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(ctrl) + 512);
+  // push mode: [32 tokens][128 features] bf16 staging tile (one accumulator chunk) behind the control block;
+  // fix-up mode: 512 bytes of reduction scratch first, then the staging tile
+  __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(ctrl) +
+                                                              (Fix::kind != FIX_NONE ? 1024 : 512));
+  float* fix_red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctrl) + 512);
 
   const int acc_cols = BN * (args.gated ? 2 : 1);
   uint32_t tmem_cols = 32;
@@ -436,8 +444,44 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
         }
       }
+      if constexpr (Fix::kind != FIX_NONE) {
+        // this CTA's partial of the tile is stored: count it, and finish the tile if it was the last one
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int pairs = Fix::kind == FIX_SWIGLU ? args.num_row_tiles / 2 : args.num_row_tiles;
+          unsigned int* ctr = fix.c.tile_counters + (rt % pairs);
+          const unsigned int target = unsigned(args.splits) * (Fix::kind == FIX_SWIGLU ? 2u : 1u);
+          const unsigned int old = atomicAdd(ctr, 1u);
+          const int last = old == target - 1u;
+          if (last) *ctr = 0u;   // all arrivals of this launch are in; the next launch starts from zero
+          ctrl->fix_last = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ctrl->fix_last) {
+          __threadfence();
+          const int pairs = Fix::kind == FIX_SWIGLU ? args.num_row_tiles / 2 : args.num_row_tiles;
+          run_fix<Fix>(fix, rt % pairs, Fix::kind == FIX_SWIGLU ? args.rows / 2 : args.rows, args.cols, args.splits,
+                       args.split_stride, stage_out, fix_red);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if constexpr (Fix::kind == FIX_PUSH) {
+      // same completion protocol as the push epilogue below: every CTA counts itself after its last tile, the
+      // last CTA of the grid publishes all peer stores with one system-scope fence and bumps the peers' flags
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        __threadfence();
+        const unsigned int old = atomicAdd(fix.push.done_counter, 1u);
+        if (old == gridDim.x - 1) {
+          *fix.push.done_counter = 0u;
+          __threadfence_system();
+          for (int pr = 0; pr < fix.push.n_peers; ++pr) atomicAdd_system(fix.push.peer_flag[pr], 1u);
+        }
+      }
     }
     if constexpr (PUSH) {
       // all peer stores of this CTA are issued: publish them, count the CTA, and let the
@@ -475,6 +519,13 @@ __global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs args, const PushArgs push) {
   gemm_bf16_body<BN, PUSH, false>(tmA, tmB, args, push, GroupArgs{});
+}
+
+template <int BN, int MINB, class Fix>
+__global__ void __launch_bounds__(kGemmThreads, MINB)
+gemm_bf16_fix_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmArgs args, const typename Fix::Args fix) {
+  gemm_bf16_body<BN, false, false, Fix>(tmA, tmB, args, PushArgs{}, GroupArgs{}, fix);
 }
 
 template <int BN, int MINB>

@@ -131,8 +131,10 @@ class TransformerLM:
         self.split_qkv = pick_splits(self.layers[0].qkv.shape[0], H)
         self.split_o = pick_splits(H, self.layers[0].o.shape[1])
         self.split_down = 1 if cfg.is_moe else pick_splits(H, self.layers[0].down.shape[1])
-        # NKIPY_B200_DECODE_GEMM=legacy: persistent split-K GEMMs that leave fp32 partials to the next kernel
-        self.cluster_gemm = os.environ.get("NKIPY_B200_DECODE_GEMM", "cluster") != "legacy"
+        # "legacy": persistent split-K GEMMs that leave fp32 partials to the next kernel; otherwise the projections
+        # finish their own split-K sum and apply RoPE / SwiGLU / the push themselves (ops.DECODE_GEMM_IMPL)
+        self.cluster_gemm = ops.DECODE_GEMM_IMPL != "legacy"
+        self.fix_gemm = ops.DECODE_GEMM_IMPL == "fixup"
         self.split_gate_up = 1
         if not cfg.is_moe:
             two_i = self.layers[0].gate_up.shape[0]
@@ -161,8 +163,11 @@ class TransformerLM:
         key = (w.shape[0], w.shape[1], tokens, gated)
         cache = self.__dict__.setdefault("_csplit_cache", {})
         if key not in cache:
-            tiles = (w.shape[0] // 2 + 63) // 64 if gated else (w.shape[0] + 127) // 128
-            cache[key] = pick_cluster_splits(tiles, w.shape[1], tokens)
+            if self.fix_gemm:
+                cache[key] = pick_splits(w.shape[0], w.shape[1])
+            else:
+                tiles = (w.shape[0] // 2 + 63) // 64 if gated else (w.shape[0] + 127) // 128
+                cache[key] = pick_cluster_splits(tiles, w.shape[1], tokens)
         return cache[key]
 
     def _ffn_decode(self, lw: LayerWeights, normed: torch.Tensor, resid: torch.Tensor, next_norm: torch.Tensor):

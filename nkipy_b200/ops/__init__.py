@@ -188,6 +188,30 @@ def linear(
     return out_view
 
 
+# How the decode projections sum their split-K partials (NKIPY_B200_DECODE_GEMM):
+#   fixup   (default) inside the persistent GEMM: the CTA that arrives last at a tile's counter sums the
+#           partials and applies the epilogue (csrc/kernels/splitk_fix.cuh)
+#   cluster thread-block clusters exchanging partials through distributed shared memory
+#           (csrc/kernels/gemm_decode.cu)
+#   legacy  fp32 partials left to the next kernel of the chain
+DECODE_GEMM_IMPL = os.environ.get("NKIPY_B200_DECODE_GEMM", "fixup")
+_FIX_SCRATCH = {}
+_FIX_COUNTERS = 4096
+
+
+def fix_scratch(device: torch.device, floats: int):
+    """(partials fp32, counters int32) scratch of the fix-up GEMMs, one per (device, stream), grown on demand.
+    Counters start at zero and every launch leaves them at zero, so consecutive launches share them."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ent = _FIX_SCRATCH.get(key)
+    if ent is None or ent[0].numel() < floats:
+        part = torch.empty((max(int(floats), 1 << 20),), dtype=torch.float32, device=device)
+        ctr = ent[1] if ent is not None else torch.zeros((_FIX_COUNTERS,), dtype=torch.int32, device=device)
+        ent = (part, ctr)
+        _FIX_SCRATCH[key] = ent
+    return ent
+
+
 def decode_linear(
     x: torch.Tensor,
     w: torch.Tensor,
@@ -200,10 +224,13 @@ def decode_linear(
     ctas_per_sm: int = 2,
     act_limit: float = 0.0,
     act_alpha: float = 1.702,
+    impl: Optional[str] = None,
 ) -> torch.Tensor:
     """``y = x @ w.T`` for a decode-sized batch (at most 128 rows) with the split-K reduction inside the
-    kernel: the `splits` CTAs of one 128-feature tile form a cluster and exchange their partial sums
-    through distributed shared memory, so the result is final bf16 (csrc/kernels/gemm_decode.cu).
+    kernel, so the result is final bf16.  impl "fixup" (default, see DECODE_GEMM_IMPL): the CTA that
+    completes a tile's arrival counter sums the fp32 partials (csrc/kernels/splitk_fix.cuh); "cluster":
+    the `splits` CTAs of one 128-feature tile form a cluster and exchange their partial sums through
+    distributed shared memory (csrc/kernels/gemm_decode.cu; splits rounded down to a power of two <= 8).
     gated: w holds [gate; up] rows and the result is ``silu(x @ gate.T) * (x @ up.T)`` (act_limit > 0:
     the clamped form ``(up + 1) * gate * sigmoid(act_alpha * gate)``); bias then is [gate bias; up bias].
     splits is rounded down to a power of two (at most 8)."""
@@ -220,6 +247,22 @@ def decode_linear(
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     block_n = 32 if M <= 32 else (64 if M <= 64 else 128)
+    impl = DECODE_GEMM_IMPL if impl is None else impl
+    if impl != "cluster" and (not gated or N % 128 == 0) and (2 * N if gated else N) <= 128 * _FIX_COUNTERS:
+        L = _lib.lib()
+        rows = 2 * N if gated else N
+        part, ctr = fix_scratch(x.device, L.nkb_gemm_fix_scratch_floats(rows, M, K, int(splits)))
+        if gated:
+            rc = L.nkb_gemm_fix_swiglu(w.data_ptr(), x.data_ptr(), out.data_ptr(), N, M, K, w.stride(0), x.stride(0),
+                                       out.stride(0), int(splits), _ptr(bias), float(act_limit), float(act_alpha),
+                                       part.data_ptr(), ctr.data_ptr(), block_n, _stream())
+        else:
+            rc = L.nkb_gemm_fix_store(w.data_ptr(), x.data_ptr(), out.data_ptr(), N, M, K, w.stride(0), x.stride(0),
+                                      out.stride(0), int(splits), _ptr(bias), _ptr(residual), part.data_ptr(),
+                                      ctr.data_ptr(), block_n, _stream())
+        _lib.check(rc, "nkb_gemm_fix")
+        _launches += 1
+        return out
     rc = _lib.lib().nkb_decode_gemm(w.data_ptr(), x.data_ptr(), out.data_ptr(), N, M, K, w.stride(0), x.stride(0),
                                     out.stride(0), int(splits), 1 if gated else 0, N if gated else 0, _ptr(bias),
                                     _ptr(residual), float(act_limit), float(act_alpha), block_n, int(ctas_per_sm),
@@ -247,6 +290,7 @@ def qkv_rope_append(
     k_norm_w: Optional[torch.Tensor] = None,
     norm_eps: float = 1e-6,
     q_out: Optional[torch.Tensor] = None,
+    impl: Optional[str] = None,
 ) -> torch.Tensor:
     """The fused QKV projection of a decode step in one launch: ``x @ w_qkv.T`` (+ bias), per-head
     QK-norm, RoPE, K / V written to their cache slots; returns the rotated queries [T, nq * head_dim].
@@ -264,6 +308,18 @@ def qkv_rope_append(
         q_out = torch.empty((T, nq * head_dim), dtype=torch.bfloat16, device=x.device)
     block_n = 32 if T <= 32 else (64 if T <= 64 else 128)
     max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    impl = DECODE_GEMM_IMPL if impl is None else impl
+    if impl != "cluster" and w_qkv.shape[0] <= 128 * _FIX_COUNTERS:
+        L = _lib.lib()
+        part, ctr = fix_scratch(x.device, L.nkb_gemm_fix_scratch_floats(w_qkv.shape[0], T, K, int(splits)))
+        rc = L.nkb_gemm_fix_rope(
+            w_qkv.data_ptr(), x.data_ptr(), T, K, w_qkv.stride(0), x.stride(0), int(splits), _ptr(bias),
+            _ptr(positions), _ptr(slots), _ptr(cos_sin), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps),
+            q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv, head_dim, max_pos, k_cache.shape[2],
+            part.data_ptr(), ctr.data_ptr(), block_n, _stream())
+        _lib.check(rc, "nkb_gemm_fix_rope")
+        _launches += 1
+        return q_out
     rc = _lib.lib().nkb_decode_gemm_rope(
         w_qkv.data_ptr(), x.data_ptr(), T, K, w_qkv.stride(0), x.stride(0), int(splits), _ptr(bias), _ptr(positions),
         _ptr(slots), _ptr(cos_sin), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), q_out.data_ptr(),
@@ -674,11 +730,13 @@ def _ref_attention(q, k, v, scale, q_pos0, causal, window, sinks):
 
 
 def pick_kv_splits(ctas: int, max_pages: int, sms: int = 148) -> int:
-    """KV split count for decode attention: no split once there are two CTAs per SM;
-    otherwise split until there are, keeping at least 8 pages per split."""
-    if ctas >= 2 * sms:
+    """KV split count for decode attention.  Every warp of the kernel streams its own pages, an SM holds four
+    warps, and the kernel picks 4 / 2 / 1 warps per CTA so that the grid stays within one wave.  Splitting
+    only pays while the unsplit grid leaves SMs without a CTA: then split until about one four-warp CTA sits
+    on every SM, keeping at least two pages per warp."""
+    if ctas >= sms:
         return 1
-    s = min(-(-2 * sms // ctas), max(max_pages // 8, 1), 16)
+    s = min(sms // ctas, max(max_pages // 8, 1), 16)
     return max(s, 1)
 
 

@@ -47,6 +47,15 @@ _SIGNATURES = {
     "nkb_decode_gemm_rope": (c_int, [_P, _P, c_int, c_int, c_longlong, c_longlong, c_int, _P, _P, _P, _P, _P, _P,
                                      c_float, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "nkb_noalloc_status": (c_int, [c_int]),
+    "nkb_gemm_fix_scratch_floats": (c_longlong, [c_int, c_int, c_int, c_int]),
+    "nkb_gemm_fix_store": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P, _P,
+                                   _P, _P, c_int, _P]),
+    "nkb_gemm_fix_swiglu": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P,
+                                    c_float, c_float, _P, _P, c_int, _P]),
+    "nkb_gemm_fix_rope": (c_int, [_P, _P, c_int, c_int, c_longlong, c_longlong, c_int, _P, _P, _P, _P, _P, _P, c_float,
+                                  _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P]),
+    "nkb_gemm_fix_push": (c_int, [_P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_int, _P, ctypes.POINTER(_P),
+                                  ctypes.POINTER(_P), c_int, c_int, _P, _P, _P, c_int, _P]),
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_add_rmsnorm": (c_int, [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_silu_mul": (c_int, [_P, _P, c_int, c_int, c_float, c_float, _P]),

@@ -88,7 +88,7 @@ def case_gemm_decode(name, features, k, tokens, splits, gated, args, row_paralle
     """One decode projection.  --impl splitk: the persistent GEMM (fp32 split-K partials left to the next
     kernel); --impl cluster: the cluster GEMM that sums the splits through distributed shared memory and
     applies the epilogue itself.  --tp N takes the per-rank shard of an N-way tensor-parallel layer."""
-    if args.splits > 0 and (not gated or args.impl == "cluster"):
+    if args.splits > 0 and (not gated or args.impl != "splitk"):
         splits = args.splits
     if args.tokens > 0:
         tokens = args.tokens
@@ -102,8 +102,8 @@ def case_gemm_decode(name, features, k, tokens, splits, gated, args, row_paralle
     sets = _sets_for(nbytes, max(args.sets, 2))
     ws = [_bf16(wrows, k, scale=0.02) for _ in range(sets)]
     x = _bf16(tokens, k)
-    if args.impl == "cluster":
-        fns = [lambda w=w: decode_linear(x, w, splits=splits, gated=gated) for w in ws]
+    if args.impl in ("cluster", "fixup"):
+        fns = [lambda w=w: decode_linear(x, w, splits=splits, gated=gated, impl=args.impl) for w in ws]
         out_bytes = tokens * features * 2
     else:
         fns = [lambda w=w: linear(x, w, splits=splits, gated=gated) for w in ws]
@@ -126,8 +126,8 @@ def case_gemm_decode_sweep(args):
               ("gate-up", 14336, 4096, True, False), ("down", 4096, 14336, False, True)]
     for tp in (1, 8):
         for nm, feat, k, gated, rowp in shapes:
-            for impl in ("splitk", "cluster"):
-                cands = (1, 2, 4, 8) if impl == "cluster" else ((1,) if gated else (1, 4, 6, 8))
+            for impl in ("splitk", "fixup", "cluster"):
+                cands = (2, 4, 8) if impl == "cluster" else ((1,) if gated and impl == "splitk" else (1, 4, 6, 8))
                 for sp in cands:
                     a = copy.copy(args)
                     a.impl, a.tp, a.splits, a.tokens = impl, tp, sp, 64
@@ -213,6 +213,8 @@ def case_gemm_ar(args):
 
 def case_attn_decode(args):
     B, ctx, nkv, nq, D = 64, 1056, 8, 32, 128
+    if args.tp > 1:                       # one rank's heads of an N-way tensor-parallel layer
+        nkv, nq = max(1, nkv // args.tp), nq // args.tp
     pages = (ctx + 31) // 32
     nb = B * pages
     per_set = 2 * nb * nkv * 32 * D * 2
@@ -347,8 +349,9 @@ def main(argv=None):
     ap.add_argument("--splits", type=int, default=0, help="override the split-K factor of the gemm-decode-* cases")
     ap.add_argument("--kv-splits", type=int, default=0, help="split-KV factor of attn-decode (0 = heuristic)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count of the gemm-decode-* cases")
-    ap.add_argument("--impl", default="cluster", choices=["cluster", "splitk"],
-                    help="gemm-decode-*: cluster = split-K summed inside the kernel, splitk = fp32 partials")
+    ap.add_argument("--impl", default="fixup", choices=["fixup", "cluster", "splitk"],
+                    help="gemm-decode-*: fixup / cluster = split-K summed inside the kernel (last-arriver fix-up / "
+                         "CTA clusters), splitk = fp32 partials left to the next kernel")
     ap.add_argument("--tp", type=int, default=1, help="gemm-decode-*: per-rank shard of an N-way tensor-parallel layer")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():

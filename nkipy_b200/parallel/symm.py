@@ -110,10 +110,10 @@ class FusedTP:
         self.done = torch.zeros((4,), dtype=torch.int32, device=dev)   # [producer, reduce0, reduce1, spare]
         self._parity = 0
         self.ops_issued = 0
-        # NKIPY_B200_DECODE_GEMM=legacy keeps the persistent split-K producer that pushes one partial per split
-        import os
+        # how the producer sums its split-K partials: see ops.DECODE_GEMM_IMPL ("legacy" pushes one partial per split)
+        from .. import ops as _ops
 
-        self.cluster_splitk = os.environ.get("NKIPY_B200_DECODE_GEMM", "cluster") != "legacy"
+        self.impl = _ops.DECODE_GEMM_IMPL
         lib = _lib.lib()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         PP = ctypes.POINTER(P)
@@ -155,7 +155,20 @@ class FusedTP:
         block_n = 32 if M <= 32 else (64 if M <= 64 else 128)
         stream = torch.cuda.current_stream().cuda_stream
         n = self.tp.world_size
-        if self.cluster_splitk and M <= 128:
+        if self.impl == "fixup" and M <= 128:
+            # split-K summed inside the producer (last-arriver fix-up): exactly one bf16 partial leaves this rank
+            b = self._parity
+            self._parity ^= 1
+            self.ops_issued += 1
+            part, ctr = ops.fix_scratch(x.device, lib.nkb_gemm_fix_scratch_floats(N, M, K, max(1, int(splits))))
+            rc = lib.nkb_gemm_fix_push(w.data_ptr(), x.data_ptr(), N, M, K, w.stride(0), x.stride(0),
+                                       max(1, int(splits)), None if bias is None else bias.data_ptr(),
+                                       self._peer_out[b], self._peer_flag[b], n, self.tp.rank, self.done.data_ptr(),
+                                       part.data_ptr(), ctr.data_ptr(), block_n, stream)
+            _lib.check(rc, "nkb_gemm_fix_push")
+            ops._launches += 1
+            return self._reduce(b, n, M, resid, next_norm, eps, x.device)
+        if self.impl == "cluster" and M <= 128:
             # split-K summed inside the producer (CTA clusters): exactly one bf16 partial leaves this rank
             b = self._parity
             self._parity ^= 1
