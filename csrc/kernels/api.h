@@ -57,7 +57,8 @@ int nkb_gemm_bf16_2cta(const void* A, const void* B, void* out, int m, int n, in
                        long long ldo, const void* bias, const void* residual, int gated, int gate_off, void* stream);
 int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tokens, int k, long long ldw,
                        long long ldx, long long ldo, int splits, const void* bias, int block_n, void* const* peer_out,
-                       void* const* peer_flag, int n_peers, int rank, void* done_counter, void* stream);
+                       void* const* peer_flag, int n_peers, int rank, void* done_counter, void* mc_out, void* mc_flag,
+                       void* stream);
 
 int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, void* out, const int* group_offsets, int num_groups,
                           int features, int k, int total_rows, int max_rows_per_group, long long ldx, long long ldo,
@@ -81,7 +82,7 @@ int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void* flags, in
                           void* normed_out, int rows, int hidden, float eps, void* stream);
 int nkb_moe_combine_push(const void* y_sorted, const int* pair_pos, const float* weights, int tokens, int top_k,
                          int hidden, void* const* peer_out, void* const* peer_flag, int n_peers, int rank,
-                         void* done_counter, void* stream);
+                         void* done_counter, void* mc_out, void* mc_flag, void* stream);
 int nkb_argmax_exchange(const float* vals, const int* ids, int rows, int max_rows, int id_offset,
                         void* const* peer_pairs, void* const* peer_flag, int n_peers, int rank, const void* local_pairs,
                         const void* local_flags, void* seen, int* out_ids, void* stream);

@@ -193,7 +193,7 @@ __global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ y_sort
     const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
                                pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
     const long long off = ((long long)push.rank * tokens + t) * hidden + v * 8;
-    for (int pr = 0; pr < push.n_peers; ++pr) *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = o;
+    push_store_16(push, off, o);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -204,7 +204,7 @@ __global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ y_sort
     if (old == gridDim.x - 1) {
       *push.done_counter = 0u;
       __threadfence_system();
-      for (int pr = 0; pr < push.n_peers; ++pr) atomicAdd_system(push.peer_flag[pr], 1u);
+      push_signal(push);
     }
   }
 }
@@ -324,7 +324,7 @@ extern "C" int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void
 // rank r's partial array [n_peers, tokens, hidden] bf16, peer_flag[r] this rank's counter on rank r.
 extern "C" int nkb_moe_combine_push(const void* y_sorted, const int* pair_pos, const float* weights, int tokens,
                                     int top_k, int hidden, void* const* peer_out, void* const* peer_flag, int n_peers,
-                                    int rank, void* done_counter, void* stream) {
+                                    int rank, void* done_counter, void* mc_out, void* mc_flag, void* stream) {
   if (tokens <= 0) return 0;
   if ((hidden & 7) || n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return -2;
   if (!status_word() && nkb_init() != 0) return -1;
@@ -336,6 +336,8 @@ extern "C" int nkb_moe_combine_push(const void* y_sorted, const int* pair_pos, c
     pa.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
   }
   pa.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  pa.mc_out = reinterpret_cast<__nv_bfloat16*>(mc_out);
+  pa.mc_flag = reinterpret_cast<unsigned int*>(mc_flag);
   return launch_pdl(moe_combine_push_kernel, dim3(tokens), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                     (const __nv_bfloat16*)y_sorted, pair_pos, weights, tokens, top_k, hidden, pa);
 }

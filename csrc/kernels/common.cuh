@@ -371,6 +371,38 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
 }
 
 // ---------------------------------------------------------------------------
+// NVLink multicast (NVLS): `addr` is an address inside the multicast mapping of a symmetric buffer.
+// A store is replicated by the switch into every rank's copy; a reduction is applied to every copy.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void multimem_st_16(void* addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void multimem_add_release_u32(unsigned int* addr, unsigned int v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+// One 16-byte piece of a push epilogue: through the multicast view when there is one, else to every peer.
+template <class PushT>
+__device__ __forceinline__ void push_store_16(const PushT& push, long long off, uint4 val) {
+  if (push.mc_out) {
+    multimem_st_16(push.mc_out + off, val);
+  } else {
+    for (int pr = 0; pr < push.n_peers; ++pr) *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
+  }
+}
+// Called by the last CTA of a pushing grid after its system-scope fence.
+template <class PushT>
+__device__ __forceinline__ void push_signal(const PushT& push) {
+  if (push.mc_flag) {
+    multimem_add_release_u32(push.mc_flag, 1u);
+  } else {
+    for (int pr = 0; pr < push.n_peers; ++pr) atomicAdd_system(push.peer_flag[pr], 1u);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Small numeric helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

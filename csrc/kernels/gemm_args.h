@@ -63,6 +63,11 @@ struct PushArgs {
   __nv_bfloat16* peer_out[kMaxPeers];
   unsigned int* peer_flag[kMaxPeers];   // this rank's arrival counter inside each peer's flag array
   unsigned int* done_counter;           // local: CTAs of this grid that finished their stores
+  // NVLink multicast view of the same symmetric buffers (nullptr = none): one multimem store through mc_out
+  // lands in every rank's partial array, one multimem reduction on mc_flag bumps this rank's arrival counter
+  // on every rank, so a partial leaves the GPU once instead of once per peer.
+  __nv_bfloat16* mc_out;
+  unsigned int* mc_flag;
 };
 
 }  // namespace nkb

@@ -340,7 +340,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (gtok < args.tokens && gfeat < args.features) {
               const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tl * kTileRows + ch * 8);
               const long long off = ((long long)epi.rank * args.tokens + gtok) * args.ldo + gfeat;
-              for (int pr = 0; pr < epi.n_peers; ++pr) *reinterpret_cast<uint4*>(epi.peer_out[pr] + off) = val;
+              push_store_16(epi, off, val);
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -435,7 +435,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           *epi.done_counter = 0u;
           __threadfence_system();
           if (ok)
-            for (int pr = 0; pr < epi.n_peers; ++pr) atomicAdd_system(epi.peer_flag[pr], 1u);
+            push_signal(epi);
         }
       }
     }
@@ -573,7 +573,7 @@ extern "C" int nkb_decode_gemm(const void* w, const void* x, void* out, int feat
 extern "C" int nkb_decode_gemm_push(const void* w, const void* x, int features, int tokens, int k, long long ldw,
                                     long long ldx, long long ldo, int splits, const void* bias, int block_n,
                                     void* const* peer_out, void* const* peer_flag, int n_peers, int rank,
-                                    void* done_counter, void* stream) {
+                                    void* done_counter, void* mc_out, void* mc_flag, void* stream) {
   if (!status_word() && nkb_init() != 0) return -1;
   if ((ldw & 7) || (ldx & 7) || (ldo & 7) || (features & 7)) return -2;
   if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return -2;
@@ -588,6 +588,8 @@ extern "C" int nkb_decode_gemm_push(const void* w, const void* x, int features, 
     pa.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
   }
   pa.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  pa.mc_out = reinterpret_cast<__nv_bfloat16*>(mc_out);
+  pa.mc_flag = reinterpret_cast<unsigned int*>(mc_flag);
   CUtensorMap ta, tb;
   if (encode_tmap_bf16_2d(&ta, w, k, features, ldw, kBlockK, kTileRows)) return -4;
   if (encode_tmap_bf16_2d(&tb, x, k, tokens, ldx, kBlockK, block_n)) return -4;

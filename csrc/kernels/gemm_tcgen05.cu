@@ -216,7 +216,7 @@ extern "C" int nkb_gemm_effective_splits(int k, int splits) {
 extern "C" int nkb_gemm_bf16_push(const void* weights, const void* x, int features, int tokens, int k, long long ldw,
                                   long long ldx, long long ldo, int splits, const void* bias, int block_n,
                                   void* const* peer_out, void* const* peer_flag, int n_peers, int rank,
-                                  void* done_counter, void* stream) {
+                                  void* done_counter, void* mc_out, void* mc_flag, void* stream) {
   if (!status_word() && nkb_init() != 0) return -1;
   if (features <= 0 || tokens <= 0 || k <= 0 || (k & 7) || (ldw & 7) || (ldx & 7) || (ldo & 7) || (features & 7))
     return -2;
@@ -246,6 +246,8 @@ extern "C" int nkb_gemm_bf16_push(const void* weights, const void* x, int featur
     pa.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
   }
   pa.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  pa.mc_out = reinterpret_cast<__nv_bfloat16*>(mc_out);
+  pa.mc_flag = reinterpret_cast<unsigned int*>(mc_flag);
   CUtensorMap ta, tb;
   if (encode_tmap_bf16_2d(&ta, weights, k, features, ldw, kBlockK, kTileRows)) return -4;
   if (encode_tmap_bf16_2d(&tb, x, k, tokens, ldx, kBlockK, block_n)) return -4;
@@ -408,8 +410,8 @@ extern "C" int nkb_gemm_fix_rope(const void* w, const void* x, int tokens, int k
 // peer's partial array [n_peers, tokens, rows]; the last CTA bumps this rank's arrival counter on every peer.
 extern "C" int nkb_gemm_fix_push(const void* w, const void* x, int rows, int tokens, int k, long long ldw,
                                  long long ldx, int splits, const void* bias, void* const* peer_out,
-                                 void* const* peer_flag, int n_peers, int rank, void* done_counter, float* partials,
-                                 unsigned int* counters, int block_n, void* stream) {
+                                 void* const* peer_flag, int n_peers, int rank, void* done_counter, void* mc_out,
+                                 void* mc_flag, float* partials, unsigned int* counters, int block_n, void* stream) {
   if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers || (rows & 7)) return -2;
   GemmArgs args;
   PushFix::Args fx{};
@@ -423,6 +425,8 @@ extern "C" int nkb_gemm_fix_push(const void* w, const void* x, int rows, int tok
     fx.push.peer_flag[i] = reinterpret_cast<unsigned int*>(peer_flag[i]);
   }
   fx.push.done_counter = reinterpret_cast<unsigned int*>(done_counter);
+  fx.push.mc_out = reinterpret_cast<__nv_bfloat16*>(mc_out);
+  fx.push.mc_flag = reinterpret_cast<unsigned int*>(mc_flag);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   NKB_FIX_DISPATCH(PushFix, fx)
 }

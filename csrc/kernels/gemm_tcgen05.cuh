@@ -369,8 +369,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
             if (gtok < cols_end && gfeat < args.rows) {
               const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
               const long long off = (slot * args.cols + gtok) * args.ldo + gfeat;
-              for (int pr = 0; pr < push.n_peers; ++pr)
-                *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
+              push_store_16(push, off, val);
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -479,7 +478,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
         if (old == gridDim.x - 1) {
           *fix.push.done_counter = 0u;
           __threadfence_system();
-          for (int pr = 0; pr < fix.push.n_peers; ++pr) atomicAdd_system(fix.push.peer_flag[pr], 1u);
+          push_signal(fix.push);
         }
       }
     }
@@ -496,7 +495,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
         if (old == gridDim.x - 1) {
           *push.done_counter = 0u;
           __threadfence_system();
-          for (int pr = 0; pr < push.n_peers; ++pr) atomicAdd_system(push.peer_flag[pr], 1u);
+          push_signal(push);
         }
       }
     }

@@ -271,7 +271,7 @@ __device__ __forceinline__ void run_fix(const typename Fix::Args& fx, int rt, in
         if (gfeat < rows) {
           const uint4 val = *reinterpret_cast<const uint4*>(stage + tl * kTileRows + chn * 8);
           const long long off = ((long long)push.rank * tokens + gtok) * c.ld + gfeat;
-          for (int pr = 0; pr < push.n_peers; ++pr) *reinterpret_cast<uint4*>(push.peer_out[pr] + off) = val;
+          push_store_16(push, off, val);
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");

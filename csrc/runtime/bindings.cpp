@@ -7,6 +7,7 @@
 #include <pybind11/stl.h>
 
 #include "spike.h"
+#include "symmetric.h"
 
 namespace py = pybind11;
 using namespace spike;
@@ -72,6 +73,26 @@ PYBIND11_MODULE(_spike, m) {
       .def_property_readonly("is_collective", &LoadedModule::is_collective)
       .def_property_readonly("num_launches", &LoadedModule::num_launches)
       .def_property_readonly("unloaded", &LoadedModule::unloaded);
+
+  py::class_<SymmetricBuffer>(m, "SymmetricBuffer")
+      .def(py::init<int, size_t>(), py::arg("device_ordinal"), py::arg("bytes"))
+      .def_static("supported", &SymmetricBuffer::supported)
+      .def_static("multicast_supported", &SymmetricBuffer::multicast_supported)
+      .def_property_readonly("size", &SymmetricBuffer::size)
+      .def_property_readonly("device_ordinal", &SymmetricBuffer::device_ordinal)
+      .def_property_readonly("local_ptr", &SymmetricBuffer::local_ptr)
+      .def_property_readonly("multicast_ptr", &SymmetricBuffer::multicast_ptr)
+      .def_property_readonly("has_multicast", &SymmetricBuffer::has_multicast)
+      .def_property_readonly("closed", &SymmetricBuffer::closed)
+      .def("export_fd", &SymmetricBuffer::export_fd)
+      .def("import_peer", &SymmetricBuffer::import_peer, py::arg("rank"), py::arg("fd"))
+      .def("peer_ptr", &SymmetricBuffer::peer_ptr, py::arg("rank"))
+      .def("multicast_create", &SymmetricBuffer::multicast_create, py::arg("num_devices"))
+      .def("multicast_import", &SymmetricBuffer::multicast_import, py::arg("fd"))
+      .def("multicast_add_device", &SymmetricBuffer::multicast_add_device)
+      .def("multicast_bind", &SymmetricBuffer::multicast_bind)
+      .def("zero", &SymmetricBuffer::zero)
+      .def("close", &SymmetricBuffer::close);
 
   py::class_<Spike>(m, "Spike")
       .def(py::init<int, int>(), py::arg("verbose_level") = 0, py::arg("device_ordinal") = -1)

@@ -62,6 +62,28 @@ static void load() {
   SPIKE_LOAD(cuTensorMapEncodeTiled);
 #undef SPIKE_LOAD
   g_driver.loaded = ok;
+  bool vmm = true, mc = true;
+#define SPIKE_OPT(flag, name)                                                 \
+  g_driver.name = reinterpret_cast<decltype(g_driver.name)>(dlsym(h, #name)); \
+  if (!g_driver.name) flag = false;
+  SPIKE_OPT(vmm, cuMemCreate);
+  SPIKE_OPT(vmm, cuMemRelease);
+  SPIKE_OPT(vmm, cuMemAddressReserve);
+  SPIKE_OPT(vmm, cuMemAddressFree);
+  SPIKE_OPT(vmm, cuMemMap);
+  SPIKE_OPT(vmm, cuMemUnmap);
+  SPIKE_OPT(vmm, cuMemSetAccess);
+  SPIKE_OPT(vmm, cuMemGetAllocationGranularity);
+  SPIKE_OPT(vmm, cuMemExportToShareableHandle);
+  SPIKE_OPT(vmm, cuMemImportFromShareableHandle);
+  SPIKE_OPT(mc, cuMulticastCreate);
+  SPIKE_OPT(mc, cuMulticastAddDevice);
+  SPIKE_OPT(mc, cuMulticastBindMem);
+  SPIKE_OPT(mc, cuMulticastUnbind);
+  SPIKE_OPT(mc, cuMulticastGetGranularity);
+#undef SPIKE_OPT
+  g_driver.vmm_loaded = ok && vmm;
+  g_driver.multicast_loaded = ok && vmm && mc;
 }
 
 const Driver& driver() {

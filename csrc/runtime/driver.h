@@ -46,7 +46,26 @@ struct Driver {
   SPIKE_DRV(cuGetErrorString);
   SPIKE_DRV(cuGetErrorName);
   SPIKE_DRV(cuTensorMapEncodeTiled);
+  // virtual memory management + NVLink multicast objects (symmetric.cpp).  Optional: a driver without them
+  // still loads, `vmm_loaded` / `multicast_loaded` say what is there.
+  SPIKE_DRV(cuMemCreate);
+  SPIKE_DRV(cuMemRelease);
+  SPIKE_DRV(cuMemAddressReserve);
+  SPIKE_DRV(cuMemAddressFree);
+  SPIKE_DRV(cuMemMap);
+  SPIKE_DRV(cuMemUnmap);
+  SPIKE_DRV(cuMemSetAccess);
+  SPIKE_DRV(cuMemGetAllocationGranularity);
+  SPIKE_DRV(cuMemExportToShareableHandle);
+  SPIKE_DRV(cuMemImportFromShareableHandle);
+  SPIKE_DRV(cuMulticastCreate);
+  SPIKE_DRV(cuMulticastAddDevice);
+  SPIKE_DRV(cuMulticastBindMem);
+  SPIKE_DRV(cuMulticastUnbind);
+  SPIKE_DRV(cuMulticastGetGranularity);
 #undef SPIKE_DRV
+  bool vmm_loaded = false;
+  bool multicast_loaded = false;
 };
 
 // Loads libcuda on first use; never throws (check `loaded`).

@@ -189,12 +189,16 @@ def linear(
 
 
 # How the decode projections sum their split-K partials (NKIPY_B200_DECODE_GEMM):
-#   fixup   (default) inside the persistent GEMM: the CTA that arrives last at a tile's counter sums the
-#           partials and applies the epilogue (csrc/kernels/splitk_fix.cuh)
+#   legacy  (default) fp32 partials left to the next kernel of the chain (RoPE + append, SwiGLU, residual +
+#           RMSNorm), which sums them with the parallelism of a whole grid
+#   fixup   inside the persistent GEMM: the CTA that arrives last at a tile's counter sums the partials and
+#           applies the epilogue (csrc/kernels/splitk_fix.cuh)
 #   cluster thread-block clusters exchanging partials through distributed shared memory
 #           (csrc/kernels/gemm_decode.cu)
-#   legacy  fp32 partials left to the next kernel of the chain
-DECODE_GEMM_IMPL = os.environ.get("NKIPY_B200_DECODE_GEMM", "fixup")
+# Measured on B200 (Llama-3-8B shapes, batch 64): the two fused forms save three launches per layer but lose
+# more than that inside the kernel -- the fix-up's one CTA per tile sums with too little memory parallelism,
+# cluster launches delay their successors -- so the unfused chain stays the default.
+DECODE_GEMM_IMPL = os.environ.get("NKIPY_B200_DECODE_GEMM", "legacy")
 _FIX_SCRATCH = {}
 _FIX_COUNTERS = 4096
 
@@ -247,7 +251,7 @@ def decode_linear(
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     block_n = 32 if M <= 32 else (64 if M <= 64 else 128)
-    impl = DECODE_GEMM_IMPL if impl is None else impl
+    impl = ("fixup" if DECODE_GEMM_IMPL == "legacy" else DECODE_GEMM_IMPL) if impl is None else impl
     if impl != "cluster" and (not gated or N % 128 == 0) and (2 * N if gated else N) <= 128 * _FIX_COUNTERS:
         L = _lib.lib()
         rows = 2 * N if gated else N
@@ -308,7 +312,7 @@ def qkv_rope_append(
         q_out = torch.empty((T, nq * head_dim), dtype=torch.bfloat16, device=x.device)
     block_n = 32 if T <= 32 else (64 if T <= 64 else 128)
     max_pos = cos_sin.shape[0] if cos_sin is not None else 0
-    impl = DECODE_GEMM_IMPL if impl is None else impl
+    impl = ("fixup" if DECODE_GEMM_IMPL == "legacy" else DECODE_GEMM_IMPL) if impl is None else impl
     if impl != "cluster" and w_qkv.shape[0] <= 128 * _FIX_COUNTERS:
         L = _lib.lib()
         part, ctr = fix_scratch(x.device, L.nkb_gemm_fix_scratch_floats(w_qkv.shape[0], T, K, int(splits)))

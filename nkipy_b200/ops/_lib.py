@@ -43,7 +43,7 @@ _SIGNATURES = {
     "nkb_decode_gemm": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
                                 c_int, _P, _P, c_float, c_float, c_int, c_int, _P]),
     "nkb_decode_gemm_push": (c_int, [_P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P, c_int,
-                                     ctypes.POINTER(_P), ctypes.POINTER(_P), c_int, c_int, _P, _P]),
+                                     ctypes.POINTER(_P), ctypes.POINTER(_P), c_int, c_int, _P, _P, _P, _P]),
     "nkb_decode_gemm_rope": (c_int, [_P, _P, c_int, c_int, c_longlong, c_longlong, c_int, _P, _P, _P, _P, _P, _P,
                                      c_float, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "nkb_noalloc_status": (c_int, [c_int]),
@@ -55,7 +55,7 @@ _SIGNATURES = {
     "nkb_gemm_fix_rope": (c_int, [_P, _P, c_int, c_int, c_longlong, c_longlong, c_int, _P, _P, _P, _P, _P, _P, c_float,
                                   _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P]),
     "nkb_gemm_fix_push": (c_int, [_P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_int, _P, ctypes.POINTER(_P),
-                                  ctypes.POINTER(_P), c_int, c_int, _P, _P, _P, c_int, _P]),
+                                  ctypes.POINTER(_P), c_int, c_int, _P, _P, _P, _P, _P, c_int, _P]),
     "nkb_rmsnorm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_add_rmsnorm": (c_int, [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),
     "nkb_silu_mul": (c_int, [_P, _P, c_int, c_int, c_float, c_float, _P]),

@@ -35,12 +35,142 @@ class _CudaArray:
         self._owner = owner
 
 
-class SymmetricMemory:
-    """One device allocation per rank, mapped into every rank of the group."""
+def exchange_fds(tp: TPGroup, fd: int, only_from: Optional[int] = None) -> List[Optional[int]]:
+    """Pass file descriptors between the rank processes of one node over Unix sockets (SCM_RIGHTS).
 
-    def __init__(self, tp: TPGroup, nbytes: int):
+    Every rank listens on an abstract socket whose name is all-gathered.  With ``only_from`` None every
+    rank sends `fd` to every other rank and the result holds the descriptor received from each rank
+    (None at this rank's own index); with ``only_from`` = r only rank r sends (fd is ignored elsewhere)
+    and the others get its descriptor at index r.  Received descriptors belong to the caller."""
+    import os
+    import socket
+    import uuid
+
+    n, me = tp.world_size, tp.rank
+    out: List[Optional[int]] = [None] * n
+    if n == 1:
+        return out
+    srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    name = f"\0nkipy-b200-symm-{os.getpid()}-{uuid.uuid4().hex}"
+    srv.bind(name)
+    srv.listen(n)
+    srv.settimeout(60.0)
+    try:
+        names = tp.all_gather_object(name)
+        senders = list(range(n)) if only_from is None else [only_from]
+        if me in senders:
+            for p in range(n):
+                if p == me:
+                    continue
+                c = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+                c.settimeout(60.0)
+                c.connect(names[p])          # queues in the listener's backlog: no accept needed yet
+                socket.send_fds(c, [me.to_bytes(4, "little")], [fd])
+                c.close()
+        expect = [r for r in senders if r != me]
+        for _ in expect:
+            conn, _addr = srv.accept()
+            msg, fds, _flags, _a = socket.recv_fds(conn, 4, 1)
+            conn.close()
+            if len(msg) != 4 or len(fds) != 1:
+                raise RuntimeError("descriptor exchange: short message")
+            out[int.from_bytes(msg, "little")] = fds[0]
+        tp.barrier()
+    finally:
+        srv.close()
+    return out
+
+
+def _vmm_runtime():
+    """The C++ runtime module when it offers `SymmetricBuffer`, else None."""
+    try:
+        from ..spike import _spike
+    except Exception:      # noqa: BLE001 - the runtime module is optional for the IPC path
+        return None
+    return _spike if hasattr(_spike, "SymmetricBuffer") else None
+
+
+class SymmetricMemory:
+    """One device allocation per rank, mapped into every rank of the group.
+
+    backend "vmm" (default where supported): the C++ runtime's `SymmetricBuffer` -- `cuMemCreate` with POSIX
+    file-descriptor handles, every peer mapped with `cuMemMap`, and with ``multicast=True`` an NVLink
+    multicast object bound to all ranks' memory, so kernels can use `multimem` stores / reductions through
+    `mc_ptr` (0 when there is none).  backend "ipc": `cudaMalloc` + CUDA IPC handles (no multicast).
+    ``NKIPY_B200_SYMM=ipc`` forces the latter, ``NKIPY_B200_NVLS=0`` turns multicast off."""
+
+    def __init__(self, tp: TPGroup, nbytes: int, multicast: bool = False, backend: Optional[str] = None):
+        import os
+
         self.tp = tp
         self.nbytes = int(nbytes)
+        self.mc_ptr = 0
+        self._closed = False
+        self._buf = None
+        rt = _vmm_runtime()
+        dev_index = tp.device.index if tp.device is not None and tp.device.index is not None else 0
+        if backend is None:
+            backend = os.environ.get("NKIPY_B200_SYMM", "vmm")
+        ok = backend == "vmm" and rt is not None and rt.SymmetricBuffer.supported(dev_index)
+        # every rank must take the same path
+        if not all(tp.all_gather_object(bool(ok))):
+            ok = False
+        self.backend = "vmm" if ok else "ipc"
+        if self.backend == "vmm":
+            want_mc = (multicast and tp.world_size > 1 and os.environ.get("NKIPY_B200_NVLS", "1") != "0"
+                       and rt.SymmetricBuffer.multicast_supported(dev_index))
+            want_mc = all(tp.all_gather_object(bool(want_mc)))
+            self._init_vmm(rt, dev_index, want_mc)
+        else:
+            self._init_ipc()
+
+    # ------------------------------------------------------------------ VMM + multicast
+    def _init_vmm(self, rt, dev_index: int, want_mc: bool) -> None:
+        import os
+
+        tp = self.tp
+        torch.cuda.synchronize()
+        buf = rt.SymmetricBuffer(dev_index, self.nbytes)
+        self._buf = buf
+        buf.zero()
+        self.local_ptr = int(buf.local_ptr)
+        fd = buf.export_fd()
+        try:
+            got = exchange_fds(tp, fd)
+        finally:
+            os.close(fd)
+        self.ptrs: List[int] = []
+        for r, pfd in enumerate(got):
+            if r == tp.rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            try:
+                buf.import_peer(r, pfd)
+            finally:
+                os.close(pfd)
+            self.ptrs.append(int(buf.peer_ptr(r)))
+        tp.barrier()
+        if want_mc:
+            mfd = buf.multicast_create(tp.world_size) if tp.rank == 0 else -1
+            try:
+                got = exchange_fds(tp, mfd, only_from=0)
+            finally:
+                if mfd >= 0:
+                    os.close(mfd)
+            if tp.rank != 0:
+                try:
+                    buf.multicast_import(got[0])
+                finally:
+                    os.close(got[0])
+            buf.multicast_add_device()
+            tp.barrier()                      # every device is part of the object before anyone binds
+            buf.multicast_bind()
+            tp.barrier()
+            self.mc_ptr = int(buf.multicast_ptr)
+
+    # ------------------------------------------------------------------ cudaMalloc + CUDA IPC
+    def _init_ipc(self) -> None:
+        tp = self.tp
         lib = _lib.lib()
         for name, res, args in (
             ("nkb_symm_alloc", ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_longlong]),
@@ -58,7 +188,7 @@ class SymmetricMemory:
         handle = ctypes.create_string_buffer(64)
         _lib.check(lib.nkb_ipc_get_handle(local, handle), "nkb_ipc_get_handle")
         handles = tp.all_gather_object(bytes(handle.raw))
-        self.ptrs: List[int] = []
+        self.ptrs = []
         self._opened: List[int] = []
         for r, h in enumerate(handles):
             if r == tp.rank:
@@ -69,7 +199,6 @@ class SymmetricMemory:
             self.ptrs.append(int(p.value))
             self._opened.append(int(p.value))
         tp.barrier()
-        self._closed = False
 
     def view(self, offset: int, nbytes: int, dtype: torch.dtype, shape: Tuple[int, ...]) -> torch.Tensor:
         """torch view of a region of the *local* buffer."""
@@ -77,11 +206,16 @@ class SymmetricMemory:
         return raw.view(dtype).view(shape)
 
     def close(self) -> None:
+        """Collective: every rank calls it.  Nothing is unmapped or released while a peer may still use it."""
         if self._closed:
             return
         self._closed = True
         torch.cuda.synchronize()
         self.tp.barrier()
+        if self.backend == "vmm":
+            self._buf.close()
+            self.tp.barrier()
+            return
         for p in self._opened:
             self._lib.nkb_ipc_close(ctypes.c_void_p(p))
         self.tp.barrier()
@@ -104,7 +238,7 @@ class FusedTP:
         self.buf_bytes = n * max_splits * max_tokens * hidden * 2
         self.buf_bytes = (self.buf_bytes + 255) // 256 * 256
         self.pair_bytes = (2 * n * max_tokens * 8 + 255) // 256 * 256
-        self.mem = SymmetricMemory(tp, self.FLAG_BYTES + 2 * self.buf_bytes + self.pair_bytes)
+        self.mem = SymmetricMemory(tp, self.FLAG_BYTES + 2 * self.buf_bytes + self.pair_bytes, multicast=True)
         dev = tp.device
         self.seen = torch.zeros((4,), dtype=torch.int32, device=dev)   # [buffer 0, buffer 1, argmax, spare]
         self.done = torch.zeros((4,), dtype=torch.int32, device=dev)   # [producer, reduce0, reduce1, spare]
@@ -118,17 +252,22 @@ class FusedTP:
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         PP = ctypes.POINTER(P)
         lib.nkb_gemm_bf16_push.restype = I
-        lib.nkb_gemm_bf16_push.argtypes = [P, P, I, I, I, LL, LL, LL, I, P, I, PP, PP, I, I, P, P]
+        lib.nkb_gemm_bf16_push.argtypes = [P, P, I, I, I, LL, LL, LL, I, P, I, PP, PP, I, I, P, P, P, P]
         lib.nkb_tp_reduce_rmsnorm.restype = I
         lib.nkb_tp_reduce_rmsnorm.argtypes = [P, I, P, I, P, P, P, P, P, P, I, I, ctypes.c_float, P]
         lib.nkb_moe_combine_push.restype = I
-        lib.nkb_moe_combine_push.argtypes = [P, P, P, I, I, I, PP, PP, I, I, P, P]
+        lib.nkb_moe_combine_push.argtypes = [P, P, P, I, I, I, PP, PP, I, I, P, P, P, P]
         lib.nkb_argmax_exchange.restype = I
         lib.nkb_argmax_exchange.argtypes = [P, P, I, I, I, PP, PP, I, I, P, P, P, P, P]
         self._lib = lib
         self._peer_out = [(P * n)(*[p + self.FLAG_BYTES + b * self.buf_bytes for p in self.mem.ptrs])
                           for b in range(2)]
         self._peer_flag = [(P * n)(*[p + (b * n + tp.rank) * 4 for p in self.mem.ptrs]) for b in range(2)]
+        # the same two locations inside the NVLink multicast mapping (None without one): a store there lands
+        # in every rank's buffer, so a partial crosses this GPU's links once instead of once per peer
+        mc = self.mem.mc_ptr
+        self._mc_out = [P(mc + self.FLAG_BYTES + b * self.buf_bytes) if mc else None for b in range(2)]
+        self._mc_flag = [P(mc + (b * n + tp.rank) * 4) if mc else None for b in range(2)]
         pair_off = self.FLAG_BYTES + 2 * self.buf_bytes
         self._pair_off = pair_off
         self._peer_pairs = (P * n)(*[p + pair_off for p in self.mem.ptrs])
@@ -164,7 +303,8 @@ class FusedTP:
             rc = lib.nkb_gemm_fix_push(w.data_ptr(), x.data_ptr(), N, M, K, w.stride(0), x.stride(0),
                                        max(1, int(splits)), None if bias is None else bias.data_ptr(),
                                        self._peer_out[b], self._peer_flag[b], n, self.tp.rank, self.done.data_ptr(),
-                                       part.data_ptr(), ctr.data_ptr(), block_n, stream)
+                                       self._mc_out[b], self._mc_flag[b], part.data_ptr(), ctr.data_ptr(), block_n,
+                                       stream)
             _lib.check(rc, "nkb_gemm_fix_push")
             ops._launches += 1
             return self._reduce(b, n, M, resid, next_norm, eps, x.device)
@@ -176,7 +316,7 @@ class FusedTP:
             rc = lib.nkb_decode_gemm_push(w.data_ptr(), x.data_ptr(), N, M, K, w.stride(0), x.stride(0), N,
                                           max(1, int(splits)), None if bias is None else bias.data_ptr(), block_n,
                                           self._peer_out[b], self._peer_flag[b], n, self.tp.rank,
-                                          self.done.data_ptr(), stream)
+                                          self.done.data_ptr(), self._mc_out[b], self._mc_flag[b], stream)
             _lib.check(rc, "nkb_decode_gemm_push")
             ops._launches += 1
             return self._reduce(b, n, M, resid, next_norm, eps, x.device)
@@ -186,7 +326,8 @@ class FusedTP:
         self.ops_issued += 1
         rc = lib.nkb_gemm_bf16_push(w.data_ptr(), x.data_ptr(), N, M, K, w.stride(0), x.stride(0), N, eff,
                                     None if bias is None else bias.data_ptr(), block_n, self._peer_out[b],
-                                    self._peer_flag[b], n, self.tp.rank, self.done.data_ptr(), stream)
+                                    self._peer_flag[b], n, self.tp.rank, self.done.data_ptr(), self._mc_out[b],
+                                    self._mc_flag[b], stream)
         _lib.check(rc, "nkb_gemm_bf16_push")
         ops._launches += 1
         return self._reduce(b, n * eff, M, resid, next_norm, eps, x.device)
@@ -224,7 +365,7 @@ class FusedTP:
         n = self.tp.world_size
         rc = self._lib.nkb_moe_combine_push(y_sorted.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(), tokens,
                                             weights.shape[1], self.hidden, self._peer_out[b], self._peer_flag[b], n,
-                                            self.tp.rank, self.done.data_ptr(),
+                                            self.tp.rank, self.done.data_ptr(), self._mc_out[b], self._mc_flag[b],
                                             torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "nkb_moe_combine_push")
         ops._launches += 1

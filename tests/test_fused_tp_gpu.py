@@ -19,10 +19,17 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q):
+# how the symmetric buffers are made: CUDA IPC, virtual memory management with file-descriptor handles, and
+# the latter bound to an NVLink multicast object (multimem stores in the push epilogue)
+MODES = {"ipc": dict(NKIPY_B200_SYMM="ipc", NKIPY_B200_NVLS="0"),
+         "vmm": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="0"),
+         "nvls": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1")}
+
+
+def _worker(rank, world, port, q, mode="ipc"):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", **MODES[mode])
     import torch.distributed as dist
 
     from nkipy_b200 import ops
@@ -83,26 +90,38 @@ def _worker(rank, world, port, q):
         errs.append(((outs[i][0].float() - rh).norm() / rh.norm()).item())
     status = ops.device_status()
     tp.barrier()
+    used = (fused.mem.backend, bool(fused.mem.mc_ptr))
     fused.close()
-    q.put((rank, max(errs), status))
+    q.put((rank, max(errs), status, used))
     dist.destroy_process_group()
 
 
+def _worlds():
+    n = torch.cuda.device_count()
+    return [w for w in (2, 4, 8) if w <= n] or [2]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_gemm_allreduce_two_ranks():
+@pytest.mark.parametrize("mode", ["ipc", "vmm", "nvls"])
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_gemm_allreduce_ranks(world, mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=240) for _ in range(2)]
+    res = [q.get(timeout=240) for _ in range(world)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, err, status in res:
+    for rank, err, status, used in res:
         assert status == 0, (rank, status)
         assert err < 2e-2, (rank, err)
+        if mode == "ipc":
+            assert used == ("ipc", False)
+        elif mode == "vmm":
+            assert used[1] is False
 
 
 def test_fused_gemm_allreduce_single_rank():
