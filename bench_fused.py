@@ -12,6 +12,9 @@ Shapes (per rank, bf16):
       combine whose kernel stores every token's weighted partial sum into all peers' buffers (the all-to-all of
       this layout) followed by the summing residual + RMSNorm kernel.  Baseline: the same experts with a local
       combine, NCCL all-reduce and a separate residual + RMSNorm.  `combine_*` fields time the exchange alone.
+      From 256 tokens per rank on the tokens are sharded over the ranks and the block runs over the token
+      all-to-all in peer memory (op "moe_a2a_block"): dispatch, arrival-gated grouped GEMMs, combine;
+      `dispatch_frac_link` / `combine_frac_link` = bytes crossing NVLink each way / 770 GB/s / measured time.
 for M = 16 ... 16384.  "fused" is one kernel per rank (csrc/kernels/gemm_comm.cu: tcgen05 tiles + peer stores
 over NVLink + arrival counters); "baseline" is torch.matmul (cuBLAS) with NCCL reduce_scatter_tensor /
 all_gather_into_tensor.  Every iteration is timed on the device with CUDA events after an L2 flush (a 256 MB
@@ -140,6 +143,74 @@ def bench_moe(tp, m, args, pk, flush, g):
         fused.close()
 
 
+def bench_moe_a2a(tp, m, args, pk, flush, g):
+    """One Qwen3-30B-A3B-shaped expert-parallel MoE block on m tokens sharded over the ranks (m / tp each):
+    the token all-to-all in peer memory against replicating the tokens with NCCL (all-gather, local experts,
+    reduce-scatter).  `dispatch_*` / `combine_*` time the two exchanges alone against the bytes they move."""
+    from nkipy_b200.models import config as C
+    from nkipy_b200.models.moe import MoEBlock
+    from nkipy_b200.parallel.moe_a2a import MoEAllToAll
+
+    n_r, dev = tp.world_size, tp.device
+    cfg = C.qwen3_30b_a3b()
+    H, E, I, K = cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size, cfg.top_k
+    e_l, t_l = E // n_r, m // n_r
+
+    class LW:
+        pass
+
+    lw = LW()
+    gs = torch.Generator(device=dev).manual_seed(3)          # replicated tensors: same seed on every rank
+    lw.router = (torch.randn(E, H, device=dev, generator=gs) * 0.02).to(torch.bfloat16)
+    lw.router_bias = lw.gate_up_bias = lw.down_bias = None
+    lw.gate_up = (torch.randn(e_l, 2 * I, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    lw.down = (torch.randn(e_l, H, I, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(t_l, H, device=dev, generator=g).to(torch.bfloat16)      # this rank's tokens
+    blk = MoEBlock(cfg, tp, "ep")
+    a2a = MoEAllToAll(tp, t_l, K, H, E, capacity_factor=2.0)
+    weights, experts = blk.route(lw, x)
+
+    def run():
+        return a2a.forward(x, experts, weights, lw.gate_up, lw.down)
+
+    def base():
+        full = tp.all_gather(x).reshape(m, H)
+        w_all, e_all = blk.route(lw, full)
+        plan = ops.moe_dispatch(full, e_all, blk.expert_lo, blk.num_local)
+        h = ops.grouped_linear(plan.x_sorted, lw.gate_up, plan.offsets, max_rows_per_group=m, gated=True,
+                               tiles=plan.tiles)
+        y_sorted = ops.grouped_linear(h, lw.down, plan.offsets, max_rows_per_group=m, tiles=plan.tiles)
+        y = ops.moe_combine(y_sorted, plan.pair_pos, w_all, m)
+        return tp.reduce_scatter(y)
+
+    a, b = run().float(), base().float()
+    rel = ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
+    t_f, t_b = timed(tp, run, args.iters, args.warmup, flush), timed(tp, base, args.iters, args.warmup, flush)
+    t_d = timed(tp, lambda: a2a.dispatch(x, experts), args.iters, args.warmup, flush)
+    a2a.run_experts(lw.gate_up, lw.down)
+    t_c = timed(tp, lambda: a2a.combine(weights, t_l), args.iters, args.warmup, flush)
+    link_bytes = a2a.bytes_sent_per_rank(t_l)                 # each way
+    t_l_us = link_bytes / (NVLINK_GBS * 1e3)
+    flops = 2.0 * t_l * K * 3 * H * I                          # expected pairs per rank under uniform routing
+    t_cmp = flops / (pk["bf16_tflops"] * 1e6)
+    t_h = (e_l * 3 * H * I * 2 + 4 * t_l * K * H * 2) / (pk["hbm_gbs"] * 1e3)
+    roof = max(t_cmp, 2 * t_l_us, t_h)
+    status = ops.device_status()
+    if tp.rank == 0:
+        print(json.dumps({
+            "op": "moe_a2a_block", "tp": n_r, "tokens": m, "tokens_per_rank": t_l, "experts_per_rank": e_l,
+            "fused_us": round(t_f, 1), "nccl_us": round(t_b, 1), "speedup": round(t_b / t_f, 2),
+            "roofline_us": round(roof, 1), "frac_roofline": round(roof / t_f, 3),
+            "bound": "compute" if roof == t_cmp else ("nvlink" if roof == 2 * t_l_us else "hbm"),
+            "dispatch_us": round(t_d, 1), "combine_us": round(t_c, 1), "link_us_each_way": round(t_l_us, 1),
+            "dispatch_frac_link": round(t_l_us / t_d, 3), "combine_frac_link": round(t_l_us / t_c, 3),
+            "link_mb_each_way": round(link_bytes / 1e6, 1), "rel_err_vs_baseline": round(rel, 5), "status": status,
+            "peaks": pk["source"]}), flush=True)
+    torch.cuda.synchronize()
+    tp.barrier()
+    a2a.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ms", type=str, default="16,64,256,1024,4096,16384")
@@ -162,8 +233,11 @@ def main():
             if m % n_r:
                 continue
             if op == "moe":
+                # few tokens: replicated-token form; from 256 tokens per rank on: the token all-to-all
                 if m <= 256:
                     bench_moe(tp, m, args, pk, flush, g)
+                if m // n_r >= 256:
+                    bench_moe_a2a(tp, m, args, pk, flush, g)
                 continue
             if op == "ar":
                 if m > 128 or n_r < 2:

@@ -64,10 +64,19 @@ int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, void* out, 
                           int features, int k, int total_rows, int max_rows_per_group, long long ldx, long long ldo,
                           int gated, int gate_off, const void* bias, long long bias_group_stride, float act_limit,
                           float act_alpha, int block_n, const int* tile_list, const int* tile_count, int max_tiles,
-                          void* stream);
+                          const void* arrive, unsigned int arrive_target, void* stream);
 int nkb_moe_dispatch(const int* experts, int tokens, int top_k, int expert_lo, int num_local, const void* x, int hidden,
                      void* x_sorted, int* counts, int* offsets, int* cursors, int* pair_pos, int bn_a, int* tiles_a,
                      int* ntiles_a, int bn_b, int* tiles_b, int* ntiles_b, void* stream);
+// expert-parallel token all-to-all (moe_a2a.cu)
+int nkb_moe_a2a_dispatch(const void* x, const int* experts, int tokens, int top_k, int hidden, int num_experts,
+                         int n_ranks, int rank, unsigned int epoch, void* const* cnt, void* const* cnt_flag,
+                         void* const* arrive, void* const* ready, void* const* x_recv, void* const* y, int* cursors,
+                         int* sent, int* offsets, int* pair_dest, int capacity_rows, int bn_a, int* tiles_a,
+                         int* ntiles_a, int bn_b, int* tiles_b, int* ntiles_b, int* total_rows, void* stream);
+int nkb_moe_a2a_combine(const int* pair_dest, const float* weights, int tokens, int top_k, int hidden, int n_ranks,
+                        int rank, unsigned int epoch, void* const* cnt, void* const* cnt_flag, void* const* arrive,
+                        void* const* ready, void* const* x_recv, void* const* y, void* out, void* stream);
 int nkb_moe_combine(const void* y_sorted, const int* pair_pos, const float* weights, int tokens, int top_k, int hidden,
                     void* out, void* stream);
 

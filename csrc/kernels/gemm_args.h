@@ -47,6 +47,10 @@ struct GroupArgs {
   long long bias_group_stride;
   float act_limit;         // > 0: clamped SwiGLU (up + 1) * gate * sigmoid(act_alpha * gate)
   float act_alpha;
+  // expert-parallel all-to-all (moe_a2a.cu): the rows of group g are complete once arrive[g] reaches
+  // arrive_target (every source rank has delivered its rows); nullptr = rows are local, no wait
+  const unsigned int* arrive;
+  unsigned int arrive_target;
 };
 
 // Fused collective epilogue ("push" mode, decode orientation only): every finished

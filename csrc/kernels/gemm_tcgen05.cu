@@ -270,7 +270,8 @@ extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, 
                                      int num_groups, int features, int k, int total_rows, int max_rows_per_group,
                                      long long ldx, long long ldo, int gated, int gate_off, const void* bias,
                                      long long bias_group_stride, float act_limit, float act_alpha, int block_n,
-                                     const int* tile_list, const int* tile_count, int max_tiles, void* stream) {
+                                     const int* tile_list, const int* tile_count, int max_tiles, const void* arrive,
+                                     unsigned int arrive_target, void* stream) {
   if (!status_word() && nkb_init() != 0) return -1;
   if (num_groups <= 0 || features <= 0 || k <= 0 || total_rows <= 0) return 0;
   if ((k & 7) || (ldx & 7)) return -2;
@@ -307,6 +308,8 @@ extern "C" int nkb_gemm_bf16_grouped(const void* weights, const void* x_sorted, 
   }
   grp.act_limit = act_limit;
   grp.act_alpha = act_alpha;
+  grp.arrive = reinterpret_cast<const unsigned int*>(arrive);
+  grp.arrive_target = arrive_target;
   const long long rows_per_group = gated ? (long long)gate_off + features : features;
   CUtensorMap ta, tb;
   {

@@ -204,6 +204,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
+    int arrived_group = -1;
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
       const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
       if (!wi.valid) continue;
@@ -211,6 +212,36 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
       const int row0 = wi.rt * kTileRows, col0 = wi.col0;
       const int kb0 = sp * args.kb_per_split;
       const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
+      if constexpr (GROUPED) {
+        if (grp.arrive && wi.group != arrived_group) {
+          // rows of this expert come from other ranks: wait (bounded) until every source has delivered
+          int ok = 1;
+          if (lane == 0) {
+            const unsigned int* flag = grp.arrive + wi.group;
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (int(v - grp.arrive_target) < 0) {
+              const unsigned long long t0 = globaltimer_ns();
+              unsigned int spins = 0;
+              while (true) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                if (int(v - grp.arrive_target) >= 0) break;
+                if ((++spins & 255u) == 0 && (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs)) {
+                  *abort_flag = 1;
+                  atomicCAS(args.status, 0, ERR_WAIT_PEER_FLAG | (wi.group << 8) | (5 << 16));
+                  ok = 0;
+                  break;
+                }
+              }
+            }
+            // peers wrote these rows through the generic proxy; order them before the async-proxy reads
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) { alive = false; break; }
+          arrived_group = wi.group;
+        }
+      }
       for (int kb = kb0; kb < kb1; ++kb) {
         bool ok = mbar_wait(&ctrl->empty[stage], phase ^ 1u, abort_flag, args.status, ERR_WAIT_SMEM_EMPTY);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }

@@ -67,3 +67,21 @@ class MoEBlock:
                                                            cfg.rms_eps)
         y = self.forward(lw, x)
         return ops.add_rmsnorm(y, next_norm, residual_in=resid, eps=cfg.rms_eps)
+
+    def forward_sharded(self, lw, x_local: torch.Tensor) -> torch.Tensor:
+        """Expert-parallel block for tokens that are sharded over the ranks (x_local [T / ranks, H], this rank's
+        slab): the rows travel to their experts' owners and back through peer memory
+        (`parallel.moe_a2a.MoEAllToAll`).  Returns this rank's slab of the block output."""
+        from ..parallel.moe_a2a import MoEAllToAll
+
+        cfg = self.cfg
+        T = x_local.shape[0]
+        a2a = getattr(self, "_a2a", None)
+        if a2a is None or a2a.max_local_tokens < T:
+            if a2a is not None:
+                a2a.close()
+            cap = max(2048, 1 << (T - 1).bit_length())
+            a2a = self._a2a = MoEAllToAll(self.tp, cap, cfg.top_k, cfg.hidden_size, cfg.num_experts)
+        weights, experts = self.route(lw, x_local)
+        return a2a.forward(x_local, experts, weights, lw.gate_up, lw.down, gate_up_bias=lw.gate_up_bias,
+                           down_bias=lw.down_bias, act_limit=cfg.swiglu_limit, act_alpha=cfg.swiglu_alpha)

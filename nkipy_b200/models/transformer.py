@@ -269,7 +269,8 @@ class TransformerLM:
         cfg = self.cfg
         tp1 = self.tp.world_size == 1
         if (not tp1 and not return_hidden and inputs is None and getattr(self.tp, "fused", None) is not None
-                and ids.shape[0] % self.tp.world_size == 0 and ids.shape[0] >= 128 * self.tp.world_size):
+                and ids.shape[0] % self.tp.world_size == 0 and ids.shape[0] >= 128 * self.tp.world_size
+                and ids.shape[0] <= self._sp_max_rows()):
             return self._prefill_sequence_parallel(ids, positions, slots, cache, block_table, q_start, q_lens,
                                                    context_lens, max_q_len)
         if inputs is None:
@@ -317,6 +318,41 @@ class TransformerLM:
             return normed, taps
         return normed
 
+    SP_MIN_CAPACITY = 16384       # tokens; the engine's default prefill chunk
+    # Local token count from which the MoE block of the sequence-parallel prefill exchanges tokens with the
+    # expert owners (all-to-all in peer memory) instead of replicating them: below it the exchange's fixed
+    # cost (count round trip, per-expert counters) outweighs the bytes saved.
+    MOE_A2A_MIN_TOKENS = 256
+
+    def _sp_max_rows(self) -> int:
+        """Longest chunk the fused sequence-parallel kernels can describe; longer ones take the NCCL path."""
+        from ..parallel.symm import _FusedGemmCollective
+
+        return _FusedGemmCollective.max_rows(self.tp.world_size) // 2
+
+    def _sp_pair(self, tokens: int):
+        """The (reduce-scatter GEMM, all-gather GEMM) pair of the sequence-parallel prefill.  One pair serves
+        every prompt length up to its capacity (the kernels take the row count per call); a longer chunk
+        replaces it with one of twice the size, releasing the old symmetric buffers first, so the buffers
+        neither multiply with the number of distinct prompt lengths nor are set up inside the hot path more
+        than a handful of times."""
+        from ..parallel.symm import AllGatherGemm, GemmReduceScatter
+
+        pair = getattr(self, "_sp_ops", None)
+        if pair is not None and tokens <= pair[0].m:
+            return pair
+        n = self.tp.world_size
+        cap = max(self.SP_MIN_CAPACITY, pair[0].m if pair is not None else 0)
+        while cap < tokens:
+            cap *= 2
+        cap = (cap + 128 * n - 1) // (128 * n) * (128 * n)
+        if pair is not None:
+            pair[0].close()
+            pair[1].close()
+        self._sp_ops = (GemmReduceScatter(self.tp, cap, self.cfg.hidden_size),
+                        AllGatherGemm(self.tp, cap, self.cfg.hidden_size))
+        return self._sp_ops
+
     def _prefill_sequence_parallel(self, ids, positions, slots, cache, block_table, q_start, q_lens, context_lens,
                                    max_q_len):
         """Prefill for tp > 1 in the sequence-parallel layout: the residual stream lives as one row slab
@@ -329,11 +365,7 @@ class TransformerLM:
         T = ids.shape[0]
         n, r = tp.world_size, tp.rank
         rows = T // n
-        if not hasattr(self, "_sp_ops"):
-            self._sp_ops = {}
-        if T not in self._sp_ops:
-            self._sp_ops[T] = (GemmReduceScatter(tp, T, cfg.hidden_size), AllGatherGemm(tp, T, cfg.hidden_size))
-        rs, ag = self._sp_ops[T]
+        rs, ag = self._sp_pair(T)
         if not hasattr(self, "_o_bias_full"):
             # the row-parallel bias is stored on rank 0 only (zeros elsewhere); every slab needs it
             self._o_bias_full = [None if lw.o_bias is None else tp.all_reduce(lw.o_bias.clone())
@@ -352,7 +384,11 @@ class TransformerLM:
             resid, normed = ops.add_rmsnorm(o, lw.post_norm, residual_in=resid, bias=self._o_bias_full[i],
                                             eps=cfg.rms_eps)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
-            if cfg.is_moe:
+            if cfg.is_moe and self._moe.mode == "ep" and rows >= self.MOE_A2A_MIN_TOKENS:
+                # tokens stay sharded: route this rank's rows, exchange them with the expert owners
+                dn = self._moe.forward_sharded(lw, normed)
+            elif cfg.is_moe:
+                # few tokens: replicate them, run the local experts, sum over ranks (library collectives)
                 full = tp.all_gather(normed).reshape(T, cfg.hidden_size)
                 y_sorted, plan, weights = self._moe._experts(lw, full)
                 y = ops.moe_combine(y_sorted, plan.pair_pos, weights, T)

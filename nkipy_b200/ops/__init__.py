@@ -939,7 +939,8 @@ def moe_dispatch(x: torch.Tensor, experts: torch.Tensor, expert_lo: int, num_loc
 
 def grouped_linear(x_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, max_rows_per_group: int,
                    gated: bool = False, bias: Optional[torch.Tensor] = None, act_limit: float = 0.0,
-                   act_alpha: float = 1.702, tiles=None) -> torch.Tensor:
+                   act_alpha: float = 1.702, tiles=None, out: Optional[torch.Tensor] = None,
+                   arrive: Optional[int] = None, arrive_target: int = 0) -> torch.Tensor:
     """Per-group ``y[r] = x_sorted[r] @ w[g(r)].T`` for rows sorted by group (group g owns rows
     offsets[g] .. offsets[g + 1]).  w [G, N, K] bf16 (gated: [G, 2 * I, K], gate rows then up
     rows, output ``act(gate) * up`` of width I).  bias [G, N] is added before the activation."""
@@ -968,7 +969,8 @@ def grouped_linear(x_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tenso
         return out
     global _launches
     _check_bf16(x_sorted, w, bias)
-    out = torch.empty((R, N), dtype=torch.bfloat16, device=x_sorted.device)
+    if out is None:
+        out = torch.empty((R, N), dtype=torch.bfloat16, device=x_sorted.device)
     tl = tc = None
     max_tiles = 0
     if tiles is not None:
@@ -984,7 +986,7 @@ def grouped_linear(x_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tenso
         w.data_ptr(), x_sorted.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, N, K, R, int(max_rows_per_group),
         x_sorted.stride(0), N, 1 if gated else 0, N if gated else 0, _ptr(bias),
         bias.stride(0) if bias is not None else 0, float(act_limit), float(act_alpha), block_n, tl, tc,
-        int(max_tiles), _stream())
+        int(max_tiles), arrive, int(arrive_target), _stream())
     _lib.check(rc, "nkb_gemm_bf16_grouped")
     _launches += 1
     return out

@@ -33,8 +33,15 @@ _SIGNATURES = {
     "nkb_gemm_bf16_grouped": (
         c_int,
         [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, _P, c_longlong,
-         c_float, c_float, c_int, _P, _P, c_int, _P],
+         c_float, c_float, c_int, _P, _P, c_int, _P, ctypes.c_uint, _P],
     ),
+    "nkb_moe_a2a_dispatch": (c_int, [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_uint,
+                                     ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P),
+                                     ctypes.POINTER(_P), ctypes.POINTER(_P), _P, _P, _P, _P, c_int, c_int, _P, _P,
+                                     c_int, _P, _P, _P, _P]),
+    "nkb_moe_a2a_combine": (c_int, [_P, _P, c_int, c_int, c_int, c_int, c_int, ctypes.c_uint, ctypes.POINTER(_P),
+                                    ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P),
+                                    ctypes.POINTER(_P), _P, _P]),
     "nkb_moe_dispatch": (c_int, [_P, c_int, c_int, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
                                  _P, _P, _P]),
     "nkb_moe_combine": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P, _P]),

@@ -402,6 +402,11 @@ class _FusedGemmCollective:
 
     FLAG_BYTES = 8192
 
+    @classmethod
+    def max_rows(cls, world: int) -> int:
+        """Largest total row count the counter array can describe."""
+        return cls.FLAG_BYTES // (4 * world) * 128 * world
+
     def __init__(self, tp: TPGroup, buf_bytes: int, rows_per_rank: int):
         if tp.world_size > 8:
             raise ValueError("fused GEMM collectives support up to 8 ranks (one NVSwitch domain)")
@@ -432,6 +437,7 @@ class GemmReduceScatter(_FusedGemmCollective):
     NVLink while later tiles are computed; the owner's CTAs sum the tp partials at the end."""
 
     def __init__(self, tp: TPGroup, m: int, n: int):
+        """m is the capacity: calls may pass any row count up to it (a multiple of the number of ranks)."""
         if m % tp.world_size:
             raise ValueError("m must be divisible by the number of ranks")
         self.m, self.n = m, n
@@ -446,8 +452,9 @@ class GemmReduceScatter(_FusedGemmCollective):
 
         m, k = x.shape
         n = w.shape[0]
-        if (m, n) != (self.m, self.n) or w.shape[1] != k:
-            raise ValueError(f"GemmReduceScatter sized for [{self.m}, {self.n}], got x {tuple(x.shape)} w {tuple(w.shape)}")
+        if m > self.m or m % self.tp.world_size or n != self.n or w.shape[1] != k:
+            raise ValueError(f"GemmReduceScatter sized for up to [{self.m}, {self.n}], got x {tuple(x.shape)} "
+                             f"w {tuple(w.shape)}")
         tp = self.tp
         if out is None:
             out = torch.empty((m // tp.world_size, n), dtype=torch.bfloat16, device=x.device)
@@ -466,6 +473,7 @@ class AllGatherGemm(_FusedGemmCollective):
     gather buffer while the others multiply the slabs in arrival order."""
 
     def __init__(self, tp: TPGroup, m: int, k: int, comm_ctas: int = 0):
+        """m is the capacity: calls may gather any row count up to it (the same on every rank)."""
         if m % tp.world_size:
             raise ValueError("m must be divisible by the number of ranks")
         self.m, self.k, self.comm_ctas = m, k, comm_ctas
@@ -494,15 +502,16 @@ class AllGatherGemm(_FusedGemmCollective):
         rows, k = x_local.shape
         n = w.shape[0] // 2 if gated else w.shape[0]
         tp = self.tp
-        if rows * tp.world_size != self.m or k != self.k or w.shape[1] != k:
-            raise ValueError(f"AllGatherGemm sized for [{self.m}, {self.k}], got x {tuple(x_local.shape)} "
+        m = rows * tp.world_size
+        if m > self.m or k != self.k or w.shape[1] != k:
+            raise ValueError(f"AllGatherGemm sized for up to [{self.m}, {self.k}], got x {tuple(x_local.shape)} "
                              f"w {tuple(w.shape)}")
         if out is None:
-            out = torch.empty((self.m, n), dtype=torch.bfloat16, device=x_local.device)
-        if gated and (self.m < 256 or n < 128 or n % 8):
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=x_local.device)
+        if gated and (m < 256 or n < 128 or n % 8):
             return self._swiglu(self(x_local, w))
         epoch, bufs = self._next()
-        rc = self._lib.nkb_ag_gemm(x_local.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, n, k, x_local.stride(0),
+        rc = self._lib.nkb_ag_gemm(x_local.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x_local.stride(0),
                                    w.stride(0), out.stride(0), bufs, self._flags, self.flag_stride, tp.world_size,
                                    tp.rank, epoch, self.comm_ctas, 1 if gated else 0,
                                    torch.cuda.current_stream().cuda_stream)
