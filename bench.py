@@ -95,65 +95,33 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--baseline-steps", type=int, default=4,
+                    help="decode steps of the eager PyTorch baseline run before ours for vs_baseline (0 = skip)")
+    ap.add_argument("--no-qwen3", action="store_true", help="skip the Qwen3-30B-A3B half of the headline metric")
+    ap.add_argument("--qwen3-steps", type=int, default=20, help="timed decode steps of the Qwen3 half (at most --steps)")
     return ap.parse_args()
 
 
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+def measure_ours(args, cfg, batch, prompt_len, tp, K, W, parallelism, weights=None):
+    """Build the engine for `cfg`, prefill, then time K decode steps on the device and K through the public
+    host API.  Returns the fields of the result line that belong to this model."""
     import torch
 
     from nkipy_b200 import ops
-    from nkipy_b200.models import config as C
     from nkipy_b200.models.engine import GenerationEngine, percentile
     from nkipy_b200.models.transformer import TransformerLM
     from nkipy_b200.models.weights import random_weights
-    from nkipy_b200.parallel.comm import TPGroup
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world != args.gpus:
-        if args.gpus > 1:
-            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
-    tp = TPGroup.from_env()
-    dev = tp.device
-    if dev.type != "cuda":
-        raise SystemExit("bench.py needs a CUDA device")
-    rank0 = tp.rank == 0
-
-    if args.model == "llama3-8b":
-        cfg = C.llama3_8b()
-        batch, prompt_len = args.batch or 64, args.prompt_len or 1024
-        parallelism = f"tp{world}"
-    elif args.model == "qwen3-30b-a3b":
-        cfg = C.qwen3_30b_a3b()
-        batch, prompt_len = args.batch or 128, args.prompt_len or 512
-        parallelism = f"tp{world}-ep{world}"
-    else:
-        # the only configuration the reference publishes numbers for: gpt-oss-20b, batch 1, greedy
-        # (examples/models/gpt_oss/peagle/README.md:101-102: 31.5 / 34.7 tok/s base decode on trn2 at TP = 4)
-        cfg = C.gpt_oss_20b()
-        batch, prompt_len = args.batch or 1, args.prompt_len or 128
-        parallelism = f"tp{world}-ep{world}"
-    debug = False
-    if args.layers:
-        cfg = cfg.scaled(num_layers=args.layers)
-        debug = True
-    K, W = args.steps, max(args.warmup, 3)
+    dev, world = tp.device, tp.world_size
     EXTRA_STEPS = 400        # room for the untimed steps that keep the clock sampler fed on short runs
     total_new = 2 * (K + W) + 4 + EXTRA_STEPS
     max_seq = prompt_len + total_new + 32
-
-    torch.manual_seed(0)
     t_build = time.perf_counter()
-    weights = random_weights(cfg, tp.rank, world, device=dev, seed=0, std=0.02)
+    if weights is None:
+        torch.manual_seed(0)
+        weights = random_weights(cfg, tp.rank, world, device=dev, seed=0, std=0.02)
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(0, cfg.vocab_size, (batch, prompt_len), generator=g)
-
-    if args.impl == "eager":
-        return run_eager(args, cfg, weights, prompts, tp, K, W, parallelism)
-
     model = TransformerLM(cfg, weights, tp, device=dev)
     del weights
     torch.cuda.empty_cache()
@@ -176,8 +144,8 @@ def main():
     t0 = time.perf_counter()
     engine.prefill(seqs)
     torch.cuda.synchronize()
-    prefill_s = time.perf_counter() - t0
-    ttft_p50 = percentile(engine.stats.ttft_s, 50)
+    prefill_s = tp.max_over_ranks(time.perf_counter() - t0)
+    ttft_p50 = tp.max_over_ranks(percentile(engine.stats.ttft_s, 50))
     ops.raise_on_device_error()
 
     engine.prepare_decode(total_new)
@@ -234,10 +202,118 @@ def main():
     tp.barrier()
     clocks = sampler.stop()
     clocks["window"] = "device-timed + end-to-end regions" + (f" + {extra} identical untimed steps" if extra else "")
+    out = {
+        "value": batch * K / (dev_ms / 1e3), "ms_per_step": dev_ms / K, "e2e_value": batch * K / e2e_s,
+        "e2e_ms_per_step": e2e_s * 1e3 / K, "ttft_p50_s": ttft_p50, "prefill_s": prefill_s,
+        "launches_per_step": launches_per_step, "clocks": clocks, "build_s": build_s,
+    }
+    # release everything this model holds before the next one is built
+    torch.cuda.synchronize()
+    model.close()
+    fused = getattr(tp, "fused", None)
+    if fused is not None:
+        fused.close()
+        tp.fused = None
+    del engine, model
+    import gc
 
-    ms_per_step = dev_ms / K
-    value = batch * K / (dev_ms / 1e3)
-    e2e_value = batch * K / e2e_s
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_eager(cfg, weights, prompts, tp, steps, warmup):
+    """A few decode steps of the plain PyTorch (cuBLAS + NCCL) implementation of the same model on the same
+    weights: the baseline that `vs_baseline` refers to (the reference itself cannot run on this hardware).
+    Returns decode tokens/s (device-timed, max over ranks)."""
+    import torch
+
+    from nkipy_b200.models.reference import EagerTransformer
+
+    dev = tp.device
+    model = EagerTransformer(cfg, weights, tp, device=dev, dtype=torch.bfloat16)
+    batch, prompt_len = prompts.shape
+    ids = prompts.to(dev)
+    model.alloc_static_cache(batch, prompt_len + warmup + steps + 8)
+    chunk = max(1, 16384 // prompt_len)
+    firsts = []
+    for b0 in range(0, batch, chunk):
+        hh = EagerSlice(model, b0, min(batch, b0 + chunk)).forward(ids[b0:b0 + chunk], 0)
+        firsts.append(model.greedy(hh[:, -1]))
+    nxt = torch.cat(firsts)
+    pos = prompt_len
+    for _ in range(warmup):
+        nxt = model.greedy(model.forward_sdpa(nxt[:, None], pos)[:, -1])
+        pos += 1
+    tp.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        nxt = model.greedy(model.forward_sdpa(nxt[:, None], pos)[:, -1])
+        pos += 1
+    end.record()
+    torch.cuda.synchronize()
+    ms = tp.max_over_ranks(start.elapsed_time(end))
+    del model
+    torch.cuda.empty_cache()
+    return batch * steps / (ms / 1e3)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    import torch
+
+    from nkipy_b200.models import config as C
+    from nkipy_b200.models.weights import random_weights
+    from nkipy_b200.parallel.comm import TPGroup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    tp = TPGroup.from_env()
+    dev = tp.device
+    if dev.type != "cuda":
+        raise SystemExit("bench.py needs a CUDA device")
+    rank0 = tp.rank == 0
+
+    def shape_of(model_name):
+        if model_name == "llama3-8b":
+            return C.llama3_8b(), args.batch or 64, args.prompt_len or 1024, f"tp{world}"
+        if model_name == "qwen3-30b-a3b":
+            return C.qwen3_30b_a3b(), args.batch or 128, args.prompt_len or 512, f"tp{world}-ep{world}"
+        # the only configuration the reference publishes numbers for: gpt-oss-20b, batch 1, greedy
+        # (examples/models/gpt_oss/peagle/README.md:101-102: 31.5 / 34.7 tok/s base decode on trn2 at TP = 4)
+        return C.gpt_oss_20b(), args.batch or 1, args.prompt_len or 128, f"tp{world}-ep{world}"
+
+    cfg, batch, prompt_len, parallelism = shape_of(args.model)
+    debug = False
+    if args.layers:
+        cfg = cfg.scaled(num_layers=args.layers)
+        debug = True
+    K, W = args.steps, max(args.warmup, 3)
+
+    torch.manual_seed(0)
+    weights = random_weights(cfg, tp.rank, world, device=dev, seed=0, std=0.02)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab_size, (batch, prompt_len), generator=g)
+
+    if args.impl == "eager":
+        return run_eager(args, cfg, weights, prompts, tp, K, W, parallelism)
+
+    # baseline of the same model on the same weights, a few steps (eager PyTorch: cuBLAS, SDPA, NCCL)
+    eager_value = None
+    if args.baseline_steps > 0:
+        eager_value = measure_eager(cfg, weights, prompts, tp, args.baseline_steps, 2)
+
+    r = measure_ours(args, cfg, batch, prompt_len, tp, K, W, parallelism, weights=weights)
+    del weights
+    value = r["value"]
+    published = round(value / 34.7, 2) if (args.model == "gpt-oss-20b" and batch == 1) else None
     result = {
         "metric": {"llama3-8b": "decode tokens/s (Llama-3-8B-shaped, TP over N GPUs, batch 64, prompt 1024, greedy)",
                    "qwen3-30b-a3b": "decode tokens/s (Qwen3-30B-A3B-shaped MoE, batch 128, prompt 512, greedy)",
@@ -247,11 +323,17 @@ def main():
         "n_gpus": world,
         "steps": K,
         "warmup": W,
-        "ms_per_step": round(ms_per_step, 4),
+        "ms_per_step": round(r["ms_per_step"], 4),
         "higher_is_better": True,
         "scaling": "strong",
-        # published reference number exists only for gpt-oss-20b at batch 1 (34.7 tok/s, best base decode on trn2)
-        "vs_baseline": round(value / 34.7, 2) if (args.model == "gpt-oss-20b" and batch == 1) else None,
+        # The reference publishes a number only for gpt-oss-20b at batch 1 (34.7 tok/s, best base decode on trn2);
+        # for the other models the baseline is the eager PyTorch implementation measured a moment ago in this
+        # process on the same weights (see "baseline").
+        "vs_baseline": published if published is not None else (round(value / eager_value, 2) if eager_value else None),
+        "baseline": ({"impl": "reference, published (trn2, TP=4)", "value": 34.7} if published is not None else
+                     ({"impl": "eager-pytorch (cuBLAS + SDPA + NCCL), same process, same weights",
+                       "value": round(eager_value, 2), "unit": "tokens/s", "steps": args.baseline_steps}
+                      if eager_value else None)),
         "dtype": "bf16",
         "data": "synthetic (uniform random token ids seed 0; random-init weights N(0, 0.02))",
         "impl": "ours",
@@ -260,16 +342,29 @@ def main():
             "layers": cfg.num_layers, "new_tokens_timed": K, "kv_cache": "paged, block 32, prefix sharing on",
             "l2": "per-step working set (weights + KV) exceeds L2; no flush", "cuda_graph": not args.no_graph,
         },
-        "ttft_p50_s": round(ttft_p50, 4),
-        "prefill_s": round(prefill_s, 4),
-        "prefill_tokens_per_s": round(batch * prompt_len / prefill_s, 1),
-        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": batch * 4,
-                "d2h_bytes_per_step": batch * 4, "ms_per_step": round(e2e_s * 1e3 / K, 4)},
-        "gpu_launches": (launches_per_step or 0) * K,
-        "launches_per_step": launches_per_step,
-        "clocks": clocks,
-        "build_s": round(build_s, 1),
+        "ttft_p50_s": round(r["ttft_p50_s"], 4),
+        "prefill_s": round(r["prefill_s"], 4),
+        "prefill_tokens_per_s": round(batch * prompt_len / r["prefill_s"], 1),
+        "e2e": {"value": round(r["e2e_value"], 2), "unit": "tokens/s", "h2d_bytes_per_step": batch * 4,
+                "d2h_bytes_per_step": batch * 4, "ms_per_step": round(r["e2e_ms_per_step"], 4)},
+        "gpu_launches": (r["launches_per_step"] or 0) * K,
+        "launches_per_step": r["launches_per_step"],
+        "clocks": r["clocks"],
+        "build_s": round(r["build_s"], 1),
     }
+    # The second half of the headline metric: the Qwen3-30B-A3B-shaped MoE model (expert parallel over the same
+    # GPUs), measured after the first model's memory has been released.
+    if args.model == "llama3-8b" and not args.no_qwen3 and not debug:
+        qcfg, qbatch, qprompt, qpar = shape_of("qwen3-30b-a3b")
+        qK = max(3, min(K, args.qwen3_steps))
+        q = measure_ours(args, qcfg, qbatch, qprompt, tp, qK, W, qpar)
+        result.update({
+            "qwen3_decode_tokens_per_s": round(q["value"], 2), "qwen3_ms_per_step": round(q["ms_per_step"], 4),
+            "qwen3_ttft_p50_s": round(q["ttft_p50_s"], 4), "qwen3_prefill_s": round(q["prefill_s"], 4),
+            "qwen3_e2e_tokens_per_s": round(q["e2e_value"], 2), "qwen3_launches_per_step": q["launches_per_step"],
+            "qwen3_config": {"model": qcfg.name, "global_batch": qbatch, "seq_len": qprompt, "parallelism": qpar,
+                             "steps": qK},
+        })
     if debug:
         result["invalid"] = "debug run with a reduced layer count"
     if rank0:

@@ -402,6 +402,19 @@ class TransformerLM:
             resid, normed = ops.add_rmsnorm(dn, nxt, residual_in=resid, eps=cfg.rms_eps)
         return tp.all_gather(normed).reshape(T, cfg.hidden_size)
 
+    def close(self) -> None:
+        """Release the symmetric (peer-mapped) buffers this model set up lazily: the sequence-parallel GEMM pair
+        and the expert all-to-all.  Collective: every rank of the group calls it at the same point."""
+        pair = getattr(self, "_sp_ops", None)
+        if pair is not None:
+            pair[0].close()
+            pair[1].close()
+            self._sp_ops = None
+        a2a = getattr(self._moe, "_a2a", None) if self._moe is not None else None
+        if a2a is not None:
+            a2a.close()
+            self._moe._a2a = None
+
     # ------------------------------------------------------------------ heads
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Vocab-parallel logits [rows, V / tp] (bf16)."""
