@@ -658,11 +658,30 @@ const PassInfo* find_pass(const std::string& name) {
   return nullptr;
 }
 
+// A `loop` node carries its body as a nested graph (attribute "body", IR text): every pass also runs on
+// the bodies, innermost first, so a loop is optimised like straight-line code without being unrolled.
+static void run_on_loop_bodies(Graph& g, const PassInfo& p, const PassOptions& opts) {
+  for (Node* n : g.nodes) {
+    if (n->opcode != "loop" || !n->attrs.has("body")) continue;
+    auto body = Graph::parse(n->attrs.at("body").as_string());
+    body->verify();
+    run_on_loop_bodies(*body, p, opts);
+    p.fn(*body, opts);
+    body->verify();
+    n->attrs.set("body", Json::make_str(body->print()));
+  }
+}
+
+static void run_one(Graph& g, const PassInfo& p, const PassOptions& opts) {
+  if (p.group != "oracle") run_on_loop_bodies(g, p, opts);
+  p.fn(g, opts);
+  g.verify();
+}
+
 void run_pass(Graph& g, const std::string& name, const PassOptions& opts) {
   const PassInfo* p = find_pass(name);
   if (!p) throw CompileError("unknown pass '" + name + "'");
-  p->fn(g, opts);
-  g.verify();
+  run_one(g, *p, opts);
 }
 
 std::string apply_passes(const std::string& ir_text, const std::vector<std::string>& passes, const PassOptions& opts) {
@@ -714,8 +733,7 @@ std::string run_pipeline(const std::string& ir_text, const std::string& stop_aft
   auto g = Graph::parse(ir_text);
   g->verify();
   for (size_t i = 0; i < last; ++i) {
-    pipe[i].fn(*g, opts);
-    g->verify();
+    run_one(*g, pipe[i], opts);
     if (!dump_dir.empty()) {
       std::ostringstream name;
       name << dump_dir << "/" << std::setw(2) << std::setfill('0') << (dump_start + int(i)) << "_" << pipe[i].name << ".ir";

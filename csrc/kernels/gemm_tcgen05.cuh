@@ -106,12 +106,20 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 
 // GROUPED selects the per-expert variant (3-D weight map, group offsets / tile list, expert
 // biases and the clamped activation); the plain variant compiles none of that.
+// Elementwise epilogue hook for generated kernels: a functor applied to every fp32 accumulator value
+// (output row, output column) before the store of the non-transposed orientation.
+struct NoElemEpi {
+  static constexpr bool active = false;
+  __device__ __forceinline__ float operator()(float x, long long, long long) const { return x; }
+};
+
 // Fix selects a split-K fix-up epilogue (splitk_fix.cuh): the partial tiles go to fix.c.partials (the
 // launcher points args.out there) and the CTA that completes a tile's arrival counter finishes the tile.
-template <int BN, bool PUSH, bool GROUPED, class Fix = NoFix>
+template <int BN, bool PUSH, bool GROUPED, class Fix = NoFix, class ElemEpi = NoElemEpi>
 __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
                                                const PushArgs& push, const GroupArgs& grp,
-                                               const typename Fix::Args& fix = typename Fix::Args{}) {
+                                               const typename Fix::Args& fix = typename Fix::Args{},
+                                               const ElemEpi& elem_epi = ElemEpi{}) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -405,6 +413,13 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
           continue;
+        }
+        if constexpr (ElemEpi::active) {
+          if (row_ok && !args.transpose_out) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cbase + j < cols_end) v[j] = __float_as_uint(elem_epi(__uint_as_float(v[j]), row, cbase + j));
+          }
         }
         if (args.transpose_out) {
           // out[col * ldo + row]: consecutive lanes hold consecutive rows -> coalesced

@@ -233,6 +233,10 @@ class Generator:
 
     # ------------------------------------------------------------------ driver
     def run(self) -> Program:
+        from ..core.ir import expand_loops
+
+        # loops stay loops through the pass pipeline; launches are emitted per iteration
+        self.g = expand_loops(self.g)
         g = self.g
         for n in g.nodes:
             for i in n.inputs:
@@ -245,7 +249,10 @@ class Generator:
             self.views[p.id] = self.contiguous_view(b, p.shape, p.dtype)
             inputs.append({"name": p.name, "buffer": b, "shape": list(p.shape), "dtype": dtype_name(p.dtype)})
         pending: List[Node] = []       # pointwise nodes waiting to be flushed as one kernel
-        for n in g.nodes:
+        consumed = set()               # nodes already emitted as part of a GEMM epilogue
+        for idx, n in enumerate(g.nodes):
+            if id(n) in consumed:
+                continue
             if n.opcode in POINTWISE and self._fusable(n, pending):
                 pending.append(n)
                 continue
@@ -253,6 +260,14 @@ class Generator:
             pending = []
             if n.opcode in POINTWISE:
                 pending.append(n)
+            elif n.opcode == "dot":
+                views, chain = self._epilogue_chain(idx)
+                for v in views:
+                    self.lower(v)
+                    consumed.add(id(v))
+                for c in chain:
+                    consumed.add(id(c))
+                self.lower_dot(n, epilogue=chain)
             else:
                 self.lower(n)
         self._flush(pending)
@@ -275,6 +290,72 @@ class Generator:
         if self.uses_tcgen05:
             src = "#define NKB_USE_TCGEN05 1\n" + src
         return Program(src, self.buffers, self.launches, inputs, outputs, g.name)
+
+    def _epilogue_chain(self, idx: int):
+        """Elementwise nodes the fusion pass marked as the epilogue of the dot at position idx
+        (`_epilogue_of` = the dot's `_op_id`, continued through the same `_fuse_group`): they are emitted inside
+        the GEMM kernel, applied to the fp32 accumulator before the single store.  Returns (view / constant
+        nodes in between that only need their views set up, the chain); an empty chain means no fusion.
+        The chain must be 2-D, consume the dot's result nowhere else, let only its last value escape and end in
+        bf16 (what the GEMM stores)."""
+        g = self.g
+        dot = g.nodes[idx]
+        out = dot.outputs[0]
+        if "_op_id" not in dot.attrs or len(out.shape) != 2:
+            return [], []
+        views, chain, group = [], [], None
+        j = idx + 1
+        while j < len(g.nodes):
+            m = g.nodes[j]
+            if m.opcode in ("broadcast", "reshape", "transpose", "slice", "constant"):
+                if any(i.id == out.id or any(i.id == c.outputs[0].id for c in chain) for i in m.inputs):
+                    break                                   # a view of the dot result: it must be materialised
+                views.append(m)
+                j += 1
+                continue
+            if m.opcode not in POINTWISE or tuple(m.outputs[0].shape) != tuple(out.shape):
+                break
+            if not chain:
+                if m.attrs.get("_epilogue_of") != dot.attrs["_op_id"]:
+                    break
+                group = m.attrs.get("_fuse_group")
+            elif m.attrs.get("_fuse_group") != group:
+                break
+            chain.append(m)
+            j += 1
+        # drop trailing view nodes that no chain member reads (they belong to later code)
+        if not chain:
+            return [], []
+        inside = {out.id} | {c.outputs[0].id for c in chain}
+        internal_uses: Dict[int, int] = {}
+        for c in chain:
+            for i in c.inputs:
+                if i.id in inside:
+                    internal_uses[i.id] = internal_uses.get(i.id, 0) + 1
+        # shrink the chain until exactly its last value escapes and nothing else does
+        while chain:
+            inside = {out.id} | {c.outputs[0].id for c in chain}
+            internal_uses = {}
+            for c in chain:
+                for i in c.inputs:
+                    if i.id in inside:
+                        internal_uses[i.id] = internal_uses.get(i.id, 0) + 1
+            ok = self.uses.get(out.id, 0) == internal_uses.get(out.id, 0)
+            for c in chain[:-1]:
+                o = c.outputs[0]
+                if self.uses.get(o.id, 0) != internal_uses.get(o.id, 0):
+                    ok = False
+            last = chain[-1].outputs[0]
+            if dtype_name(last.dtype) != "bf16":
+                ok = False
+            if ok:
+                break
+            chain = chain[:-1]
+        if not chain:
+            return [], []
+        last_pos = g.nodes.index(chain[-1])
+        views = [v for v in views if g.nodes.index(v) < last_pos]
+        return views, chain
 
     def _fusable(self, n: Node, pending: List[Node]) -> bool:
         if not pending:
@@ -573,7 +654,7 @@ class Generator:
         self.views[o.id] = self.contiguous_view(buf, o.shape, o.dtype)
 
     # -- dot -----------------------------------------------------------------------------
-    def lower_dot(self, n):
+    def lower_dot(self, n, epilogue: Optional[List[Node]] = None):
         a, b = n.inputs
         o = n.outputs[0]
         at = n.attrs
@@ -607,10 +688,13 @@ class Generator:
         buf = self.new_buffer(o.shape, o.dtype)
         self.views[o.id] = self.contiguous_view(buf, o.shape, o.dtype)
         if B * M * N == 0:
+            self._flush(list(epilogue or []))
             return
-        if (self.use_tcgen05 and dtype_name(a.dtype) == "bf16" and B == 1 and K % 8 == 0 and N % 8 == 0
+        # the layout pass may have ruled the tensor-core path out for this node ("_path": "simt")
+        want_tc = n.attrs.get("_path", "tcgen05") == "tcgen05"
+        if (self.use_tcgen05 and want_tc and dtype_name(a.dtype) == "bf16" and B == 1 and K % 8 == 0 and N % 8 == 0
                 and ak[1] == 1 and am[1] % 8 == 0 and av.offset % 8 == 0 and K >= 16):
-            return self._dot_tcgen05(n, av, bv, (am, ak), (bk, bn), M, N, K, buf)
+            return self._dot_tcgen05(n, av, bv, (am, ak), (bk, bn), M, N, K, buf, epilogue=epilogue)
         name = self.kname("gemm_simt")
         ta, tb, to = ctype(a.dtype), ctype(b.dtype), ctype(o.dtype)
         acc = "double" if dtype_name(o.dtype) == "f64" else ("float" if compute_type(o.dtype) == "float" else
@@ -637,10 +721,17 @@ class Generator:
             {"buffer": av.buffer, "offset": av.offset * av.dtype.itemsize},
             {"buffer": bv.buffer, "offset": bv.offset * bv.dtype.itemsize}, {"buffer": buf, "offset": 0}],
             f"{n.loc[0]}:{n.loc[1]}" if n.loc else None))
+        self._flush(list(epilogue or []))
 
-    def _dot_tcgen05(self, n, av: View, bv: View, a_ms, b_ks, M, N, K, out_buf):
+    def _dot_tcgen05(self, n, av: View, bv: View, a_ms, b_ks, M, N, K, out_buf, epilogue=None):
         """bf16 GEMM on the hand-written tcgen05 kernel: A [M, K] K-major via TMA; B must be [N, K]
-        K-major, so a [K, N] operand is transposed once into a temporary."""
+        K-major, so a [K, N] operand is transposed once into a temporary.
+
+        What the native pass pipeline decided for this node is taken from its attributes: the CTA tile width
+        and the persistent grid from `_tiling` (knob-driven-tiling, i.e. the user's `knob(x).tile_op(...)`), the
+        ring depth from `_stages` (insert-spill-reload, which shrinks it to the shared-memory budget), and the
+        elementwise epilogue chain from knob-driven-fusion (`epilogue`), which is compiled into a functor
+        that the GEMM applies to the fp32 accumulator before its single store."""
         (am, ak), (bk, bn) = a_ms, b_ks
         if not (bk[1] == 1 and bn[1] % 8 == 0 and bv.offset % 8 == 0):
             tmp = self.new_buffer((N, K), bfloat16)
@@ -653,23 +744,91 @@ class Generator:
         self.uses_tcgen05 = True
         name = self.kname("gemm_tcgen05")
         bn_tile = 256 if N >= 256 else (128 if N > 64 else 64 if N > 32 else 32)
-        self.kernels.append(f"""extern "C" __global__ void __launch_bounds__(nkb::kGemmThreads, 1)
-{name}(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const nkb::GemmArgs args) {{
-  nkb::gemm_bf16_body<{bn_tile}, false, false>(tmA, tmB, args, nkb::PushArgs{{}}, nkb::GroupArgs{{}});
-}}
-""")
+        tiling = n.attrs.get("_tiling") or {}
+        cta = tiling.get("cta_tile")
+        if cta and len(cta) >= 2 and int(cta[1]) in (32, 64, 128, 256):
+            bn_tile = int(cta[1])
         stage_bytes = 128 * 64 * 2 + bn_tile * 64 * 2
-        stages = min(12, (232448 - 1024 - 512 - 64) // stage_bytes)
+        max_stages = min(12, (232448 - 1024 - 512 - 64) // stage_bytes)
+        stages = max_stages
+        want_stages = n.attrs.get("_stages", tiling.get("stages"))
+        if want_stages:
+            stages = max(2, min(int(want_stages), max_stages))
         smem = stages * stage_bytes + 1024 + 512 + 64
         tiles = ((M + 127) // 128) * ((N + bn_tile - 1) // bn_tile)
-        self.launches.append(Launch(name, (min(tiles, 148), 1, 1), (192, 1, 1), smem, [
+        grid = min(tiles, 148)
+        if tiling.get("grid"):
+            grid = max(1, min(int(tiling["grid"]), tiles, 148))
+        extra_params, extra_args, functor = "", [], ""
+        ee_type, ee_make = "nkb::NoElemEpi", ""
+        if epilogue:
+            functor, ptr_params, extra_args, ee_type = self._epilogue_functor(name, n, epilogue)
+            extra_params = "".join(f", {p}" for p in ptr_params)
+            ee_make = f"  const {ee_type} ee{{{', '.join(f'p{i}' for i in range(len(ptr_params)))}}};\n"
+            last = epilogue[-1].outputs[0]
+            self.views[last.id] = self.contiguous_view(out_buf, last.shape, last.dtype)
+        body_call = (f"  nkb::gemm_bf16_body<{bn_tile}, false, false, nkb::NoFix, {ee_type}>(tmA, tmB, args, "
+                     f"nkb::PushArgs{{}}, nkb::GroupArgs{{}}, nkb::NoFix::Args{{}}"
+                     + (", ee" if epilogue else f", {ee_type}{{}}") + ");")
+        self.kernels.append(functor + f"""extern "C" __global__ void __launch_bounds__(nkb::kGemmThreads, 1)
+{name}(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const nkb::GemmArgs args,
+       const nkb::PushArgs{extra_params}) {{
+{ee_make}{body_call}
+}}
+""")
+        self.launches.append(Launch(name, (grid, 1, 1), (192, 1, 1), smem, [
             {"tensormap": {"buffer": av.buffer, "offset": av.offset * 2, "dims": [K, M], "strides": [am[1] * 2],
                            "box": [64, 128]}},
             {"tensormap": {"buffer": bv.buffer, "offset": bv.offset * 2, "dims": [K, N], "strides": [ldb * 2],
                            "box": [64, bn_tile]}},
             {"gemm_args": {"rows": M, "cols": N, "k": K, "block_n": bn_tile, "stages": stages, "ldo": N,
-                           "out_buffer": out_buf, "out_offset": 0}}],
+                           "out_buffer": out_buf, "out_offset": 0,
+                           "fused_epilogue": [c.opcode for c in epilogue] if epilogue else []}}] + extra_args,
             f"{n.loc[0]}:{n.loc[1]}" if n.loc else None))
+
+    def _epilogue_functor(self, kname: str, dot: Node, chain: List[Node]):
+        """C++ functor `float operator()(float acc, long long i0, long long i1)` for an elementwise chain rooted
+        at the dot's result; operands that are not chain values are read through their [M, N] views."""
+        shape = tuple(dot.outputs[0].shape)
+        params: List[str] = []
+        args: List[Dict[str, Any]] = []
+        loads: Dict[Tuple, str] = {}
+        body: List[str] = []
+        inside = {dot.outputs[0].id} | {c.outputs[0].id for c in chain}
+
+        def index_expr(vw: View) -> str:
+            if len(vw.shape) != 2:
+                raise CodegenError("epilogue operand is not two-dimensional")
+            terms = [f"i{d} * {s}LL" for d, s in enumerate(vw.strides) if s != 0 and shape[d] != 1]
+            return " + ".join(terms) if terms else "0"
+
+        def operand(val: Value, want_ctype: str) -> str:
+            if val.id in inside:
+                return f"v{val.id}"
+            vw = self.view_of(val)
+            key = (vw.buffer, vw.offset, vw.strides, want_ctype)
+            if key not in loads:
+                pname = f"p{len(params)}"
+                params.append(f"const {ctype(vw.dtype)}* __restrict__ {pname}")
+                args.append({"buffer": vw.buffer, "offset": vw.offset * vw.dtype.itemsize})
+                var = f"l{len(loads)}"
+                body.append(f"    const {want_ctype} {var} = ld<{want_ctype}>({pname}, {index_expr(vw)});")
+                loads[key] = var
+            return loads[key]
+
+        body.append(f"    const float v{dot.outputs[0].id} = acc;")
+        for c in chain:
+            o = c.outputs[0]
+            in_dts = [i.dtype for i in c.inputs]
+            a = [operand(i, compute_type(dt)) for i, dt in zip(c.inputs, in_dts)]
+            ct = compute_type(o.dtype)
+            body.append(f"    const {ct} v{o.id} = {self._expr(c.opcode, a, dict(c.attrs), o.dtype, in_dts)};")
+        tname = f"Epi_{kname}"
+        fields = "".join(f"  {p.replace(' __restrict__', '')};\n" for p in params)
+        src = (f"struct {tname} {{\n  static constexpr bool active = true;\n{fields}"
+               f"  __device__ __forceinline__ float operator()(float acc, long long i0, long long i1) const {{\n"
+               + "\n".join(body) + f"\n    return float(v{chain[-1].outputs[0].id});\n  }}\n}};\n")
+        return src, params, args, tname
 
     # -- gathers / scatters -----------------------------------------------------------
     def _simple(self, name_base, n, params: List[Tuple[str, View, bool]], body_lines: List[str], total: int):

@@ -157,6 +157,12 @@ def compile_to_neff(kernel, output_dir: Optional[str] = None, neff_name: str = "
     ir = kernel if isinstance(kernel, Graph) else get_ir(kernel)
     if neff_name.endswith(".neff"):
         neff_name = neff_name[:-5] + ".cubin"
+    if getattr(kernel, "backend", None) == "nkigen":
+        # kernels traced for the native backend go through its pass pipeline first: tiling knobs, fusion
+        # groups and the shared-memory budget decide what the code generator emits
+        from ..nkigen.transforms import apply_complete_knob_pipeline
+
+        ir = Graph.from_text(apply_complete_knob_pipeline(ir.to_text()))
     cfg = CompilationConfig(target, additional_compiler_args, save_artifacts, use_tcgen05)
     return Compiler(cfg).compile_in_directory(ir, output_dir or _get_build_dir(), neff_name).neff_path
 

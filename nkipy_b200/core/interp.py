@@ -89,8 +89,23 @@ def _conv(x, w, b, attrs, out_dtype):
     return out.astype(out_dtype)
 
 
+def _eval_loop(n: Node, ins: List[np.ndarray]) -> List[np.ndarray]:
+    from .ir import loop_body
+
+    body = loop_body(n)
+    nc = int(n.attrs["num_carried"])
+    carried, captured = list(ins[:nc]), list(ins[nc:])
+    for i in range(int(n.attrs["lower"]), int(n.attrs["upper"]), int(n.attrs.get("step", 1))):
+        outs = evaluate(body, [np.asarray(i, dtype=np.int32)] + carried + captured)
+        # results of bool dtype come back as uint8 from `evaluate`; carried values keep their dtype
+        carried = [np.asarray(o).astype(c.dtype) for o, c in zip(outs, carried)]
+    return carried
+
+
 def _eval_node(n: Node, ins: List[np.ndarray], world: int = 1) -> List[np.ndarray]:
     op, a = n.opcode, n.attrs
+    if op == "loop":
+        return _eval_loop(n, ins)
     odt = n.outputs[0].dtype
     if op in _UNARY:
         return [np.asarray(_UNARY[op](_compute(ins[0]))).astype(odt)]

@@ -286,7 +286,18 @@ def _all_to_all(ins, attrs):
     return [(tuple(s), x.dtype)]
 
 
+def _loop(ins, attrs):
+    """Counted loop: inputs = carried initial values then captured values; attrs lower / upper / step,
+    num_carried and `body` = text of a nested graph with parameters (index i32[], carried..., captured...)
+    whose results are the next carried values.  Outputs: the carried values after the last iteration."""
+    n = int(attrs["num_carried"])
+    if n > len(ins):
+        raise IRError("loop: more carried values than inputs")
+    return [(v.shape, v.dtype) for v in ins[:n]]
+
+
 _INFER = {
+    "loop": _loop,
     **{op: _binary for op in ELEMENTWISE_BINARY},
     **{op: _same for op in ELEMENTWISE_UNARY},
     "is_finite": lambda ins, attrs: [(ins[0].shape, np.dtype(np.bool_))],
@@ -485,6 +496,51 @@ class Graph:
         if g is None:
             raise IRError("empty IR text")
         return g
+
+
+def loop_body(node: "Node") -> "Graph":
+    """The nested graph of a `loop` node."""
+    return Graph.from_text(node.attrs["body"])
+
+
+def expand_loops(graph: "Graph") -> "Graph":
+    """A copy of `graph` with every `loop` node replaced by its unrolled iterations (the index becomes a
+    constant per iteration).  The IR keeps loops through the whole pass pipeline; the code generator
+    expands them when it emits launches."""
+    if not any(n.opcode == "loop" for n in graph.nodes):
+        return graph
+    out = Graph(graph.name)
+    env: Dict[int, Value] = {}
+    for p in graph.params:
+        env[id(p)] = out.add_parameter(p.shape, p.dtype, p.name)
+
+    def clone_into(src: "Graph", bind: Dict[int, Value]) -> List[Value]:
+        local = dict(bind)
+        for n in src.nodes:
+            out.set_source_location(n.loc)
+            ins = [local[id(v)] for v in n.inputs]
+            if n.opcode == "loop":
+                body = loop_body(n)
+                nc = int(n.attrs["num_carried"])
+                carried, captured = ins[:nc], ins[nc:]
+                for i in range(int(n.attrs["lower"]), int(n.attrs["upper"]), int(n.attrs.get("step", 1))):
+                    idx = out.op("constant", value=np.asarray(i, dtype=np.int32))
+                    b = {id(body.params[0]): idx}
+                    for bp, v in zip(body.params[1:1 + nc], carried):
+                        b[id(bp)] = v
+                    for bp, v in zip(body.params[1 + nc:], captured):
+                        b[id(bp)] = v
+                    carried = clone_into(body, b)
+                outs = carried
+            else:
+                outs = out.add_node(n.opcode, ins, dict(n.attrs))
+            for o, v in zip(n.outputs, outs):
+                local[id(o)] = v
+        return [local[id(r)] for r in src.results]
+
+    results = clone_into(graph, env)
+    out.set_results(results, list(graph.result_names), list(graph.alias_list))
+    return out
 
 
 def _parse_types(s: str):
