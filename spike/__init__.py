@@ -1,0 +1,37 @@
+"""Import-name compatibility: code written against the reference imports ``spike`` (and its
+submodules); here the implementation lives in ``nkipy_b200.spike``.  Importing ``spike`` or any
+``spike.x.y`` returns the very same module objects as ``nkipy_b200.spike`` / ``nkipy_b200.spike.x.y``."""
+
+import importlib
+import importlib.abc
+import importlib.util
+import sys
+
+_ALIAS, _REAL = "spike", "nkipy_b200.spike"
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    def find_spec(self, fullname, path=None, target=None):
+        if fullname.startswith(_ALIAS + "."):
+            real = _REAL + fullname[len(_ALIAS):]
+            try:
+                if importlib.util.find_spec(real) is None:
+                    return None
+            except (ImportError, ValueError):
+                return None
+            return importlib.util.spec_from_loader(fullname, self)
+        return None
+
+    def create_module(self, spec):
+        return importlib.import_module(_REAL + spec.name[len(_ALIAS):])
+
+    def exec_module(self, module):
+        return None
+
+
+if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder())
+
+_impl = importlib.import_module(_REAL)
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith("__")})
+__all__ = getattr(_impl, "__all__", [k for k in vars(_impl) if not k.startswith("_")])

@@ -210,3 +210,85 @@ def test_custom_cuda_op_and_native_backend_on_device(tmp_path):
     x, w = f32(64, 128), f32(96, 128)
     out = model({"in_tensor_0": DeviceTensor.from_numpy(x), "in_tensor_1": DeviceTensor.from_numpy(w)})
     np.testing.assert_allclose(out["output"].numpy(), np.tanh(x @ w.T) ** 2, rtol=1e-3, atol=1e-4)
+
+
+def _run_nkigen(kernel, tmp, inputs, name="k"):
+    """Compile a nkigen-traced kernel through the native pass pipeline and run it on the device."""
+    from nkipy_b200.nkigen.compile import compile_to_neff
+    from nkipy_b200.runtime import DeviceKernel, DeviceTensor
+
+    path = compile_to_neff(kernel, str(tmp), f"{name}.cubin")
+    plan = json.loads(open(os.path.splitext(path)[0] + ".json").read())
+    model = DeviceKernel.load_from_neff(path)
+    out = model({f"in_tensor_{i}": DeviceTensor.from_numpy(a) for i, a in enumerate(inputs)})
+    return out, plan
+
+
+def test_knobs_change_the_emitted_gemm_and_not_its_result(tmp_path):
+    import ml_dtypes
+
+    from nkipy_b200 import nkigen
+
+    bf = ml_dtypes.bfloat16
+    x, w = f32(512, 1024).astype(bf), (f32(768, 1024) * 0.05).astype(bf)
+    ref = x.astype(np.float32) @ w.astype(np.float32).T
+    results, shapes = [], []
+    for i, tile in enumerate((None, [128, 64], [128, 128])):
+        @nkigen.trace(input_specs=[((512, 1024), "bf16"), ((768, 1024), "bf16")])
+        def mm(a, b):
+            y = a @ b.T
+            if tile:
+                nkigen.knob(y).tile_op(tile_size=tile)
+            return y
+
+        out, plan = _run_nkigen(mm, tmp_path / f"t{i}", [x, w])
+        ga = plan["launches"][0]["args"][2]["gemm_args"]
+        shapes.append((ga["block_n"], ga["stages"]))
+        results.append(out["output"].numpy().astype(np.float32))
+    assert [s[0] for s in shapes] == [256, 64, 128] and len({s[1] for s in shapes}) >= 2
+    for r in results:
+        assert np.linalg.norm(r - ref) / np.linalg.norm(ref) < 1e-2
+    for r in results[1:]:
+        # the same k-order and fp32 accumulation whatever the tile: identical bf16 results
+        np.testing.assert_array_equal(r, results[0])
+
+
+def test_fused_gemm_epilogue_on_device(tmp_path):
+    import ml_dtypes
+
+    from nkipy_b200 import nkigen
+
+    bf = ml_dtypes.bfloat16
+
+    @nkigen.trace(input_specs=[((256, 512), "bf16"), ((384, 512), "bf16"), ((384,), "bf16"), ((256, 384), "bf16")])
+    def k(x, w, b, r):
+        z = x @ w.T + b
+        return z / (1.0 + np.exp(-z)) + r
+
+    x, w = f32(256, 512).astype(bf), (f32(384, 512) * 0.05).astype(bf)
+    b, r = f32(384).astype(bf), f32(256, 384).astype(bf)
+    out, plan = _run_nkigen(k, tmp_path, [x, w, b, r])
+    assert len(plan["launches"]) == 1 and plan["launches"][0]["args"][2]["gemm_args"]["fused_epilogue"]
+    z = x.astype(np.float32) @ w.astype(np.float32).T + b.astype(np.float32)
+    ref = z / (1.0 + np.exp(-z)) + r.astype(np.float32)
+    got = out["output"].numpy().astype(np.float32)
+    assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < 1e-2
+    # per 128-column block, so that a wrong tile cannot hide in the norm
+    for c in range(0, 384, 128):
+        e = np.linalg.norm(got[:, c:c + 128] - ref[:, c:c + 128]) / np.linalg.norm(ref[:, c:c + 128])
+        assert e < 1.5e-2, (c, e)
+
+
+def test_loop_kernel_on_device(tmp_path):
+    from nkipy_b200 import nkigen
+
+    @nkigen.trace(input_specs=[((6, 32), "f32"), ((32, 32), "f32")])
+    def k(x, w):
+        def body(i, h):
+            return np.tanh(h @ w + x[i])
+
+        return nkigen.fori_loop(0, 6, body, np.zeros(32, np.float32))
+
+    x, w = f32(6, 32), f32(32, 32) * 0.3
+    out, plan = _run_nkigen(k, tmp_path, [x, w])
+    np.testing.assert_allclose(out["output"].numpy(), k(x, w), rtol=1e-4, atol=1e-5)
