@@ -52,5 +52,12 @@ def build(force: bool = False):
     return module_path(), opt_path()
 
 
+def opt_main(argv=None) -> int:
+    """Console entry `nkipy-b200-opt`: builds the native driver if needed and runs it with the given arguments
+    (same role as the reference's `nkigen-opt`, nkigen/tools/nkigen-opt/nkigen-opt.cpp)."""
+    _, exe = build()
+    return subprocess.call([str(exe), *(sys.argv[1:] if argv is None else argv)])
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))

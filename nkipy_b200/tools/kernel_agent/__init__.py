@@ -8,7 +8,7 @@ import os as _os
 from .executor import ExecutionResult, compare, gpu_available, run_kernel  # noqa: E402,F401
 from .generator import BedrockClient, TemplateClient, load_kernel, system_prompt  # noqa: E402,F401
 from .ops import TARGET_OPS, all_ops, build_kernel, discover, test_op  # noqa: E402,F401
-from .sweep import rerun_failed, run_sweep  # noqa: E402,F401
+from .sweep import SweepRecord, load_records, rerun_failed, run_rerun, run_sweep  # noqa: E402,F401
 
 
 @_dc.dataclass
@@ -17,15 +17,6 @@ class StageResult:
     stage: str
     ok: bool
     error: str = ""
-
-
-@_dc.dataclass
-class SweepRecord:
-    """One line of a sweep result file."""
-    file: str
-    ops: list
-    passed: bool
-    error_stage: str = ""
 
 
 def stages(result: ExecutionResult):
@@ -44,7 +35,6 @@ def stages(result: ExecutionResult):
 get_all_ops = all_ops
 discover_ops = discover
 make_kernel = build_kernel
-run_rerun = rerun_failed
 
 
 def generate_kernel(ops, client=None, prompt: str = "") -> str:

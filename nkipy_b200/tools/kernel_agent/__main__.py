@@ -10,7 +10,7 @@ import sys
 from . import ops as ops_mod
 from .generator import BedrockClient, TemplateClient, load_kernel
 from .executor import run_kernel
-from .sweep import rerun_failed, run_sweep
+from .sweep import rerun_failed, run_rerun, run_sweep
 
 
 def main(argv=None) -> int:
@@ -28,13 +28,19 @@ def main(argv=None) -> int:
     g.add_argument("--client", choices=["template", "bedrock"], default="template")
     g.add_argument("-o", "--output", default=None)
     s = sub.add_parser("sweep", help="generate and test random kernels")
-    s.add_argument("--num-kernels", type=int, default=10)
+    s.add_argument("--num-kernels", type=int, default=10, help="0: keep going until SIGINT / SIGTERM")
+    s.add_argument("--timeout", type=int, default=120, help="seconds per kernel before it is abandoned")
+    s.add_argument("--delay", type=float, default=0.0, help="pause between kernels, seconds")
+    s.add_argument("--summary-interval", type=int, default=10)
     s.add_argument("--ops-per-kernel", type=int, default=4)
     s.add_argument("--out-dir", default="kernel_agent_sweep")
     s.add_argument("--seed", type=int, default=0)
     s.add_argument("--no-gpu", action="store_true")
-    r = sub.add_parser("rerun", help="re-run the failed kernels of a sweep directory")
-    r.add_argument("out_dir")
+    r = sub.add_parser("rerun", help="re-run a sweep: a .jsonl log (all of its kernels, or --only-failed) or a "
+                                     "sweep directory (its failed kernels)")
+    r.add_argument("out_dir", help="a sweep_*.jsonl log or a sweep directory")
+    r.add_argument("--only-failed", action="store_true")
+    r.add_argument("--timeout", type=int, default=120)
     r.add_argument("--no-gpu", action="store_true")
     args = ap.parse_args(argv)
 
@@ -69,11 +75,17 @@ def main(argv=None) -> int:
             print(src)
         return 0
     if args.cmd == "sweep":
-        summary = run_sweep(args.num_kernels, args.ops_per_kernel, args.out_dir, args.seed, use_gpu)
-        print(f"{summary['passed']}/{summary['num_kernels']} kernels pass; results in {args.out_dir}/sweep_results.json")
+        summary = run_sweep(args.num_kernels or None, args.ops_per_kernel, args.out_dir, args.seed, use_gpu,
+                            timeout=args.timeout, delay=args.delay, summary_interval=args.summary_interval,
+                            verbose=True)
+        print(f"{summary['passed']}/{summary['num_kernels']} kernels pass; log {summary['log']}")
         return 0 if summary["passed"] == summary["num_kernels"] else 1
     if args.cmd == "rerun":
-        summary = rerun_failed(args.out_dir, use_gpu)
+        if args.out_dir.endswith(".jsonl"):
+            summary = run_rerun(args.out_dir, use_gpu, timeout=args.timeout, only_failed=args.only_failed,
+                                verbose=True)
+        else:
+            summary = rerun_failed(args.out_dir, use_gpu, timeout=args.timeout)
         print(f"{summary['passed']}/{summary['num_kernels']} kernels pass")
         return 0
     return 2

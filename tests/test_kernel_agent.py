@@ -55,3 +55,78 @@ def test_sweep_on_device(tmp_path):
     s = run_sweep(3, 4, str(tmp_path), seed=2)
     assert s["passed"] == 3, s
     assert all(r["hardware_ok"] for r in s["results"])
+
+
+def test_sweep_log_is_jsonl_with_full_records(tmp_path):
+    from nkipy_b200.tools.kernel_agent import SweepRecord, load_records, run_rerun
+
+    s = run_sweep(3, 3, str(tmp_path), seed=3, use_gpu=False)
+    recs = load_records(s["log"])
+    assert len(recs) == 3 and all(isinstance(r, SweepRecord) for r in recs)
+    r = recs[0]
+    assert r.passed and r.numpy_success and r.compile_success and r.hardware_success is None
+    assert "def kernel" in r.generated_code and r.input_specs["arg0"]["shape"]
+    assert r.duration_seconds >= 0 and r.timestamp.endswith("Z")
+    # a torn last line (killed writer) is skipped, not fatal
+    with open(s["log"], "a") as f:
+        f.write('{"iteration": 9, "times')
+    assert len(load_records(s["log"])) == 3
+    # replay from the saved source
+    again = run_rerun(s["log"], use_gpu=False, out_dir=str(tmp_path / "again"))
+    assert again["passed"] == 3 and again["results"][0]["rerun_source"] == os.path.basename(s["log"])
+    with pytest.raises(ValueError):
+        run_rerun(str(tmp_path / "sweep_results.json"), use_gpu=False)
+    with pytest.raises(FileNotFoundError):
+        run_rerun(str(tmp_path / "missing.jsonl"), use_gpu=False)
+
+
+class _SlowClient:
+    """Generator stand-in whose second kernel never finishes on its own."""
+    model_id = "slow"
+
+    def __init__(self):
+        self.inner, self.calls = TemplateClient(0), 0
+
+    def generate(self, ops, prompt):
+        self.calls += 1
+        if self.calls == 2:
+            import time
+            time.sleep(30)
+        return self.inner.generate(ops, prompt)
+
+
+def test_sweep_abandons_an_iteration_that_exceeds_its_timeout(tmp_path):
+    s = run_sweep(3, 2, str(tmp_path), seed=4, use_gpu=False, client=_SlowClient(), timeout=1)
+    assert [r["passed"] for r in s["results"]] == [True, False, True]
+    assert s["results"][1]["failure_stage"] == "timeout" and s["failed_by_stage"] == {"timeout": 1}
+
+
+class _InterruptingClient:
+    """Sends this process SIGTERM while the second kernel is generated."""
+    model_id = "interrupt"
+
+    def __init__(self):
+        self.inner, self.calls = TemplateClient(0), 0
+
+    def generate(self, ops, prompt):
+        import signal
+        self.calls += 1
+        if self.calls == 2:
+            os.kill(os.getpid(), signal.SIGTERM)
+        return self.inner.generate(ops, prompt)
+
+
+def test_sweep_stops_gracefully_on_sigterm_and_restores_handlers(tmp_path):
+    import signal
+    before = signal.getsignal(signal.SIGTERM)
+    s = run_sweep(None, 2, str(tmp_path), seed=5, use_gpu=False, client=_InterruptingClient())
+    # the iteration in flight is finished and logged, then the sweep returns
+    assert s["interrupted"] and s["num_kernels"] == 2 and s["passed"] == 2
+    assert signal.getsignal(signal.SIGTERM) is before
+    from nkipy_b200.tools.kernel_agent import load_records
+    assert len(load_records(s["log"])) == 2
+
+
+def test_generation_failure_is_a_record_not_a_crash(tmp_path):
+    s = run_sweep(2, 2, str(tmp_path), seed=6, use_gpu=False, client=BedrockClient())
+    assert s["passed"] == 0 and s["failed_by_stage"] == {"generate": 2}
