@@ -138,6 +138,10 @@ class Compiler:
             raise CompilationError(
                 f"nvcc failed with exit code {res.returncode}\ncommand: {' '.join(cmd)}\nstderr:\n{res.stderr}\n"
                 f"stdout:\n{res.stdout}", cmd, res.stdout, res.stderr)
+        if not out.exists():
+            raise CompilationError(
+                f"{out.name} was expected but not generated by nvcc although it exited 0\ncommand: {' '.join(cmd)}\n"
+                f"stderr:\n{res.stderr}\nstdout:\n{res.stdout}", cmd, res.stdout, res.stderr)
         plan.write_text(program.plan_json())
         if not self.config.save_artifacts:
             src.unlink(missing_ok=True)

@@ -254,3 +254,112 @@ class CounterProtocolSim:
         for t in threads:
             t.join()
         return out
+
+
+# ----------------------------------------------------------------------------- recovery
+@dataclasses.dataclass
+class Recovered:
+    """What `recover` hands back: the new group (with `.fused` rebuilt when the old one had it), the generation
+    number that names this incarnation of the group, and how long the restart took."""
+    tp: "object"
+    generation: int
+    seconds: float
+
+
+def _release_comm_objects(tp, extra=()) -> int:
+    """Release, without any collective, every symmetric buffer that hangs off the group or was passed in."""
+    n = 0
+    fused = getattr(tp, "fused", None)
+    for obj in (fused, *extra):
+        if obj is None:
+            continue
+        (getattr(obj, "abandon", None) or obj.close)()
+        n += 1
+    if fused is not None:
+        tp.fused = None
+    return n
+
+
+def _drop_process_group() -> None:
+    """End the current default process group although some of its ranks may be gone: abort where the backend
+    offers it (NCCL: no handshake with the peers), destroy otherwise."""
+    import torch.distributed as dist
+
+    if not dist.is_initialized():
+        return
+    abort = getattr(dist.distributed_c10d, "_abort_process_group", None)
+    try:
+        if abort is not None and dist.get_backend() == "nccl":
+            abort()
+            return
+    except Exception:
+        pass
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def recover(tp, *, rank: int, world_size: int, master_port: int, generation: int = 1,
+            master_addr: str = "127.0.0.1", timeout_s: int = 60, extra=(), fused_args: Optional[dict] = None,
+            backend: Optional[str] = None) -> Recovered:
+    """Restart the communication layer of this process after a rank was lost (or to join as its replacement).
+
+    Survivors pass their old group as `tp`; a replacement process passes None.  Steps, all on the host:
+
+      1. no kernel of this process is in flight (device synchronize), the device status word is cleared;
+      2. the symmetric buffers reachable from `tp` (`tp.fused`) and those in `extra` (sequence-parallel GEMM
+         pairs, the expert all-to-all) are released without a barrier (`abandon`);
+      3. the old process group is aborted;
+      4. a new group of `world_size` ranks is formed at `master_port` (a port not used by the old group: the
+         old store may live in a process that is gone) under the new `generation`;
+      5. `FusedTP` is rebuilt with its old sizes (or `fused_args`), which zeroes its flags and restarts its
+         call counters, so no stale arrival count survives.
+
+    `rank` / `world_size` describe the NEW group: the same numbers when a replacement process takes the lost
+    rank's place, fewer ranks when the job shrinks (the caller then reloads weight shards for the new
+    sharding).  KV caches are not carried over; requests in flight are prefilled again.  The reference has
+    no counterpart: its runtime reports a failed collective as a status code and stops
+    (spike/src/error.h:24-43)."""
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    from .comm import TPGroup
+
+    t0 = time.time()
+    use_cuda = torch.cuda.is_available()
+    if tp is not None:
+        fused = getattr(tp, "fused", None)
+        if fused_args is None and fused is not None:
+            fused_args = dict(max_tokens=fused.max_tokens, hidden=fused.hidden, max_splits=fused.max_splits)
+        if use_cuda:
+            torch.cuda.synchronize()
+            from .. import ops
+
+            ops.device_status(reset=True) if _accepts_reset(ops.device_status) else ops.device_status()
+        _release_comm_objects(tp, extra)
+        _drop_process_group()
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if tp is not None and tp.device is not None:
+        device = tp.device
+    else:
+        device = torch.device(f"cuda:{local}") if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world_size), MASTER_ADDR=master_addr,
+                      MASTER_PORT=str(master_port), NKIPY_B200_GENERATION=str(generation))
+    if world_size == 1:
+        new_tp = TPGroup(0, 1, None, device)
+    else:
+        if backend is None:
+            backend = "nccl" if use_cuda else "gloo"
+        kwargs = {"device_id": device} if backend == "nccl" else {}
+        dist.init_process_group(backend=backend, init_method=f"tcp://{master_addr}:{master_port}", rank=rank,
+                                world_size=world_size, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+        new_tp = TPGroup(rank, world_size, dist.group.WORLD, device)
+        new_tp.barrier()
+    if fused_args and use_cuda:
+        from .symm import FusedTP
+
+        new_tp.fused = FusedTP(new_tp, **fused_args)
+    return Recovered(new_tp, generation, time.time() - t0)

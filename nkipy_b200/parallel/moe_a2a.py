@@ -159,3 +159,7 @@ class MoEAllToAll:
 
     def close(self) -> None:
         self.mem.close()
+
+    def abandon(self) -> None:
+        """Non-collective release for the recovery path (`SymmetricMemory.abandon`)."""
+        self.mem.abandon()

@@ -205,6 +205,22 @@ class SymmetricMemory:
         raw = torch.as_tensor(_CudaArray(self.local_ptr + offset, nbytes, self), device=self.tp.device)
         return raw.view(dtype).view(shape)
 
+    def abandon(self) -> None:
+        """Release this rank's mappings and memory WITHOUT talking to the peers: the recovery path, for when a
+        peer has left and a barrier would never complete.  The caller guarantees that no kernel of this process
+        that touches the buffer is in flight (a device synchronize is done here) and that this rank will not be
+        addressed by a live peer's kernel any more -- a peer that left between steps satisfies both."""
+        if self._closed:
+            return
+        self._closed = True
+        torch.cuda.synchronize()
+        if self.backend == "vmm":
+            self._buf.close()
+            return
+        for p in self._opened:
+            self._lib.nkb_ipc_close(ctypes.c_void_p(p))
+        self._lib.nkb_symm_free(ctypes.c_void_p(self.local_ptr))
+
     def close(self) -> None:
         """Collective: every rank calls it.  Nothing is unmapped or released while a peer may still use it."""
         if self._closed:
@@ -395,6 +411,10 @@ class FusedTP:
     def close(self) -> None:
         self.mem.close()
 
+    def abandon(self) -> None:
+        """Non-collective release for the recovery path (`SymmetricMemory.abandon`)."""
+        self.mem.abandon()
+
 
 class _FusedGemmCollective:
     """Shared plumbing of `GemmReduceScatter` and `AllGatherGemm`: two alternating symmetric buffers
@@ -429,6 +449,9 @@ class _FusedGemmCollective:
 
     def close(self) -> None:
         self.mem.close()
+
+    def abandon(self) -> None:
+        self.mem.abandon()
 
 
 class GemmReduceScatter(_FusedGemmCollective):

@@ -54,14 +54,18 @@ class DeviceKernel(SpikeModel):
         build_dir = build_dir or _get_build_dir()
         distributed = _is_distributed()
         dist = _dist()
-        rank = dist.get_rank() if distributed else 0
-        if distributed and not is_spmd:
-            build_dir = os.path.join(build_dir, f"rank_{rank}")
+        dist_rank = dist.get_rank() if distributed else 0
+        if not is_spmd:
+            # MPMD: every rank traces its own program, so nothing is broadcast and nobody waits; the artifacts of
+            # different ranks live side by side under rank_<r> (explicit rank first, else the group's)
+            ns = rank_id if rank_id is not None else (dist_rank if distributed else None)
+            if ns is not None:
+                build_dir = os.path.join(build_dir, f"rank_{ns}")
             neff_path, key = cls._trace_and_compile(kernel, name, build_dir, additional_compiler_args,
                                                     use_cached_if_exists, target, args, kwargs)
         elif distributed:
             payload = [None, None]
-            if rank == 0:
+            if dist_rank == 0:
                 payload = list(cls._trace_and_compile(kernel, name, build_dir, additional_compiler_args,
                                                       use_cached_if_exists, target, args, kwargs))
             dist.broadcast_object_list(payload, src=0)
@@ -69,25 +73,29 @@ class DeviceKernel(SpikeModel):
         else:
             neff_path, key = cls._trace_and_compile(kernel, name, build_dir, additional_compiler_args,
                                                     use_cached_if_exists, target, args, kwargs)
-        if key in _LOADED_KERNELS:
+        if use_cached_if_exists and key in _LOADED_KERNELS:
             return _LOADED_KERNELS[key]
-        # collectives: default on when running distributed; explicit rank / world override
+        # collectives: on by default when running distributed; explicit rank / world win over the group's
         if cc_enabled is None:
             cc_enabled = distributed
         if cc_enabled:
-            if rank_id is None:
-                rank_id = rank
-            if world_size is None:
-                world_size = dist.get_world_size() if distributed else 1
+            if rank_id is None and distributed:
+                rank_id = dist_rank
+            if world_size is None and distributed:
+                world_size = dist.get_world_size()
+            if rank_id is None or world_size is None:
+                raise ValueError("rank_id and world_size are required when cc_enabled=True and no process group "
+                                 "is initialised")
             if not (0 <= rank_id < world_size):
                 raise ValueError(f"rank_id {rank_id} outside world of size {world_size}")
         else:
             rank_id, world_size = 0, 1
-        if distributed:
+        if distributed and is_spmd:
             dist.barrier()        # the artifact must be visible on every rank's file system view
         loaded = cls.load_from_neff(neff_path, name=name, core_id=core_id, cc_enabled=cc_enabled, rank_id=rank_id,
                                     world_size=world_size)
-        _LOADED_KERNELS[key] = loaded
+        if use_cached_if_exists:
+            _LOADED_KERNELS[key] = loaded
         return loaded
 
     @staticmethod

@@ -192,3 +192,134 @@ def test_rank_leaves_between_steps_and_peer_notices():
         p.join(timeout=60)
     assert res[1][1] == "left" and res[1][3] == 3
     assert res[0][1] == "peer-left" and res[0][2] == [1] and res[0][3] == 3
+
+
+# ----------------------------------------------------------------------------- recovery
+def _recover_worker(role, rank, world, ports, hb_port, q, use_gpu):
+    """role "first": a member of the original group (rank 1 leaves before step 2).  role "replacement": a new
+    process that takes the lost rank's place.  After recovery both run one more reduced step and report it."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0", NKIPY_B200_NVLS="0")
+    import datetime
+
+    import torch.distributed as dist
+    from torch.distributed import TCPStore
+
+    from nkipy_b200.parallel.comm import TPGroup
+    from nkipy_b200.parallel.health import recover
+
+    hidden, rows = 256, 8
+
+    def fused_step(tp, seed):
+        """One row-parallel GEMM + all-reduce + residual + RMSNorm through FusedTP against an fp32 oracle."""
+        from nkipy_b200 import ops
+
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        x_full = torch.randn(rows, hidden * world, generator=g).to(torch.bfloat16)
+        w_full = (torch.randn(hidden, hidden * world, generator=g) * 0.05).to(torch.bfloat16)
+        resid = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
+        norm = torch.ones(hidden).to(torch.bfloat16)
+        sl = slice(tp.rank * hidden, (tp.rank + 1) * hidden)
+        dev = tp.device
+        tp.fused.begin_step()
+        outs = [tp.fused.gemm_allreduce_add_rmsnorm(x_full[:, sl].contiguous().to(dev), w_full[:, sl].contiguous().to(dev),
+                                                    resid.to(dev), norm.to(dev), None, 1e-5) for _ in range(2)]
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        h = x_full.float() @ w_full.float().T + resid.float()
+        want = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)
+        got = outs[1][1].float().cpu()
+        return float((got - want).norm() / want.norm())
+
+    def plain_step(tp):
+        x = torch.full((4,), float(tp.rank + 1), device=tp.device)
+        tp.all_reduce(x)
+        return float(x[0])
+
+    if role == "first":
+        os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(ports[0]))
+        tp = TPGroup.from_env(backend="nccl" if use_gpu else "gloo", timeout_s=20)
+        if use_gpu:
+            from nkipy_b200.parallel.symm import FusedTP
+
+            tp.fused = FusedTP(tp, rows, hidden)
+        store = TCPStore("127.0.0.1", hb_port, world + 1, is_master=(rank == 0),
+                         timeout=datetime.timedelta(seconds=60), wait_for_workers=False)
+        hb = Heartbeat(store, rank, world, interval_s=0.05)
+        plan = FaultPlan.from_env("kill_rank:1:2")
+        try:
+            for step in range(4):
+                plan.before_step(rank, step)                  # rank 1 leaves before step 2, nothing in flight
+                time.sleep(0.4)
+                if hb.dead_ranks(timeout_s=0.3):
+                    break
+                fused_step(tp, step) if use_gpu else plain_step(tp)
+        except InjectedRankExit:
+            if use_gpu:
+                torch.cuda.synchronize()
+                tp.fused.abandon()                            # between steps: no kernel addresses this rank now
+            hb.stop()
+            q.put(("left", rank, step))
+            time.sleep(1.0)
+            return
+        dead = hb.dead_ranks(timeout_s=0.3)
+        hb.stop()
+        q.put(("detected", rank, dead))
+        rec = recover(tp, rank=rank, world_size=world, master_port=ports[1], generation=1, timeout_s=60,
+                      backend="nccl" if use_gpu else "gloo")
+    else:
+        rec = recover(None, rank=rank, world_size=world, master_port=ports[1], generation=1, timeout_s=60,
+                      backend="nccl" if use_gpu else "gloo",
+                      fused_args=dict(max_tokens=rows, hidden=hidden) if use_gpu else None)
+    tp = rec.tp
+    assert tp.world_size == world and rec.generation == 1
+    if use_gpu:
+        assert tp.fused is not None and tp.fused.ops_issued == 0
+        val = max(fused_step(tp, 100 + s) for s in range(2))
+    else:
+        val = plain_step(tp)
+    tp.barrier()
+    q.put(("recovered", rank, val, round(rec.seconds, 2)))
+    if use_gpu:
+        tp.fused.close()
+    dist.destroy_process_group()
+
+
+def _run_recovery(use_gpu):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ports, hb_port = (_free_port(), _free_port()), _free_port()
+    procs = [ctx.Process(target=_recover_worker, args=("first", r, 2, ports, hb_port, q, use_gpu)) for r in range(2)]
+    for p in procs:
+        p.start()
+    events, replacement = [], None
+    try:
+        while sum(e[0] == "recovered" for e in events) < 2:
+            e = q.get(timeout=180)
+            events.append(e)
+            if e[0] == "left" and replacement is None:
+                replacement = ctx.Process(target=_recover_worker, args=("replacement", 1, 2, ports, hb_port, q, use_gpu))
+                replacement.start()
+    finally:
+        for p in procs + ([replacement] if replacement else []):
+            p.join(timeout=90)
+            if p.is_alive():
+                p.kill()
+    kinds = [e[0] for e in events]
+    assert kinds.count("left") == 1 and ("detected", 0, [1]) in events
+    return {e[1]: e for e in events if e[0] == "recovered"}
+
+
+def test_recover_rebuilds_the_group_with_a_replacement_rank_gloo():
+    rec = _run_recovery(use_gpu=False)
+    assert set(rec) == {0, 1} and all(e[2] == 3.0 for e in rec.values())       # 1 + 2 over the new group
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_recover_rebuilds_fused_tp_after_a_rank_left():
+    """A rank leaves between steps (NVLS and multimem off), the survivor learns of it from the heartbeat,
+    abandons its symmetric buffers and its NCCL group, a replacement process joins, and a fused GEMM +
+    all-reduce + RMSNorm step is right again on both."""
+    rec = _run_recovery(use_gpu=True)
+    assert set(rec) == {0, 1} and all(e[2] < 2e-2 for e in rec.values()), rec
