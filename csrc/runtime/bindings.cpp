@@ -154,5 +154,5 @@ PYBIND11_MODULE(_spike, m) {
            py::arg("save_trace") = false)
       .def("get_tensor_info", &Spike::get_tensor_info)
       .def("read_status", &Spike::read_status, py::arg("reset") = true)
-      .def("close", &Spike::close);
+      .def("close", [](Spike& s) { s.close(); return 0; });   // 0 = success, like the other status-returning calls
 }
