@@ -232,6 +232,9 @@ class TransformerLM:
             resid, normed = inputs
         taps = [] if return_hidden else None
         T = normed.shape[0]
+        if self._persistent_layers(T, normed):
+            return self._decode_step_persistent(resid, normed, positions, slots, cache, block_table, context_lens,
+                                                q_len, taps)
         cluster = self.cluster_gemm and T <= 128 and normed.is_cuda and self.d in (64, 128)
         for i, lw in enumerate(self.layers):
             if cluster:
@@ -256,6 +259,97 @@ class TransformerLM:
             if taps is not None:
                 taps.append(resid)
         if return_hidden:
+            return normed, taps
+        return normed
+
+    # ------------------------------------------------------------------ decode, one launch per layer
+    def _persistent_layers(self, T: int, normed: torch.Tensor) -> bool:
+        """Whether the decode step runs on the persistent layer kernel: dense-FFN models on a GPU, at most 128
+        tokens, and either one rank or the fused tensor-parallel buffers."""
+        if ops.DECODE_LAYER_IMPL != "persistent" or self.cfg.is_moe or not normed.is_cuda or T > 128:
+            return False
+        if self.d not in (64, 128, 256) or self.cfg.hidden_size % 8 or self.cfg.hidden_size > 6144:
+            return False
+        if self.tp.world_size > 1 or self.force_fused:
+            fused = getattr(self.tp, "fused", None)
+            return fused is not None and T <= fused.max_tokens
+        return True
+
+    def _layer_splits(self):
+        """Split-K factors (o, gate/up, down, qkv) of the persistent layer kernel's GEMM stages, and whether
+        gate / up applies SwiGLU in its own epilogue (enough tile pairs to fill the SMs) or from partials."""
+        if getattr(self, "_lsplits", None) is None:
+            from ..ops.decode_layer import env_splits, pick_layer_splits
+
+            lw, H = self.layers[0], self.cfg.hidden_size
+            inter = lw.gate_up.shape[0] // 2
+            fused_gate = self.cfg.swiglu_limit <= 0 and lw.gate_up_bias is None and inter // 128 >= 100
+            s = [pick_layer_splits(H, lw.o.shape[1]), 1 if fused_gate else pick_layer_splits(2 * inter, H),
+                 pick_layer_splits(H, lw.down.shape[1]), pick_layer_splits(lw.qkv.shape[0], H)]
+            env = env_splits()
+            if env:
+                s = [e if e > 0 else d for e, d in zip(env, s)]
+                if env[1] > 1:
+                    fused_gate = False
+            fused = getattr(self.tp, "fused", None)
+            if fused is not None and (self.tp.world_size > 1 or self.force_fused):
+                s[0], s[2] = min(s[0], fused.max_splits), min(s[2], fused.max_splits)
+            self._lsplits = (tuple(s), fused_gate)
+        return self._lsplits
+
+    def _decode_step_persistent(self, resid, normed, positions, slots, cache, block_table, context_lens, q_len, taps):
+        """The decode step as  QKV+RoPE(layer 0), then per layer: attention, one persistent launch."""
+        from ..ops import decode_layer as DL
+
+        cfg = self.cfg
+        T, H = normed.shape
+        dev = normed.device
+        (s_o, s_gu, s_down, s_qkv), fused_gate = self._layer_splits()
+        lw0 = self.layers[0]
+        inter = lw0.gate_up.shape[0] // 2
+        qkv_w = lw0.qkv.shape[0]
+        scratch = DL.layer_scratch(dev, DL.scratch_floats(DL.block_n_for(T), [
+            (H, s_o), (0 if fused_gate else 2 * inter, s_gu), (H, s_down), (qkv_w, s_qkv)]))
+        fused = getattr(self.tp, "fused", None) if (self.tp.world_size > 1 or self.force_fused) else None
+        bf = dict(dtype=torch.bfloat16, device=dev)
+
+        def qkv_args(i, q_out):
+            lw = self.layers[i]
+            return dict(w_qkv=lw.qkv, splits_qkv=s_qkv, nq=self.nq, nkv=self.nkv, head_dim=self.d, bias_qkv=lw.qkv_bias,
+                        positions=positions, slots=slots, cos_sin=self.rope, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
+                        q_out=q_out, k_cache=cache.k[i], v_cache=cache.v[i])
+
+        q = torch.empty((T, self.nq * self.d), **bf)
+        DL.decode_layer(DL.ST_QKV | DL.ST_ROPE, T, H, cfg.rms_eps, scratch, normed_out=normed, **qkv_args(0, q))
+        n_layers = len(self.layers)
+        for i, lw in enumerate(self.layers):
+            attn = ops.paged_attn_decode(q, cache.k[i], cache.v[i], block_table, context_lens, self.scale,
+                                         q_len=q_len, window=cfg.window_for_layer(i), sinks=lw.sinks)
+            last = i + 1 == n_layers
+            mask = DL.ST_O | DL.ST_RED1 | DL.ST_GU | DL.ST_DOWN | DL.ST_RED2
+            if not fused_gate:
+                mask |= DL.ST_SILU
+            resid_mid, normed_mid = torch.empty((T, H), **bf), torch.empty((T, H), **bf)
+            resid_out, normed_out = torch.empty((T, H), **bf), torch.empty((T, H), **bf)
+            act = torch.empty((T, inter), **bf)
+            extra = {}
+            if not last:
+                mask |= DL.ST_QKV | DL.ST_ROPE
+                q = torch.empty((T, self.nq * self.d), **bf)
+                extra = qkv_args(i + 1, q)
+            DL.decode_layer(mask, T, H, cfg.rms_eps, scratch,
+                            w_o=lw.o, attn=attn, splits_o=s_o, bias_o=lw.o_bias,
+                            resid_in=resid, norm1_w=lw.post_norm, resid_mid=resid_mid, normed_mid=normed_mid,
+                            w_gu=lw.gate_up, inter=inter, splits_gu=s_gu, fused_gate=fused_gate,
+                            bias_gu=lw.gate_up_bias, act_limit=cfg.swiglu_limit, act_alpha=cfg.swiglu_alpha, act=act,
+                            w_down=lw.down, splits_down=s_down, bias_down=lw.down_bias,
+                            norm2_w=self.final_norm if last else self.layers[i + 1].input_norm,
+                            resid_out=resid_out, normed_out=normed_out,
+                            tp_buffers=None if fused is None else fused.layer_buffers(T, H), **extra)
+            resid, normed = resid_out, normed_out
+            if taps is not None:
+                taps.append(resid)
+        if taps is not None:
             return normed, taps
         return normed
 

@@ -46,6 +46,11 @@ def reset_launch_count() -> None:
     _launches = 0
 
 
+def _count_launch(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
 def native_available() -> bool:
     return _lib.available()
 
@@ -199,6 +204,12 @@ def linear(
 # more than that inside the kernel -- the fix-up's one CTA per tile sums with too little memory parallelism,
 # cluster launches delay their successors -- so the unfused chain stays the default.
 DECODE_GEMM_IMPL = os.environ.get("NKIPY_B200_DECODE_GEMM", "legacy")
+# How a decode step runs what lies between two attention calls:
+#   persistent  one launch per layer (csrc/kernels/decode_layer.cu): the projections, the sums over ranks or
+#               split-K partials, norms, SwiGLU, RoPE and the cache append are stages of one kernel on one CTA
+#               per SM that meet at grid-wide barriers
+#   chain       one launch per operation (eight or nine per layer)
+DECODE_LAYER_IMPL = os.environ.get("NKIPY_B200_DECODE_LAYER", "chain")
 _FIX_SCRATCH = {}
 _FIX_COUNTERS = 4096
 

@@ -42,7 +42,7 @@ NVCC_FLAGS = [
 # fast-math turns exp2f / division into their approximate forms, which is what the
 # GEMM epilogue and the attention softmax want; the normalisation and sampling
 # files keep IEEE division and sqrt.
-NO_FAST_MATH = {"sampling.cu", "elementwise.cu"}
+NO_FAST_MATH = {"sampling.cu", "elementwise.cu", "decode_layer.cu"}
 
 
 def _nvcc() -> str:

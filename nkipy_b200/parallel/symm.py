@@ -296,6 +296,23 @@ class FusedTP:
             raise RuntimeError("a decode step must issue an even number of fused TP operations")
         self._parity = 0
 
+    def _buffer(self, b: int) -> dict:
+        """Addresses of buffer b for a kernel that runs both halves of a fused operation itself."""
+        n, base = self.tp.world_size, self.mem.local_ptr
+        return dict(n=n, rank=self.tp.rank, max_slots=n * self.max_splits, peer_out=self._peer_out[b],
+                    peer_flag=self._peer_flag[b], mc_out=self._mc_out[b], mc_flag=self._mc_flag[b],
+                    slabs=base + self.FLAG_BYTES + b * self.buf_bytes, flags=base + b * n * 4,
+                    seen=self.seen.data_ptr() + 4 * b, done=self.done.data_ptr())
+
+    def layer_buffers(self, tokens: int, hidden: int):
+        """The two buffers (o_proj, down) of one launch of the persistent decode-layer kernel
+        (`ops.decode_layer.decode_layer`): counts as two fused operations of the step."""
+        if tokens > self.max_tokens or hidden != self.hidden:
+            raise ValueError(f"FusedTP sized for [{self.max_tokens}, {self.hidden}], got [{tokens}, {hidden}]")
+        b = self._parity
+        self.ops_issued += 2
+        return self._buffer(b), self._buffer(b ^ 1)
+
     def gemm_allreduce_add_rmsnorm(self, x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor],
                                    next_norm: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
                                    splits: int = 1):
