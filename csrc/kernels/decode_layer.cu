@@ -46,6 +46,7 @@ struct ReduceArgs {
   const float* partials;           // [splits][tokens][hidden] fp32
   long long split_stride;
   const __nv_bfloat16* bias;       // [hidden] or nullptr (local partials only; pushed slabs carry the bias)
+  const __nv_bfloat16* x;          // [tokens][hidden] bf16 addend or nullptr (a block output computed elsewhere)
   const __nv_bfloat16* residual_in;
   const __nv_bfloat16* w;          // norm weight; nullptr: no norm output
   __nv_bfloat16* residual_out;
@@ -246,6 +247,7 @@ __device__ __forceinline__ bool reduce_stage(const ReduceArgs& r, int tokens, in
           }
           if (r.bias) add_bf16x8(a, *reinterpret_cast<const uint4*>(r.bias + (long long)v * 8));
         }
+        if (r.x) add_bf16x8(a, __ldcg(reinterpret_cast<const uint4*>(r.x + off)));
         if (r.residual_in) add_bf16x8(a, __ldcg(reinterpret_cast<const uint4*>(r.residual_in + off)));
         uint4 o;
         o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
@@ -486,6 +488,9 @@ extern "C" struct NkbDecodeLayer {
   void* const* peer_out_d; void* const* peer_flag_d; void* mc_out_d; void* mc_flag_d;
   const void* slabs_d; const void* flags_d; void* seen_d; void* done_d;
   int max_slots, _pad3;
+  // second reduction without the down stage (the block between the two ends ran elsewhere, e.g. MoE experts):
+  // with ranks the pushed slabs of buffer "d" (red2_slots of them) are summed, else red2_x [tokens, hidden] bf16
+  const void* red2_x; int red2_slots, _pad4;
 };
 
 namespace {
@@ -677,10 +682,24 @@ extern "C" int nkb_decode_layer(const NkbDecodeLayer* d, void* stream) {
     if (s > smem) smem = s;
   }
   if (mask & ST_RED2) {
-    if (!(mask & ST_DOWN)) return -2;
     if (!d->resid_out || (d->norm2_w && !d->normed_out)) return -2;
-    fill_reduce(L.red2, L.down.args, d->slabs_d, d->flags_d, d->seen_d, d->resid_mid, d->norm2_w, d->resid_out,
-                d->normed_out);
+    if (mask & ST_DOWN) {
+      fill_reduce(L.red2, L.down.args, d->slabs_d, d->flags_d, d->seen_d, d->resid_mid, d->norm2_w, d->resid_out,
+                  d->normed_out);
+    } else {
+      // the block output comes from other kernels: pushed slabs (ranks) or one bf16 tensor
+      GemmArgs none{};
+      none.splits = 0;
+      fill_reduce(L.red2, none, d->slabs_d, d->flags_d, d->seen_d, d->resid_mid, d->norm2_w, d->resid_out,
+                  d->normed_out);
+      if (tp) {
+        if (d->red2_slots < 1 || d->red2_slots > d->max_slots) return -2;
+        L.red2.slots = d->red2_slots;
+      } else {
+        if (!d->red2_x) return -2;
+        L.red2.x = bf(d->red2_x);
+      }
+    }
   }
   if (mask & ST_QKV) {
     const int width = (d->nq + 2 * d->nkv) * d->head_dim;

@@ -266,7 +266,7 @@ class TransformerLM:
     def _persistent_layers(self, T: int, normed: torch.Tensor) -> bool:
         """Whether the decode step runs on the persistent layer kernel: dense-FFN models on a GPU, at most 128
         tokens, and either one rank or the fused tensor-parallel buffers."""
-        if ops.DECODE_LAYER_IMPL != "persistent" or self.cfg.is_moe or not normed.is_cuda or T > 128:
+        if ops.DECODE_LAYER_IMPL != "persistent" or not normed.is_cuda or T > 128:
             return False
         if self.d not in (64, 128, 256) or self.cfg.hidden_size % 8 or self.cfg.hidden_size > 6144:
             return False
@@ -282,10 +282,14 @@ class TransformerLM:
             from ..ops.decode_layer import env_splits, pick_layer_splits
 
             lw, H = self.layers[0], self.cfg.hidden_size
-            inter = lw.gate_up.shape[0] // 2
-            fused_gate = self.cfg.swiglu_limit <= 0 and lw.gate_up_bias is None and inter // 128 >= 100
-            s = [pick_layer_splits(H, lw.o.shape[1]), 1 if fused_gate else pick_layer_splits(2 * inter, H),
-                 pick_layer_splits(H, lw.down.shape[1]), pick_layer_splits(lw.qkv.shape[0], H)]
+            if self.cfg.is_moe:              # the experts run in their own kernels: only the two ends are stages
+                inter, fused_gate = 0, False
+                s = [pick_layer_splits(H, lw.o.shape[1]), 1, 1, pick_layer_splits(lw.qkv.shape[0], H)]
+            else:
+                inter = lw.gate_up.shape[0] // 2
+                fused_gate = self.cfg.swiglu_limit <= 0 and lw.gate_up_bias is None and inter // 128 >= 100
+                s = [pick_layer_splits(H, lw.o.shape[1]), 1 if fused_gate else pick_layer_splits(2 * inter, H),
+                     pick_layer_splits(H, lw.down.shape[1]), pick_layer_splits(lw.qkv.shape[0], H)]
             env = env_splits()
             if env:
                 s = [e if e > 0 else d for e, d in zip(env, s)]
@@ -306,7 +310,8 @@ class TransformerLM:
         dev = normed.device
         (s_o, s_gu, s_down, s_qkv), fused_gate = self._layer_splits()
         lw0 = self.layers[0]
-        inter = lw0.gate_up.shape[0] // 2
+        moe = cfg.is_moe
+        inter = 0 if moe else lw0.gate_up.shape[0] // 2
         qkv_w = lw0.qkv.shape[0]
         scratch = DL.layer_scratch(dev, DL.scratch_floats(DL.block_n_for(T), [
             (H, s_o), (0 if fused_gate else 2 * inter, s_gu), (H, s_down), (qkv_w, s_qkv)]))
@@ -326,6 +331,12 @@ class TransformerLM:
             attn = ops.paged_attn_decode(q, cache.k[i], cache.v[i], block_table, context_lens, self.scale,
                                          q_len=q_len, window=cfg.window_for_layer(i), sinks=lw.sinks)
             last = i + 1 == n_layers
+            if moe:
+                q, resid, normed = self._moe_layer_persistent(DL, i, lw, attn, resid, scratch, fused, qkv_args, T, H,
+                                                              s_o, last)
+                if taps is not None:
+                    taps.append(resid)
+                continue
             mask = DL.ST_O | DL.ST_RED1 | DL.ST_GU | DL.ST_DOWN | DL.ST_RED2
             if not fused_gate:
                 mask |= DL.ST_SILU
@@ -352,6 +363,36 @@ class TransformerLM:
         if taps is not None:
             return normed, taps
         return normed
+
+    def _moe_layer_persistent(self, DL, i, lw, attn, resid, scratch, fused, qkv_args, T, H, s_o, last):
+        """A mixture-of-experts layer around the persistent kernel: launch A runs o_proj and the first reduction,
+        the experts run in their own kernels, launch B sums their outputs (pushed by every rank, or local),
+        adds the residual, norms, and runs the next layer's QKV projection with RoPE and the cache append."""
+        cfg = self.cfg
+        bf = dict(dtype=torch.bfloat16, device=attn.device)
+        resid_mid, normed_mid = torch.empty((T, H), **bf), torch.empty((T, H), **bf)
+        buf_o = None if fused is None else fused.next_buffer(T, H)
+        DL.decode_layer(DL.ST_O | DL.ST_RED1, T, H, cfg.rms_eps, scratch, w_o=lw.o, attn=attn, splits_o=s_o,
+                        bias_o=lw.o_bias, resid_in=resid, norm1_w=lw.post_norm, resid_mid=resid_mid,
+                        normed_mid=normed_mid, tp_buffers=None if buf_o is None else (buf_o, buf_o))
+        resid_out, normed_out = torch.empty((T, H), **bf), torch.empty((T, H), **bf)
+        mask, extra, q = DL.ST_RED2, {}, None
+        if not last:
+            mask |= DL.ST_QKV | DL.ST_ROPE
+            q = torch.empty((T, self.nq * self.d), **bf)
+            extra = qkv_args(i + 1, q)
+        norm2 = self.final_norm if last else self.layers[i + 1].input_norm
+        if fused is not None:
+            y_sorted, plan, weights = self._moe._experts(lw, normed_mid)
+            b = fused.moe_combine_push(y_sorted, plan.pair_pos, weights, T)
+            buf = fused.buffer(b)
+            DL.decode_layer(mask, T, H, cfg.rms_eps, scratch, resid_mid=resid_mid, norm2_w=norm2, resid_out=resid_out,
+                            normed_out=normed_out, tp_buffers=(buf, buf), red2_slots=self.tp.world_size, **extra)
+        else:
+            y = self._moe.forward(lw, normed_mid)
+            DL.decode_layer(mask, T, H, cfg.rms_eps, scratch, resid_mid=resid_mid, norm2_w=norm2, resid_out=resid_out,
+                            normed_out=normed_out, red2_x=y, **extra)
+        return q, resid_out, normed_out
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: PagedKVCache,

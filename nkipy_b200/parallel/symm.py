@@ -304,6 +304,18 @@ class FusedTP:
                     slabs=base + self.FLAG_BYTES + b * self.buf_bytes, flags=base + b * n * 4,
                     seen=self.seen.data_ptr() + 4 * b, done=self.done.data_ptr())
 
+    def buffer(self, b: int) -> dict:
+        return self._buffer(b)
+
+    def next_buffer(self, tokens: int, hidden: int) -> dict:
+        """The buffer of ONE fused operation whose two halves run inside another kernel (counts as one)."""
+        if tokens > self.max_tokens or hidden != self.hidden:
+            raise ValueError(f"FusedTP sized for [{self.max_tokens}, {self.hidden}], got [{tokens}, {hidden}]")
+        b = self._parity
+        self._parity ^= 1
+        self.ops_issued += 1
+        return self._buffer(b)
+
     def layer_buffers(self, tokens: int, hidden: int):
         """The two buffers (o_proj, down) of one launch of the persistent decode-layer kernel
         (`ops.decode_layer.decode_layer`): counts as two fused operations of the step."""
@@ -392,6 +404,18 @@ class FusedTP:
 
         if tokens > self.max_tokens or y_sorted.shape[1] != self.hidden:
             raise ValueError(f"FusedTP sized for [{self.max_tokens}, {self.hidden}]")
+        b = self.moe_combine_push(y_sorted, pair_pos, weights, tokens)
+        return self._reduce(b, self.tp.world_size, tokens, resid, next_norm, eps, y_sorted.device)
+
+    def moe_combine_push(self, y_sorted: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor,
+                         tokens: int) -> int:
+        """The producer half alone: this rank's weighted expert outputs go into slot [rank] of the next buffer on
+        every rank.  Returns the buffer index; the caller runs the consumer (`_reduce`, or the reducing stage of the
+        persistent layer kernel through `buffer(b)`)."""
+        from .. import ops
+
+        if tokens > self.max_tokens or y_sorted.shape[1] != self.hidden:
+            raise ValueError(f"FusedTP sized for [{self.max_tokens}, {self.hidden}]")
         b = self._parity
         self._parity ^= 1
         self.ops_issued += 1
@@ -402,7 +426,7 @@ class FusedTP:
                                             torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "nkb_moe_combine_push")
         ops._launches += 1
-        return self._reduce(b, n, tokens, resid, next_norm, eps, y_sorted.device)
+        return b
 
     def argmax_exchange(self, vals: torch.Tensor, ids: torch.Tensor, id_offset: int,
                         out_ids: Optional[torch.Tensor] = None) -> torch.Tensor:

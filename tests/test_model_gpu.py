@@ -50,8 +50,15 @@ def ref_forward(ref, ids):
     return ref.forward(ids, 0).reshape(-1, ref.cfg.hidden_size)
 
 
+@pytest.fixture(params=["chain", "persistent"])
+def layer_impl(request, monkeypatch):
+    """Both ways of running a decode step: one launch per operation, and the persistent layer kernel."""
+    monkeypatch.setattr(ops, "DECODE_LAYER_IMPL", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("graph", [False, True])
-def test_tiny_generate_matches_oracle_tokens(graph):
+def test_tiny_generate_matches_oracle_tokens(graph, layer_impl):
     cfg = C.tiny(hidden_size=512, head_dim=128, num_heads=4, num_kv_heads=2, intermediate_size=1024,
                  vocab_size=2048, num_layers=3)
     dev = torch.device("cuda")
@@ -67,7 +74,7 @@ def test_tiny_generate_matches_oracle_tokens(graph):
     assert agree >= 30, (outs, expect)
 
 
-def test_decode_hidden_matches_oracle():
+def test_decode_hidden_matches_oracle(layer_impl):
     cfg = C.llama3_8b(num_layers=2, vocab_size=4096, max_position=2048)
     dev = torch.device("cuda")
     w = random_weights(cfg, device=dev, seed=1, std=0.02)
@@ -88,7 +95,7 @@ def test_decode_hidden_matches_oracle():
     assert err < 2e-2, err
 
 
-def test_moe_model_prefill_and_decode_match_oracle():
+def test_moe_model_prefill_and_decode_match_oracle(layer_impl):
     cfg = C.tiny(name="tiny-qwen3-moe", hidden_size=512, head_dim=128, num_heads=4, num_kv_heads=2, qk_norm=True,
                  num_experts=16, top_k=4, moe_intermediate_size=256, intermediate_size=0, vocab_size=2048,
                  num_layers=2, rms_eps=1e-6)

@@ -32,7 +32,8 @@ def _cfg(kind):
 def _worker(rank, world, port, q, kind):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      NKIPY_B200_DECODE_LAYER="persistent" if "persistent" in kind else "chain")
     from nkipy_b200 import ops
     from nkipy_b200.models.engine import GenerationEngine
     from nkipy_b200.models.transformer import TransformerLM
@@ -60,7 +61,7 @@ def _worker(rank, world, port, q, kind):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("kind", ["dense", "moe", "dense_sp", "moe_sp"])
+@pytest.mark.parametrize("kind", ["dense", "moe", "dense_sp", "moe_sp", "dense_persistent", "moe_persistent"])
 def test_tp2_fused_generation(kind):
     from nkipy_b200.models.reference import EagerTransformer
     from nkipy_b200.models.weights import random_weights
