@@ -106,15 +106,16 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// All CTAs of the grid meet here.  Returns false when the wait ran out (or another CTA already reported an
-// error): the caller leaves the kernel.  Writes made before the barrier by any thread of any CTA are
-// visible after it to generic loads and, through the proxy fence, to TMA loads.
-__device__ __forceinline__ bool grid_barrier(unsigned int* bar, int* status, int where) {
-  __shared__ int ok_s;
+// Grid-wide barrier in two halves.  `grid_arrive` (all threads of the CTA) publishes this CTA's writes and
+// counts it; the CTA that completes the count opens the next generation.  `grid_wait` spins (bounded) until
+// the generation read at arrival has passed.  Writes made before a CTA's arrival are visible after another
+// CTA's wait to generic loads and, through the proxy fence, to TMA loads.  A GEMM stage that follows takes the
+// wait inside (GridSync): its producer warp first fills the ring with weight tiles.
+__device__ __forceinline__ unsigned int grid_arrive(unsigned int* bar) {
+  __shared__ unsigned int gen_s;
   asm volatile("fence.proxy.async;" ::: "memory");
   __syncthreads();
   if (threadIdx.x == 0) {
-    int ok = 1;
     const unsigned int gen = ld_acquire_gpu(bar + 1);   // cannot advance before this CTA has arrived
     __threadfence();
     const unsigned int prev = atomicAdd(bar, 1u);
@@ -122,31 +123,60 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, int* status, int
       bar[0] = 0u;
       __threadfence();
       st_release_gpu(bar + 1, gen + 1u);
-    } else {
-      const unsigned long long t0 = globaltimer_ns();
-      unsigned int spins = 0;
-      while (ld_acquire_gpu(bar + 1) == gen) {
-        if ((++spins & 127u) == 0) {
-          if (*reinterpret_cast<volatile int*>(status) != 0) { ok = 0; break; }
-          if (globaltimer_ns() - t0 > kWaitLimitNs) {
-            atomicCAS(status, 0, ERR_WAIT_PEER_FLAG | (where << 8) | (int(blockIdx.x) << 16));
-            ok = 0;
-            break;
-          }
-        }
+    }
+    gen_s = gen;
+  }
+  __syncthreads();
+  return gen_s;
+}
+
+// One thread's wait.  Returns false when the limit ran out or another CTA already reported an error.
+__device__ __forceinline__ bool grid_wait_thread(const unsigned int* bar, unsigned int gen, int* status, int where) {
+  if (ld_acquire_gpu(bar + 1) != gen) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned int spins = 0;
+  while (ld_acquire_gpu(bar + 1) == gen) {
+    if ((++spins & 127u) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        atomicCAS(status, 0, ERR_WAIT_PEER_FLAG | (where << 8) | (int(blockIdx.x) << 16));
+        return false;
       }
     }
-    ok_s = ok;
   }
+  return true;
+}
+
+// The whole CTA waits.
+__device__ __forceinline__ bool grid_wait(const unsigned int* bar, unsigned int gen, int* status, int where) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = grid_wait_thread(bar, gen, status, where) ? 1 : 0;
   __syncthreads();
   asm volatile("fence.proxy.async;" ::: "memory");
   return ok_s != 0;
 }
 
+struct GridSync {
+  static constexpr bool active = true;
+  const unsigned int* bar;
+  unsigned int gen;
+  int* status;
+  int where;
+  bool pending;     // false: nothing to wait for (first stage of a launch)
+  __device__ __forceinline__ bool wait(volatile int* abort_flag) const {
+    if (!pending) return true;
+    const bool ok = grid_wait_thread(bar, gen, status, where);
+    if (!ok) *abort_flag = 1;
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return ok;
+  }
+};
+
 template <int BN, bool PUSH>
-__device__ __noinline__ void gemm_stage(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
-                                        const PushArgs& push) {
-  gemm_bf16_body<BN, PUSH, false>(tmA, tmB, args, push, GroupArgs{});
+__device__ __noinline__ bool gemm_stage(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
+                                        const PushArgs& push, const GridSync& sync) {
+  return gemm_bf16_body<BN, PUSH, false, NoFix, NoElemEpi, GridSync>(tmA, tmB, args, push, GroupArgs{}, NoFix::Args{},
+                                                                     NoElemEpi{}, sync);
 }
 
 constexpr int kRedIters = 4;   // 8 elements per thread per iteration: hidden <= 192 * 8 * 4
@@ -411,46 +441,78 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   // a kernel of an earlier, failed step left its error: do nothing (the host reads and clears the word)
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
   if (!(mask & ST_O)) griddep_wait();     // the GEMM body orders itself against the preceding kernel
+  unsigned int* bar = L.grid_bar;
   int nbar = 0;
-  auto barrier = [&]() { return grid_barrier(L.grid_bar, status, 32 + nbar++); };
+  GridSync sync{bar, 0u, status, 0, false};
+  // arrive now, wait later: the next stage (or `settle`) completes the barrier
+  auto arrive = [&]() {
+    sync.gen = grid_arrive(bar);
+    sync.where = 32 + nbar++;
+    sync.pending = true;
+  };
+  auto settle = [&]() -> bool {
+    if (!sync.pending) return true;
+    sync.pending = false;
+    return grid_wait(bar, sync.gen, status, sync.where);
+  };
+  // which reduction still has to advance its "uses consumed" counter once every CTA has read it
+  unsigned int* bump = nullptr;
+  auto bump_seen = [&]() {
+    if (TP && bump && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(bump, 1u);
+    bump = nullptr;
+  };
 
   if (mask & ST_O) {
-    gemm_stage<BN, TP>(L.o.tmA, L.o.tmB, L.o.args, L.push_o);
-    if (!TP && !barrier()) return;        // pushed partials are ordered by the ranks' arrival counters instead
+    if (!gemm_stage<BN, TP>(L.o.tmA, L.o.tmB, L.o.args, L.push_o, sync)) return;
+    if (!TP) arrive();                    // pushed partials are ordered by the ranks' arrival counters instead
   }
   if (mask & ST_RED1) {
+    if (!settle()) return;
     if (!reduce_stage(L.red1, L.tokens, L.hidden, L.eps, status)) return;
-    if (!barrier()) return;
-    if (TP && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(L.red1.seen, 1u);
+    arrive();
+    bump = L.red1.seen;
   }
   if (mask & ST_GU) {
-    gemm_stage<BN, false>(L.gu.tmA, L.gu.tmB, L.gu.args, L.push_o);
-    if (!barrier()) return;
+    if (!gemm_stage<BN, false>(L.gu.tmA, L.gu.tmB, L.gu.args, L.push_o, sync)) return;
+    sync.pending = false;
+    bump_seen();
+    arrive();
   }
   if (mask & ST_SILU) {
+    if (!settle()) return;
     silu_stage(L.silu, L.tokens);
-    if (!barrier()) return;
+    arrive();
   }
   if (mask & ST_DOWN) {
-    gemm_stage<BN, TP>(L.down.tmA, L.down.tmB, L.down.args, L.push_down);
-    if (!TP && !barrier()) return;
+    if (!gemm_stage<BN, TP>(L.down.tmA, L.down.tmB, L.down.args, L.push_down, sync)) return;
+    sync.pending = false;
+    bump_seen();
+    if (!TP) arrive();
   }
   if (mask & ST_RED2) {
+    if (!settle()) return;
+    bump_seen();
     if (!reduce_stage(L.red2, L.tokens, L.hidden, L.eps, status)) return;
-    if (!barrier()) return;
-    if (TP && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(L.red2.seen, 1u);
+    arrive();
+    bump = L.red2.seen;
   }
   if (mask & ST_QKV) {
-    gemm_stage<BN, false>(L.qkv.tmA, L.qkv.tmB, L.qkv.args, L.push_o);
-    if (!barrier()) return;
+    if (!gemm_stage<BN, false>(L.qkv.tmA, L.qkv.tmB, L.qkv.args, L.push_o, sync)) return;
+    sync.pending = false;
+    bump_seen();
+    arrive();
   }
   if (mask & ST_ROPE) {
+    if (!settle()) return;
     switch (L.rope.head_dim) {
       case 64: rope_stage<64>(L.rope, L.tokens); break;
       case 128: rope_stage<128>(L.rope, L.tokens); break;
       default: rope_stage<256>(L.rope, L.tokens); break;
     }
   }
+  // a barrier that is still open (the launch ends with a reduction): complete it, the counter needs it
+  if (!settle()) return;
+  bump_seen();
 }
 
 }  // namespace nkb

@@ -113,13 +113,23 @@ struct NoElemEpi {
   __device__ __forceinline__ float operator()(float x, long long, long long) const { return x; }
 };
 
+// Optional hook for kernels that run this body as one stage of a longer persistent kernel: `wait` is called
+// once by the producer warp (after it has filled the ring with weight tiles, which depend on nothing) and once
+// by every epilogue warp before their first use of data or buffers of the preceding stage.  It returns false
+// when the wait gave up.
+struct NoSync {
+  static constexpr bool active = false;
+  __device__ __forceinline__ bool wait(volatile int*) const { return true; }
+};
+
 // Fix selects a split-K fix-up epilogue (splitk_fix.cuh): the partial tiles go to fix.c.partials (the
 // launcher points args.out there) and the CTA that completes a tile's arrival counter finishes the tile.
-template <int BN, bool PUSH, bool GROUPED, class Fix = NoFix, class ElemEpi = NoElemEpi>
-__device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
+// Returns false when a bounded wait inside gave up (the status word then holds the reason).
+template <int BN, bool PUSH, bool GROUPED, class Fix = NoFix, class ElemEpi = NoElemEpi, class Sync = NoSync>
+__device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
                                                const PushArgs& push, const GroupArgs& grp,
                                                const typename Fix::Args& fix = typename Fix::Args{},
-                                               const ElemEpi& elem_epi = ElemEpi{}) {
+                                               const ElemEpi& elem_epi = ElemEpi{}, const Sync& sync = Sync{}) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -213,6 +223,11 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     uint32_t phase = 0;
     bool alive = true;
     int arrived_group = -1;
+    if constexpr (Sync::active) {
+      int ok = 1;
+      if (lane == 0) ok = sync.wait(abort_flag) ? 1 : 0;
+      alive = __shfl_sync(0xffffffffu, ok, 0) != 0;
+    }
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
       const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
       if (!wi.valid) continue;
@@ -316,7 +331,13 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
     griddep_wait();  // residual / output buffers may still be in use by the preceding kernel
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+    bool synced = true;
+    if constexpr (Sync::active) {
+      int ok = 1;
+      if (lane == 0) ok = sync.wait(abort_flag) ? 1 : 0;
+      synced = __shfl_sync(0xffffffffu, ok, 0) != 0;
+    }
+    for (int w = blockIdx.x; w < total_work && synced; w += gridDim.x) {
       const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
       if (!wi.valid) continue;
       const int rt = wi.rt, sp = wi.sp;
@@ -553,10 +574,12 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tmA, const CUt
   }
   tc_fence_before();
   __syncthreads();
+  const bool all_ok = *abort_flag == 0;
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
+  return all_ok;
 }
 
 template <int BN, int MINB, bool PUSH>
