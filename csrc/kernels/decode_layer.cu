@@ -86,6 +86,7 @@ struct DecodeLayerArgs {
   SiluArgs silu;
   RopeArgs rope;
   unsigned int* grid_bar;          // [0] arrivals of the current barrier, [1] generation
+  unsigned long long* timing;      // optional [16]: CTA 0 records the global timer after every stage (ns)
   int* status;
   int mask, tokens, hidden;
   float eps;
@@ -442,7 +443,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
   if (!(mask & ST_O)) griddep_wait();     // the GEMM body orders itself against the preceding kernel
   unsigned int* bar = L.grid_bar;
-  int nbar = 0;
+  int nbar = 0, ntick = 0;
+  auto tick = [&]() {
+    if (L.timing && blockIdx.x == 0 && threadIdx.x == 0) L.timing[ntick] = globaltimer_ns();
+    ++ntick;
+  };
+  tick();
   GridSync sync{bar, 0u, status, 0, false};
   // arrive now, wait later: the next stage (or `settle`) completes the barrier
   auto arrive = [&]() {
@@ -465,29 +471,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   if (mask & ST_O) {
     if (!gemm_stage<BN, TP>(L.o.tmA, L.o.tmB, L.o.args, L.push_o, sync)) return;
     if (!TP) arrive();                    // pushed partials are ordered by the ranks' arrival counters instead
+    tick();
   }
   if (mask & ST_RED1) {
     if (!settle()) return;
     if (!reduce_stage(L.red1, L.tokens, L.hidden, L.eps, status)) return;
     arrive();
     bump = L.red1.seen;
+    tick();
   }
   if (mask & ST_GU) {
     if (!gemm_stage<BN, false>(L.gu.tmA, L.gu.tmB, L.gu.args, L.push_o, sync)) return;
     sync.pending = false;
     bump_seen();
     arrive();
+    tick();
   }
   if (mask & ST_SILU) {
     if (!settle()) return;
     silu_stage(L.silu, L.tokens);
     arrive();
+    tick();
   }
   if (mask & ST_DOWN) {
     if (!gemm_stage<BN, TP>(L.down.tmA, L.down.tmB, L.down.args, L.push_down, sync)) return;
     sync.pending = false;
     bump_seen();
     if (!TP) arrive();
+    tick();
   }
   if (mask & ST_RED2) {
     if (!settle()) return;
@@ -495,12 +506,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
     if (!reduce_stage(L.red2, L.tokens, L.hidden, L.eps, status)) return;
     arrive();
     bump = L.red2.seen;
+    tick();
   }
   if (mask & ST_QKV) {
     if (!gemm_stage<BN, false>(L.qkv.tmA, L.qkv.tmB, L.qkv.args, L.push_o, sync)) return;
     sync.pending = false;
     bump_seen();
     arrive();
+    tick();
   }
   if (mask & ST_ROPE) {
     if (!settle()) return;
@@ -513,6 +526,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   // a barrier that is still open (the launch ends with a reduction): complete it, the counter needs it
   if (!settle()) return;
   bump_seen();
+  tick();
 }
 
 }  // namespace nkb
@@ -553,6 +567,8 @@ extern "C" struct NkbDecodeLayer {
   // second reduction without the down stage (the block between the two ends ran elsewhere, e.g. MoE experts):
   // with ranks the pushed slabs of buffer "d" (red2_slots of them) are summed, else red2_x [tokens, hidden] bf16
   const void* red2_x; int red2_slots, _pad4;
+  // optional: 16 unsigned 64-bit words; CTA 0 stores the global timer (ns) at kernel start and after every stage
+  void* timing;
 };
 
 namespace {
@@ -642,6 +658,7 @@ extern "C" int nkb_decode_layer(const NkbDecodeLayer* d, void* stream) {
   L.hidden = H;
   L.eps = d->eps;
   L.grid_bar = d->grid_bar;
+  L.timing = reinterpret_cast<unsigned long long*>(d->timing);
   L.status = status_word();
   int smem = 4096;
   auto bf = [](const void* p) { return reinterpret_cast<const __nv_bfloat16*>(p); };

@@ -47,6 +47,7 @@ class _Desc(ctypes.Structure):
         ("slabs_d", _P), ("flags_d", _P), ("seen_d", _P), ("done_d", _P),
         ("max_slots", _I), ("_pad3", _I),
         ("red2_x", _P), ("red2_slots", _I), ("_pad4", _I),
+        ("timing", _P),
     ]
 
 
@@ -126,11 +127,13 @@ def decode_layer(mask: int, tokens: int, hidden: int, eps: float, scratch: Decod
                  norm2_w=None, resid_out=None, normed_out=None,
                  w_qkv=None, splits_qkv: int = 1, nq: int = 0, nkv: int = 0, head_dim: int = 0, bias_qkv=None,
                  positions=None, slots=None, cos_sin=None, q_norm_w=None, k_norm_w=None,
-                 q_out=None, k_cache=None, v_cache=None, tp_buffers=None, red2_x=None, red2_slots: int = 0) -> None:
+                 q_out=None, k_cache=None, v_cache=None, tp_buffers=None, red2_x=None, red2_slots: int = 0,
+                 timing: Optional[torch.Tensor] = None) -> None:
     """One launch of the persistent layer kernel.  Tensors are bf16 unless the kernel's header says otherwise;
     `mask` selects the stages (ST_*).  ST_RED2 without ST_DOWN sums a block output that other
     kernels produced: `red2_x` [tokens, hidden] on one rank, or `red2_slots` pushed slabs of the second buffer with
-    ranks (the residual is `resid_mid`).  tp_buffers: (o, down) buffer descriptions from
+    ranks (the residual is `resid_mid`).  timing: int64[16] that receives the device's global
+    timer (ns) at kernel start and after every stage that ran, from CTA 0.  tp_buffers: (o, down) buffer descriptions from
     `FusedTP.layer_buffers()` when the row-parallel GEMMs push to the ranks of a tensor-parallel group."""
     from . import _count_launch
 
@@ -153,6 +156,10 @@ def decode_layer(mask: int, tokens: int, hidden: int, eps: float, scratch: Decod
         d.inter = inter
     d.norm2_w, d.resid_out, d.normed_out = _ptr(norm2_w), _ptr(resid_out), _ptr(normed_out)
     d.red2_x, d.red2_slots = _ptr(red2_x), red2_slots
+    if timing is not None:
+        if timing.dtype != torch.int64 or timing.numel() < 16:
+            raise ValueError("timing must be an int64 tensor of 16 elements")
+        d.timing = timing.data_ptr()
     if mask & ST_QKV:
         d.w_qkv, d.ld_wqkv, d.splits_qkv = w_qkv.data_ptr(), w_qkv.stride(0), splits_qkv
         d.nq, d.nkv, d.head_dim, d.bias_qkv = nq, nkv, head_dim, _ptr(bias_qkv)

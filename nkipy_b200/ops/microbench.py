@@ -319,7 +319,61 @@ def case_addnorm(args):
                 shape=dict(tokens=T, hidden=H, splits=S))
 
 
+def case_decode_layer(args):
+    """One launch of the persistent decode-layer kernel at Llama-3-8B shapes (the per-rank shard with --tp N),
+    rotating over enough weight sets to exceed L2; `stages_us` are CTA 0's global-timer intervals per stage
+    (o_proj, reduce, gate/up, [silu], down, reduce, qkv, rope + exit), averaged over the sets."""
+    from . import decode_layer as DL
+    from . import rope_table
+
+    tp = max(1, args.tp)
+    T, H, D = (args.tokens or 64), 4096, 128
+    nq, nkv, inter = 32 // tp, max(1, 8 // tp), 14336 // tp
+    k_o, qkv_w = nq * D, (nq + 2 * nkv) * D
+    per_set = 2 * (H * k_o + 2 * inter * H + H * inter + qkv_w * H)
+    sets = _sets_for(per_set, args.sets)
+    fused_gate = inter // 128 >= 100
+    env = DL.env_splits() or (0, 0, 0, 0)
+    pick = DL.pick_layer_splits
+    sp = [pick(H, k_o), 1 if fused_gate else pick(2 * inter, H), pick(H, inter), pick(qkv_w, H)]
+    sp = [e if e > 0 else d for e, d in zip(env, sp)]
+    if sp[1] > 1:
+        fused_gate = False
+    scratch = DL.layer_scratch("cuda", DL.scratch_floats(DL.block_n_for(T), [
+        (H, sp[0]), (0 if fused_gate else 2 * inter, sp[1]), (H, sp[2]), (qkv_w, sp[3])]))
+    cos_sin = rope_table(D, 4096, theta=500000.0, device="cuda")
+    pos = torch.randint(0, 4096, (T,), device="cuda", dtype=torch.int32)
+    slots = torch.arange(T, device="cuda", dtype=torch.int32)
+    bs = 32
+    kc = torch.zeros((T + bs - 1) // bs + 1, nkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    mask = DL.ST_ALL if not fused_gate else DL.ST_ALL & ~DL.ST_SILU
+    timings, fns = [], []
+    for _ in range(sets):
+        w = dict(w_o=_bf16(H, k_o, scale=0.02), w_gu=_bf16(2 * inter, H, scale=0.02), w_down=_bf16(H, inter, scale=0.02),
+                 w_qkv=_bf16(qkv_w, H, scale=0.02))
+        io = dict(attn=_bf16(T, k_o), resid_in=_bf16(T, H), norm1_w=_bf16(H), norm2_w=_bf16(H),
+                  resid_mid=_bf16(T, H), normed_mid=_bf16(T, H), act=_bf16(T, inter), resid_out=_bf16(T, H),
+                  normed_out=_bf16(T, H), q_out=_bf16(T, nq * D))
+        tm = torch.zeros(16, dtype=torch.int64, device="cuda")
+        timings.append(tm)
+
+        def fn(w=w, io=io, tm=tm):
+            DL.decode_layer(mask, T, H, 1e-5, scratch, splits_o=sp[0], inter=inter, splits_gu=sp[1],
+                            fused_gate=fused_gate, splits_down=sp[2], splits_qkv=sp[3], nq=nq, nkv=nkv, head_dim=D,
+                            positions=pos, slots=slots, cos_sin=cos_sin, k_cache=kc, v_cache=vc, timing=tm, **w, **io)
+        fns.append(fn)
+    us = _time(fns, args.iters, args.warmup, graph=not args.no_graph)
+    torch.cuda.synchronize()
+    n_stage = bin(mask).count("1") + 1
+    ticks = torch.stack(timings).double().cpu()[:, :n_stage + 1]
+    stages = (ticks[:, 1:] - ticks[:, :-1]).mean(0) / 1e3
+    return dict(case="decode-layer", tp=tp, tokens=T, splits=sp, fused_gate=fused_gate, sets=sets, us=us,
+                bytes=per_set, flops=2.0 * T * per_set / 2, stages_us=[round(float(x), 2) for x in stages])
+
+
 CASES = {
+    "decode-layer": case_decode_layer,
     "gemm-decode-qkv": lambda a: case_gemm_decode("gemm-decode-qkv", 6144, 4096, 64, 6, False, a),
     "gemm-decode-o": lambda a: case_gemm_decode("gemm-decode-o", 4096, 4096, 64, 8, False, a, True),
     "gemm-decode-gate-up": lambda a: case_gemm_decode("gemm-decode-gate-up", 14336, 4096, 64, 1, True, a),
