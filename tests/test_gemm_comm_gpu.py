@@ -147,15 +147,23 @@ def _worker_body(rank, world, port, q):
     dist.destroy_process_group()
 
 
+def _worlds():
+    n = torch.cuda.device_count()
+    return [w for w in (2, 4, 8) if w <= n] or [2]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_gemm_comm_two_ranks():
+@pytest.mark.parametrize("world", _worlds())
+def test_gemm_comm_ranks(world):
+    """Every rank count the box offers: the peer rotation, the per-rank counter stride and the slab ownership
+    all depend on it."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=240) for _ in range(2)]
+    res = [q.get(timeout=300) for _ in range(world)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
