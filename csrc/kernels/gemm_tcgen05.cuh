@@ -579,6 +579,21 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
+  if constexpr (Sync::active) {
+    // a stage of a longer kernel: the next stage creates its barriers in the same place.  After a time-out
+    // some barrier may still have a transaction pending, so the words are left alone (the caller returns).
+    if (threadIdx.x == 0 && all_ok) {
+      for (int s = 0; s < stages; ++s) {
+        mbar_inval(&ctrl->full[s]);
+        mbar_inval(&ctrl->empty[s]);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_inval(&ctrl->tfull[i]);
+        mbar_inval(&ctrl->tempty[i]);
+      }
+    }
+    __syncthreads();
+  }
   return all_ok;
 }
 
