@@ -89,7 +89,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager", "eager-graph"],
+                    help="eager-graph: the eager PyTorch decode step captured in a CUDA graph (static cache, position "
+                         "on the device), so the comparison is not against Python launch overhead; dense models")
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen3-30b-a3b", "gpt-oss-20b"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
@@ -302,8 +304,8 @@ def main():
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(0, cfg.vocab_size, (batch, prompt_len), generator=g)
 
-    if args.impl == "eager":
-        return run_eager(args, cfg, weights, prompts, tp, K, W, parallelism)
+    if args.impl in ("eager", "eager-graph"):
+        return run_eager(args, cfg, weights, prompts, tp, K, W, parallelism, graph=args.impl == "eager-graph")
 
     # baseline of the same model on the same weights, a few steps (eager PyTorch: cuBLAS, SDPA, NCCL)
     eager_value = None
@@ -390,8 +392,9 @@ class EagerSlice:
             m.k_static, m.v_static = full_k, full_v
 
 
-def run_eager(args, cfg, weights, prompts, tp, K, W, parallelism):
-    """Baseline arm: plain PyTorch (cuBLAS, NCCL) decoder with a dense cache."""
+def run_eager(args, cfg, weights, prompts, tp, K, W, parallelism, graph=False):
+    """Baseline arm: plain PyTorch (cuBLAS, NCCL) decoder with a dense cache; with graph=True the decode step is
+    captured in a CUDA graph and replayed."""
     import torch
 
     from nkipy_b200.models.reference import EagerTransformer
@@ -403,7 +406,7 @@ def run_eager(args, cfg, weights, prompts, tp, K, W, parallelism):
     tp.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    model.alloc_static_cache(batch, prompt_len + W + K + 8)
+    model.alloc_static_cache(batch, prompt_len + W + K + 12)
     chunk0 = max(1, 16384 // prompt_len)
     EagerSlice(model, 0, min(batch, chunk0)).forward(ids[:chunk0].flip(1), 0)      # untimed warm-up chunk
     torch.cuda.synchronize()
@@ -423,10 +426,38 @@ def run_eager(args, cfg, weights, prompts, tp, K, W, parallelism):
     ttfts.sort()
     ttft_p50 = ttfts[len(ttfts) // 2]
     pos = prompt_len
-    for _ in range(W):
+    step_graph = None
+    if graph:
+        pos_t = torch.tensor([pos], dtype=torch.int64, device=dev)
+        cur = nxt.clone()
+
+        def body():
+            h = model.forward_decode_static(cur[:, None], pos_t)
+            cur.copy_(model.greedy(h[:, -1]))
+            pos_t.add_(1)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        step_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(step_graph):
+            body()
+
+    def step():
+        nonlocal nxt, pos
+        if step_graph is not None:
+            step_graph.replay()
+            return
         h = model.forward_sdpa(nxt[:, None], pos)
         nxt = model.greedy(h[:, -1])
         pos += 1
+
+    for _ in range(W):
+        step()
     sampler = ClockSampler(dev.index or 0)
     tp.barrier()
     torch.cuda.synchronize()
@@ -434,16 +465,14 @@ def run_eager(args, cfg, weights, prompts, tp, K, W, parallelism):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(K):
-        h = model.forward_sdpa(nxt[:, None], pos)
-        nxt = model.greedy(h[:, -1])
-        pos += 1
+        step()
     end.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms = tp.max_over_ranks(start.elapsed_time(end))
     if tp.rank == 0:
         print(json.dumps({
-            "metric": "decode tokens/s", "impl": "eager-pytorch", "value": round(batch * K / (ms / 1e3), 2),
+            "metric": "decode tokens/s", "impl": "eager-pytorch-graph" if graph else "eager-pytorch", "value": round(batch * K / (ms / 1e3), 2),
             "unit": "tokens/s", "n_gpus": tp.world_size, "steps": K, "warmup": W,
             "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
             "data": "synthetic", "ttft_p50_s": round(ttft_p50, 4), "prefill_s": round(prefill_s, 4),

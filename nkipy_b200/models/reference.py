@@ -232,6 +232,52 @@ class EagerTransformer:
             x = x + y
         return _rms(x, w["norm_weight"], cfg.rms_eps)
 
+    def forward_decode_static(self, ids: torch.Tensor, pos_t: torch.Tensor) -> torch.Tensor:
+        """One decode step whose position is a device tensor (int64 [1]), so the step can be captured in a CUDA
+        graph and replayed: the cache row is written with `index_copy_`, attention runs over the whole static
+        cache under a mask `key position <= pos`.  Dense-FFN causal models only (the expert loops of the MoE
+        path branch on device data)."""
+        cfg, w = self.cfg, self.w
+        if cfg.is_moe or cfg.attention_sinks or any(cfg.window_for_layer(i) > 0 for i in range(cfg.num_layers)):
+            raise NotImplementedError("graph-capturable eager decode covers dense causal models")
+        B = ids.shape[0]
+        d = cfg.head_dim
+        max_len = self.k_static[0].shape[2]
+        x = w["tok_embedding"][ids.long()]
+        pos = pos_t[None, :].expand(B, 1)
+        mask = (torch.arange(max_len, device=self.device) <= pos_t)[None, None, None, :]
+        g = self.nq // self.nkv
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            in_name = p + ("input_layernorm_weight" if p + "input_layernorm_weight" in w else "input_weight")
+            post_name = p + ("post_attention_layernorm_weight" if p + "post_attention_layernorm_weight" in w
+                             else "post_attention_weight")
+            h = _rms(x, w[in_name], cfg.rms_eps)
+            qkv = h @ w[p + "qkv_weight"]
+            if cfg.attn_bias:
+                qkv = qkv + w[p + "qkv_bias"]
+            q, k, v = qkv.split([self.nq * d, self.nkv * d, self.nkv * d], dim=-1)
+            q, k, v = q.reshape(B, 1, self.nq, d), k.reshape(B, 1, self.nkv, d), v.reshape(B, 1, self.nkv, d)
+            if cfg.qk_norm:
+                q, k = _rms(q, w[p + "q_norm_weight"], cfg.rms_eps), _rms(k, w[p + "k_norm_weight"], cfg.rms_eps)
+            q, k = self._rope(q, pos), self._rope(k, pos)
+            self.k_static[i].index_copy_(2, pos_t, k.transpose(1, 2))
+            self.v_static[i].index_copy_(2, pos_t, v.transpose(1, 2))
+            a = F.scaled_dot_product_attention(q.reshape(B, self.nkv, g, d), self.k_static[i], self.v_static[i],
+                                               attn_mask=mask)
+            o = a.reshape(B, 1, self.nq * d) @ w[p + "o_weight"]
+            if cfg.attn_bias:
+                o = o + w[p + "o_bias"]
+            self.tp.all_reduce(o)
+            x = x + o
+            h = _rms(x, w[post_name], cfg.rms_eps)
+            gu = h @ w[p + "gate_up_weight"]
+            i_l = gu.shape[-1] // 2
+            y = (F.silu(gu[..., :i_l]) * gu[..., i_l:]) @ w[p + "down_weight"]
+            self.tp.all_reduce(y)
+            x = x + y
+        return _rms(x, w["norm_weight"], cfg.rms_eps)
+
     def greedy(self, hidden_last: torch.Tensor) -> torch.Tensor:
         """hidden_last [B, H] -> global greedy ids (vocab-parallel aware)."""
         logits = (hidden_last @ self.w["lm_head_weight"]).float()
