@@ -600,12 +600,16 @@ int setup_gemm(StageGemm& g, const void* w, const void* x, int rows, int tokens,
   return 0;
 }
 
+// Dynamic shared memory of the layer kernel: an SM's 227 KB minus room for the kernel's static variables
+// (reduction scratch, barrier hand-over words).
+constexpr int kLayerDynSmem = 232448 - 2048;
+
 // Ring depth for one CTA per SM; returns the dynamic shared memory the stage needs.
 int ring(GemmArgs& a, int block_n, bool push) {
   const int a_tiles = a.gated == 1 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + block_n * kBlockK * 2;
   const int extra = 512 + (push ? 32 * kTileRows * 2 : 0);
-  const int budget = 232448 - 1024 - extra - 64;
+  const int budget = kLayerDynSmem - 1024 - extra - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   a.stages = stages;
@@ -633,7 +637,7 @@ int launch_layer(const DecodeLayerArgs& L, int smem, cudaStream_t stream) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLayerDynSmem);
     if (e != cudaSuccess) return int(e);
     attr_set[dev] = true;
   }
