@@ -168,7 +168,9 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
   }
   if (warp == 1) {
     tmem_alloc(&ctrl->tmem_base, tmem_cols);
-    tmem_relinquish();
+    // a CTA that has given up its allocation permit may never allocate again: a body that runs as one stage of
+    // a longer kernel (and allocates once per stage) keeps the permit
+    if constexpr (!Sync::active) tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
