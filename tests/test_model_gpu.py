@@ -69,9 +69,20 @@ def test_tiny_generate_matches_oracle_tokens(graph, layer_impl):
     outs = eng.generate(prompts.tolist(), 12)
     ref = EagerTransformer(cfg, w, device=dev, dtype=torch.float32)
     expect = ref.generate(prompts.to(dev), 12).tolist()
-    agree = sum(int(a == b) for o, e in zip(outs, expect) for a, b in zip(o, e))
     assert [o[0] for o in outs] == [e[0] for e in expect]
-    assert agree >= 30, (outs, expect)
+    # Greedy decoding follows whichever token wins a near-tie, so after one flipped tie two correct
+    # implementations produce different continuations.  Judge every generated token on its own instead: given the
+    # tokens generated so far it must be (nearly) the oracle's best choice.
+    agree = sum(int(a == b) for o, e in zip(outs, expect) for a, b in zip(o, e))
+    assert agree >= 18, (outs, expect)
+    for b in range(len(outs)):
+        seq = prompts[b].tolist()
+        for tok in outs[b]:
+            ref.reset()
+            h = ref.forward(torch.tensor([seq], device=dev))[:, -1]
+            logits = (h @ ref.w["lm_head_weight"].float()).float()[0]
+            assert logits[tok] >= logits.max() - 0.05 * logits.std(), (b, tok, int(logits.argmax()))
+            seq.append(tok)
 
 
 def test_decode_hidden_matches_oracle(layer_impl):
