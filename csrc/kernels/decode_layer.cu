@@ -86,7 +86,7 @@ struct DecodeLayerArgs {
   SiluArgs silu;
   RopeArgs rope;
   unsigned int* grid_bar;          // [0] arrivals of the current barrier, [1] generation
-  unsigned long long* timing;      // optional [16]: CTA 0 records the global timer after every stage (ns)
+  unsigned long long* timing;      // optional [80]: CTA 0 records the global timer after every stage, [16 + 16 g + p]: phase p of GEMM stage g (ns)
   int* status;
   int mask, tokens, hidden;
   float eps;
@@ -164,6 +164,10 @@ struct GridSync {
   int* status;
   int where;
   bool pending;     // false: nothing to wait for (first stage of a launch)
+  unsigned long long* marks;   // optional [16]: CTA 0 stores the global timer at the phases of the GEMM body
+  __device__ __forceinline__ void mark(int slot) const {
+    if (marks && blockIdx.x == 0) marks[slot] = globaltimer_ns();
+  }
   __device__ __forceinline__ bool wait(volatile int* abort_flag) const {
     if (!pending) return true;
     const bool ok = grid_wait_thread(bar, gen, status, where);
@@ -173,8 +177,11 @@ struct GridSync {
   }
 };
 
+// Inlined into the kernel on purpose: the argument blocks then stay kernel parameters (constant-bank operands).
+// Behind a call they would be read through generic pointers, and the epilogue's store loop -- one warp per
+// scheduler, nothing to hide a load behind -- ran five times slower that way.
 template <int BN, bool PUSH>
-__device__ __noinline__ bool gemm_stage(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
+__device__ __forceinline__ bool gemm_stage(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
                                         const PushArgs& push, const GridSync& sync) {
   return gemm_bf16_body<BN, PUSH, false, NoFix, NoElemEpi, GridSync>(tmA, tmB, args, push, GroupArgs{}, NoFix::Args{},
                                                                      NoElemEpi{}, sync);
@@ -327,11 +334,24 @@ __device__ __forceinline__ void silu_stage(const SiluArgs& s, int tokens) {
     const long long r = i / per_row;
     const int c = int(i % per_row) * 4;
     float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int sp = 0; sp < s.splits; ++sp) {
-      const float4 gv = __ldcg(reinterpret_cast<const float4*>(s.parts + sp * s.stride + r * 2 * s.inter + c));
-      const float4 uv = __ldcg(reinterpret_cast<const float4*>(s.parts + sp * s.stride + r * 2 * s.inter + s.inter + c));
-      g[0] += gv.x; g[1] += gv.y; g[2] += gv.z; g[3] += gv.w;
-      u[0] += uv.x; u[1] += uv.y; u[2] += uv.z; u[3] += uv.w;
+    // four splits per batch: eight independent 16-byte loads in flight instead of a chain of round trips
+    for (int s0 = 0; s0 < s.splits; s0 += 4) {
+      float4 gv[4], uv[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (s0 + q < s.splits) {
+          const float* base = s.parts + (s0 + q) * s.stride + r * 2 * s.inter + c;
+          gv[q] = __ldcg(reinterpret_cast<const float4*>(base));
+          uv[q] = __ldcg(reinterpret_cast<const float4*>(base + s.inter));
+        } else {
+          gv[q] = uv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        g[0] += gv[q].x; g[1] += gv[q].y; g[2] += gv[q].z; g[3] += gv[q].w;
+        u[0] += uv[q].x; u[1] += uv[q].y; u[2] += uv[q].z; u[3] += uv[q].w;
+      }
     }
     float o[4];
 #pragma unroll
@@ -372,19 +392,37 @@ __device__ __forceinline__ void rope_stage(const RopeArgs& a, int tokens) {
     const long long base = (long long)t * width + (long long)h * D;
     float lo[PER], hi[PER];
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const int i = lane * PER + j;
-      float x = 0.f, y = 0.f;
-      for (int s = 0; s < a.splits; ++s) {
-        x += __ldcg(a.partials + s * a.split_stride + base + i);
-        y += __ldcg(a.partials + s * a.split_stride + base + D / 2 + i);
+    for (int j = 0; j < PER; ++j) lo[j] = hi[j] = 0.f;
+    // four splits per batch: all loads of a batch are issued before the first sum needs one
+    for (int s0 = 0; s0 < a.splits; s0 += 4) {
+      float xv[4][PER], yv[4][PER];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          const int i = lane * PER + j;
+          const bool on = s0 + q < a.splits;
+          const float* src = a.partials + (long long)(s0 + q) * a.split_stride + base + i;
+          xv[q][j] = on ? __ldcg(src) : 0.f;
+          yv[q][j] = on ? __ldcg(src + D / 2) : 0.f;
+        }
       }
-      if (a.bias) {
-        x += __bfloat162float(a.bias[h * D + i]);
-        y += __bfloat162float(a.bias[h * D + D / 2 + i]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          lo[j] += xv[q][j];
+          hi[j] += yv[q][j];
+        }
       }
-      lo[j] = x;
-      hi[j] = y;
+    }
+    if (a.bias) {
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = lane * PER + j;
+        lo[j] += __bfloat162float(a.bias[h * D + i]);
+        hi[j] += __bfloat162float(a.bias[h * D + D / 2 + i]);
+      }
     }
     const bool is_q = h < a.nq, is_k = !is_q && h < a.nq + a.nkv;
     const int slot = a.slots ? a.slots[t] : -1;
@@ -449,7 +487,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
     ++ntick;
   };
   tick();
-  GridSync sync{bar, 0u, status, 0, false};
+  GridSync sync{bar, 0u, status, 0, false, nullptr};
+  int ngemm = 0;
+  auto marks = [&]() { sync.marks = L.timing ? L.timing + 16 + 16 * ngemm++ : nullptr; };
   // arrive now, wait later: the next stage (or `settle`) completes the barrier
   auto arrive = [&]() {
     sync.gen = grid_arrive(bar);
@@ -469,6 +509,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   };
 
   if (mask & ST_O) {
+    marks();
     if (!gemm_stage<BN, TP>(L.o.tmA, L.o.tmB, L.o.args, L.push_o, sync)) return;
     if (!TP) arrive();                    // pushed partials are ordered by the ranks' arrival counters instead
     tick();
@@ -481,6 +522,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
     tick();
   }
   if (mask & ST_GU) {
+    marks();
     if (!gemm_stage<BN, false>(L.gu.tmA, L.gu.tmB, L.gu.args, L.push_o, sync)) return;
     sync.pending = false;
     bump_seen();
@@ -494,6 +536,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
     tick();
   }
   if (mask & ST_DOWN) {
+    marks();
     if (!gemm_stage<BN, TP>(L.down.tmA, L.down.tmB, L.down.args, L.push_down, sync)) return;
     sync.pending = false;
     bump_seen();
@@ -509,6 +552,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
     tick();
   }
   if (mask & ST_QKV) {
+    marks();
     if (!gemm_stage<BN, false>(L.qkv.tmA, L.qkv.tmB, L.qkv.args, L.push_o, sync)) return;
     sync.pending = false;
     bump_seen();
@@ -567,7 +611,8 @@ extern "C" struct NkbDecodeLayer {
   // second reduction without the down stage (the block between the two ends ran elsewhere, e.g. MoE experts):
   // with ranks the pushed slabs of buffer "d" (red2_slots of them) are summed, else red2_x [tokens, hidden] bf16
   const void* red2_x; int red2_slots, _pad4;
-  // optional: 16 unsigned 64-bit words; CTA 0 stores the global timer (ns) at kernel start and after every stage
+  // optional: 80 unsigned 64-bit words; CTA 0 stores the global timer (ns) at kernel start and after every stage
+  // ([0..15]) and at eight phases of each GEMM stage ([16 + 16 * stage + phase], ten phases)
   void* timing;
 };
 

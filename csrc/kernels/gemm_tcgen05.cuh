@@ -120,6 +120,7 @@ struct NoElemEpi {
 struct NoSync {
   static constexpr bool active = false;
   __device__ __forceinline__ bool wait(volatile int*) const { return true; }
+  __device__ __forceinline__ void mark(int) const {}     // optional time stamps of the body's phases
 };
 
 // Fix selects a split-K fix-up epilogue (splitk_fix.cuh): the partial tiles go to fix.c.partials (the
@@ -135,6 +136,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) sync.mark(0);
   const int a_tiles = (args.gated == 1) ? 2 : 1;
   const int b_tiles = (args.gated == 2) ? 2 : 1;
   constexpr int kBTileBytes = BN * kBlockK * 2;
@@ -177,6 +179,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
   volatile int* abort_flag = &ctrl->abort;
+  if (threadIdx.x == 0) sync.mark(1);
 
   const int total_work = GROUPED ? grp.num_groups * args.num_row_tiles * grp.max_col_tiles
                                  : args.num_row_tiles * args.num_col_tiles * args.splits;
@@ -229,6 +232,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
       int ok = 1;
       if (lane == 0) ok = sync.wait(abort_flag) ? 1 : 0;
       alive = __shfl_sync(0xffffffffu, ok, 0) != 0;
+      if (lane == 0) sync.mark(2);
     }
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
       const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
@@ -300,6 +304,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
       for (int kb = kb0; kb < kb1; ++kb) {
         ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        if (lane == 0 && kb == kb0 && w == int(blockIdx.x)) sync.mark(3);
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
@@ -323,6 +328,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
       }
       if (!alive) break;
       if (lane == 0) umma_commit(&ctrl->tfull[acc]);
+      if (lane == 0 && w == int(blockIdx.x)) sync.mark(4);
       __syncwarp();
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -354,6 +360,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
         if (!__all_sync(0xffffffffu, ok)) break;
       }
       tc_fence_after();
+      if (threadIdx.x == 64 && w == int(blockIdx.x)) sync.mark(5);
       const uint32_t t0 = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * acc_cols);
       const bool row_ok = row < args.rows;
       float* out_f = reinterpret_cast<float*>(args.out) + (args.out_fp32 ? sp * args.split_stride : 0);
@@ -394,6 +401,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
         } else {
           tmem_ld_wait();
         }
+        if (threadIdx.x == 64 && w == int(blockIdx.x) && c == 0) sync.mark(8);
         if (c + 32 >= BN) {
           // accumulator fully read: hand it back to the MMA warp before the stores
           tc_fence_before();
@@ -512,6 +520,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
         }
       }
+      if (threadIdx.x == 64 && w == int(blockIdx.x)) sync.mark(9);
       if constexpr (Fix::kind != FIX_NONE) {
         // this CTA's partial of the tile is stored: count it, and finish the tile if it was the last one
         __threadfence();
@@ -570,6 +579,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
     }
   }
 
+  if (threadIdx.x == 64) sync.mark(6);
   if (*abort_flag) {
     // let copies / MMAs that were already issued drain before shared memory goes away
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -577,6 +587,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
   tc_fence_before();
   __syncthreads();
   const bool all_ok = *abort_flag == 0;
+  if (threadIdx.x == 0) sync.mark(7);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);

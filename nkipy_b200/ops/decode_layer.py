@@ -105,7 +105,7 @@ def block_n_for(tokens: int) -> int:
     return 32 if tokens <= 32 else (64 if tokens <= 64 else 128)
 
 
-def pick_layer_splits(rows: int, k: int, sms: int = 148, max_splits: int = DecodeLayerScratch.MAX_SPLITS) -> int:
+def pick_layer_splits(rows: int, k: int, sms: int = 148, max_splits: int = 8) -> int:
     """Split-K factor of a GEMM stage that runs on one CTA per SM: the largest factor whose work units
     (row tiles x splits) still fit one wave, as long as every split keeps four 64-wide k-blocks."""
     tiles = (rows + 127) // 128
@@ -132,8 +132,10 @@ def decode_layer(mask: int, tokens: int, hidden: int, eps: float, scratch: Decod
     """One launch of the persistent layer kernel.  Tensors are bf16 unless the kernel's header says otherwise;
     `mask` selects the stages (ST_*).  ST_RED2 without ST_DOWN sums a block output that other
     kernels produced: `red2_x` [tokens, hidden] on one rank, or `red2_slots` pushed slabs of the second buffer with
-    ranks (the residual is `resid_mid`).  timing: int64[16] that receives the device's global
-    timer (ns) at kernel start and after every stage that ran, from CTA 0.  tp_buffers: (o, down) buffer descriptions from
+    ranks (the residual is `resid_mid`).  timing: int64[80] that receives the device's global
+    timer (ns) from CTA 0: [0..15] kernel start and the end of every stage that ran, [16 + 16 g + p] phase p of the
+    g-th GEMM stage (entry, set-up done, barrier passed, first operands in shared memory, last MMA issued, first
+    accumulator ready, epilogue done, exit, first accumulator chunk in registers, stores of the first tile issued).  tp_buffers: (o, down) buffer descriptions from
     `FusedTP.layer_buffers()` when the row-parallel GEMMs push to the ranks of a tensor-parallel group."""
     from . import _count_launch
 
@@ -157,8 +159,8 @@ def decode_layer(mask: int, tokens: int, hidden: int, eps: float, scratch: Decod
     d.norm2_w, d.resid_out, d.normed_out = _ptr(norm2_w), _ptr(resid_out), _ptr(normed_out)
     d.red2_x, d.red2_slots = _ptr(red2_x), red2_slots
     if timing is not None:
-        if timing.dtype != torch.int64 or timing.numel() < 16:
-            raise ValueError("timing must be an int64 tensor of 16 elements")
+        if timing.dtype != torch.int64 or timing.numel() < 80:
+            raise ValueError("timing must be an int64 tensor of 80 elements")
         d.timing = timing.data_ptr()
     if mask & ST_QKV:
         d.w_qkv, d.ld_wqkv, d.splits_qkv = w_qkv.data_ptr(), w_qkv.stride(0), splits_qkv

@@ -355,7 +355,7 @@ def case_decode_layer(args):
         io = dict(attn=_bf16(T, k_o), resid_in=_bf16(T, H), norm1_w=_bf16(H), norm2_w=_bf16(H),
                   resid_mid=_bf16(T, H), normed_mid=_bf16(T, H), act=_bf16(T, inter), resid_out=_bf16(T, H),
                   normed_out=_bf16(T, H), q_out=_bf16(T, nq * D))
-        tm = torch.zeros(16, dtype=torch.int64, device="cuda")
+        tm = torch.zeros(80, dtype=torch.int64, device="cuda")
         timings.append(tm)
 
         def fn(w=w, io=io, tm=tm):
@@ -365,11 +365,18 @@ def case_decode_layer(args):
         fns.append(fn)
     us = _time(fns, args.iters, args.warmup, graph=not args.no_graph)
     torch.cuda.synchronize()
-    n_stage = bin(mask).count("1") + 1
-    ticks = torch.stack(timings).double().cpu()[:, :n_stage + 1]
+    n_stage = bin(mask).count("1")
+    raw = torch.stack(timings).double().cpu()
+    ticks = raw[:, :n_stage + 1]
     stages = (ticks[:, 1:] - ticks[:, :-1]).mean(0) / 1e3
+    # phases of the four GEMM stages relative to each stage's entry
+    phases = []
+    for g in range(4):
+        m = raw[:, 16 + 16 * g:26 + 16 * g]
+        phases.append([round(float(x), 2) for x in ((m - m[:, :1]).mean(0) / 1e3)])
     return dict(case="decode-layer", tp=tp, tokens=T, splits=sp, fused_gate=fused_gate, sets=sets, us=us,
-                bytes=per_set, flops=2.0 * T * per_set / 2, stages_us=[round(float(x), 2) for x in stages])
+                bytes=per_set, flops=2.0 * T * per_set / 2, stages_us=[round(float(x), 2) for x in stages],
+                gemm_phases_us=phases)
 
 
 CASES = {
