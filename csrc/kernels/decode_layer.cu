@@ -159,6 +159,7 @@ __device__ __forceinline__ bool grid_wait(const unsigned int* bar, unsigned int 
 
 struct GridSync {
   static constexpr bool active = true;
+  static constexpr bool lean = true;
   const unsigned int* bar;
   unsigned int gen;
   int* status;
@@ -177,14 +178,15 @@ struct GridSync {
   }
 };
 
-// Inlined into the kernel on purpose: the argument blocks then stay kernel parameters (constant-bank operands).
-// Behind a call they would be read through generic pointers, and the epilogue's store loop -- one warp per
-// scheduler, nothing to hide a load behind -- ran five times slower that way.
+// One copy of the GEMM body per (BN, PUSH) serves every GEMM stage of the kernel, so its instructions stay in
+// the instruction cache from stage to stage and from layer to layer.  The argument block and the barrier state
+// are passed by value (registers); behind a reference they would be re-read from the kernel's parameter
+// space through generic loads after every memory clobber.
 template <int BN, bool PUSH>
-__device__ __forceinline__ bool gemm_stage(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
-                                        const PushArgs& push, const GridSync& sync) {
-  return gemm_bf16_body<BN, PUSH, false, NoFix, NoElemEpi, GridSync>(tmA, tmB, args, push, GroupArgs{}, NoFix::Args{},
-                                                                     NoElemEpi{}, sync);
+__device__ __noinline__ bool gemm_stage(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmArgs args,
+                                        const PushArgs* push, const GridSync sync) {
+  return gemm_bf16_body<BN, PUSH, false, NoFix, NoElemEpi, GridSync>(*tmA, *tmB, args, *push, GroupArgs{},
+                                                                     NoFix::Args{}, NoElemEpi{}, sync);
 }
 
 constexpr int kRedIters = 4;   // 8 elements per thread per iteration: hidden <= 192 * 8 * 4
@@ -211,7 +213,7 @@ __device__ __forceinline__ void add_bf16x8(float (&a)[8], uint4 r) {
 }
 
 // Returns false when the wait for the ranks' partials ran out.
-__device__ __forceinline__ bool reduce_stage(const ReduceArgs& r, int tokens, int hidden, float eps, int* status) {
+__device__ __noinline__ bool reduce_stage(const ReduceArgs r, int tokens, int hidden, float eps, int* status) {
   __shared__ float red[32];
   __shared__ int ok_s;
   if (int(blockIdx.x) >= tokens) return true;
@@ -510,7 +512,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
 
   if (mask & ST_O) {
     marks();
-    if (!gemm_stage<BN, TP>(L.o.tmA, L.o.tmB, L.o.args, L.push_o, sync)) return;
+    if (!gemm_stage<BN, TP>(&L.o.tmA, &L.o.tmB, L.o.args, &L.push_o, sync)) return;
     if (!TP) arrive();                    // pushed partials are ordered by the ranks' arrival counters instead
     tick();
   }
@@ -523,7 +525,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   }
   if (mask & ST_GU) {
     marks();
-    if (!gemm_stage<BN, false>(L.gu.tmA, L.gu.tmB, L.gu.args, L.push_o, sync)) return;
+    if (!gemm_stage<BN, false>(&L.gu.tmA, &L.gu.tmB, L.gu.args, &L.push_o, sync)) return;
     sync.pending = false;
     bump_seen();
     arrive();
@@ -537,7 +539,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   }
   if (mask & ST_DOWN) {
     marks();
-    if (!gemm_stage<BN, TP>(L.down.tmA, L.down.tmB, L.down.args, L.push_down, sync)) return;
+    if (!gemm_stage<BN, TP>(&L.down.tmA, &L.down.tmB, L.down.args, &L.push_down, sync)) return;
     sync.pending = false;
     bump_seen();
     if (!TP) arrive();
@@ -553,7 +555,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) decode_layer_kernel(const __g
   }
   if (mask & ST_QKV) {
     marks();
-    if (!gemm_stage<BN, false>(L.qkv.tmA, L.qkv.tmB, L.qkv.args, L.push_o, sync)) return;
+    if (!gemm_stage<BN, false>(&L.qkv.tmA, &L.qkv.tmB, L.qkv.args, &L.push_o, sync)) return;
     sync.pending = false;
     bump_seen();
     arrive();

@@ -1,6 +1,7 @@
 // Host launchers of the tcgen05 GEMM (device code in gemm_tcgen05.cuh).
 #include "gemm_tcgen05.cuh"
 #include "api.h"
+#include <cstdlib>
 
 namespace nkb {
 
@@ -23,25 +24,32 @@ static int ring_stages(const GemmArgs& args, int& smem) {
   return stages;
 }
 
+// The decode orientation (transposed output, bias per row or none) runs the kernel with the compact epilogue.
+static bool lean_ok(const GemmArgs& a) {
+  static const bool off = getenv("NKIPY_B200_GENERAL_EPILOGUE") != nullptr;
+  return !off && a.transpose_out && (!a.bias || a.bias_on_rows);
+}
+
 template <int BN, int MINB, bool PUSH = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
                        cudaStream_t stream, const PushArgs* push = nullptr) {
   int smem = 0;
   args.stages = ring_stages<BN, MINB, PUSH, false>(args, smem);
   if (args.stages < 2) return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, MINB, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  const bool lean = BN <= 128 && lean_ok(args);
+  auto kernel = lean ? gemm_bf16_lean_kernel<(BN <= 128 ? BN : 128), MINB, PUSH> : gemm_bf16_kernel<BN, MINB, PUSH>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[lean]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          MINB == 2 ? 113 * 1024 : 232448);
     if (e != cudaSuccess) return int(e);
-    attr_set = true;
+    attr_set[lean] = true;
   }
   const int total = args.num_row_tiles * args.num_col_tiles * args.splits;
   const int grid = total < max_ctas ? total : max_ctas;
   PushArgs pa{};
   if (push) pa = *push;
-  return launch_pdl(gemm_bf16_kernel<BN, MINB, PUSH>, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb,
-                    args, pa);
+  return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), size_t(smem), stream, ta, tb, args, pa);
 }
 
 // Split-K with the fix-up epilogue (splitk_fix.cuh), decode orientation, two CTAs per SM.

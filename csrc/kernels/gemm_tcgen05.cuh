@@ -119,8 +119,16 @@ struct NoElemEpi {
 // when the wait gave up.
 struct NoSync {
   static constexpr bool active = false;
+  // lean: compile only the compact epilogue of the decode orientation (transposed output, bias per row; fp32
+  // partials / bf16 (+ residual) / SwiGLU / push).  It reads the accumulator sixteen columns at a time in rolled
+  // loops: an epilogue runs once per tile, so its instructions are always fetched cold, and the fully unrolled
+  // general epilogue (tens of kilobytes of straight-line code) spent microseconds on instruction fetch alone.
+  static constexpr bool lean = false;
   __device__ __forceinline__ bool wait(volatile int*) const { return true; }
   __device__ __forceinline__ void mark(int) const {}     // optional time stamps of the body's phases
+};
+struct LeanSync : NoSync {
+  static constexpr bool lean = true;
 };
 
 // Fix selects a split-K fix-up epilogue (splitk_fix.cuh): the partial tiles go to fix.c.partials (the
@@ -372,9 +380,94 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
         if (GROUPED && args.gated) bias_u = __bfloat162float(bp[args.gate_off]);   // up-projection bias
       }
 
+      constexpr bool kLean = Sync::lean && !GROUPED && Fix::kind == FIX_NONE && !ElemEpi::active;
+      if constexpr (kLean) {
+        // ---- compact epilogue (decode orientation): out[col * ldo + row], sixteen columns per iteration
+        auto release_acc = [&]() {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctrl->tempty[acc]);
+        };
+        if constexpr (PUSH) {
+          const int et = threadIdx.x - 64;  // 0..127 over the four epilogue warps
+          const int row0 = rt * kTileRows;
+          const long long slot = (long long)push.rank * args.splits + sp;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            const bool live = col0 + c0 < cols_end;   // CTA-uniform: the four warps take the barriers together
+            if (live) {
+#pragma unroll 1
+              for (int c = 0; c < 32; c += 16) {
+                uint32_t v[16];
+                tmem_ld_32x16(t0 + c0 + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  stage_out[(c + j) * kTileRows + quad * 32 + lane] = __float2bfloat16(__uint_as_float(v[j]) + bias_r);
+              }
+            }
+            if (c0 + 32 >= BN) release_acc();
+            if (!live) continue;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 1
+            for (int idx = et; idx < 32 * 16; idx += 128) {
+              const int tok = idx >> 4, ch = idx & 15;
+              const int gtok = col0 + c0 + tok, gfeat = row0 + ch * 8;
+              if (gtok < cols_end && gfeat < args.rows) {
+                const uint4 val = *reinterpret_cast<const uint4*>(stage_out + tok * kTileRows + ch * 8);
+                push_store_16(push, (slot * args.cols + gtok) * args.ldo + gfeat, val);
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+        } else if (args.gated) {
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            uint32_t g[16], u[16];
+            tmem_ld_32x16(t0 + c, g);
+            tmem_ld_32x16(t0 + BN + c, u);
+            tmem_ld_wait();
+            if (c + 16 >= BN) release_acc();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int col = col0 + c + j;
+                if (col < cols_end)
+                  out_h[(long long)col * args.ldo + row] =
+                      __float2bfloat16(silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]));
+              }
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            uint32_t v[16];
+            tmem_ld_32x16(t0 + c, v);
+            tmem_ld_wait();
+            if (c + 16 >= BN) release_acc();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int col = col0 + c + j;
+                if (col < cols_end) {
+                  const long long idx = (long long)col * args.ldo + row;
+                  float x = __uint_as_float(v[j]) + bias_r;
+                  if (args.out_fp32) {
+                    out_f[idx] = x;
+                  } else {
+                    if (args.residual) x += __bfloat162float(args.residual[idx]);
+                    out_h[idx] = __float2bfloat16(x);
+                  }
+                }
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
+        if (threadIdx.x == 64 && w == int(blockIdx.x) && c == 32) sync.mark(10);
         tmem_ld_32x32(t0 + c, v);
         if (args.gated) {
           uint32_t u[32];
@@ -401,7 +494,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
         } else {
           tmem_ld_wait();
         }
-        if (threadIdx.x == 64 && w == int(blockIdx.x) && c == 0) sync.mark(8);
+        if (threadIdx.x == 64 && w == int(blockIdx.x)) sync.mark(c == 0 ? 8 : 11);
         if (c + 32 >= BN) {
           // accumulator fully read: hand it back to the MMA warp before the stores
           tc_fence_before();
@@ -520,6 +613,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
           }
         }
       }
+      }  // general epilogue
       if (threadIdx.x == 64 && w == int(blockIdx.x)) sync.mark(9);
       if constexpr (Fix::kind != FIX_NONE) {
         // this CTA's partial of the tile is stored: count it, and finish the tile if it was the last one
@@ -615,6 +709,15 @@ __global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs args, const PushArgs push) {
   gemm_bf16_body<BN, PUSH, false>(tmA, tmB, args, push, GroupArgs{});
+}
+
+// Decode orientation only (transposed output, bias per row): the compact epilogue.
+template <int BN, int MINB, bool PUSH>
+__global__ void __launch_bounds__(kGemmThreads, MINB)
+gemm_bf16_lean_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmArgs args, const PushArgs push) {
+  gemm_bf16_body<BN, PUSH, false, NoFix, NoElemEpi, LeanSync>(tmA, tmB, args, push, GroupArgs{}, NoFix::Args{},
+                                                              NoElemEpi{}, LeanSync{});
 }
 
 template <int BN, int MINB, class Fix>
