@@ -12,6 +12,8 @@ int encode_tmap_bf16_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_
 int encode_tmap_bf16(CUtensorMap* m, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                      const uint32_t* box);
 int* status_word();
+struct GemmArgs;
+void mark_bulk(GemmArgs& a);   // gemm_tcgen05.cu: enables the bulk-copy epilogue when the output is 16-byte aligned
 int num_sms();
 bool pdl_enabled();
 }  // namespace nkb

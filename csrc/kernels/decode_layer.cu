@@ -653,9 +653,10 @@ constexpr int kLayerDynSmem = 232448 - 2048;
 
 // Ring depth for one CTA per SM; returns the dynamic shared memory the stage needs.
 int ring(GemmArgs& a, int block_n, bool push) {
+  if (!push) mark_bulk(a);
   const int a_tiles = a.gated == 1 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + block_n * kBlockK * 2;
-  const int extra = 512 + (push ? 32 * kTileRows * 2 : 0);
+  const int extra = 512 + (push ? 32 * kTileRows * 2 : 2 * 16 * kTileRows * 4);
   const int budget = kLayerDynSmem - 1024 - extra - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;

@@ -12,10 +12,12 @@ namespace nkb {
 // the stream, started early by programmatic dependent launch) fit on one SM: the
 // successor then prefetches its weight tiles while this kernel drains.
 template <int BN, int MINB, bool PUSH, bool GROUPED>
-static int ring_stages(const GemmArgs& args, int& smem) {
+static int ring_stages(const GemmArgs& args, int& smem, bool lean = false) {
   const int a_tiles = args.gated == 1 ? 2 : 1, b_tiles = args.gated == 2 ? 2 : 1;
   const int stage_bytes = a_tiles * kATileBytes + b_tiles * BN * kBlockK * 2;
-  const int extra = 512 + (PUSH ? 32 * kTileRows * 2 : 0);   // control block (+ push staging tile: 32 tokens)
+  // control block + staging: the push tile (32 tokens x 128 features bf16), or the compact epilogue's two
+  // 16-column buffers of fp32
+  const int extra = 512 + (PUSH ? 32 * kTileRows * 2 : (lean ? 2 * 16 * kTileRows * 4 : 0));
   const int budget = (MINB == 2 ? 113 * 1024 : 232448) - 1024 - extra - 64;
   int stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -30,13 +32,24 @@ static bool lean_ok(const GemmArgs& a) {
   return !off && a.transpose_out && (!a.bias || a.bias_on_rows);
 }
 
+// transpose_out = 2 tells the compact epilogue that every token row of the output may go out as one bulk
+// copy: base, leading dimension, split stride and row count all on 16-byte boundaries.
+void mark_bulk(GemmArgs& a) {
+  if (!a.transpose_out) return;
+  const long long esz = (a.out_fp32 && !a.gated) ? 4 : 2;
+  const bool ok = (reinterpret_cast<uintptr_t>(a.out) % 16 == 0) && (a.ldo * esz) % 16 == 0 &&
+                  (a.rows * esz) % 16 == 0 && (a.split_stride * 4) % 16 == 0;
+  a.transpose_out = ok ? 2 : 1;
+}
+
 template <int BN, int MINB, bool PUSH = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, int max_ctas,
                        cudaStream_t stream, const PushArgs* push = nullptr) {
   int smem = 0;
-  args.stages = ring_stages<BN, MINB, PUSH, false>(args, smem);
-  if (args.stages < 2) return -3;
   const bool lean = BN <= 128 && lean_ok(args);
+  if (lean && !PUSH) mark_bulk(args);
+  args.stages = ring_stages<BN, MINB, PUSH, false>(args, smem, lean);
+  if (args.stages < 2) return -3;
   auto kernel = lean ? gemm_bf16_lean_kernel<(BN <= 128 ? BN : 128), MINB, PUSH> : gemm_bf16_kernel<BN, MINB, PUSH>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[lean]) {

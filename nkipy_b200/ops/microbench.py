@@ -372,7 +372,7 @@ def case_decode_layer(args):
     # phases of the four GEMM stages relative to each stage's entry
     phases = []
     for g in range(4):
-        m = raw[:, 16 + 16 * g:28 + 16 * g]
+        m = raw[:, 16 + 16 * g:32 + 16 * g]
         phases.append([round(float(x), 2) for x in ((m - m[:, :1]).mean(0) / 1e3)])
     return dict(case="decode-layer", tp=tp, tokens=T, splits=sp, fused_gate=fused_gate, sets=sets, us=us,
                 bytes=per_set, flops=2.0 * T * per_set / 2, stages_us=[round(float(x), 2) for x in stages],
