@@ -137,6 +137,9 @@ __device__ __forceinline__ bool grid_wait_thread(const unsigned int* bar, unsign
   const unsigned long long t0 = globaltimer_ns();
   unsigned int spins = 0;
   while (ld_acquire_gpu(bar + 1) == gen) {
+    // polite polling: CTAs that arrive early (or have no work in a stage) would otherwise hammer the L2 slice
+    // that holds this word and slow down the stores of the CTAs still working
+    __nanosleep(100);
     if ((++spins & 127u) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -225,6 +228,7 @@ __device__ __noinline__ bool reduce_stage(const ReduceArgs r, int tokens, int hi
       for (int s = 0; s < r.n_src && ok; ++s) {
         unsigned int spins = 0;
         while (int(ld_acquire_system(r.flags + s) - target) < 0) {
+          __nanosleep(100);
           if ((++spins & 127u) == 0) {
             if (*reinterpret_cast<volatile int*>(status) != 0) { ok = 0; break; }
             if (globaltimer_ns() - t0 > kWaitLimitNs) {

@@ -35,7 +35,10 @@ static bool lean_ok(const GemmArgs& a) {
 // transpose_out = 2 tells the compact epilogue that every token row of the output may go out as one bulk
 // copy: base, leading dimension, split stride and row count all on 16-byte boundaries.
 void mark_bulk(GemmArgs& a) {
-  if (!a.transpose_out) return;
+  // measured slower than plain stores for these 16-column chunks (sixteen 512-byte copies per chunk keep the
+  // copy engine busy for 1.7 us): opt-in only
+  static const bool on = getenv("NKIPY_B200_BULK_EPILOGUE") != nullptr;
+  if (!a.transpose_out || !on) return;
   const long long esz = (a.out_fp32 && !a.gated) ? 4 : 2;
   const bool ok = (reinterpret_cast<uintptr_t>(a.out) % 16 == 0) && (a.ldo * esz) % 16 == 0 &&
                   (a.rows * esz) % 16 == 0 && (a.split_stride * 4) % 16 == 0;

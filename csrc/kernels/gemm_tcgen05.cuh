@@ -453,7 +453,6 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
 #pragma unroll
               for (int j = 0; j < 16; ++j) x[j] = __uint_as_float(v[j]) + bias_r;
             }
-            if (threadIdx.x == 64 && w == int(blockIdx.x) && c < 64) sync.mark(8 + it);
             if (c + 16 >= BN) release_acc();
             if (col0 + c >= cols_end) continue;          // CTA-uniform
             if (bulk) {
@@ -498,7 +497,6 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
                 }
               }
             }
-            if (threadIdx.x == 64 && w == int(blockIdx.x) && c < 64) sync.mark(12 + it);
           }
         }
       } else {
