@@ -88,6 +88,12 @@ int nkb_symm_free(void* p);
 int nkb_ipc_get_handle(void* p, void* handle_out64);
 int nkb_ipc_open(const void* handle64, void** out);
 int nkb_ipc_close(void* p);
+int nkb_tp_exchange_reduce_rmsnorm(const float* partials, int splits, long long split_stride, const void* y,
+                                   void* const* peer_slots, void* const* peer_rowflags, void* mc_slots,
+                                   void* mc_rowflags, int n_peers, int rank, const void* local_slots,
+                                   const void* local_rowflags, void* seen, void* done_counter,
+                                   const void* residual_in, const void* w, void* residual_out, void* normed_out,
+                                   int rows, int hidden, float eps, void* stream);
 int nkb_tp_reduce_rmsnorm(const void* partials, int slots, const void* flags, int n_src, void* seen,
                           void* done_counter, const void* residual_in, const void* w, void* residual_out,
                           void* normed_out, int rows, int hidden, float eps, void* stream);

@@ -242,8 +242,10 @@ class FusedTP:
     """Fused row-parallel GEMM + all-reduce + residual + RMSNorm for decode-sized batches.  One rank is allowed
     (the same two kernels, the only "peer" being this GPU): single-GPU tests and profiles use it."""
 
-    FLAG_BYTES = 4096
+    FLAG_BYTES = 16384
     ARGMAX_FLAG_OFFSET = 1024      # byte offset of the argmax arrival counters inside the flag page
+    ROWFLAG_OFFSET = 4096          # per-row arrival counters of the pre-summing exchange: [2 buffers][8 ranks][128 rows]
+    ROWFLAG_ROWS = 128
 
     def __init__(self, tp: TPGroup, max_tokens: int, hidden: int, max_splits: int = 8):
         if tp.world_size > 8:
@@ -257,6 +259,8 @@ class FusedTP:
         self.mem = SymmetricMemory(tp, self.FLAG_BYTES + 2 * self.buf_bytes + self.pair_bytes, multicast=True)
         dev = tp.device
         self.seen = torch.zeros((4,), dtype=torch.int32, device=dev)   # [buffer 0, buffer 1, argmax, spare]
+        # uses of each buffer by the pre-summing exchange (its row counters advance only with those uses)
+        self.seen_rows = torch.zeros((2,), dtype=torch.int32, device=dev)
         self.done = torch.zeros((4,), dtype=torch.int32, device=dev)   # [producer, reduce0, reduce1, spare]
         self._parity = 0
         self.ops_issued = 0
@@ -264,6 +268,11 @@ class FusedTP:
         from .. import ops as _ops
 
         self.impl = _ops.DECODE_GEMM_IMPL
+        # "presum" (default): the GEMM leaves fp32 split-K partials locally and one kernel sums them, exchanges one
+        # bf16 row per rank, sums over ranks and norms; "push": the GEMM epilogue pushes one partial per split
+        import os as _os
+
+        self.exchange = _os.environ.get("NKIPY_B200_TP_EXCHANGE", "presum")
         lib = _lib.lib()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         PP = ctypes.POINTER(P)
@@ -271,6 +280,9 @@ class FusedTP:
         lib.nkb_gemm_bf16_push.argtypes = [P, P, I, I, I, LL, LL, LL, I, P, I, PP, PP, I, I, P, P, P, P]
         lib.nkb_tp_reduce_rmsnorm.restype = I
         lib.nkb_tp_reduce_rmsnorm.argtypes = [P, I, P, I, P, P, P, P, P, P, I, I, ctypes.c_float, P]
+        lib.nkb_tp_exchange_reduce_rmsnorm.restype = I
+        lib.nkb_tp_exchange_reduce_rmsnorm.argtypes = [P, I, LL, P, PP, PP, P, P, I, I, P, P, P, P, P, P, P, P, I, I,
+                                                       ctypes.c_float, P]
         lib.nkb_moe_combine_push.restype = I
         lib.nkb_moe_combine_push.argtypes = [P, P, P, I, I, I, PP, PP, I, I, P, P, P, P]
         lib.nkb_argmax_exchange.restype = I
@@ -284,6 +296,11 @@ class FusedTP:
         mc = self.mem.mc_ptr
         self._mc_out = [P(mc + self.FLAG_BYTES + b * self.buf_bytes) if mc else None for b in range(2)]
         self._mc_flag = [P(mc + (b * n + tp.rank) * 4) if mc else None for b in range(2)]
+        rf = self.ROWFLAG_OFFSET
+        rf_bytes = 8 * self.ROWFLAG_ROWS * 4
+        self._peer_rowflag = [(P * n)(*[p + rf + b * rf_bytes for p in self.mem.ptrs]) for b in range(2)]
+        self._mc_rowflag = [P(mc + rf + b * rf_bytes) if mc else None for b in range(2)]
+        self._rowflag_bytes = rf_bytes
         pair_off = self.FLAG_BYTES + 2 * self.buf_bytes
         self._pair_off = pair_off
         self._peer_pairs = (P * n)(*[p + pair_off for p in self.mem.ptrs])
@@ -365,6 +382,9 @@ class FusedTP:
             _lib.check(rc, "nkb_decode_gemm_push")
             ops._launches += 1
             return self._reduce(b, n, M, resid, next_norm, eps, x.device)
+        if self.exchange == "presum" and M <= self.ROWFLAG_ROWS:
+            return self.exchange_add_rmsnorm(ops.linear(x, w, bias=bias, splits=max(2, int(splits))), resid,
+                                             next_norm, eps)
         eff = lib.nkb_gemm_effective_splits(K, max(1, min(splits, self.max_splits)))
         b = self._parity
         self._parity ^= 1
@@ -376,6 +396,38 @@ class FusedTP:
         _lib.check(rc, "nkb_gemm_bf16_push")
         ops._launches += 1
         return self._reduce(b, n * eff, M, resid, next_norm, eps, x.device)
+
+    def exchange_add_rmsnorm(self, parts: torch.Tensor, resid: Optional[torch.Tensor],
+                             next_norm: Optional[torch.Tensor], eps: float):
+        """parts: this rank's result of a row-parallel GEMM, fp32 split-K partials [S, M, N] (or bf16 [M, N]).
+        One launch sums the partials, sends one bf16 row per rank over NVLink, sums over ranks, adds the residual
+        and applies the RMSNorm.  Returns (new residual bf16, normed)."""
+        from .. import ops
+
+        if parts.dim() == 3:
+            S, M, N = parts.shape
+            p_ptr, y_ptr, stride = parts.data_ptr(), None, M * N
+        else:
+            (M, N), S = parts.shape, 0
+            p_ptr, y_ptr, stride = None, parts.data_ptr(), 0
+        if M > min(self.max_tokens, self.ROWFLAG_ROWS) or N != self.hidden:
+            raise ValueError(f"exchange sized for [{min(self.max_tokens, self.ROWFLAG_ROWS)}, {self.hidden}]")
+        b = self._parity
+        self._parity ^= 1
+        self.ops_issued += 1
+        n, base, dev = self.tp.world_size, self.mem.local_ptr, parts.device
+        resid_out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        normed = torch.empty((M, N), dtype=torch.bfloat16, device=dev) if next_norm is not None else None
+        rc = self._lib.nkb_tp_exchange_reduce_rmsnorm(
+            p_ptr, S, stride, y_ptr, self._peer_out[b], self._peer_rowflag[b], self._mc_out[b], self._mc_rowflag[b], n,
+            self.tp.rank, base + self.FLAG_BYTES + b * self.buf_bytes,
+            base + self.ROWFLAG_OFFSET + b * self._rowflag_bytes, self.seen_rows.data_ptr() + 4 * b,
+            self.done.data_ptr() + 4 * (1 + b), None if resid is None else resid.data_ptr(),
+            None if next_norm is None else next_norm.data_ptr(), resid_out.data_ptr(),
+            None if normed is None else normed.data_ptr(), M, N, float(eps), torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "nkb_tp_exchange_reduce_rmsnorm")
+        ops._launches += 1
+        return resid_out, normed
 
     def _reduce(self, b: int, slots: int, M: int, resid, next_norm, eps: float, device):
         """Consumer of buffer b: wait for all ranks, sum the slots, add the residual, RMSNorm."""

@@ -23,7 +23,10 @@ def _free_port():
 # the latter bound to an NVLink multicast object (multimem stores in the push epilogue)
 MODES = {"ipc": dict(NKIPY_B200_SYMM="ipc", NKIPY_B200_NVLS="0"),
          "vmm": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="0"),
-         "nvls": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1")}
+         "nvls": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1"),
+         # the older exchange: the GEMM epilogue pushes one partial per split (default is the pre-summing kernel)
+         "vmm-push": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="0", NKIPY_B200_TP_EXCHANGE="push"),
+         "nvls-push": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1", NKIPY_B200_TP_EXCHANGE="push")}
 
 
 def _worker(rank, world, port, q, mode="ipc"):
@@ -102,7 +105,7 @@ def _worlds():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("mode", ["ipc", "vmm", "nvls"])
+@pytest.mark.parametrize("mode", ["ipc", "vmm", "nvls", "vmm-push", "nvls-push"])
 @pytest.mark.parametrize("world", _worlds())
 def test_fused_gemm_allreduce_ranks(world, mode):
     ctx = mp.get_context("spawn")
@@ -180,3 +183,42 @@ def test_fused_gemm_allreduce_single_rank():
     assert torch.equal(got, ids + 7)
     assert ops.device_status() == 0
     fused.close()
+
+
+def test_presum_exchange_single_rank_matches_fp32():
+    """The pre-summing exchange on one rank (the only peer is this GPU): split-K partials -> sum -> slot ->
+    sum over ranks -> residual -> RMSNorm, against fp32; mixed with the push protocol on the same buffers."""
+    sys.path.insert(0, ROOT)
+    from nkipy_b200 import ops
+    from nkipy_b200.parallel.comm import TPGroup
+    from nkipy_b200.parallel.symm import FusedTP
+
+    dev = torch.device("cuda:0")
+    tp = TPGroup.single(dev)
+    M, N, K = 64, 1024, 1536
+    fused = FusedTP(tp, M, N)
+    try:
+        g = torch.Generator(device=dev).manual_seed(5)
+        resid = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+        wn = (1 + 0.1 * torch.randn(N, device=dev, generator=g)).to(torch.bfloat16)
+        for i in range(6):
+            x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+            w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+            fused.exchange = "presum" if i % 3 else "push"          # both protocols share the two buffers
+            if i % 2 == 0:
+                fused.begin_step()
+            h, nrm = fused.gemm_allreduce_add_rmsnorm(x, w, resid, wn, None, 1e-5, splits=1 + i)
+            rh = (x.float() @ w.float().T + resid.float()).to(torch.bfloat16).float()
+            rn = rh * torch.rsqrt(rh.pow(2).mean(-1, keepdim=True) + 1e-5) * wn.float()
+            assert ((h.float() - rh).norm() / rh.norm()).item() < 1e-2
+            assert ((nrm.float() - rn).norm() / rn.norm()).item() < 1e-2
+        # a bf16 result (no split-K) goes through the same exchange
+        y = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+        fused.begin_step()
+        h, _ = fused.exchange_add_rmsnorm(y, resid, wn, 1e-5)
+        fused.exchange_add_rmsnorm(y, resid, wn, 1e-5)
+        assert ((h.float() - (y.float() + resid.float())).norm() / h.float().norm()).item() < 1e-2
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+    finally:
+        fused.close()
