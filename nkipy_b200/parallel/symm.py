@@ -273,6 +273,9 @@ class FusedTP:
         import os as _os
 
         self.exchange = _os.environ.get("NKIPY_B200_TP_EXCHANGE", "presum")
+        # the pre-summing kernel pays one more hop of latency (sum, store, flag, wait, sum) and wins when it saves
+        # traffic: from this many split-K partials on; below, the GEMM pushes its partials itself
+        self.presum_min_splits = int(_os.environ.get("NKIPY_B200_PRESUM_MIN_SPLITS", "3"))
         lib = _lib.lib()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         PP = ctypes.POINTER(P)
@@ -382,9 +385,8 @@ class FusedTP:
             _lib.check(rc, "nkb_decode_gemm_push")
             ops._launches += 1
             return self._reduce(b, n, M, resid, next_norm, eps, x.device)
-        if self.exchange == "presum" and M <= self.ROWFLAG_ROWS:
-            return self.exchange_add_rmsnorm(ops.linear(x, w, bias=bias, splits=max(2, int(splits))), resid,
-                                             next_norm, eps)
+        if self.exchange == "presum" and M <= self.ROWFLAG_ROWS and int(splits) >= self.presum_min_splits:
+            return self.exchange_add_rmsnorm(ops.linear(x, w, bias=bias, splits=int(splits)), resid, next_norm, eps)
         eff = lib.nkb_gemm_effective_splits(K, max(1, min(splits, self.max_splits)))
         b = self._parity
         self._parity ^= 1
