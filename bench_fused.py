@@ -213,7 +213,7 @@ def bench_moe_a2a(tp, m, args, pk, flush, g):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ms", type=str, default="16,64,256,1024,4096,16384")
+    ap.add_argument("--ms", type=str, default="16,32,64,128,256,512,1024,2048,4096,8192,16384")
     ap.add_argument("--ops", type=str, default="ar,rs,ag,moe")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
