@@ -176,7 +176,7 @@ __global__ void tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ parti
 // push.peer_out[p]: slot array [n][rows][hidden] of rank p; push.peer_flag[p]: row counters [n][kRowFlags] of
 // rank p; push.mc_out / push.mc_flag: the same arrays through the multicast mapping, or nullptr.
 constexpr int kRowFlags = 128;
-__global__ void tp_exchange_reduce_rmsnorm_kernel(const float* __restrict__ partials, int splits,
+__global__ void __launch_bounds__(512) tp_exchange_reduce_rmsnorm_kernel(const float* __restrict__ partials, int splits,
                                                   long long split_stride, const __nv_bfloat16* __restrict__ y,
                                                   const PushArgs push, const __nv_bfloat16* __restrict__ slots,
                                                   const unsigned int* __restrict__ rowflags,
@@ -506,9 +506,9 @@ extern "C" int nkb_tp_exchange_reduce_rmsnorm(const float* partials, int splits,
   if ((hidden & 7) || rows > kRowFlags || n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return -2;
   if ((!partials && !y) || (partials && splits < 1) || (w && !normed_out)) return -2;
   const int nvec = hidden >> 3;
-  if (nvec > 1024 * kTpMaxIters) return -2;
-  int threads = nvec <= 1024 ? (nvec + 31) / 32 * 32 : ((nvec + kTpMaxIters - 1) / kTpMaxIters + 31) / 32 * 32;
-  if (threads > 1024) threads = 1024;
+  if (nvec > 512 * kTpMaxIters) return -2;
+  int threads = nvec <= 512 ? (nvec + 31) / 32 * 32 : ((nvec + kTpMaxIters - 1) / kTpMaxIters + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
   if (!status_word() && nkb_init() != 0) return -1;
   PushArgs pa{};
   pa.n_peers = n_peers;
