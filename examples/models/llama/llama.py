@@ -1,5 +1,5 @@
 """A Llama-style decoder run through the tracing frontend: the layer, the embedding and the sampler are NumPy
-kernel functions (`kernels/`), compiled once with `DeviceKernel.compile_and_load` and called layer by layer
+kernel functions (`llama_kernels/`), compiled once with `DeviceKernel.compile_and_load` and called layer by layer
 with device tensors -- the same way the reference drives its models
 (examples/models/qwen3/qwen3.py:139-260 there).  Without a GPU the same functions run on NumPy arrays.
 
@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(_HERE, "..", "..", ".."))
 sys.path.insert(0, _HERE)
 
-from kernels import decode_layer, greedy_token, prefill_layer  # noqa: E402
+from llama_kernels import decode_layer, greedy_token, prefill_layer  # noqa: E402
 
 
 def embed(ids, table):

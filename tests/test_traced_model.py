@@ -1,5 +1,5 @@
 """The flagship decoder through the framework's own front door: layer, embedding and sampler as NumPy kernel
-functions (examples/models/llama/kernels), called directly (CPU), traced and interpreted (CPU), and compiled +
+functions (examples/models/llama/llama_kernels), called directly (CPU), traced and interpreted (CPU), and compiled +
 run by the device runtime (GPU) -- each against the eager fp32 oracle."""
 import os
 import sys
@@ -12,7 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "examples", "models", "llama"))
 
 from llama import TracedLlama, embed  # noqa: E402
-from kernels import decode_layer, greedy_token, prefill_layer  # noqa: E402
+from llama_kernels import decode_layer, greedy_token, prefill_layer  # noqa: E402
 
 from nkipy_b200.core.compile import trace  # noqa: E402
 from nkipy_b200.core.interp import evaluate  # noqa: E402
