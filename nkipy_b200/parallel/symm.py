@@ -276,6 +276,9 @@ class FusedTP:
         # the pre-summing kernel pays one more hop of latency (sum, store, flag, wait, sum) and wins when it saves
         # traffic: from this many split-K partials on; below, the GEMM pushes its partials itself
         self.presum_min_splits = int(_os.environ.get("NKIPY_B200_PRESUM_MIN_SPLITS", "3"))
+        # ... and from this many ranks on (measured: 2 ranks 15.3K tok/s with the push against 15.1K, Qwen3 12.3K
+        # against 11.5K; 4 ranks 20.3K against 18.0K; 8 ranks 20.9K against 19.8K)
+        self.presum_min_world = int(_os.environ.get("NKIPY_B200_PRESUM_MIN_WORLD", "4"))
         lib = _lib.lib()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         PP = ctypes.POINTER(P)
@@ -385,7 +388,8 @@ class FusedTP:
             _lib.check(rc, "nkb_decode_gemm_push")
             ops._launches += 1
             return self._reduce(b, n, M, resid, next_norm, eps, x.device)
-        if self.exchange == "presum" and M <= self.ROWFLAG_ROWS and int(splits) >= self.presum_min_splits:
+        if (self.exchange == "presum" and M <= self.ROWFLAG_ROWS and int(splits) >= self.presum_min_splits
+                and self.tp.world_size >= self.presum_min_world):
             return self.exchange_add_rmsnorm(ops.linear(x, w, bias=bias, splits=int(splits)), resid, next_norm, eps)
         eff = lib.nkb_gemm_effective_splits(K, max(1, min(splits, self.max_splits)))
         b = self._parity

@@ -21,9 +21,9 @@ def _free_port():
 
 # how the symmetric buffers are made: CUDA IPC, virtual memory management with file-descriptor handles, and
 # the latter bound to an NVLink multicast object (multimem stores in the push epilogue)
-MODES = {"ipc": dict(NKIPY_B200_SYMM="ipc", NKIPY_B200_NVLS="0", NKIPY_B200_PRESUM_MIN_SPLITS="2"),
-         "vmm": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="0", NKIPY_B200_PRESUM_MIN_SPLITS="2"),
-         "nvls": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1", NKIPY_B200_PRESUM_MIN_SPLITS="2"),
+MODES = {"ipc": dict(NKIPY_B200_SYMM="ipc", NKIPY_B200_NVLS="0", NKIPY_B200_PRESUM_MIN_SPLITS="2", NKIPY_B200_PRESUM_MIN_WORLD="1"),
+         "vmm": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="0", NKIPY_B200_PRESUM_MIN_SPLITS="2", NKIPY_B200_PRESUM_MIN_WORLD="1"),
+         "nvls": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1", NKIPY_B200_PRESUM_MIN_SPLITS="2", NKIPY_B200_PRESUM_MIN_WORLD="1"),
          # the older exchange: the GEMM epilogue pushes one partial per split (default is the pre-summing kernel)
          "vmm-push": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="0", NKIPY_B200_TP_EXCHANGE="push"),
          "nvls-push": dict(NKIPY_B200_SYMM="vmm", NKIPY_B200_NVLS="1", NKIPY_B200_TP_EXCHANGE="push")}
@@ -206,7 +206,7 @@ def test_presum_exchange_single_rank_matches_fp32(N):
             x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
             w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
             fused.exchange = "presum" if i % 3 else "push"          # both protocols share the two buffers
-            fused.presum_min_splits = 2
+            fused.presum_min_splits, fused.presum_min_world = 2, 1
             if i % 2 == 0:
                 fused.begin_step()
             h, nrm = fused.gemm_allreduce_add_rmsnorm(x, w, resid, wn, None, 1e-5, splits=1 + i)
