@@ -107,10 +107,14 @@ class TracedLlama:
     def _run_layers_device(self, which: str, x, start_pos=None):
         """x: DeviceTensor [B, T, H]; runs every layer in place of the residual stream, returns the last output."""
         kern = self.kernels[which]
+        # an argument that the kernel writes through appears among the compiled inputs as
+        # "<name>.must_alias_input" (the reference's naming): address every input by the name the kernel expects
+        expected = {n.replace(".must_alias_input", ""): n for n in kern.input_info}
         for lw in self.dev_layers:
-            inputs = {"x": x, **{k: lw[k] for k in lw}}
+            by_arg = {"x": x, **{k: lw[k] for k in lw}}
             if start_pos is not None:
-                inputs["start_pos"] = start_pos
+                by_arg["start_pos"] = start_pos
+            inputs = {expected[k]: v for k, v in by_arg.items()}
             out = self._DeviceTensor.empty(x.shape, x.dtype, "output0")
             # the caches are written through: the same device tensors are passed as outputs
             kern(inputs=inputs, outputs={"output0": out, "cache_k": lw["cache_k"], "cache_v": lw["cache_v"]})
