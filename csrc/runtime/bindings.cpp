@@ -72,6 +72,10 @@ PYBIND11_MODULE(_spike, m) {
       .def_property_readonly("world_size", &LoadedModule::world_size)
       .def_property_readonly("is_collective", &LoadedModule::is_collective)
       .def_property_readonly("num_launches", &LoadedModule::num_launches)
+      .def_property_readonly("has_collectives", &LoadedModule::has_collectives)
+      .def_property_readonly("collective_world", &LoadedModule::collective_world)
+      .def_property_readonly("workspace_bytes", &LoadedModule::workspace_bytes)
+      .def("set_collective_workspace", &LoadedModule::set_collective_workspace, py::arg("peer_ws"))
       .def_property_readonly("unloaded", &LoadedModule::unloaded);
 
   py::class_<SymmetricBuffer>(m, "SymmetricBuffer")

@@ -132,6 +132,8 @@ LoadedModule::LoadedModule(const CudaRuntime& rt, const std::string& path, int c
       } else if (ja.has("gemm_args")) {
         arg.kind = Arg::GemmArgs;
         arg.gemm = ja.at("gemm_args");
+      } else if (ja.has("cc")) {
+        arg.kind = Arg::CcTable;
       } else {
         throw SpikeError("unknown launch argument kind in plan of " + path);
       }
@@ -139,6 +141,58 @@ LoadedModule::LoadedModule(const CudaRuntime& rt, const std::string& path, int c
     }
     launches_.push_back(std::move(rec));
   }
+  if (plan.has("collective")) {
+    const Json& c = plan.at("collective");
+    cc_world_ = static_cast<int>(c.at("world").as_int());
+    cc_half_bytes_ = static_cast<size_t>(c.at("half_bytes").as_int());
+    cc_workspace_bytes_ = static_cast<size_t>(c.at("workspace_bytes").as_int());
+    if (cc_world_ > 1 && (!cc_enabled || world_size != cc_world_))
+      throw SpikeError("'" + path + "' contains collectives over " + std::to_string(cc_world_) +
+                       " ranks: load it with cc_enabled and world_size " + std::to_string(cc_world_));
+    if (cc_world_ == 1) {
+      // traced for a single rank: the only peer is this process
+      check(d.cuMemAlloc_v2(&cc_private_ws_, cc_workspace_bytes_), "cuMemAlloc(collective workspace)");
+      check(d.cuMemsetD8_v2(cc_private_ws_, 0, cc_workspace_bytes_), "cuMemsetD8(collective workspace)");
+      set_collective_workspace({static_cast<unsigned long long>(cc_private_ws_)});
+    }
+  }
+}
+
+namespace {
+// Must match `CcTable` in the prelude of the generated source (nkipy_b200/compiler/codegen.py).
+struct CcTableHost {
+  unsigned long long peer_ws[8];
+  unsigned long long local_ws;
+  unsigned long long seen;
+  unsigned long long done;
+  unsigned long long status;
+  long long half_bytes;
+  int rank, world;
+};
+}  // namespace
+
+void LoadedModule::set_collective_workspace(const std::vector<unsigned long long>& peer_ws) {
+  if (!module_) throw SpikeError("model '" + name_ + "' was unloaded");
+  if (cc_world_ <= 0) throw SpikeError("'" + name_ + "' has no collectives");
+  if (static_cast<int>(peer_ws.size()) != cc_world_)
+    throw SpikeError("collective workspace table needs " + std::to_string(cc_world_) + " entries");
+  if (cc_table_) throw SpikeError("collective workspace of '" + name_ + "' is already set");
+  const int rank = cc_world_ == 1 ? 0 : rank_id_;
+  rt_.make_current();
+  const Driver& d = driver();
+  check(d.cuMemAlloc_v2(&cc_counters_, 64), "cuMemAlloc(collective counters)");
+  check(d.cuMemsetD8_v2(cc_counters_, 0, 64), "cuMemsetD8(collective counters)");
+  CcTableHost t{};
+  for (int i = 0; i < cc_world_; ++i) t.peer_ws[i] = peer_ws[i];
+  t.local_ws = peer_ws[rank];
+  t.seen = static_cast<unsigned long long>(cc_counters_);
+  t.done = static_cast<unsigned long long>(cc_counters_) + 16;
+  t.status = reinterpret_cast<unsigned long long>(rt_.status_word());
+  t.half_bytes = static_cast<long long>(cc_half_bytes_);
+  t.rank = rank;
+  t.world = cc_world_;
+  check(d.cuMemAlloc_v2(&cc_table_, sizeof(t)), "cuMemAlloc(collective table)");
+  check(d.cuMemcpyHtoD_v2(cc_table_, &t, sizeof(t)), "cuMemcpyHtoD(collective table)");
 }
 
 void LoadedModule::unload() {
@@ -148,9 +202,13 @@ void LoadedModule::unload() {
     rt_.make_current();
     for (auto& b : bufs_)
       if (b.owned) d.cuMemFree_v2(b.owned);
+    if (cc_table_) d.cuMemFree_v2(cc_table_);
+    if (cc_counters_) d.cuMemFree_v2(cc_counters_);
+    if (cc_private_ws_) d.cuMemFree_v2(cc_private_ws_);
     d.cuModuleUnload(module_);
   }
   for (auto& b : bufs_) b.owned = 0;
+  cc_table_ = cc_counters_ = cc_private_ws_ = 0;
   module_ = nullptr;
 }
 
@@ -165,6 +223,9 @@ void LoadedModule::execute(const TensorSet& inputs, const TensorSet& outputs, co
                            bool save_trace) {
   if (!module_) throw SpikeError("model '" + name_ + "' was unloaded");
   if (runtime_closed_->load()) throw SpikeError("runtime is closed");
+  if (cc_world_ > 0 && !cc_table_)
+    throw SpikeError("'" + name_ + "' contains collectives: call set_collective_workspace with the ranks' symmetric "
+                     "workspaces before the first execute");
   rt_.make_current();
   const Driver& d = driver();
   CUstream stream = rt_.stream();
@@ -261,6 +322,12 @@ void LoadedModule::execute(const TensorSet& inputs, const TensorSet& outputs, co
                                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
                 "cuTensorMapEncodeTiled");
+          break;
+        }
+        case Arg::CcTable: {
+          CUdeviceptr p = cc_table_;
+          storage.emplace_back(sizeof(p));
+          std::memcpy(storage.back().data(), &p, sizeof(p));
           break;
         }
         case Arg::GemmArgs: {

@@ -58,6 +58,14 @@ class LoadedModule {
   bool is_collective() const { return cc_enabled_; }
   size_t num_launches() const { return launches_.size(); }
 
+  // Collectives inside the module (plan section "collective"): the symmetric workspace of every rank of the
+  // group, in rank order (peer_ws[rank] is this process's own mapping), each `workspace_bytes()` long and zeroed.
+  // Modules traced for one rank get a private workspace automatically.  Called once, before the first execute.
+  void set_collective_workspace(const std::vector<unsigned long long>& peer_ws);
+  bool has_collectives() const { return cc_world_ > 0; }
+  int collective_world() const { return cc_world_; }
+  size_t workspace_bytes() const { return cc_workspace_bytes_; }
+
  private:
   struct Buf {
     size_t nbytes = 0;
@@ -66,7 +74,7 @@ class LoadedModule {
     CUdeviceptr owned = 0;     // temp / const storage owned by the module
   };
   struct Arg {
-    enum Kind { Buffer, I32, I64, F32, TensorMap, GemmArgs } kind = Buffer;
+    enum Kind { Buffer, I32, I64, F32, TensorMap, GemmArgs, CcTable } kind = Buffer;
     int buffer = -1;
     long long offset = 0;
     long long ival = 0;
@@ -93,6 +101,10 @@ class LoadedModule {
   ModelTensorInfo info_;
   std::map<std::string, int> input_buf_, output_buf_;
   std::shared_ptr<std::atomic<bool>> runtime_closed_;
+  // collectives: device copy of the table the generated kernels read, its counters, a private workspace
+  int cc_world_ = 0;
+  size_t cc_workspace_bytes_ = 0, cc_half_bytes_ = 0;
+  CUdeviceptr cc_table_ = 0, cc_counters_ = 0, cc_private_ws_ = 0;
 };
 
 }  // namespace spike

@@ -126,6 +126,9 @@ class Program:
     inputs: List[Dict[str, Any]]
     outputs: List[Dict[str, Any]]
     name: str = "kernel"
+    # set when the module contains collectives: {"world": ranks, "half_bytes": bytes of one data half of the
+    # symmetric workspace, "workspace_bytes": flags + two halves}
+    collective: Optional[Dict[str, int]] = None
 
     def plan_json(self) -> str:
         def buf(b: BufferInfo):
@@ -145,6 +148,7 @@ class Program:
             "launches": [{"kernel": l.kernel, "grid": list(l.grid), "block": list(l.block), "smem": l.smem,
                           "args": l.args, "loc": l.loc} for l in self.launches],
             "inputs": self.inputs, "outputs": self.outputs,
+            **({"collective": self.collective} if self.collective else {}),
         }, indent=1)
 
 
@@ -184,6 +188,92 @@ template <typename T> __device__ __forceinline__ T pow_i(T a, T b) { return T(po
 __device__ __forceinline__ float pow_i(float a, float b) { return powf(a, b); }
 __device__ __forceinline__ float warp_reduce_sum(float v) { for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(~0u, v, o); return v; }
 }  // namespace
+
+// ---- collectives inside a module ------------------------------------------------------------------------
+// Every rank of the group loads the same module; the runtime hands each collective kernel this table: the
+// module's symmetric workspace on every rank (flags, then two data halves of `half_bytes`), this rank's
+// index, and two device counters.  Protocol of collective number u (u = *seen, the same on all ranks):
+//   cc_push    copies the operand into slot [rank] of half (u & 1) of every rank's workspace; the last CTA
+//              publishes with a system-scope fence and adds 1 to flags[rank] on every rank;
+//   cc_consume waits (bounded, one second) until flags[s] >= u + 1 for every rank s, builds the result from
+//              the n slots, and its last CTA advances *seen.
+// Counters only grow and the halves alternate, so a rank that runs ahead cannot overwrite a slot a peer
+// still reads (it needs that peer's operand of the next collective first).
+struct CcTable {
+  unsigned long long peer_ws[8];     // base of every rank's workspace
+  unsigned long long local_ws;
+  unsigned int* seen;                // collectives completed by this module
+  unsigned int* done;                // [2] CTA counters of the two kernels
+  int* status;                       // bounded-wait status word (0 = fine)
+  long long half_bytes;
+  int rank, world;
+};
+static constexpr long long kCcFlagBytes = 256;
+__device__ __forceinline__ unsigned int cc_ld_acquire(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long cc_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+template <typename T>
+__device__ __forceinline__ void cc_push(const T* __restrict__ in, long long n, const CcTable& t) {
+  const unsigned int use = *reinterpret_cast<volatile unsigned int*>(t.seen);
+  const long long slot = kCcFlagBytes + (long long)(use & 1u) * t.half_bytes + (long long)t.rank * n * (long long)sizeof(T);
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {
+    const T v = in[e];
+    for (int p = 0; p < t.world; ++p) reinterpret_cast<T*>(t.peer_ws[p] + slot)[e] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(t.done, 1u);
+    if (old == gridDim.x - 1) {
+      *t.done = 0u;
+      __threadfence_system();
+      for (int p = 0; p < t.world; ++p)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(t.peer_ws[p] + 4ull * t.rank), "r"(1u) : "memory");
+    }
+  }
+}
+// Returns false when a rank's operand did not arrive in time (the status word then says which).
+__device__ __forceinline__ bool cc_wait(const CcTable& t, unsigned int use) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const unsigned int* flags = reinterpret_cast<const unsigned int*>(t.local_ws);
+    const unsigned long long t0 = cc_timer();
+    for (int s = 0; s < t.world && ok; ++s) {
+      unsigned int spins = 0;
+      while (int(cc_ld_acquire(flags + s) - (use + 1u)) < 0) {
+        __nanosleep(64);
+        if ((++spins & 255u) == 0 && cc_timer() - t0 > 1000000000ull) {
+          atomicCAS(t.status, 0, 5 | (s << 8) | (9 << 16));
+          ok = 0;
+          break;
+        }
+      }
+    }
+    ok_s = ok;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+__device__ __forceinline__ void cc_finish(const CcTable& t, unsigned int use, bool ok) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(t.done + 1, 1u);
+    if (old == gridDim.x - 1) {
+      t.done[1] = 0u;
+      if (ok) *t.seen = use + 1u;
+      __threadfence();
+    }
+  }
+}
 """
 
 
@@ -289,7 +379,11 @@ class Generator:
         src = _PRELUDE + "\n".join(self.kernels)
         if self.uses_tcgen05:
             src = "#define NKB_USE_TCGEN05 1\n" + src
-        return Program(src, self.buffers, self.launches, inputs, outputs, g.name)
+        prog = Program(src, self.buffers, self.launches, inputs, outputs, g.name)
+        if getattr(self, "cc_half_bytes", 0):
+            half = (self.cc_half_bytes + 255) // 256 * 256
+            prog.collective = {"world": self.cc_world, "half_bytes": half, "workspace_bytes": 256 + 2 * half}
+        return prog
 
     def _epilogue_chain(self, idx: int):
         """Elementwise nodes the fusion pass marked as the epilogue of the dot at position idx
@@ -1039,8 +1133,83 @@ class Generator:
             self._simple("conv", n, params, lines, o.size)
 
     def _collective(self, n):
-        raise CodegenError(f"collective '{n.opcode}' cannot be part of one generated module: compile the kernel with "
-                           "nkipy_b200.runtime.segmented.SegmentedKernel, which cuts the graph at its collectives")
+        """A collective as two kernels of the module itself: every rank stores its operand into slot [rank] of
+        all ranks' symmetric workspace (`cc_push`), then builds the result from the slots (`cc_consume`):
+        a reduction over the slots (all_reduce, reduce_scatter) or a re-indexing of them (all_gather,
+        all_to_all).  The runtime supplies the workspace and the peer table when the module is loaded with
+        collectives enabled (reference: spike/src/model.cpp:38-46 loads collectives with the program)."""
+        x, o = n.inputs[0], n.outputs[0]
+        at = n.attrs
+        groups = at.get("replica_groups") or [[0]]
+        world = len(groups[0])
+        if any(len(g) != world for g in groups):
+            raise CodegenError("replica groups of different sizes")
+        if world > 8:
+            raise CodegenError("collectives inside a module support up to 8 ranks (one NVSwitch domain)")
+        xv = self.materialize(x)
+        ov = self._out(o)
+        ct = ctype(x.dtype)
+        acc = compute_type(x.dtype)
+        nelem = max(x.size, 1)
+        self.cc_world = max(getattr(self, "cc_world", 1), world)
+        self.cc_half_bytes = max(getattr(self, "cc_half_bytes", 0), world * nelem * x.dtype.itemsize)
+        loc = f"{n.loc[0]}:{n.loc[1]}" if n.loc else None
+        push = self.kname("cc_push")
+        self.kernels.append(f'extern "C" __global__ void {push}(const {ct}* __restrict__ in, const CcTable* __restrict__ t) '
+                            f'{{\n  cc_push<{ct}>(in, {nelem}LL, *t);\n}}\n')
+        grid = min(max((nelem + 255) // 256, 1), 296)
+        self.launches.append(Launch(push, (grid, 1, 1), (256, 1, 1), 0,
+                                    [{"buffer": xv.buffer, "offset": xv.offset * x.dtype.itemsize}, {"cc": "table"}], loc))
+        # consumer: output element e -> source slot(s) and element
+        shape_in, shape_out = list(x.shape), list(o.shape)
+        strides_in = _contig_strides(shape_in)
+        red = {"add": "a + b", "multiply": "a * b", "maximum": "(a > b ? a : b)", "minimum": "(a < b ? a : b)"}
+        lines = [f"  const unsigned int use = *reinterpret_cast<volatile unsigned int*>(t->seen);",
+                 f"  const bool ok = cc_wait(*t, use);",
+                 f"  const {ct}* slots = reinterpret_cast<const {ct}*>(t->local_ws + kCcFlagBytes + "
+                 f"(long long)(use & 1u) * t->half_bytes);",
+                 f"  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; ok && e < {max(o.size, 1)}LL; "
+                 f"e += (long long)gridDim.x * blockDim.x) {{"]
+        op = n.opcode
+        if op == "all_reduce":
+            lines += [f"    {acc} a = ld<{acc}>(slots, e);",
+                      f"    for (int s = 1; s < {world}; ++s) {{ const {acc} b = ld<{acc}>(slots, (long long)s * {nelem}LL + e); "
+                      f"a = {red[at.get('op', 'add')]}; }}",
+                      f"    st(out, e, a);"]
+        else:
+            # coordinates of the output element
+            lines.append("    long long r = e, src = 0; int slot = 0;")
+            dims = {"all_gather": (at.get("dim"), None), "reduce_scatter": (at.get("dim"), None),
+                    "all_to_all": (at.get("concat_dim"), at.get("split_dim"))}[op]
+            for d in range(len(shape_out) - 1, -1, -1):
+                lines.append(f"    {{ long long c = r % {shape_out[d]}; r /= {shape_out[d]};")
+                if op == "all_gather" and d == dims[0]:
+                    lines.append(f"      slot = int(c / {shape_in[d]}); c = c % {shape_in[d]};")
+                elif op == "reduce_scatter" and d == dims[0]:
+                    lines.append(f"      c += (long long)t->rank * {shape_out[d]};")
+                elif op == "all_to_all" and d == dims[0] and d == dims[1]:
+                    # split and concatenation on the same axis: block j of the result is block `rank` of rank j
+                    lines.append(f"      slot = int(c / {shape_out[d] // world}); "
+                                 f"c = c % {shape_out[d] // world} + (long long)t->rank * {shape_in[d] // world};")
+                elif op == "all_to_all" and d == dims[0]:
+                    lines.append(f"      slot = int(c / {shape_in[d]}); c = c % {shape_in[d]};")
+                elif op == "all_to_all" and d == dims[1]:
+                    lines.append(f"      c += (long long)t->rank * {shape_out[d]};")
+                lines.append(f"      src += c * {strides_in[d]}LL; }}")
+            if op == "reduce_scatter":
+                lines += [f"    {acc} a = ld<{acc}>(slots, src);",
+                          f"    for (int s = 1; s < {world}; ++s) {{ const {acc} b = ld<{acc}>(slots, (long long)s * {nelem}LL + src); "
+                          f"a = {red[at.get('op', 'add')]}; }}",
+                          f"    st(out, e, a);"]
+            else:
+                lines.append(f"    out[e] = slots[(long long)slot * {nelem}LL + src];")
+        lines += ["  }", "  cc_finish(*t, use, ok);"]
+        cons = self.kname("cc_" + op)
+        self.kernels.append(f'extern "C" __global__ void {cons}({ct}* __restrict__ out, const CcTable* __restrict__ t) {{\n'
+                            + "\n".join(lines) + "\n}\n")
+        grid = min(max((max(o.size, 1) + 255) // 256, 1), 296)
+        self.launches.append(Launch(cons, (grid, 1, 1), (256, 1, 1), 0,
+                                    [{"buffer": ov.buffer, "offset": 0}, {"cc": "table"}], loc))
 
     lower_all_gather = lower_all_reduce = lower_reduce_scatter = lower_all_to_all = _collective
 

@@ -72,7 +72,24 @@ class SpikeModel:
         if not os.path.exists(neff_path):
             raise FileNotFoundError(neff_path)
         ref = get_spike_singleton().load_model(str(neff_path), core_id, cc_enabled, rank_id, world_size)
-        return cls(ref, name or ref.name, str(neff_path))
+        model = cls(ref, name or ref.name, str(neff_path))
+        if ref.has_collectives and ref.collective_world > 1:
+            model._attach_collective_workspace(rank_id, world_size)
+        return model
+
+    def _attach_collective_workspace(self, rank_id: int, world_size: int) -> None:
+        """Collectives inside the module run over a symmetric workspace: one allocation per rank mapped into every
+        rank.  It is made here, at load time, over the process group of the job (every rank loads the same module
+        at the same point of the program), and its addresses go to the C++ module as the peer table."""
+        from ..parallel.comm import TPGroup
+        from ..parallel.symm import SymmetricMemory
+
+        tp = TPGroup.from_env()
+        if tp.world_size != world_size or tp.rank != rank_id:
+            raise RuntimeError(f"module with collectives over {world_size} ranks loaded as rank {rank_id}, but the "
+                               f"process group says rank {tp.rank} of {tp.world_size}")
+        self._cc_mem = SymmetricMemory(tp, int(self.model_ref.workspace_bytes))
+        self.model_ref.set_collective_workspace([int(p) for p in self._cc_mem.ptrs])
 
     load_from_cubin = load_from_neff
 
@@ -142,4 +159,9 @@ class SpikeModel:
         raise ValueError("mode must be 'device' or 'host'")
 
     def unload(self) -> None:
+        """Collective for modules with collectives (the symmetric workspace is released by all ranks together)."""
         get_spike_singleton().unload_model(self.model_ref)
+        mem = getattr(self, "_cc_mem", None)
+        if mem is not None:
+            self._cc_mem = None
+            mem.close()
