@@ -7,6 +7,8 @@ runtime maps onto the caller's device tensors (the reference's kernels do the sa
 examples/models/qwen3/kernels/attention.py:100-106)."""
 import numpy as np
 
+from nkipy_b200.core import tensor_apis
+
 from .rmsnorm import rmsnorm
 from .rope import rope_tables, rotate_halves
 
@@ -27,8 +29,6 @@ def attention_block(x, qkv_weight, o_weight, cache_k, cache_v, start_pos, *, n_h
     if start_pos is None:
         cos_t, sin_t = cos[:T][None, :, None, :], sin[:T][None, :, None, :]
     else:
-        from nkipy_b200.core import tensor_apis
-
         cos_t = tensor_apis.constant(cos)[start_pos][None, :, None, :]        # [1, 1, 1, D / 2]
         sin_t = tensor_apis.constant(sin)[start_pos][None, :, None, :]
     q, k = rotate_halves(q, cos_t, sin_t), rotate_halves(k, cos_t, sin_t)
@@ -50,12 +50,8 @@ def attention_block(x, qkv_weight, o_weight, cache_k, cache_v, start_pos, *, n_h
         visible = key_pos[None, :] <= np.arange(T, dtype=np.int32)[:, None]   # [T, S], trace-time constant
         scores = np.where(visible[None, None], scores, np.float32(-1e30))
     else:
-        from nkipy_b200.core import tensor_apis
-
         visible = tensor_apis.constant(key_pos)[None, :] <= start_pos[:, None]   # [1, S]
         scores = np.where(visible[None, None], scores, np.float32(-1e30))
-    scores = scores - np.max(scores, axis=-1, keepdims=True)
-    p = np.exp(scores)
-    p = (p / np.sum(p, axis=-1, keepdims=True)).astype(x.dtype)
+    p = tensor_apis.softmax(scores).astype(x.dtype)       # one row kernel when compiled
     ctx = np.matmul(p, vh).transpose(0, 2, 1, 3).reshape(B, T, nq * D)
     return np.matmul(ctx, o_weight)

@@ -1,9 +1,8 @@
 """RMSNorm over the last axis with fp32 statistics (same arithmetic as the reference's
-examples/models/qwen3/kernels/rmsnorm.py:4-21: mean of squares, eps inside the root, weight, cast back)."""
-import numpy as np
+examples/models/qwen3/kernels/rmsnorm.py:4-21: mean of squares, eps inside the root, weight, cast back).
+`tensor_apis.rms_norm` is NumPy in direct mode and one row kernel when the function is compiled."""
+from nkipy_b200.core import tensor_apis
 
 
 def rmsnorm(x, weight, eps: float):
-    xf = x.astype(np.float32)
-    inv = 1.0 / np.sqrt(np.mean(xf * xf, axis=-1, keepdims=True) + np.float32(eps))
-    return (xf * inv * weight.astype(np.float32)).astype(x.dtype)
+    return tensor_apis.rms_norm(x, weight, eps)

@@ -1132,6 +1132,62 @@ class Generator:
         if o.size:
             self._simple("conv", n, params, lines, o.size)
 
+    # ------------------------------------------------------------------ row operations (one warp per row)
+    def _row_kernel(self, n, base: str, body: List[str], extra_params: List[Tuple[str, View]] = ()):
+        """Emit a kernel in which one warp owns one row of the (dense) input over its last axis: `L` is the row
+        length, `x` / `out` point at the row, `lane` is the lane; fp32 arithmetic, shuffles for the row sums."""
+        x, o = n.inputs[0], n.outputs[0]
+        xv = self.materialize(x)
+        ov = self._out(o)
+        L = x.shape[-1]
+        rows = max(x.size // max(L, 1), 1)
+        ct = ctype(x.dtype)
+        name = self.kname(base)
+        sig = f"const {ct}* __restrict__ xin, {ct}* __restrict__ oout" + "".join(
+            f", const {ctype(v.dtype)}* __restrict__ {p}" for p, v in extra_params)
+        head = [f"  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;",
+                f"  const int lane = threadIdx.x & 31;",
+                f"  if (row >= {rows}LL) return;",
+                f"  const {ct}* x = xin + row * {L}LL; {ct}* out = oout + row * {L}LL;",
+                f"  const int L = {L};"]
+        self.kernels.append(f'extern "C" __global__ void {name}({sig}) {{\n' + "\n".join(head + body) + "\n}\n")
+        self.launches.append(Launch(name, ((rows * 32 + 255) // 256, 1, 1), (256, 1, 1), 0,
+                                    [{"buffer": xv.buffer, "offset": xv.offset * x.dtype.itemsize},
+                                     {"buffer": ov.buffer, "offset": 0}]
+                                    + [{"buffer": v.buffer, "offset": v.offset * v.dtype.itemsize} for _, v in extra_params],
+                                    f"{n.loc[0]}:{n.loc[1]}" if n.loc else None))
+
+    def lower_softmax(self, n):
+        """softmax over the last axis in one launch: running maximum, exponentials and their sum per warp."""
+        body = ["  float m = -INFINITY;",
+                "  for (int i = lane; i < L; i += 32) m = fmaxf(m, ld<float>(x, i));",
+                "  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));",
+                "  float s = 0.f;",
+                "  for (int i = lane; i < L; i += 32) s += expf(ld<float>(x, i) - m);",
+                "  s = warp_reduce_sum(s);",
+                "  const float inv = 1.f / s;",
+                "  for (int i = lane; i < L; i += 32) st(out, i, expf(ld<float>(x, i) - m) * inv);"]
+        if n.outputs[0].size:
+            self._row_kernel(n, "softmax", body)
+        else:
+            self._out(n.outputs[0])
+
+    def lower_rms_norm(self, n):
+        """RMSNorm over the last axis in one launch (fp32 statistics, eps inside the root, optional weight)."""
+        eps = float(n.attrs["eps"])
+        has_w = len(n.inputs) > 1
+        body = ["  float ss = 0.f;",
+                "  for (int i = lane; i < L; i += 32) { const float v = ld<float>(x, i); ss += v * v; }",
+                "  ss = warp_reduce_sum(ss);",
+                f"  const float inv = 1.f / sqrtf(ss / float(L) + {eps!r}f);",
+                "  for (int i = lane; i < L; i += 32) st(out, i, ld<float>(x, i) * inv"
+                + (" * ld<float>(w, i));" if has_w else ");")]
+        extra = [("w", self.materialize(n.inputs[1]))] if has_w else []
+        if n.outputs[0].size:
+            self._row_kernel(n, "rms_norm", body, extra)
+        else:
+            self._out(n.outputs[0])
+
     def _collective(self, n):
         """A collective as two kernels of the module itself: every rank stores its operand into slot [rank] of
         all ranks' symmetric workspace (`cc_push`), then builds the result from the slots (`cc_consume`):

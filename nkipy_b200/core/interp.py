@@ -188,6 +188,16 @@ def _eval_node(n: Node, ins: List[np.ndarray], world: int = 1) -> List[np.ndarra
         return [np.asarray(_REDUCE[kind].reduce(xc, axis=axes)).astype(odt)]
     if op == "dot":
         return [_dot(ins[0], ins[1], a, odt)]
+    if op == "softmax":
+        x = ins[0].astype(np.float32)
+        e = np.exp(x - x.max(axis=-1, keepdims=True))
+        return [(e / e.sum(axis=-1, keepdims=True)).astype(odt)]
+    if op == "rms_norm":
+        x = ins[0].astype(np.float32)
+        y = x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + np.float32(a["eps"]))
+        if len(ins) > 1:
+            y = y * ins[1].astype(np.float32)
+        return [y.astype(odt)]
     if op == "conv":
         return [_conv(ins[0], ins[1], ins[2] if len(ins) > 2 else None, a, odt)]
     if op == "take":

@@ -308,6 +308,8 @@ _INFER = {
     "dynamic_update_slice": _scatter_like, "dynamic_slice": _dynamic_slice, "topk": _topk,
     "custom_call": _custom_call, "conv": _conv, "all_gather": _all_gather, "all_reduce": _same,
     "reduce_scatter": _reduce_scatter, "all_to_all": _all_to_all,
+    # row operations over the last axis: softmax(x); rms_norm(x[, weight]) with attr eps (fp32 statistics)
+    "softmax": _same, "rms_norm": _same,
 }
 
 OPCODES = tuple(sorted(_INFER))

@@ -6,8 +6,9 @@ The set and the names match the reference registry
 other ops have a backend-agnostic composed implementation; ops without a NumPy
 equivalent (`topk`, `softmax`, `rms_norm`, `conv2d/3d`, creation helpers and the four
 collectives) also have a CPU implementation so kernels using them run unchanged in
-CPU direct mode.  Unlike the reference, `softmax` and `rms_norm` are implemented
-(composed), and `erf` / `rsqrt` / `all` exist as extra primitives.
+CPU direct mode.  `softmax` and `rms_norm` over the last axis trace to one node each (one row kernel on the
+device); for other axes, and in direct mode, they are compositions of primitives.  `erf` / `rsqrt` / `all`
+exist as extra primitives.
 """
 
 from __future__ import annotations
@@ -78,7 +79,7 @@ def _register_ir():
         "split": I.split, "copy": I.copy, "repeat": I.repeat, "broadcast_to": I.broadcast_to, "astype": I.astype,
         "squeeze": I.squeeze, "pad": I.pad, "swapaxes": I.swapaxes, "stack": I.stack, "flip": I.flip,
         "tile": I.tile, "roll": I.roll,
-        "topk": I.topk, "conv2d": I.conv2d, "conv3d": I.conv3d,
+        "topk": I.topk, "conv2d": I.conv2d, "conv3d": I.conv3d, "softmax": I.softmax, "rms_norm": I.rms_norm,
         "where": I.where, "take": I.take, "take_along_axis": I.take_along_axis, "put_along_axis": I.put_along_axis,
         "scatter_along_axis": I.scatter_along_axis, "static_slice": I.static_slice,
         "dynamic_update_slice": I.dynamic_update_slice, "scatter_strided": I.scatter_strided,

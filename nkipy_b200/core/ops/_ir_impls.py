@@ -813,6 +813,30 @@ def scatter_strided(x, value, starts, strides, sizes):
 
 
 # --------------------------------------------------------------------------- nn / conv
+def softmax(x, axis=-1):
+    """Softmax over the last axis as ONE node (one row kernel on the device); other axes use the composition."""
+    v = as_value(x)
+    nd = len(v.shape)
+    if nd == 0 or axis not in (-1, nd - 1) or np.dtype(v.dtype).kind != "f":
+        return NotImplemented
+    return wrap(G().op("softmax", v))
+
+
+def rms_norm(x, weight=None, eps=1e-6, axis=-1):
+    """RMSNorm over the last axis (fp32 statistics, optional weight of the row's length) as one node."""
+    v = as_value(x)
+    nd = len(v.shape)
+    if nd == 0 or axis not in (-1, nd - 1) or np.dtype(v.dtype).kind != "f":
+        return NotImplemented
+    ins = [v]
+    if weight is not None:
+        wv = as_value(weight)
+        if tuple(wv.shape) != (v.shape[-1],):
+            return NotImplemented
+        ins.append(wv)
+    return wrap(G().add_node("rms_norm", ins, {"eps": float(eps)})[0])
+
+
 def topk(x, k, axis=-1, is_ascend=False):
     v = as_value(x)
     nd = len(v.shape)

@@ -49,7 +49,11 @@ class Op:
             fn = self._composed
         if fn is None:
             raise NotImplementedError(f"Operation '{self.name}' is not implemented for backend '{backend}'")
-        return fn(*args, **kwargs)
+        out = fn(*args, **kwargs)
+        if out is NotImplemented and fn is not self._composed and self._composed is not None:
+            # a backend implementation may decline a case (an axis, a dtype): the composition covers it
+            out = self._composed(*args, **kwargs)
+        return out
 
     def __repr__(self) -> str:
         return f"<Op '{self.name}' backends={sorted(self._impls)}{' +composed' if self._composed else ''}>"

@@ -292,3 +292,25 @@ def test_loop_kernel_on_device(tmp_path):
     x, w = f32(6, 32), f32(32, 32) * 0.3
     out, plan = _run_nkigen(k, tmp_path, [x, w])
     np.testing.assert_allclose(out["output"].numpy(), k(x, w), rtol=1e-4, atol=1e-5)
+
+
+def test_softmax_and_rms_norm_ops_are_single_launches(tmp_path):
+    """`tensor_apis.softmax` / `rms_norm` over the last axis are one node and one row kernel each."""
+    from nkipy_b200.core import tensor_apis as T
+    from nkipy_b200.core.compile import compile_to_neff, trace
+
+    def k(x, w):
+        return T.softmax(x), T.rms_norm(x, w, 1e-5), T.rms_norm(x * 2.0)
+
+    x, w = f32(33, 1000), f32(1000)
+    check(k, x, w, rtol=1e-4, atol=1e-5)
+    kern = trace(k)
+    kern.specialize(x, w)
+    compile_to_neff(kern, str(tmp_path), "rows.cubin")
+    plan = json.load(open(tmp_path / "rows.json"))
+    names = [l["kernel"].split("_", 1)[1] for l in plan["launches"]]
+    assert names.count("softmax") == 1 and names.count("rms_norm") == 2 and "reduce" not in names
+    import ml_dtypes
+
+    xb, wb = x.astype(ml_dtypes.bfloat16), w.astype(ml_dtypes.bfloat16)
+    check(lambda a, b: (T.softmax(a), T.rms_norm(a, b)), xb, wb, rtol=2e-2, atol=2e-2)
