@@ -41,7 +41,8 @@ def pick_splits(n_out: int, k: int, sms: int = 148) -> int:
     if tiles >= 2 * sms * 3 // 4:
         return 1
     want = max(1, (2 * sms) // tiles)
-    return max(1, min(want, k // 512, 8))
+    min_k = int(os.environ.get("NKIPY_B200_SPLIT_MIN_K", "512"))
+    return max(1, min(want, k // min_k, 8))
 
 
 def pick_cluster_splits(tiles: int, k: int, tokens: int, sms: int = 148) -> int:
