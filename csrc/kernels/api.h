@@ -137,6 +137,13 @@ int nkb_paged_attn_decode(const void* q, const void* k_cache, const void* v_cach
                           const int* context_lens, void* out, float* scratch, int batch, int q_len, int nq, int nkv,
                           int head_dim, int block_size, int num_blocks, int max_blocks_per_seq, float scale,
                           int window, const float* sinks, int num_splits, void* stream);
+int nkb_paged_attn_decode_fused(const float* qkv_partials, int qkv_splits, long long qkv_split_stride,
+                                const void* qkv_bias, const int* positions, const int* slots, const float* cos_sin,
+                                const void* q_norm_w, const void* k_norm_w, float norm_eps, int max_pos, void* k_cache,
+                                void* v_cache, const int* block_table, const int* context_lens, void* out,
+                                float* scratch, int batch, int nq, int nkv, int head_dim, int block_size,
+                                int num_blocks, int max_blocks_per_seq, float scale, int window, const float* sinks,
+                                int num_splits, void* stream);
 long long nkb_paged_attn_decode_scratch_floats(int batch, int q_len, int nq, int head_dim, int num_splits);
 
 int nkb_flash_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_table,

@@ -48,7 +48,126 @@ struct DecodeParams {
   int* status;
   int batch, q_len, nq, nkv, group, max_blocks, num_splits, window;
   float scale_log2;
+  // Fused mode (qkv_partials != nullptr, q_len == 1): the kernel takes the split-K partials of the fused QKV
+  // projection [splits][batch][(nq + 2 nkv) * D] instead of finished queries.  Every CTA builds its group's
+  // query rows itself (sum, bias, QK-norm, rotate-halves RoPE); the CTA of split 0 also builds the new
+  // token's key and value, writes them to their cache slot for later steps and adds them to the softmax
+  // as one extra key, so the pages it streams stop one token earlier.  This removes the separate
+  // RoPE + append launch from every layer of a decode step.
+  const float* qkv_partials;
+  long long qkv_split_stride;
+  const __nv_bfloat16* qkv_bias;
+  const int* positions;
+  const int* slots;
+  const float* cos_sin;
+  const __nv_bfloat16* q_norm_w;
+  const __nv_bfloat16* k_norm_w;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  float norm_eps;
+  int qkv_splits, max_pos;
 };
+
+// One head row of the fused QKV output for token `tok`, in two steps so that a warp can have the loads of two
+// heads in flight at once: `load` issues every global read the row needs (the partials of up to kFuseChunk splits,
+// bias, norm weight, the cos / sin row), `finish` sums, normalises, rotates and rounds to bf16 the way the
+// stand-alone RoPE kernel does.  One warp; lane owns elements lane * PER + j of each half.
+constexpr int kFuseChunk = 8;
+template <int D>
+struct FusedRow {
+  static constexpr int PER = D / 64;
+  float x[kFuseChunk][PER], y[kFuseChunk][PER];
+  float bx[PER], by[PER], wx[PER], wy[PER], c[PER], sn[PER];
+  long long base;
+  bool has_norm, rotate;
+
+  __device__ __forceinline__ void load(const DecodeParams& p, int tok, int head, const __nv_bfloat16* norm_w,
+                                       bool rot, int lane) {
+    const int width = (p.nq + 2 * p.nkv) * D;
+    base = (long long)tok * width + (long long)head * D + lane * PER;
+    has_norm = norm_w != nullptr;
+    rotate = rot && p.cos_sin != nullptr;
+    int pos = rotate ? p.positions[tok] : 0;
+#pragma unroll
+    for (int q = 0; q < kFuseChunk; ++q) {
+      const bool on = q < p.qkv_splits;
+      const float* src = p.qkv_partials + (long long)q * p.qkv_split_stride + base;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        x[q][j] = on ? __ldcg(src + j) : 0.f;
+        y[q][j] = on ? __ldcg(src + D / 2 + j) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = lane * PER + j;
+      bx[j] = p.qkv_bias ? __bfloat162float(p.qkv_bias[head * D + i]) : 0.f;
+      by[j] = p.qkv_bias ? __bfloat162float(p.qkv_bias[head * D + D / 2 + i]) : 0.f;
+      wx[j] = has_norm ? __bfloat162float(norm_w[i]) : 1.f;
+      wy[j] = has_norm ? __bfloat162float(norm_w[D / 2 + i]) : 1.f;
+    }
+    pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = lane * PER + j;
+      c[j] = rotate ? p.cos_sin[(long long)pos * D + i] : 1.f;
+      sn[j] = rotate ? p.cos_sin[(long long)pos * D + D / 2 + i] : 0.f;
+    }
+  }
+
+  __device__ __forceinline__ void finish(const DecodeParams& p, float (&lo)[PER], float (&hi)[PER]) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) lo[j] = hi[j] = 0.f;
+#pragma unroll
+    for (int q = 0; q < kFuseChunk; ++q) {
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        lo[j] += x[q][j];
+        hi[j] += y[q][j];
+      }
+    }
+    // more splits than one chunk holds (rare): the rest in order, without the overlap
+    for (int q = kFuseChunk; q < p.qkv_splits; ++q) {
+      const float* src = p.qkv_partials + (long long)q * p.qkv_split_stride + base;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        lo[j] += __ldcg(src + j);
+        hi[j] += __ldcg(src + D / 2 + j);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      lo[j] += bx[j];
+      hi[j] += by[j];
+    }
+    if (has_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / float(D) + p.norm_eps);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        lo[j] = __bfloat162float(__float2bfloat16(lo[j] * inv * wx[j]));
+        hi[j] = __bfloat162float(__float2bfloat16(hi[j] * inv * wy[j]));
+      }
+    }
+    if (rotate) {
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const float a = lo[j], b = hi[j];
+        lo[j] = a * c[j] - b * sn[j];
+        hi[j] = b * c[j] + a * sn[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      lo[j] = __bfloat162float(__float2bfloat16(lo[j]));
+      hi[j] = __bfloat162float(__float2bfloat16(hi[j]));
+    }
+  }
+};
+
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -66,6 +185,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+
 
 template <int D, int kDecWarps>
 __global__ void __launch_bounds__(kDecWarps * 32)
@@ -98,40 +218,20 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   griddep_wait();   // q, the cache and the tables come from the preceding kernels
   griddep_launch();
   const int ctx = p.context_lens[b];
+  const bool fused = p.qkv_partials != nullptr;       // then q_len == 1
+  const bool owner = fused && split == 0 && ctx > 0;   // this CTA handles the new token's key and value
+  // tokens that are read from the cache pages: all of them, or all but the new one
+  const int ctx_paged = fused ? ctx - 1 : ctx;
 
   // ---- page range of this split
   int first_tok = 0;
   if (p.window > 0) first_tok = max(0, ctx - p.q_len - p.window + 1);
-  const int page_lo = first_tok / kPage, page_hi = (ctx + kPage - 1) / kPage;
+  const int page_lo = first_tok / kPage, page_hi = (ctx_paged + kPage - 1) / kPage;
   const int npages = max(page_hi - page_lo, 0);
   const int per_split = (npages + p.num_splits - 1) / p.num_splits;
   const int p0 = page_lo + split * per_split;
   const int p1 = min(page_hi, p0 + per_split);
   const int* table = p.block_table + (long long)b * p.max_blocks;
-
-  // ---- query fragments
-  uint32_t qf[D / 16][4];
-  {
-    const int r0 = g, r1 = g + 8;
-    const __nv_bfloat16* q0 = nullptr;
-    const __nv_bfloat16* q1 = nullptr;
-    if (r0 < rows)
-      q0 = p.q + (((long long)b * p.q_len + r0 / p.group) * p.nq + kvh * p.group + r0 % p.group) * D;
-    if (r1 < rows)
-      q1 = p.q + (((long long)b * p.q_len + r1 / p.group) * p.nq + kvh * p.group + r1 % p.group) * D;
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t) : 0u;
-      qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t) : 0u;
-      qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t) : 0u;
-      qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t) : 0u;
-    }
-  }
-  // last visible kv position (inclusive) and first visible one, per owned row
-  const int lim0 = ctx - p.q_len + (g < rows ? g / p.group : 0);
-  const int lim1 = ctx - p.q_len + (g + 8 < rows ? (g + 8) / p.group : 0);
-  const int low0 = p.window > 0 ? lim0 - p.window + 1 : 0;
-  const int low1 = p.window > 0 ? lim1 - p.window + 1 : 0;
 
   float o[D / 8][4];
 #pragma unroll
@@ -159,6 +259,95 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     const int pg = my_first + s * kDecWarps;
     if (pg < p1) issue(pg, s);
   }
+  // (the first pages are in flight while the queries are built)
+  __shared__ __align__(16) __nv_bfloat16 q_s[16 * D]; // the group's query rows (fused mode)
+  __shared__ float kn_s[D], vn_s[D], snew_s[16];
+  if (fused) {
+    constexpr int PER = D / 64;
+    // heads of this CTA: the group's queries, then (owner only) the key and the value of this kv head; a warp
+    // takes two of them per round so that both rows' loads are in flight together
+    const int nheads = p.group + (owner ? 2 : 0);
+    const int slot = p.slots ? p.slots[b] : -1;
+    auto head_of = [&](int hh) { return hh < p.group ? kvh * p.group + hh : (hh == p.group ? p.nq + kvh : p.nq + p.nkv + kvh); };
+    auto store = [&](int hh, const float (&lo)[PER], const float (&hi)[PER]) {
+      if (hh < p.group) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          q_s[hh * D + lane * PER + j] = __float2bfloat16(lo[j]);
+          q_s[hh * D + D / 2 + lane * PER + j] = __float2bfloat16(hi[j]);
+        }
+        return;
+      }
+      const bool is_k = hh == p.group;
+      float* dst_s = is_k ? kn_s : vn_s;
+      __nv_bfloat16* dst = nullptr;
+      if (slot >= 0) {
+        const long long blk = slot / kPage, off = slot % kPage;
+        dst = (is_k ? p.k_cache : p.v_cache) + ((blk * p.nkv + kvh) * kPage + off) * D;
+      }
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = lane * PER + j;
+        dst_s[i] = lo[j];
+        dst_s[D / 2 + i] = hi[j];
+        if (dst) {
+          dst[i] = __float2bfloat16(lo[j]);
+          dst[D / 2 + i] = __float2bfloat16(hi[j]);
+        }
+      }
+    };
+    for (int h0 = warp; h0 < nheads; h0 += 2 * kDecWarps) {
+      const int h1 = h0 + kDecWarps;
+      FusedRow<D> ra, rb;
+      float lo[PER], hi[PER];
+      ra.load(p, b, head_of(h0), h0 < p.group ? p.q_norm_w : (h0 == p.group ? p.k_norm_w : nullptr), h0 <= p.group, lane);
+      if (h1 < nheads)
+        rb.load(p, b, head_of(h1), h1 < p.group ? p.q_norm_w : (h1 == p.group ? p.k_norm_w : nullptr), h1 <= p.group, lane);
+      ra.finish(p, lo, hi);
+      store(h0, lo, hi);
+      if (h1 < nheads) {
+        rb.finish(p, lo, hi);
+        store(h1, lo, hi);
+      }
+    }
+    __syncthreads();
+    if (owner) {
+      // scores of the new token against the group's queries (log2 domain like the paged part)
+      for (int r = warp; r < p.group; r += kDecWarps) {
+        float acc = 0.f;
+        for (int i = lane; i < D; i += 32) acc += __bfloat162float(q_s[r * D + i]) * kn_s[i];
+        acc = warp_sum(acc);
+        if (lane == 0) snew_s[r] = acc * p.scale_log2;
+      }
+    }
+  }
+  // ---- query fragments
+  uint32_t qf[D / 16][4];
+  {
+    const int r0 = g, r1 = g + 8;
+    const __nv_bfloat16* q0 = nullptr;
+    const __nv_bfloat16* q1 = nullptr;
+    if (r0 < rows)
+      q0 = fused ? q_s + r0 * D
+                 : p.q + (((long long)b * p.q_len + r0 / p.group) * p.nq + kvh * p.group + r0 % p.group) * D;
+    if (r1 < rows)
+      q1 = fused ? q_s + r1 * D
+                 : p.q + (((long long)b * p.q_len + r1 / p.group) * p.nq + kvh * p.group + r1 % p.group) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t) : 0u;
+      qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t) : 0u;
+      qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t) : 0u;
+      qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  // last visible kv position (inclusive) and first visible one, per owned row
+  const int qpos0 = ctx - p.q_len + (g < rows ? g / p.group : 0);
+  const int qpos1 = ctx - p.q_len + (g + 8 < rows ? (g + 8) / p.group : 0);
+  const int lim0 = fused ? qpos0 - 1 : qpos0, lim1 = fused ? qpos1 - 1 : qpos1;   // fused: the new token is not paged
+  const int low0 = p.window > 0 ? qpos0 - p.window + 1 : 0;
+  const int low1 = p.window > 0 ? qpos1 - p.window + 1 : 0;
+
   int stage = 0;
   uint32_t phase = 0;
   for (int pg = my_first; pg < p1; pg += kDecWarps) {
@@ -286,6 +475,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     float mf = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kDecWarps; ++w) mf = fmaxf(mf, mm[w * 16 + r]);
+    if (owner) mf = fmaxf(mf, snew_s[r]);
     float acc = 0.f, l = 0.f;
 #pragma unroll
     for (int w = 0; w < kDecWarps; ++w) {
@@ -293,6 +483,12 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - mf);
       acc += sc * mo[(w * 16 + r) * D + d];
       l += sc * ml[w * 16 + r];
+    }
+    if (owner) {
+      // the new token: one more key with probability mass exp2(score - max) and its value row
+      const float sc = exp2f(snew_s[r] - mf);
+      acc += sc * vn_s[d];
+      l += sc;
     }
     if (p.num_splits == 1) {
       const int head = kvh * p.group + r % p.group;
@@ -430,6 +626,59 @@ extern "C" int nkb_paged_attn_decode(const void* q, const void* k_cache, const v
   p.batch = batch; p.q_len = q_len; p.nq = nq; p.nkv = nkv; p.group = group;
   p.max_blocks = max_blocks_per_seq; p.num_splits = num_splits; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap tk, tv;
+  const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(kPage), uint64_t(nkv), uint64_t(num_blocks)};
+  const uint64_t strides[3] = {uint64_t(head_dim) * 2, uint64_t(head_dim) * kPage * 2,
+                               uint64_t(head_dim) * kPage * nkv * 2};
+  const uint32_t box[4] = {64, uint32_t(kPage), 1, 1};
+  if (encode_tmap_bf16(&tk, k_cache, 4, dims, strides, box)) return -4;
+  if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return dispatch_decode(head_dim, (long long)batch * nkv * num_splits, num_sms(), tk, tv, p, s);
+}
+
+// Decode attention that starts from the split-K partials of the fused QKV projection: bias, QK-norm, RoPE and the
+// append of the new token's key and value to the paged cache happen inside the attention kernel (q_len == 1).
+// `context_lens` already counts the new token; `slots[b]` is its flat cache slot (negative: not stored).
+extern "C" int nkb_paged_attn_decode_fused(const float* qkv_partials, int qkv_splits, long long qkv_split_stride,
+                                           const void* qkv_bias, const int* positions, const int* slots,
+                                           const float* cos_sin, const void* q_norm_w, const void* k_norm_w,
+                                           float norm_eps, int max_pos, void* k_cache, void* v_cache,
+                                           const int* block_table, const int* context_lens, void* out, float* scratch,
+                                           int batch, int nq, int nkv, int head_dim, int block_size, int num_blocks,
+                                           int max_blocks_per_seq, float scale, int window, const float* sinks,
+                                           int num_splits, void* stream) {
+  if (batch <= 0) return 0;
+  if (block_size != kPage || nq % nkv != 0 || !qkv_partials || qkv_splits < 1 || !positions || !slots) return -2;
+  const int group = nq / nkv;
+  if (group > 16) return -2;
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && (!scratch || (long long)batch * nkv > kDecCounters)) return -2;
+  if (!status_word() && nkb_init() != 0) return -1;
+  DecodeParams p{};
+  p.block_table = block_table;
+  p.context_lens = context_lens;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.scratch = num_splits > 1 ? scratch + kDecCounters : nullptr;
+  p.counters = reinterpret_cast<unsigned int*>(scratch);
+  p.sinks = sinks;
+  p.status = status_word();
+  p.batch = batch; p.q_len = 1; p.nq = nq; p.nkv = nkv; p.group = group;
+  p.max_blocks = max_blocks_per_seq; p.num_splits = num_splits; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.qkv_partials = qkv_partials;
+  p.qkv_split_stride = qkv_split_stride;
+  p.qkv_splits = qkv_splits;
+  p.qkv_bias = reinterpret_cast<const __nv_bfloat16*>(qkv_bias);
+  p.positions = positions;
+  p.slots = slots;
+  p.cos_sin = cos_sin;
+  p.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(q_norm_w);
+  p.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(k_norm_w);
+  p.k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache);
+  p.v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache);
+  p.norm_eps = norm_eps;
+  p.max_pos = max_pos;
   CUtensorMap tk, tv;
   const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(kPage), uint64_t(nkv), uint64_t(num_blocks)};
   const uint64_t strides[3] = {uint64_t(head_dim) * 2, uint64_t(head_dim) * kPage * 2,

@@ -1,16 +1,22 @@
 // Blockwise (flash) prefill attention on tcgen05 for sm_100a, reading K/V from
 // the paged cache through the per-sequence block table.
 //
-// One CTA per (128-row query tile, query head, sequence):
-//   warp 0   TMA producer: Q tile once, then a 2-stage ring of 128-token K and V
-//            tiles (four 32-token pages each, 128-byte swizzle, non-multicast)
-//   warp 1   issues tcgen05.mma:  S = Q K^T  (M=128, N=128, fp32 in TMEM, two S
-//            buffers so QK^T of tile j+1 overlaps the softmax of tile j), then
-//            O_tile = P V with V as an MN-major B operand
-//   warps 2-5 one thread per query row: online softmax straight out of TMEM
-//            (row max / sum need no cross-thread reduction), P written to shared
-//            memory in the swizzled K-major layout the MMA reads, O accumulated
-//            in registers.
+// One CTA per (256 query rows, query head, sequence), as two 128-row query tiles in ping-pong:
+//   warp 0     TMA producer: both Q tiles once, then a 3-stage ring that holds the 128-token K and V
+//              tiles in turn (four 32-token pages each, 128-byte swizzle, non-multicast)
+//   warp 1     issues tcgen05.mma.  Per KV tile and query tile t: S_t = Q_t K^T (M = N = 128, fp32 in
+//              TMEM) and O_t += P_t V with V as an MN-major B operand.  The order
+//              PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1) keeps the tensor pipe busy with one tile's
+//              MMAs while the other tile's softmax runs.
+//   warps 4-7  softmax of tile 0, warps 8-11 softmax of tile 1: one thread per query row reads its
+//              128 scores from TMEM once, keeps them in registers, writes P as bf16 to shared memory
+//              in the swizzled K-major layout the MMA reads.
+// O_0 and O_1 stay in TMEM for the whole KV loop (S_0, S_1, O_0, O_1 = 4 x 128 columns).  The row maximum
+// that scales the exponentials is only raised when the true maximum has grown by more than 2^8 since it
+// was last set; then the row's O is rescaled in TMEM (load, multiply, store).  With a stale maximum the
+// probabilities are at most 2^8 too large, which fp32 sums and bf16 P hold without loss, and O / l is
+// unchanged because both carry the same factor.  KV tiles past a query tile's causal diagonal or before
+// its window are skipped for that tile; the mask is only evaluated on tiles that cross either edge.
 // GQA needs no repeat of K/V: the query head picks its kv head.  Supports causal
 // masking with a cached prefix (q_len <= context_len), sliding windows and
 // attention-sink logits.
@@ -26,10 +32,13 @@
 
 namespace nkb {
 
-constexpr int kQTile = 128;
+constexpr int kQTile = 128;          // rows of one MMA tile
+constexpr int kQPair = 2 * kQTile;   // query rows per CTA
 constexpr int kKVTile = 128;
 constexpr int kPfPage = 32;
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 384;          // warpgroup 0: TMA warp, MMA warp, two idle; warpgroups 1, 2: softmax
+constexpr int kKVStages = 3;
+constexpr float kRescaleStep = 8.f;  // log2 of the growth of the row maximum that triggers a rescale of O
 
 struct PrefillParams {
   const int* block_table;
@@ -45,12 +54,40 @@ struct PrefillParams {
 
 struct PrefillCtrl {
   uint64_t q_full;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t kv_full[kKVStages], kv_empty[kKVStages];
   uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, o_full, o_empty;
+  uint64_t p_full[2], o_full[2];
   uint32_t tmem_base;
   int abort;
 };
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// KV tile range [lo, hi) that query tile `t` of the CTA attends to (empty when the tile has no rows).
+struct TileRange {
+  int lo, hi, pos0, rows;
+};
+__device__ __forceinline__ TileRange tile_range(const PrefillParams& p, int row0, int q_len, int ctx) {
+  TileRange r{0, 0, 0, 0};
+  if (row0 >= q_len) return r;
+  r.rows = min(kQTile, q_len - row0);
+  r.pos0 = ctx - q_len + row0;                       // kv position of the tile's first query
+  r.hi = (ctx + kKVTile - 1) / kKVTile;
+  if (p.causal) r.hi = min(r.hi, (r.pos0 + r.rows - 1) / kKVTile + 1);
+  if (p.window > 0) r.lo = max(0, r.pos0 - p.window + 1) / kKVTile;
+  if (r.hi < r.lo) r.hi = r.lo;
+  return r;
+}
 
 template <int D>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -58,37 +95,34 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
                           const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
   constexpr int NH = D / 64;
   constexpr int kHalf = 128 * 128;          // [128 rows][64 bf16] swizzled slab = 16 KB
-  constexpr int kQBytes = NH * kHalf;
-  constexpr int kKVBytes = NH * kHalf;
+  constexpr int kQBytes = NH * kHalf;       // one query tile
+  constexpr int kKVBytes = NH * kHalf;      // one K or V tile
   constexpr int kPBytes = 2 * kHalf;        // [128 rows][128 tokens]
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol = 256;
+  constexpr uint32_t kSCol = 0, kOCol = 256;   // S_t at kSCol + 128 t, O_t at kOCol + 128 t
 
-  const int qt = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  // the heaviest CTAs (last query rows of a causal sequence) start first
+  const int qt = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, b = blockIdx.z;
   griddep_wait();
   griddep_launch();
   const int q_len = p.q_lens[b];
-  if (qt * kQTile >= q_len) return;
+  if (qt * kQPair >= q_len) return;
   const int ctx = p.context_lens[b];
-  const int q_row0 = p.q_start[b] + qt * kQTile;        // row in the packed q / out arrays
-  const int pos0 = ctx - q_len + qt * kQTile;           // kv position of the tile's first query
-  const int rows_here = min(kQTile, q_len - qt * kQTile);
+  const int q_row0 = p.q_start[b] + qt * kQPair;        // row in the packed q / out arrays
   const int kvh = head / (p.nq / p.nkv);
-
-  // kv tile range
-  int j_hi = (ctx + kKVTile - 1) / kKVTile;
-  if (p.causal) j_hi = min(j_hi, (pos0 + rows_here - 1) / kKVTile + 1);
-  int j_lo = 0;
-  if (p.window > 0) j_lo = max(0, pos0 - p.window + 1) / kKVTile;
-  const int n_tiles = j_hi - j_lo;
+  const TileRange tr0 = tile_range(p, qt * kQPair, q_len, ctx);
+  const TileRange tr1 = tile_range(p, qt * kQPair + kQTile, q_len, ctx);
+  const bool two = tr1.rows > 0;
+  // union of the two ranges; every tile of it is attended to by at least one query tile
+  const int u_lo = tr0.lo, u_hi = two ? max(tr0.hi, tr1.hi) : tr0.hi;
+  const int n_union = u_hi - u_lo;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = smem;
-  uint8_t* k_s = q_s + kQBytes;              // 2 stages
-  uint8_t* v_s = k_s + 2 * kKVBytes;         // 2 stages
-  uint8_t* p_s = v_s + 2 * kKVBytes;
-  PrefillCtrl* ctrl = reinterpret_cast<PrefillCtrl*>(p_s + kPBytes);
+  uint8_t* q_s = smem;                              // 2 query tiles
+  uint8_t* kv_s = q_s + 2 * kQBytes;                // ring: K(j), V(j), K(j+1), ...
+  uint8_t* p_s = kv_s + kKVStages * kKVBytes;       // 2 probability tiles
+  PrefillCtrl* ctrl = reinterpret_cast<PrefillCtrl*>(p_s + 2 * kPBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -96,17 +130,16 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     mbar_init(&ctrl->q_full, 1);
+    for (int i = 0; i < kKVStages; ++i) {
+      mbar_init(&ctrl->kv_full[i], 1);
+      mbar_init(&ctrl->kv_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&ctrl->k_full[i], 1);
-      mbar_init(&ctrl->k_empty[i], 1);
-      mbar_init(&ctrl->v_full[i], 1);
-      mbar_init(&ctrl->v_empty[i], 1);
       mbar_init(&ctrl->s_full[i], 1);
       mbar_init(&ctrl->s_empty[i], 4);
+      mbar_init(&ctrl->p_full[i], 4);
+      mbar_init(&ctrl->o_full[i], 1);
     }
-    mbar_init(&ctrl->p_full, 4);
-    mbar_init(&ctrl->o_full, 1);
-    mbar_init(&ctrl->o_empty, 4);
     ctrl->abort = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -124,42 +157,34 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&ctrl->q_full, kQBytes);
+      mbar_expect_tx(&ctrl->q_full, 2 * kQBytes);
 #pragma unroll
-      for (int h = 0; h < NH; ++h) tma_load_3d(q_s + h * kHalf, &tmQ, &ctrl->q_full, h * 64, head, q_row0);
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+          tma_load_3d(q_s + t * kQBytes + h * kHalf, &tmQ, &ctrl->q_full, h * 64, head, q_row0 + t * kQTile);
     }
     __syncwarp();
     const int* table = p.block_table + (long long)b * p.max_blocks;
     const int last_page = max((ctx + kPfPage - 1) / kPfPage - 1, 0);
-    for (int it = 0; it < n_tiles; ++it) {
-      const int j = j_lo + it;
-      const int st = it & 1;
-      const uint32_t ph = (uint32_t(it) >> 1) & 1u;
-      bool ok = mbar_wait(&ctrl->k_empty[st], ph ^ 1u, abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
+    for (int n = 0; n < 2 * n_union; ++n) {          // item n: K of tile n / 2 (even n) or its V (odd n)
+      const int j = u_lo + (n >> 1);
+      const int st = n % kKVStages;
+      const uint32_t ph = uint32_t(n / kKVStages) & 1u;
+      bool ok = mbar_wait(&ctrl->kv_empty[st], ph ^ 1u, abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
       if (!__all_sync(0xffffffffu, ok)) break;
       int blk[4];
 #pragma unroll
       for (int pi = 0; pi < 4; ++pi) blk[pi] = table[min(j * 4 + pi, last_page)];
       if (lane == 0) {
-        mbar_expect_tx(&ctrl->k_full[st], kKVBytes);
+        const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
+        uint8_t* dst = kv_s + st * kKVBytes;
+        mbar_expect_tx(&ctrl->kv_full[st], kKVBytes);
 #pragma unroll
         for (int pi = 0; pi < 4; ++pi)
 #pragma unroll
           for (int h = 0; h < NH; ++h)
-            tma_load_4d(k_s + st * kKVBytes + h * kHalf + pi * (kPfPage * 128), &tmK, &ctrl->k_full[st], h * 64, 0,
-                        kvh, blk[pi]);
-      }
-      __syncwarp();
-      ok = mbar_wait(&ctrl->v_empty[st], ph ^ 1u, abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      if (lane == 0) {
-        mbar_expect_tx(&ctrl->v_full[st], kKVBytes);
-#pragma unroll
-        for (int pi = 0; pi < 4; ++pi)
-#pragma unroll
-          for (int h = 0; h < NH; ++h)
-            tma_load_4d(v_s + st * kKVBytes + h * kHalf + pi * (kPfPage * 128), &tmV, &ctrl->v_full[st], h * 64, 0,
-                        kvh, blk[pi]);
+            tma_load_4d(dst + h * kHalf + pi * (kPfPage * 128), tm, &ctrl->kv_full[st], h * 64, 0, kvh, blk[pi]);
       }
       __syncwarp();
     }
@@ -168,189 +193,213 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     constexpr uint32_t idesc_qk = make_idesc_bf16(128, kKVTile, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);  // B = V is MN-major
     bool alive = true;
-    bool ok = mbar_wait(&ctrl->q_full, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-    if (!__all_sync(0xffffffffu, ok)) alive = false;
-    auto issue_qk = [&](int it) -> bool {
-      const int st = it & 1;
-      const uint32_t ph = (uint32_t(it) >> 1) & 1u;
-      bool ok2 = mbar_wait(&ctrl->k_full[st], ph, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      if (!__all_sync(0xffffffffu, ok2)) return false;
-      ok2 = mbar_wait(&ctrl->s_empty[st], ph ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok2)) return false;
+    {
+      bool ok = mbar_wait(&ctrl->q_full, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+      if (!__all_sync(0xffffffffu, ok)) alive = false;
+    }
+    auto active = [&](int t, int u) {
+      const int j = u_lo + u;
+      return t == 0 ? (j >= tr0.lo && j < tr0.hi) : (two && j >= tr1.lo && j < tr1.hi);
+    };
+    auto local_it = [&](int t, int u) { return u_lo + u - (t == 0 ? tr0.lo : tr1.lo); };
+    auto wait_item = [&](int n) -> bool {
+      bool ok = mbar_wait(&ctrl->kv_full[n % kKVStages], uint32_t(n / kKVStages) & 1u, abort_flag, p.status,
+                          ERR_WAIT_SMEM_FULL);
+      return __all_sync(0xffffffffu, ok);
+    };
+    auto release_item = [&](int n) {
+      if (lane == 0) umma_commit(&ctrl->kv_empty[n % kKVStages]);
+      __syncwarp();
+    };
+    // S_t = Q_t K(u)^T
+    auto issue_qk = [&](int t, int u) -> bool {
+      if (!wait_item(2 * u)) return false;
+      const int lit = local_it(t, u);
+      bool ok = mbar_wait(&ctrl->s_empty[t], (uint32_t(lit) & 1u) ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
+      if (!__all_sync(0xffffffffu, ok)) return false;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + st * kKVBytes);
-        const uint32_t d = tmem_base + (st ? kSCol1 : kSCol0);
+        const uint32_t qa = smem_u32(q_s + t * kQBytes), ka = smem_u32(kv_s + ((2 * u) % kKVStages) * kKVBytes);
+        const uint32_t d = tmem_base + kSCol + t * 128;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 32;
           umma_f16(d, make_smem_desc_sw128(qa + off, 0, 1024), make_smem_desc_sw128(ka + off, 0, 1024), idesc_qk,
                    ks > 0 ? 1u : 0u);
         }
-        umma_commit(&ctrl->s_full[st]);
-        umma_commit(&ctrl->k_empty[st]);
+        umma_commit(&ctrl->s_full[t]);
       }
       __syncwarp();
       return true;
     };
-    if (alive && n_tiles > 0) alive = issue_qk(0);
-    for (int it = 0; it < n_tiles && alive; ++it) {
-      if (it + 1 < n_tiles) {
-        alive = issue_qk(it + 1);
-        if (!alive) break;
-      }
-      const int st = it & 1;
-      const uint32_t ph = (uint32_t(it) >> 1) & 1u;
-      ok = mbar_wait(&ctrl->p_full, uint32_t(it) & 1u, abort_flag, p.status, ERR_WAIT_SOFTMAX);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      ok = mbar_wait(&ctrl->v_full[st], ph, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      ok = mbar_wait(&ctrl->o_empty, (uint32_t(it) & 1u) ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok)) break;
+    // O_t (+)= P_t V(u)
+    auto issue_pv = [&](int t, int u) -> bool {
+      const int lit = local_it(t, u);
+      bool ok = mbar_wait(&ctrl->p_full[t], uint32_t(lit) & 1u, abort_flag, p.status, ERR_WAIT_SOFTMAX);
+      if (!__all_sync(0xffffffffu, ok)) return false;
+      if (!wait_item(2 * u + 1)) return false;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + st * kKVBytes);
-        const uint32_t d = tmem_base + kOCol;
+        const uint32_t pa = smem_u32(p_s + t * kPBytes), va = smem_u32(kv_s + ((2 * u + 1) % kKVStages) * kKVBytes);
+        const uint32_t d = tmem_base + kOCol + t * 128;
 #pragma unroll
         for (int ks = 0; ks < kKVTile / 16; ++ks) {
           const uint64_t da = make_smem_desc_sw128(pa + (ks >> 2) * kHalf + (ks & 3) * 32, 0, 1024);
           // V tile: [token][64 dims] rows of 128 B; 16 tokens per step = 2 KB; next 64 dims one slab on
           const uint64_t db = make_smem_desc_sw128(va + ks * 2048, kHalf, 1024);
-          umma_f16(d, da, db, idesc_pv, ks > 0 ? 1u : 0u);
+          umma_f16(d, da, db, idesc_pv, (lit > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&ctrl->o_full);
-        umma_commit(&ctrl->v_empty[st]);
+        umma_commit(&ctrl->o_full[t]);
       }
       __syncwarp();
+      return true;
+    };
+    if (alive && n_union > 0) {
+      if (active(0, 0)) alive = issue_qk(0, 0);
+      if (alive && active(1, 0)) alive = issue_qk(1, 0);
+      if (alive) release_item(0);
     }
-  } else {
-    // ---------------------------------------------------------------- softmax / accumulate
-    const int quad = warp & 3;
+    for (int u = 0; u < n_union && alive; ++u) {
+      const bool more = u + 1 < n_union;
+      if (active(0, u)) alive = issue_pv(0, u);
+      if (alive && more && active(0, u + 1)) alive = issue_qk(0, u + 1);
+      if (alive && active(1, u)) alive = issue_pv(1, u);
+      if (!alive) break;
+      release_item(2 * u + 1);
+      if (more) {
+        if (active(1, u + 1)) alive = issue_qk(1, u + 1);
+        if (alive) release_item(2 * u + 2);
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- softmax
+    const int t = (warp - 4) >> 2;                  // query tile of this warp
+    const int quad = warp & 3;                      // TMEM lanes this warp may touch
+    const TileRange tr = t == 0 ? tr0 : tr1;
     const int r = quad * 32 + lane;                 // row of the query tile
-    const int q_pos = pos0 + r;
+    const int q_pos = tr.pos0 + r;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    const uint32_t s_addr = tmem_base + lane_off + kSCol + t * 128;
+    const uint32_t o_addr = tmem_base + lane_off + kOCol + t * 128;
+    uint8_t* my_p = p_s + t * kPBytes;
+    const int n_tiles = tr.hi - tr.lo;
+    float m = -INFINITY, l = 0.f;
     int hi_pos = ctx - 1;
     if (p.causal) hi_pos = min(hi_pos, q_pos);
     const int lo_pos = p.window > 0 ? q_pos - p.window + 1 : 0;
     bool alive = true;
 
-    auto accumulate_o = [&](float alpha) {
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_off + kOCol + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(v[i]);
-      }
-    };
-
     for (int it = 0; it < n_tiles; ++it) {
-      const int j = j_lo + it;
-      const int st = it & 1;
-      const uint32_t ph = (uint32_t(it) >> 1) & 1u;
-      bool ok = mbar_wait(&ctrl->s_full[st], ph, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+      const int kv0 = (tr.lo + it) * kKVTile;
+      bool ok = mbar_wait(&ctrl->s_full[t], uint32_t(it) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem_base + lane_off + (st ? kSCol1 : kSCol0);
-      const int kv0 = j * kKVTile;
-      // pass 1: row maximum
+      uint32_t v[kKVTile];
+#pragma unroll
+      for (int c = 0; c < kKVTile / 32; ++c) tmem_ld_32x32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctrl->s_empty[t]);   // the scores are in registers: S_t may be overwritten
+
+      // the mask only on tiles that cross the causal diagonal, the end of the context or the window edge
+      const bool edge = kv0 + kKVTile - 1 > hi_pos || kv0 < lo_pos;
+      if (__any_sync(0xffffffffu, edge)) {
+        const int hi_rel = hi_pos - kv0, lo_rel = lo_pos - kv0;
+#pragma unroll
+        for (int i = 0; i < kKVTile; ++i)
+          if (i > hi_rel || i < lo_rel) v[i] = 0xff800000u;   // -inf
+      }
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kKVTile / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const float x = (kv <= hi_pos && kv >= lo_pos) ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, x);
-        }
-      }
-      const float m_new = fmaxf(m, mx);
-      const float base = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m - base);
-      m = m_new;
-      // previous tile's P.V result: fold into the register accumulator, free P and the O tile
-      if (it > 0) {
-        ok = mbar_wait(&ctrl->o_full, uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+      for (int i = 0; i < kKVTile; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+      mx *= p.scale_log2;
+
+      if (it == 0) {
+        m = mx;
+      } else {
+        // P_t of the previous tile has been read and O_t holds its contribution
+        ok = mbar_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        tc_fence_after();
-        accumulate_o(alpha_prev);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctrl->o_empty);
-      }
-      alpha_prev = alpha;
-      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
-      float sum = 0.f;
+        const bool grow = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          tc_fence_after();
+          const float alpha = grow ? exp2f(m - mx) : 1.f;
 #pragma unroll 1
-      for (int c = 0; c < kKVTile / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + c * 32, o);
+            tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int kv = kv0 + c * 32 + i;
-          const float x0 = (kv <= hi_pos && kv >= lo_pos) ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
-          const float x1 =
-              (kv + 1 <= hi_pos && kv + 1 >= lo_pos) ? __uint_as_float(v[i + 1]) * p.scale_log2 : -INFINITY;
-          const float e0 = exp2f(x0 - base), e1 = exp2f(x1 - base);
-          // the row sum uses the rounded values the MMA will see
-          const uint32_t pr = pack_bf16x2(e0, e1);
-          const float2 back = unpack_bf16x2(pr);
-          sum += back.x + back.y;
-          pk[i >> 1] = pr;
-        }
-        // 32 tokens = four 16-byte chunks; chunk index within the 128-token row = c*4 + q
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = c * 4 + q;
-          uint8_t* dst = p_s + (chunk >> 3) * kHalf + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, o);
+          }
+          tmem_st_wait();
+          l *= alpha;
+          if (grow) m = mx;
         }
       }
-      l = l * alpha + sum;
+      const float base = (m == -INFINITY) ? 0.f : m;
+      const float nbase = -base;
+      float sum = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < kKVTile / 8; ++c8) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = exp2f(fmaf(__uint_as_float(v[c8 * 8 + i]), p.scale_log2, nbase));
+          sum += e[i];
+        }
+        // 16-byte chunk c8 of the row, swizzled like a TMA 128-byte-swizzle load would place it
+        uint8_t* dst = my_p + (c8 >> 3) * kHalf + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]),
+                                                    pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+      }
+      l += sum;
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&ctrl->p_full);
-        mbar_arrive(&ctrl->s_empty[st]);
+      if (lane == 0) mbar_arrive(&ctrl->p_full[t]);
+    }
+    // ---- epilogue: O_t / l to global memory
+    if (tr.rows > 0) {
+      bool have_o = false;
+      if (alive && n_tiles > 0) {
+        bool ok = mbar_wait(&ctrl->o_full[t], uint32_t(n_tiles - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+        have_o = __all_sync(0xffffffffu, ok);
+        if (have_o) tc_fence_after();
       }
-    }
-    if (alive && n_tiles > 0) {
-      bool ok = mbar_wait(&ctrl->o_full, uint32_t(n_tiles - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
-      if (__all_sync(0xffffffffu, ok)) {
-        tc_fence_after();
-        accumulate_o(alpha_prev);
+      float osc = 1.f;
+      if (p.sinks) {
+        const float sk = p.sinks[head] * 1.4426950408889634f;
+        const float m2 = fmaxf(m, sk);
+        osc = (m == -INFINITY) ? 0.f : exp2f(m - m2);
+        l = l * osc + exp2f(sk - m2);
       }
-    }
-    if (p.sinks) {
-      const float sk = p.sinks[head] * 1.4426950408889634f;
-      const float m2 = fmaxf(m, sk);
-      const float sc = (m == -INFINITY) ? 0.f : exp2f(m - m2);
-      l = l * sc + exp2f(sk - m2);
+      const float inv = l > 0.f ? osc / l : 0.f;
+      __nv_bfloat16* dst = p.out + ((long long)(q_row0 + t * kQTile + r) * p.nq + head) * D;
+      const bool store = r < tr.rows && !*abort_flag;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (have_o) {
+          tmem_ld_32x32(o_addr + c * 32, o);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-      for (int i = 0; i < D; ++i) o_acc[i] *= sc;
-    }
-    if (r < rows_here && !*abort_flag) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + ((long long)(q_row0 + r) * p.nq + head) * D;
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (store) {
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
-        uint4 o;
-        o.x = pack_bf16x2(o_acc[i] * inv, o_acc[i + 1] * inv);
-        o.y = pack_bf16x2(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-        o.z = pack_bf16x2(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-        o.w = pack_bf16x2(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = o;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
+          }
+        }
       }
     }
   }
@@ -370,7 +419,7 @@ template <int D>
 static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const PrefillParams& p, int batch, int max_q_len, cudaStream_t s) {
   constexpr int NH = D / 64;
-  constexpr int smem = NH * 16384 * 5 + 2 * 16384 + int(sizeof(PrefillCtrl)) + 1024 + 64;
+  constexpr int smem = NH * 16384 * (2 + kKVStages) + 2 * 2 * 16384 + int(sizeof(PrefillCtrl)) + 1024 + 64;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e =
@@ -378,7 +427,7 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     if (e != cudaSuccess) return int(e);
     attr_set = true;
   }
-  dim3 grid((max_q_len + kQTile - 1) / kQTile, p.nq, batch);
+  dim3 grid((max_q_len + kQPair - 1) / kQPair, p.nq, batch);
   return launch_pdl(flash_attn_prefill_kernel<D>, grid, dim3(kPfThreads), size_t(smem), s, tq, tk, tv, p);
 }
 

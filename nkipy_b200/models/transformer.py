@@ -248,11 +248,21 @@ class TransformerLM:
                     qkv = ops.linear(normed, lw.qkv, splits=self.split_qkv)
                 else:
                     qkv = ops.linear(normed, lw.qkv)
-                q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq, self.nkv,
-                                       self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm,
-                                       norm_eps=cfg.rms_eps)
-            attn = ops.paged_attn_decode(q, cache.k[i], cache.v[i], block_table, context_lens, self.scale,
-                                         q_len=q_len, window=cfg.window_for_layer(i), sinks=lw.sinks)
+                if (ops.FUSED_ROPE_ATTN and q_len == 1 and qkv.dtype == torch.float32 and qkv.is_cuda
+                        and self.d in (64, 128) and self.nq // self.nkv <= 16):
+                    # RoPE and the cache append run inside the attention kernel: one launch less per layer
+                    q = None
+                    attn = ops.rope_attn_decode(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], block_table,
+                                                context_lens, self.scale, self.nq, self.nkv, bias=lw.qkv_bias,
+                                                q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_eps,
+                                                window=cfg.window_for_layer(i), sinks=lw.sinks)
+                else:
+                    q = ops.rope_kv_append(qkv, positions, slots, self.rope, cache.k[i], cache.v[i], self.nq,
+                                           self.nkv, self.d, bias=lw.qkv_bias, q_norm_w=lw.q_norm,
+                                           k_norm_w=lw.k_norm, norm_eps=cfg.rms_eps)
+            if q is not None:
+                attn = ops.paged_attn_decode(q, cache.k[i], cache.v[i], block_table, context_lens, self.scale,
+                                             q_len=q_len, window=cfg.window_for_layer(i), sinks=lw.sinks)
             split_o = self._csplits(lw.o, T) if cluster else self.split_o
             resid, normed = self._row_parallel_reduce(attn, lw.o, split_o, resid, lw.post_norm, lw.o_bias)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm

@@ -829,6 +829,74 @@ def paged_attn_decode(
     return out
 
 
+# Decode attention reads the fused QKV projection's split-K partials itself (bias, QK-norm, RoPE and the cache
+# append included) instead of running after a separate RoPE + append launch.  "0" restores the two launches.
+FUSED_ROPE_ATTN = os.environ.get("NKIPY_B200_FUSED_ROPE_ATTN", "1") != "0"
+
+
+def rope_attn_decode(
+    qkv_partials: torch.Tensor,
+    positions: torch.Tensor,
+    slots: torch.Tensor,
+    cos_sin: Optional[torch.Tensor],
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    context_lens: torch.Tensor,
+    scale: float,
+    nq: int,
+    nkv: int,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    q_norm_w: Optional[torch.Tensor] = None,
+    k_norm_w: Optional[torch.Tensor] = None,
+    norm_eps: float = 1e-6,
+    window: int = 0,
+    sinks: Optional[torch.Tensor] = None,
+    num_splits: int = 0,
+    scratch: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One new token per sequence: ``rope_kv_append`` followed by ``paged_attn_decode`` as one launch.
+
+    qkv_partials is the fp32 split-K output ``[S, B, (nq + 2 nkv) * D]`` of the fused QKV projection.  The kernel
+    sums it, adds the bias, applies QK-norm and RoPE, stores the new key and value at ``slots`` and attends over the
+    cache pages plus the new token.  Returns ``[B, nq * D]`` bf16."""
+    D = k_cache.shape[3]
+    B = block_table.shape[0]
+    if out is None:
+        out = torch.empty((B, nq * D), dtype=torch.bfloat16, device=qkv_partials.device)
+    if not _native(qkv_partials):
+        q = rope_kv_append(qkv_partials, positions, slots, cos_sin, k_cache, v_cache, nq, nkv, D, bias=bias,
+                           q_norm_w=q_norm_w, k_norm_w=k_norm_w, norm_eps=norm_eps)
+        return paged_attn_decode(q, k_cache, v_cache, block_table, context_lens, scale, window=window, sinks=sinks,
+                                 out=out)
+    global _launches
+    _check_bf16(k_cache, v_cache)
+    if qkv_partials.dtype != torch.float32 or qkv_partials.shape[-2] != B or nq // nkv > 16:
+        raise ValueError("rope_attn_decode wants fp32 partials [S, B, W], one token per sequence, group <= 16")
+    L = _lib.lib()
+    splits = qkv_partials.shape[0] if qkv_partials.dim() == 3 else 1
+    stride = qkv_partials.stride(0) if qkv_partials.dim() == 3 else 0
+    bs = k_cache.shape[2]
+    if num_splits <= 0:
+        num_splits = pick_kv_splits(B * nkv, block_table.shape[1])
+    if num_splits > 1:
+        need = L.nkb_paged_attn_decode_scratch_floats(B, 1, nq, D, num_splits)
+        if scratch is None or scratch.numel() < need:
+            scratch = _decode_scratch(qkv_partials.device, need)
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    rc = L.nkb_paged_attn_decode_fused(
+        qkv_partials.data_ptr(), splits, stride, _ptr(bias), _ptr(positions), _ptr(slots), _ptr(cos_sin),
+        _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), max_pos, k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), context_lens.data_ptr(), out.data_ptr(), _ptr(scratch), B, nq, nkv, D, bs,
+        k_cache.shape[0], block_table.stride(0), float(scale), int(window), _ptr(sinks), num_splits, _stream(),
+    )
+    _lib.check(rc, "nkb_paged_attn_decode_fused")
+    _launches += 1
+    return out
+
+
 def flash_attn_prefill(
     q: torch.Tensor,
     k_cache: torch.Tensor,

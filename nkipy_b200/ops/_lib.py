@@ -83,6 +83,11 @@ _SIGNATURES = {
         [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P,
          c_int, _P],
     ),
+    "nkb_paged_attn_decode_fused": (
+        c_int,
+        [_P, c_int, c_longlong, _P, _P, _P, _P, _P, _P, c_float, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_float, c_int, _P, c_int, _P],
+    ),
     "nkb_paged_attn_decode_scratch_floats": (c_longlong, [c_int, c_int, c_int, c_int, c_int]),
     "nkb_flash_attn_prefill": (
         c_int,

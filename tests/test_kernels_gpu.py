@@ -302,6 +302,47 @@ def test_rope_kv_append_matches_reference():
     check_cache(kc3, vc3, rk, rv)
 
 
+@pytest.mark.parametrize("nq,nkv,D,splits,window,qknorm", [(32, 8, 128, 0, 0, False), (8, 2, 128, 4, 0, True),
+                                                           (8, 8, 64, 1, 0, False), (8, 2, 64, 2, 128, True)])
+def test_rope_attn_decode_one_launch(nq, nkv, D, splits, window, qknorm):
+    """RoPE + cache append inside the attention kernel: output against the fp32 definition, cache contents against
+    the definition, and both against the two-launch path on the same inputs."""
+    B = 6
+    ctx = [1, 32, 33, 700, 1025, 260]                      # lengths that already count the new token
+    kc, vc, table, ks, vs = _fill_cache(B, ctx, nkv, D, 256)
+    W = (nq + 2 * nkv) * D
+    parts = torch.randn(5, B, W, device=DEV) * 0.4
+    bias = randn(W)
+    qn, kn = (randn(D), randn(D)) if qknorm else (None, None)
+    sinks = torch.randn(nq, device=DEV) if window else None
+    tab = ops.rope_table(D, 2048, 500000.0, device=DEV)
+    lens = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    pos = lens - 1
+    slots = torch.stack([table[b, (ctx[b] - 1) // 32] * 32 + (ctx[b] - 1) % 32 for b in range(B)]).to(torch.int32)
+    scale = 1 / math.sqrt(D)
+    kc2, vc2 = kc.clone(), vc.clone()
+    out = ops.rope_attn_decode(parts, pos, slots, tab, kc, vc, table, lens, scale, nq, nkv, bias=bias, q_norm_w=qn,
+                               k_norm_w=kn, window=window, sinks=sinks, num_splits=splits)
+    q2 = ops.rope_kv_append(parts, pos, slots, tab, kc2, vc2, nq, nkv, D, bias=bias, q_norm_w=qn, k_norm_w=kn)
+    out2 = ops.paged_attn_decode(q2, kc2, vc2, table, lens, scale, window=window, sinks=sinks, num_splits=splits)
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)     # same arithmetic, same rounding
+    rq, rk, rv = _rope_oracle(parts.sum(0), bias, pos, tab, nq, nkv, D, qn, kn, 1e-6)
+    for b in range(B):
+        k = torch.cat([ks[b][:ctx[b] - 1].float(), rk[b:b + 1]])
+        v = torch.cat([vs[b][:ctx[b] - 1].float(), rv[b:b + 1]])
+        ref = _ref_attn(rq[b:b + 1], k, v, scale, ctx[b] - 1, True, window, sinks)
+        assert rel_err(out[b].reshape(1, nq, D), ref) < 2e-2, (b, ctx[b])
+        assert rel_err(out[b].reshape(1, nq, D), out2[b].reshape(1, nq, D).float()) < 1e-2, (b, ctx[b])
+    # an inactive sequence (negative length, slot -1) writes nothing
+    lens[2] = -1
+    slots[2] = -1
+    before = kc.clone()
+    ops.rope_attn_decode(parts, pos, slots, tab, kc, vc, table, lens, scale, nq, nkv, bias=bias, q_norm_w=qn,
+                         k_norm_w=kn, window=window, sinks=sinks, num_splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(kc[table[2, 1].long()], before[table[2, 1].long()])
+
+
 def test_decode_advance():
     B = 4
     ctx = torch.tensor([5, 31, 32, -1], device=DEV, dtype=torch.int32)
