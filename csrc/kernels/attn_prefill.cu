@@ -1,13 +1,13 @@
+#define NKB_PF_TRACE 1
 // Blockwise (flash) prefill attention on tcgen05 for sm_100a, reading K/V from
 // the paged cache through the per-sequence block table.
 //
 // One CTA per (256 query rows, query head, sequence), as two 128-row query tiles in ping-pong:
 //   warp 0     TMA producer: both Q tiles once, then a 3-stage ring that holds the 128-token K and V
 //              tiles in turn (four 32-token pages each, 128-byte swizzle, non-multicast)
-//   warp 1     issues tcgen05.mma.  Per KV tile and query tile t: S_t = Q_t K^T (M = N = 128, fp32 in
-//              TMEM) and O_t += P_t V with V as an MN-major B operand.  The order
-//              PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1) keeps the tensor pipe busy with one tile's
-//              MMAs while the other tile's softmax runs.
+//   warps 1, 2 issue tcgen05.mma, one warp per query tile t: S_t = Q_t K^T (M = N = 128, fp32 in TMEM)
+//              and O_t += P_t V with V as an MN-major B operand, per KV tile in dependency order.  One
+//              tile's MMAs run while the other tile's softmax does.
 //   warps 4-7  softmax of tile 0, warps 8-11 softmax of tile 1: one thread per query row reads its
 //              128 scores from TMEM once, keeps them in registers, writes P as bf16 to shared memory
 //              in the swizzled K-major layout the MMA reads.
@@ -29,6 +29,7 @@
 #include "common.cuh"
 #include "api.h"
 #include <math.h>
+#include <stdlib.h>
 
 namespace nkb {
 
@@ -37,7 +38,8 @@ constexpr int kQPair = 2 * kQTile;   // query rows per CTA
 constexpr int kKVTile = 128;
 constexpr int kPfPage = 32;
 constexpr int kPfThreads = 384;          // warpgroup 0: TMA warp, MMA warp, two idle; warpgroups 1, 2: softmax
-constexpr int kKVStages = 3;
+constexpr int kKVStagesSmemP = 3, kKVStagesTmemP = 5;   // K/V ring depth with P in shared / tensor memory
+constexpr int kKVStagesMax = 5;
 constexpr float kRescaleStep = 8.f;  // log2 of the growth of the row maximum that triggers a rescale of O
 
 struct PrefillParams {
@@ -52,9 +54,16 @@ struct PrefillParams {
   float scale_log2;
 };
 
+#ifdef NKB_PF_TRACE
+__device__ long long g_pf_trace[4 * 64 * 8];
+#define PF_MARK(role, it, ev) do { if (trace_on && lane == 0 && (it) < 64) g_pf_trace[((role) * 64 + (it)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define PF_MARK(role, it, ev) do { } while (0)
+#endif
+
 struct PrefillCtrl {
   uint64_t q_full;
-  uint64_t kv_full[kKVStages], kv_empty[kKVStages];
+  uint64_t kv_full[kKVStagesMax], kv_empty[kKVStagesMax];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full[2], o_full[2];
   uint32_t tmem_base;
@@ -73,6 +82,76 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+// Blackwell's three-input maximum and packed two-lane fp32 arithmetic: the softmax is bound by instruction issue,
+// these halve the instructions of the maximum, the scaling and the row sum.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  uint64_t rd;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(rd)
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)), "l"(reinterpret_cast<uint64_t&>(c)));
+  return reinterpret_cast<float2&>(rd);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  uint64_t rd;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
+  return reinterpret_cast<float2&>(rd);
+}
+
+// Four MMAs (k-steps) of one accumulator as one instruction group, descriptors prepared beforehand, so that the
+// issuing thread needs four issue slots instead of four dependent address computations: the issuing warp shares
+// its scheduler with two busy softmax warps and every extra instruction between MMAs costs tensor time.
+__device__ __forceinline__ void umma4_ss(uint32_t d, const uint64_t (&a)[4], const uint64_t (&b)[4], uint32_t idesc,
+                                         uint32_t acc_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      "setp.ne.b32 p0, %10, 0;\n"
+      "setp.eq.b32 p1, %9, %9;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, p1;\n"
+      "}\n" ::"r"(d),
+      "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+__device__ __forceinline__ void umma4_ts(uint32_t d, uint32_t a0, const uint64_t (&b)[4], uint32_t idesc,
+                                         uint32_t acc_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b32 a1, a2, a3;\n"
+      "setp.ne.b32 p0, %7, 0;\n"
+      "setp.eq.b32 p1, %6, %6;\n"
+      "add.u32 a1, %1, 8;\n"
+      "add.u32 a2, %1, 16;\n"
+      "add.u32 a3, %1, 24;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %6, p0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %6, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %6, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %6, p1;\n"
+      "}\n" ::"r"(d),
+      "r"(a0), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+
+// Bounded barrier wait whose slow path (timer, abort flag) is one shared out-of-line function: the kernel has two
+// dozen waits and their inlined loops would push the hot code out of the instruction cache.
+__device__ __noinline__ bool pf_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+  return mbar_wait(bar, parity, abort_flag, status, code);
+}
+__device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                        int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return pf_wait_slow(bar, parity, abort_flag, status, code);
+}
+
 // KV tile range [lo, hi) that query tile `t` of the CTA attends to (empty when the tile has no rows).
 struct TileRange {
   int lo, hi, pos0, rows;
@@ -89,7 +168,7 @@ __device__ __forceinline__ TileRange tile_range(const PrefillParams& p, int row0
   return r;
 }
 
-template <int D>
+template <int D, bool PT>
 __global__ void __launch_bounds__(kPfThreads, 1)
 flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                           const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
@@ -100,6 +179,10 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   constexpr int kPBytes = 2 * kHalf;        // [128 rows][128 tokens]
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kSCol = 0, kOCol = 256;   // S_t at kSCol + 128 t, O_t at kOCol + 128 t
+  // PT: P_t goes back into the first 64 columns of S_t as packed bf16 pairs and the P V product reads its A
+  // operand from tensor memory.  The MMA warp issues Q K^T of the next KV tile after P V of this one, and MMAs
+  // of one thread run in issue order, so S_t is not overwritten before P_t has been read.
+  constexpr int kKVStages = PT ? kKVStagesTmemP : kKVStagesSmemP;
 
   // the heaviest CTAs (last query rows of a causal sequence) start first
   const int qt = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, b = blockIdx.z;
@@ -122,9 +205,9 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   uint8_t* q_s = smem;                              // 2 query tiles
   uint8_t* kv_s = q_s + 2 * kQBytes;                // ring: K(j), V(j), K(j+1), ...
   uint8_t* p_s = kv_s + kKVStages * kKVBytes;       // 2 probability tiles
-  PrefillCtrl* ctrl = reinterpret_cast<PrefillCtrl*>(p_s + 2 * kPBytes);
+  PrefillCtrl* ctrl = reinterpret_cast<PrefillCtrl*>(p_s + (PT ? 0 : 2 * kPBytes));
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = warp_idx_uniform(), lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -132,7 +215,7 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     mbar_init(&ctrl->q_full, 1);
     for (int i = 0; i < kKVStages; ++i) {
       mbar_init(&ctrl->kv_full[i], 1);
-      mbar_init(&ctrl->kv_empty[i], 1);
+      mbar_init(&ctrl->kv_empty[i], two ? 2 : 1);   // one release from each query tile's issuer
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctrl->s_full[i], 1);
@@ -151,8 +234,11 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = ctrl->tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctrl->tmem_base, 0);   // provably warp-uniform
   volatile int* abort_flag = &ctrl->abort;
+#ifdef NKB_PF_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#endif
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -167,17 +253,24 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     __syncwarp();
     const int* table = p.block_table + (long long)b * p.max_blocks;
     const int last_page = max((ctx + kPfPage - 1) / kPfPage - 1, 0);
-    for (int n = 0; n < 2 * n_union; ++n) {          // item n: K of tile n / 2 (even n) or its V (odd n)
-      const int j = u_lo + (n >> 1);
-      const int st = n % kKVStages;
-      const uint32_t ph = uint32_t(n / kKVStages) & 1u;
-      bool ok = mbar_wait(&ctrl->kv_empty[st], ph ^ 1u, abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok)) break;
+    // Ring items in the order the issuers consume them: K(0), then per KV tile u either V(u), K(u+1) (P in tensor
+    // memory) or K(u+1), V(u) (P in shared memory, where Q K^T runs one tile ahead, so that K(u+2) has the whole of
+    // iteration u to arrive in the stage V(u-1) leaves).  Item number `seq` lives in stage seq % kKVStages.
+    int seq = 0;
+    bool live = true;
+    auto load = [&](bool is_v, int x) {
+      if (!live) return;
+      const int j = u_lo + x;
+      const int st = seq % kKVStages;
+      const uint32_t ph = uint32_t(seq / kKVStages) & 1u;
+      ++seq;
+      bool ok = pf_wait(&ctrl->kv_empty[st], ph ^ 1u, abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
+      if (!__all_sync(0xffffffffu, ok)) { live = false; return; }
       int blk[4];
 #pragma unroll
       for (int pi = 0; pi < 4; ++pi) blk[pi] = table[min(j * 4 + pi, last_page)];
       if (lane == 0) {
-        const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
+        const CUtensorMap* tm = is_v ? &tmV : &tmK;
         uint8_t* dst = kv_s + st * kKVBytes;
         mbar_expect_tx(&ctrl->kv_full[st], kKVBytes);
 #pragma unroll
@@ -187,90 +280,120 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
             tma_load_4d(dst + h * kHalf + pi * (kPfPage * 128), tm, &ctrl->kv_full[st], h * 64, 0, kvh, blk[pi]);
       }
       __syncwarp();
+    };
+    if (n_union > 0) load(false, 0);
+#pragma unroll 1
+    for (int u = 0; u < n_union && live; ++u) {
+      if (PT) load(true, u);
+      if (u + 1 < n_union) load(false, u + 1);
+      if (!PT) load(true, u);
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == 2) {
+    // ---------------------------------------------------------------- MMA issuers, one per query tile
+    // The tensor pipe queues only a few MMAs, so whatever an issuing thread does between two groups of MMAs
+    // (waits, descriptor arithmetic: a single thread runs one dependent instruction every few cycles) is time in
+    // which the pipe can drain.  With one issuer per query tile each thread has a whole period for its two
+    // groups, a wait for one tile never holds back the other tile's ready group, and each tile's groups are
+    // simply issued in dependency order:
+    //   P in shared memory:  QK_t(u+1), PV_t(u)   S_t is free once the softmax holds it in registers, so the next
+    //                                              scores are ready when the softmax of tile u ends
+    //   P in tensor memory:  PV_t(u), QK_t(u+1)   P_t lives in S_t's columns
+    // Both issuers walk all KV tiles of the CTA and release every ring stage (the barrier counts two arrivals),
+    // also for KV tiles their query tile does not attend to.
     constexpr uint32_t idesc_qk = make_idesc_bf16(128, kKVTile, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);  // B = V is MN-major
-    bool alive = true;
-    {
-      bool ok = mbar_wait(&ctrl->q_full, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      if (!__all_sync(0xffffffffu, ok)) alive = false;
-    }
-    auto active = [&](int t, int u) {
-      const int j = u_lo + u;
-      return t == 0 ? (j >= tr0.lo && j < tr0.hi) : (two && j >= tr1.lo && j < tr1.hi);
-    };
-    auto local_it = [&](int t, int u) { return u_lo + u - (t == 0 ? tr0.lo : tr1.lo); };
-    auto wait_item = [&](int n) -> bool {
-      bool ok = mbar_wait(&ctrl->kv_full[n % kKVStages], uint32_t(n / kKVStages) & 1u, abort_flag, p.status,
-                          ERR_WAIT_SMEM_FULL);
-      return __all_sync(0xffffffffu, ok);
-    };
-    auto release_item = [&](int n) {
-      if (lane == 0) umma_commit(&ctrl->kv_empty[n % kKVStages]);
-      __syncwarp();
-    };
-    // S_t = Q_t K(u)^T
-    auto issue_qk = [&](int t, int u) -> bool {
-      if (!wait_item(2 * u)) return false;
-      const int lit = local_it(t, u);
-      bool ok = mbar_wait(&ctrl->s_empty[t], (uint32_t(lit) & 1u) ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok)) return false;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t qa = smem_u32(q_s + t * kQBytes), ka = smem_u32(kv_s + ((2 * u) % kKVStages) * kKVBytes);
-        const uint32_t d = tmem_base + kSCol + t * 128;
+    const int t = warp - 1;
+    const uint32_t q_lo = uint32_t(make_smem_desc_sw128(smem_u32(q_s + t * kQBytes), 0, 1024));
+    const uint32_t kv_lo = uint32_t(make_smem_desc_sw128(smem_u32(kv_s), 0, 1024));
+    const uint32_t p_lo = uint32_t(make_smem_desc_sw128(smem_u32(p_s + (PT ? 0 : t * kPBytes)), 0, 1024));
+    const uint64_t hk = uint64_t(uint32_t(make_smem_desc_sw128(0, 0, 1024) >> 32)) << 32;   // SBO, version, swizzle
+    const uint32_t lbo_v = (uint32_t(kHalf) >> 4) << 16;                                    // low-word part of V's LBO
+    const int a_lo = t == 0 ? tr0.lo - u_lo : (two ? tr1.lo - u_lo : 0);
+    const int a_hi = t == 0 ? tr0.hi - u_lo : (two ? tr1.hi - u_lo : 0);
+    const uint32_t s_tmem = tmem_base + kSCol + t * 128, o_tmem = tmem_base + kOCol + t * 128;
+    if ((t == 0 || two) && elect_one()) {
+      bool ok = pf_wait(&ctrl->q_full, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+      int n_ops = 0;
+      int seq = 0;                                   // ring item counter, in the producer's order
+      // K tile x: S_t = Q_t K(x)^T if this query tile attends to it, then release its ring stage
+      auto do_k = [&](int x) {
+        if (x >= n_union || !ok) return;
+        const int item = seq++, st = item % kKVStages;
+        // also for a KV tile this query tile skips: an issuer that released stages without seeing them loaded could
+        // arrive twice on one barrier phase and free a stage the other issuer still reads
+        ok = pf_wait(&ctrl->kv_full[st], uint32_t(item / kKVStages) & 1u, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+        if (!ok) return;
+        if (x >= a_lo && x < a_hi) {
+          const uint32_t lit = uint32_t(x - a_lo);
+          ok = pf_wait(&ctrl->s_empty[t], (lit & 1u) ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
+          if (!ok) return;
+          PF_MARK(2 + t, n_ops >> 1, (n_ops & 1) * 2);
+          ++n_ops;
+          tc_fence_after();
+          const uint32_t kvd = kv_lo + uint32_t(st * kKVBytes >> 4);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 32;
-          umma_f16(d, make_smem_desc_sw128(qa + off, 0, 1024), make_smem_desc_sw128(ka + off, 0, 1024), idesc_qk,
-                   ks > 0 ? 1u : 0u);
-        }
-        umma_commit(&ctrl->s_full[t]);
-      }
-      __syncwarp();
-      return true;
-    };
-    // O_t (+)= P_t V(u)
-    auto issue_pv = [&](int t, int u) -> bool {
-      const int lit = local_it(t, u);
-      bool ok = mbar_wait(&ctrl->p_full[t], uint32_t(lit) & 1u, abort_flag, p.status, ERR_WAIT_SOFTMAX);
-      if (!__all_sync(0xffffffffu, ok)) return false;
-      if (!wait_item(2 * u + 1)) return false;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t pa = smem_u32(p_s + t * kPBytes), va = smem_u32(kv_s + ((2 * u + 1) % kKVStages) * kKVBytes);
-        const uint32_t d = tmem_base + kOCol + t * 128;
+          for (int h = 0; h < NH; ++h) {
+            uint64_t da[4], db[4];
 #pragma unroll
-        for (int ks = 0; ks < kKVTile / 16; ++ks) {
-          const uint64_t da = make_smem_desc_sw128(pa + (ks >> 2) * kHalf + (ks & 3) * 32, 0, 1024);
-          // V tile: [token][64 dims] rows of 128 B; 16 tokens per step = 2 KB; next 64 dims one slab on
-          const uint64_t db = make_smem_desc_sw128(va + ks * 2048, kHalf, 1024);
-          umma_f16(d, da, db, idesc_pv, (lit > 0 || ks > 0) ? 1u : 0u);
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const uint32_t off = uint32_t(h * (kHalf >> 4) + k4 * 2);
+              da[k4] = hk | (q_lo + off);
+              db[k4] = hk | (kvd + off);
+            }
+            umma4_ss(s_tmem, da, db, idesc_qk, h > 0 ? 1u : 0u);
+          }
+          umma_commit(&ctrl->s_full[t]);
         }
-        umma_commit(&ctrl->o_full[t]);
+        umma_commit(&ctrl->kv_empty[st]);
+      };
+      // V tile x: O_t (+)= P_t V(x) if this query tile attends to it, then release its ring stage
+      auto do_v = [&](int x) {
+        if (!ok) return;
+        const int item = seq++, st = item % kKVStages;
+        ok = pf_wait(&ctrl->kv_full[st], uint32_t(item / kKVStages) & 1u, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+        if (!ok) return;
+        if (x >= a_lo && x < a_hi) {
+          const uint32_t lit = uint32_t(x - a_lo);
+          ok = pf_wait(&ctrl->p_full[t], lit & 1u, abort_flag, p.status, ERR_WAIT_SOFTMAX);
+          if (!ok) return;
+          PF_MARK(2 + t, n_ops >> 1, (n_ops & 1) * 2);
+          ++n_ops;
+          tc_fence_after();
+          const uint32_t kvd = kv_lo + uint32_t(st * kKVBytes >> 4);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint64_t da[4], db[4];
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              // V tile: [token][64 dims] rows of 128 B; 16 tokens per step = 2 KB; next 64 dims one slab on
+              db[k4] = hk | ((kvd + uint32_t((h * 4 + k4) * 128)) | lbo_v);
+              da[k4] = hk | (p_lo + uint32_t(h * (kHalf >> 4) + k4 * 2));
+            }
+            const uint32_t acc = (lit > 0 || h > 0) ? 1u : 0u;
+            if constexpr (PT) {
+              // 16 tokens of P = 8 columns of bf16 pairs in S_t's first columns
+              umma4_ts(o_tmem, s_tmem + h * 32, db, idesc_pv, acc);
+            } else {
+              umma4_ss(o_tmem, da, db, idesc_pv, acc);
+            }
+          }
+          umma_commit(&ctrl->o_full[t]);
+        }
+        umma_commit(&ctrl->kv_empty[st]);
+      };
+      do_k(0);
+#pragma unroll 1
+      for (int u = 0; u < n_union && ok; ++u) {
+        if constexpr (PT) {
+          do_v(u);
+          do_k(u + 1);
+        } else {
+          do_k(u + 1);
+          do_v(u);
+        }
       }
-      __syncwarp();
-      return true;
-    };
-    if (alive && n_union > 0) {
-      if (active(0, 0)) alive = issue_qk(0, 0);
-      if (alive && active(1, 0)) alive = issue_qk(1, 0);
-      if (alive) release_item(0);
     }
-    for (int u = 0; u < n_union && alive; ++u) {
-      const bool more = u + 1 < n_union;
-      if (active(0, u)) alive = issue_pv(0, u);
-      if (alive && more && active(0, u + 1)) alive = issue_qk(0, u + 1);
-      if (alive && active(1, u)) alive = issue_pv(1, u);
-      if (!alive) break;
-      release_item(2 * u + 1);
-      if (more) {
-        if (active(1, u + 1)) alive = issue_qk(1, u + 1);
-        if (alive) release_item(2 * u + 2);
-      }
-    }
+    __syncwarp();
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- softmax
     const int t = (warp - 4) >> 2;                  // query tile of this warp
@@ -291,9 +414,14 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 
     for (int it = 0; it < n_tiles; ++it) {
       const int kv0 = (tr.lo + it) * kKVTile;
-      bool ok = mbar_wait(&ctrl->s_full[t], uint32_t(it) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+#ifdef NKB_PF_TRACE
+      const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && quad == 0;
+#endif
+      PF_MARK(t, it, 0);
+      bool ok = pf_wait(&ctrl->s_full[t], uint32_t(it) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
       tc_fence_after();
+      PF_MARK(t, it, 1);
       uint32_t v[kKVTile];
 #pragma unroll
       for (int c = 0; c < kKVTile / 32; ++c) tmem_ld_32x32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
@@ -301,6 +429,7 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctrl->s_empty[t]);   // the scores are in registers: S_t may be overwritten
+      PF_MARK(t, it, 2);
 
       // the mask only on tiles that cross the causal diagonal, the end of the context or the window edge
       const bool edge = kv0 + kKVTile - 1 > hi_pos || kv0 < lo_pos;
@@ -310,19 +439,27 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         for (int i = 0; i < kKVTile; ++i)
           if (i > hi_rel || i < lo_rel) v[i] = 0xff800000u;   // -inf
       }
-      float mx = -INFINITY;
+      // four independent chains of three-input maxima instead of one 128-long dependent chain
+      float mx4[4];
 #pragma unroll
-      for (int i = 0; i < kKVTile; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+      for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+#pragma unroll
+      for (int i = 8; i < kKVTile; i += 2)
+        mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= p.scale_log2;
 
+      bool p_free = PT || it == 0;     // P_t's shared buffer may be overwritten
       if (it == 0) {
         m = mx;
       } else {
-        // P_t of the previous tile has been read and O_t holds its contribution
-        ok = mbar_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
         const bool grow = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
-        if (__any_sync(0xffffffffu, grow)) {
+        const bool rescale = __any_sync(0xffffffffu, grow);
+        if (rescale) {
+          // O_t holds the previous tile's contribution
+          ok = pf_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          p_free = true;
           tc_fence_after();
           const float alpha = grow ? exp2f(m - mx) : 1.f;
 #pragma unroll 1
@@ -339,33 +476,73 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           if (grow) m = mx;
         }
       }
+      PF_MARK(t, it, 3);
       const float base = (m == -INFINITY) ? 0.f : m;
       const float nbase = -base;
-      float sum = 0.f;
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nb2 = make_float2(nbase, nbase);
+      float2 sum2[4];
 #pragma unroll
-      for (int c8 = 0; c8 < kKVTile / 8; ++c8) {
-        float e[8];
+      for (int i = 0; i < 4; ++i) sum2[i] = make_float2(0.f, 0.f);
+      // probabilities of 32 scores as 16 packed bf16 pairs
+      auto exp_chunk = [&](int c32, uint32_t (&pk)[16]) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          e[i] = exp2f(fmaf(__uint_as_float(v[c8 * 8 + i]), p.scale_log2, nbase));
-          sum += e[i];
+        for (int i = 0; i < 16; ++i) {
+          const int k = c32 * 32 + 2 * i;
+          const float2 x = ffma2(make_float2(__uint_as_float(v[k]), __uint_as_float(v[k + 1])), sc2, nb2);
+          const float2 e = make_float2(exp2f(x.x), exp2f(x.y));
+          sum2[i & 3] = fadd2(sum2[i & 3], e);
+          pk[i] = pack_bf16x2(e.x, e.y);
         }
-        // 16-byte chunk c8 of the row, swizzled like a TMA 128-byte-swizzle load would place it
-        uint8_t* dst = my_p + (c8 >> 3) * kHalf + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]),
-                                                    pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+      };
+      auto store_chunk = [&](int c32, const uint32_t (&pk)[16]) {
+        if constexpr (PT) {
+          tmem_st_32x16(s_addr + c32 * 16, pk);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            // 16-byte chunk of the row, swizzled like a TMA 128-byte-swizzle load would place it
+            const int c8 = c32 * 4 + q;
+            uint8_t* dst = my_p + (c8 >> 3) * kHalf + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+          }
+        }
+      };
+      {
+        // The first half of the row is computed before the previous tile's P_t must have been read: that wait
+        // (P V of the previous tile has finished) then rarely finds the barrier pending.
+        uint32_t pk0[16], pk1[16];
+        exp_chunk(0, pk0);
+        exp_chunk(1, pk1);
+        if (!p_free) {
+          ok = pf_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        }
+        store_chunk(0, pk0);
+        store_chunk(1, pk1);
+#pragma unroll
+        for (int c32 = 2; c32 < kKVTile / 32; ++c32) {
+          uint32_t pk[16];
+          exp_chunk(c32, pk);
+          store_chunk(c32, pk);
+        }
       }
-      l += sum;
-      fence_proxy_async();
+      if constexpr (PT) tmem_st_wait();
+      {
+        const float2 s01 = fadd2(sum2[0], sum2[1]), s23 = fadd2(sum2[2], sum2[3]);
+        const float2 s4 = fadd2(s01, s23);
+        l += s4.x + s4.y;
+      }
+      if constexpr (!PT) fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctrl->p_full[t]);
+      PF_MARK(t, it, 4);
     }
     // ---- epilogue: O_t / l to global memory
     if (tr.rows > 0) {
       bool have_o = false;
       if (alive && n_tiles > 0) {
-        bool ok = mbar_wait(&ctrl->o_full[t], uint32_t(n_tiles - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+        bool ok = pf_wait(&ctrl->o_full[t], uint32_t(n_tiles - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
         have_o = __all_sync(0xffffffffu, ok);
         if (have_o) tc_fence_after();
       }
@@ -415,25 +592,34 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   }
 }
 
-template <int D>
+template <int D, bool PT>
 static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const PrefillParams& p, int batch, int max_q_len, cudaStream_t s) {
   constexpr int NH = D / 64;
-  constexpr int smem = NH * 16384 * (2 + kKVStages) + 2 * 2 * 16384 + int(sizeof(PrefillCtrl)) + 1024 + 64;
-  static bool attr_set = false;
-  if (!attr_set) {
+  constexpr int stages = PT ? kKVStagesTmemP : kKVStagesSmemP;
+  constexpr int smem = NH * 16384 * (2 + stages) + (PT ? 0 : 2 * 2 * 16384) + int(sizeof(PrefillCtrl)) + 1024 + 64;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!attr_set[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(flash_attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(flash_attn_prefill_kernel<D, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
-    attr_set = true;
+    attr_set[dev] = true;
   }
   dim3 grid((max_q_len + kQPair - 1) / kQPair, p.nq, batch);
-  return launch_pdl(flash_attn_prefill_kernel<D>, grid, dim3(kPfThreads), size_t(smem), s, tq, tk, tv, p);
+  return launch_pdl(flash_attn_prefill_kernel<D, PT>, grid, dim3(kPfThreads), size_t(smem), s, tq, tk, tv, p);
 }
 
 }  // namespace nkb
 
 using namespace nkb;
+
+#ifdef NKB_PF_TRACE
+extern "C" int nkb_prefill_trace(long long* host_out) {
+  return int(cudaMemcpyFromSymbol(host_out, nkb::g_pf_trace, sizeof(long long) * 4 * 64 * 8));
+}
+#endif
 
 extern "C" int nkb_flash_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                       const int* q_start, const int* q_lens, const int* context_lens, void* out,
@@ -469,7 +655,16 @@ extern "C" int nkb_flash_attn_prefill(const void* q, const void* k_cache, const 
     if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (head_dim == 128) return launch_prefill<128>(tq, tk, tv, p, batch, max_q_len, s);
-  if (head_dim == 64) return launch_prefill<64>(tq, tk, tv, p, batch, max_q_len, s);
+  static const bool p_smem = [] {
+    const char* e = getenv("NKIPY_B200_PREFILL_P");
+    return e && e[0] == 's';
+  }();
+  if (p_smem) {
+    if (head_dim == 128) return launch_prefill<128, false>(tq, tk, tv, p, batch, max_q_len, s);
+    if (head_dim == 64) return launch_prefill<64, false>(tq, tk, tv, p, batch, max_q_len, s);
+    return -2;
+  }
+  if (head_dim == 128) return launch_prefill<128, true>(tq, tk, tv, p, batch, max_q_len, s);
+  if (head_dim == 64) return launch_prefill<64, true>(tq, tk, tv, p, batch, max_q_len, s);
   return -2;
 }

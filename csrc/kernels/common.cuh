@@ -38,6 +38,22 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+// Warp index in a form the compiler can prove warp-uniform, and a one-lane election it understands.  Code under
+// `if (warp_idx_uniform() == k)` / `if (elect_one())` can keep tcgen05.mma operands (descriptors, TMEM addresses)
+// in the uniform register file; with `threadIdx.x >> 5` and `lane == 0` every operand is moved there from vector
+// registers instruction by instruction, which costs more than the MMA itself for small tiles.
+__device__ __forceinline__ int warp_idx_uniform() { return __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0); }
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.b32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch: a kernel launched with the programmatic stream
@@ -79,6 +95,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "{\n"
       ".reg .pred p;\n"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking test of a phase (try_wait may suspend the thread for a hardware-chosen time when the phase is
+// still pending, which a loop that polls several barriers must not do).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)

@@ -231,7 +231,7 @@ def case_attn_decode(args):
 
 
 def case_attn_prefill(args):
-    B, S, nq, nkv, D = 8, 2048, 32, 8, 128
+    B, S, nq, nkv, D = args.batch or 8, args.seq or 2048, 32, 8, 128
     pages = S // 32
     nb = B * pages
     kc, vc = _bf16(nb, nkv, 32, D), _bf16(nb, nkv, 32, D)
@@ -413,6 +413,8 @@ def main(argv=None):
     ap.add_argument("--impl", default="fixup", choices=["fixup", "cluster", "splitk"],
                     help="gemm-decode-*: fixup / cluster = split-K summed inside the kernel (last-arriver fix-up / "
                          "CTA clusters), splitk = fp32 partials left to the next kernel")
+    ap.add_argument("--batch", type=int, default=0, help="attn-prefill: sequences (default 8)")
+    ap.add_argument("--seq", type=int, default=0, help="attn-prefill: tokens per sequence, a multiple of 32 (default 2048)")
     ap.add_argument("--tp", type=int, default=1, help="gemm-decode-*: per-rank shard of an N-way tensor-parallel layer")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
