@@ -1,16 +1,18 @@
-#define NKB_PF_TRACE 1
 // Blockwise (flash) prefill attention on tcgen05 for sm_100a, reading K/V from
 // the paged cache through the per-sequence block table.
 //
 // One CTA per (256 query rows, query head, sequence), as two 128-row query tiles in ping-pong:
-//   warp 0     TMA producer: both Q tiles once, then a 3-stage ring that holds the 128-token K and V
-//              tiles in turn (four 32-token pages each, 128-byte swizzle, non-multicast)
-//   warps 1, 2 issue tcgen05.mma, one warp per query tile t: S_t = Q_t K^T (M = N = 128, fp32 in TMEM)
-//              and O_t += P_t V with V as an MN-major B operand, per KV tile in dependency order.  One
-//              tile's MMAs run while the other tile's softmax does.
+//   warp 0     TMA producer: both Q tiles once, then a 3-stage ring of 128-token K and V tiles (four
+//              32-token pages each, 128-byte swizzle, non-multicast)
+//   warps 1, 2 issue tcgen05.mma, one warp per query tile t, per KV tile j in the order
+//              S_t(j+1) = Q_t K(j+1)^T, then O_t += P_t(j) V(j) (V is an MN-major B operand).  S_t is free
+//              as soon as the softmax holds it in registers, so the next scores are ready when the
+//              softmax of tile j ends and the softmax warps do not wait for the tensor pipe.
 //   warps 4-7  softmax of tile 0, warps 8-11 softmax of tile 1: one thread per query row reads its
-//              128 scores from TMEM once, keeps them in registers, writes P as bf16 to shared memory
-//              in the swizzled K-major layout the MMA reads.
+//              128 scores from TMEM once, keeps them in registers, and writes P as bf16 to shared memory
+//              in the swizzled K-major layout the MMA reads.  The two tiles take turns with their
+//              exponentials (see the loop), so that one tile's MMAs, score loads and row maxima run
+//              while the other tile has the special-function unit.
 // O_0 and O_1 stay in TMEM for the whole KV loop (S_0, S_1, O_0, O_1 = 4 x 128 columns).  The row maximum
 // that scales the exponentials is only raised when the true maximum has grown by more than 2^8 since it
 // was last set; then the row's O is rescaled in TMEM (load, multiply, store).  With a stale maximum the
@@ -21,6 +23,20 @@
 // masking with a cached prefix (q_len <= context_len), sliding windows and
 // attention-sink logits.
 //
+// What the structure answers to (measured on B200 with a cycle trace of one CTA and an issue-rate probe):
+// * The tensor pipe runs a 128 x 128 x 16 MMA in 64 cycles from any operand source, but queues only a few of
+//   them: whatever the issuing thread does between two groups of MMAs is time in which the pipe drains.  A single
+//   thread runs one dependent instruction every few cycles, and a blocking wait for one query tile kept the
+//   other tile's ready group from being issued.  Hence one issuer per query tile, issue by a single elected
+//   thread without warp votes, descriptors prepared before four MMAs go out as one instruction sequence, and
+//   warp roles the compiler can prove uniform.
+// * 128 exponentials per row keep the special-function unit of a scheduler busy for about as long as the rest
+//   of an iteration takes.  Left alone, the two query tiles fall into step (they share the K/V ring), compute
+//   their exponentials at half speed at the same time and then wait at the same time.
+// * Computing part of the exponentials with a polynomial on the FMA pipe, a branch per 32 scores in the
+//   exponential loop (to skip fully masked groups) and probabilities in tensor memory (which ties Q K^T of
+//   the next tile to P V of this one) were all measured slower than what is here.
+//
 // Reference parity: prefill branch of attention_kernel in
 // examples/models/qwen3/kernels/attention.py:108-137 (materialised scores +
 // additive -1e5 mask + softmax + P.V), window / sinks from
@@ -29,7 +45,6 @@
 #include "common.cuh"
 #include "api.h"
 #include <math.h>
-#include <stdlib.h>
 
 namespace nkb {
 
@@ -37,9 +52,8 @@ constexpr int kQTile = 128;          // rows of one MMA tile
 constexpr int kQPair = 2 * kQTile;   // query rows per CTA
 constexpr int kKVTile = 128;
 constexpr int kPfPage = 32;
-constexpr int kPfThreads = 384;          // warpgroup 0: TMA warp, MMA warp, two idle; warpgroups 1, 2: softmax
-constexpr int kKVStagesSmemP = 3, kKVStagesTmemP = 5;   // K/V ring depth with P in shared / tensor memory
-constexpr int kKVStagesMax = 5;
+constexpr int kPfThreads = 384;      // warpgroup 0: TMA warp, two MMA warps, one idle; warpgroups 1, 2: softmax
+constexpr int kKVStages = 3;
 constexpr float kRescaleStep = 8.f;  // log2 of the growth of the row maximum that triggers a rescale of O
 
 struct PrefillParams {
@@ -54,18 +68,12 @@ struct PrefillParams {
   float scale_log2;
 };
 
-#ifdef NKB_PF_TRACE
-__device__ long long g_pf_trace[4 * 64 * 8];
-#define PF_MARK(role, it, ev) do { if (trace_on && lane == 0 && (it) < 64) g_pf_trace[((role) * 64 + (it)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define PF_MARK(role, it, ev) do { } while (0)
-#endif
-
 struct PrefillCtrl {
   uint64_t q_full;
-  uint64_t kv_full[kKVStagesMax], kv_empty[kKVStagesMax];
+  uint64_t kv_full[kKVStages], kv_empty[kKVStages];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full[2], o_full[2];
+  uint64_t turn[2][4];
   uint32_t tmem_base;
   int abort;
 };
@@ -82,8 +90,8 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
-// Blackwell's three-input maximum and packed two-lane fp32 arithmetic: the softmax is bound by instruction issue,
-// these halve the instructions of the maximum, the scaling and the row sum.
+// Blackwell's three-input maximum and packed two-lane fp32 arithmetic halve the instructions of the row
+// maximum, the scaling and the row sum.
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -102,9 +110,7 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   return reinterpret_cast<float2&>(rd);
 }
 
-// Four MMAs (k-steps) of one accumulator as one instruction group, descriptors prepared beforehand, so that the
-// issuing thread needs four issue slots instead of four dependent address computations: the issuing warp shares
-// its scheduler with two busy softmax warps and every extra instruction between MMAs costs tensor time.
+// Four MMAs (k-steps) of one accumulator as one instruction sequence, descriptors prepared beforehand.
 __device__ __forceinline__ void umma4_ss(uint32_t d, const uint64_t (&a)[4], const uint64_t (&b)[4], uint32_t idesc,
                                          uint32_t acc_first) {
   asm volatile(
@@ -118,25 +124,6 @@ __device__ __forceinline__ void umma4_ss(uint32_t d, const uint64_t (&a)[4], con
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, p1;\n"
       "}\n" ::"r"(d),
       "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc), "r"(acc_first)
-      : "memory");
-}
-__device__ __forceinline__ void umma4_ts(uint32_t d, uint32_t a0, const uint64_t (&b)[4], uint32_t idesc,
-                                         uint32_t acc_first) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p0, p1;\n"
-      ".reg .b32 a1, a2, a3;\n"
-      "setp.ne.b32 p0, %7, 0;\n"
-      "setp.eq.b32 p1, %6, %6;\n"
-      "add.u32 a1, %1, 8;\n"
-      "add.u32 a2, %1, 16;\n"
-      "add.u32 a3, %1, 24;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %6, p0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %6, p1;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %6, p1;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %6, p1;\n"
-      "}\n" ::"r"(d),
-      "r"(a0), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc), "r"(acc_first)
       : "memory");
 }
 
@@ -168,7 +155,7 @@ __device__ __forceinline__ TileRange tile_range(const PrefillParams& p, int row0
   return r;
 }
 
-template <int D, bool PT>
+template <int D>
 __global__ void __launch_bounds__(kPfThreads, 1)
 flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                           const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
@@ -179,10 +166,6 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   constexpr int kPBytes = 2 * kHalf;        // [128 rows][128 tokens]
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kSCol = 0, kOCol = 256;   // S_t at kSCol + 128 t, O_t at kOCol + 128 t
-  // PT: P_t goes back into the first 64 columns of S_t as packed bf16 pairs and the P V product reads its A
-  // operand from tensor memory.  The MMA warp issues Q K^T of the next KV tile after P V of this one, and MMAs
-  // of one thread run in issue order, so S_t is not overwritten before P_t has been read.
-  constexpr int kKVStages = PT ? kKVStagesTmemP : kKVStagesSmemP;
 
   // the heaviest CTAs (last query rows of a causal sequence) start first
   const int qt = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, b = blockIdx.z;
@@ -203,9 +186,9 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;                              // 2 query tiles
-  uint8_t* kv_s = q_s + 2 * kQBytes;                // ring: K(j), V(j), K(j+1), ...
+  uint8_t* kv_s = q_s + 2 * kQBytes;                // ring of K and V tiles
   uint8_t* p_s = kv_s + kKVStages * kKVBytes;       // 2 probability tiles
-  PrefillCtrl* ctrl = reinterpret_cast<PrefillCtrl*>(p_s + (PT ? 0 : 2 * kPBytes));
+  PrefillCtrl* ctrl = reinterpret_cast<PrefillCtrl*>(p_s + 2 * kPBytes);
 
   const int warp = warp_idx_uniform(), lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -222,6 +205,7 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       mbar_init(&ctrl->s_empty[i], 4);
       mbar_init(&ctrl->p_full[i], 4);
       mbar_init(&ctrl->o_full[i], 1);
+      for (int q = 0; q < 4; ++q) mbar_init(&ctrl->turn[i][q], 1);
     }
     ctrl->abort = 0;
     mbar_fence_init();
@@ -236,9 +220,6 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctrl->tmem_base, 0);   // provably warp-uniform
   volatile int* abort_flag = &ctrl->abort;
-#ifdef NKB_PF_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#endif
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -253,9 +234,8 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     __syncwarp();
     const int* table = p.block_table + (long long)b * p.max_blocks;
     const int last_page = max((ctx + kPfPage - 1) / kPfPage - 1, 0);
-    // Ring items in the order the issuers consume them: K(0), then per KV tile u either V(u), K(u+1) (P in tensor
-    // memory) or K(u+1), V(u) (P in shared memory, where Q K^T runs one tile ahead, so that K(u+2) has the whole of
-    // iteration u to arrive in the stage V(u-1) leaves).  Item number `seq` lives in stage seq % kKVStages.
+    // Ring items in the order the issuers consume them: K(0), then per KV tile u: K(u+1), V(u).  Q K^T runs one
+    // tile ahead of P V, so K(u+2) has the whole of iteration u to arrive.  Item `seq` lives in stage seq % 3.
     int seq = 0;
     bool live = true;
     auto load = [&](bool is_v, int x) {
@@ -284,28 +264,20 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     if (n_union > 0) load(false, 0);
 #pragma unroll 1
     for (int u = 0; u < n_union && live; ++u) {
-      if (PT) load(true, u);
       if (u + 1 < n_union) load(false, u + 1);
-      if (!PT) load(true, u);
+      load(true, u);
     }
   } else if (warp == 1 || warp == 2) {
     // ---------------------------------------------------------------- MMA issuers, one per query tile
-    // The tensor pipe queues only a few MMAs, so whatever an issuing thread does between two groups of MMAs
-    // (waits, descriptor arithmetic: a single thread runs one dependent instruction every few cycles) is time in
-    // which the pipe can drain.  With one issuer per query tile each thread has a whole period for its two
-    // groups, a wait for one tile never holds back the other tile's ready group, and each tile's groups are
-    // simply issued in dependency order:
-    //   P in shared memory:  QK_t(u+1), PV_t(u)   S_t is free once the softmax holds it in registers, so the next
-    //                                              scores are ready when the softmax of tile u ends
-    //   P in tensor memory:  PV_t(u), QK_t(u+1)   P_t lives in S_t's columns
-    // Both issuers walk all KV tiles of the CTA and release every ring stage (the barrier counts two arrivals),
-    // also for KV tiles their query tile does not attend to.
+    // Both issuers walk all KV tiles of the CTA in the producer's order and release every ring stage (the barrier
+    // counts two arrivals), also for KV tiles their query tile does not attend to; each waits for a stage to be
+    // loaded before it releases it, so that an issuer can never arrive twice on one barrier phase.
     constexpr uint32_t idesc_qk = make_idesc_bf16(128, kKVTile, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);  // B = V is MN-major
     const int t = warp - 1;
     const uint32_t q_lo = uint32_t(make_smem_desc_sw128(smem_u32(q_s + t * kQBytes), 0, 1024));
     const uint32_t kv_lo = uint32_t(make_smem_desc_sw128(smem_u32(kv_s), 0, 1024));
-    const uint32_t p_lo = uint32_t(make_smem_desc_sw128(smem_u32(p_s + (PT ? 0 : t * kPBytes)), 0, 1024));
+    const uint32_t p_lo = uint32_t(make_smem_desc_sw128(smem_u32(p_s + t * kPBytes), 0, 1024));
     const uint64_t hk = uint64_t(uint32_t(make_smem_desc_sw128(0, 0, 1024) >> 32)) << 32;   // SBO, version, swizzle
     const uint32_t lbo_v = (uint32_t(kHalf) >> 4) << 16;                                    // low-word part of V's LBO
     const int a_lo = t == 0 ? tr0.lo - u_lo : (two ? tr1.lo - u_lo : 0);
@@ -313,22 +285,17 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     const uint32_t s_tmem = tmem_base + kSCol + t * 128, o_tmem = tmem_base + kOCol + t * 128;
     if ((t == 0 || two) && elect_one()) {
       bool ok = pf_wait(&ctrl->q_full, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      int n_ops = 0;
       int seq = 0;                                   // ring item counter, in the producer's order
       // K tile x: S_t = Q_t K(x)^T if this query tile attends to it, then release its ring stage
       auto do_k = [&](int x) {
         if (x >= n_union || !ok) return;
         const int item = seq++, st = item % kKVStages;
-        // also for a KV tile this query tile skips: an issuer that released stages without seeing them loaded could
-        // arrive twice on one barrier phase and free a stage the other issuer still reads
         ok = pf_wait(&ctrl->kv_full[st], uint32_t(item / kKVStages) & 1u, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
         if (!ok) return;
         if (x >= a_lo && x < a_hi) {
           const uint32_t lit = uint32_t(x - a_lo);
           ok = pf_wait(&ctrl->s_empty[t], (lit & 1u) ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
           if (!ok) return;
-          PF_MARK(2 + t, n_ops >> 1, (n_ops & 1) * 2);
-          ++n_ops;
           tc_fence_after();
           const uint32_t kvd = kv_lo + uint32_t(st * kKVBytes >> 4);
 #pragma unroll
@@ -356,8 +323,6 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           const uint32_t lit = uint32_t(x - a_lo);
           ok = pf_wait(&ctrl->p_full[t], lit & 1u, abort_flag, p.status, ERR_WAIT_SOFTMAX);
           if (!ok) return;
-          PF_MARK(2 + t, n_ops >> 1, (n_ops & 1) * 2);
-          ++n_ops;
           tc_fence_after();
           const uint32_t kvd = kv_lo + uint32_t(st * kKVBytes >> 4);
 #pragma unroll
@@ -369,28 +334,17 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
               db[k4] = hk | ((kvd + uint32_t((h * 4 + k4) * 128)) | lbo_v);
               da[k4] = hk | (p_lo + uint32_t(h * (kHalf >> 4) + k4 * 2));
             }
-            const uint32_t acc = (lit > 0 || h > 0) ? 1u : 0u;
-            if constexpr (PT) {
-              // 16 tokens of P = 8 columns of bf16 pairs in S_t's first columns
-              umma4_ts(o_tmem, s_tmem + h * 32, db, idesc_pv, acc);
-            } else {
-              umma4_ss(o_tmem, da, db, idesc_pv, acc);
-            }
+            umma4_ss(o_tmem, da, db, idesc_pv, (lit > 0 || h > 0) ? 1u : 0u);
           }
-          umma_commit(&ctrl->o_full[t]);
+          umma_commit(&ctrl->o_full[t]);            // P_t has been read, O_t holds its product
         }
         umma_commit(&ctrl->kv_empty[st]);
       };
       do_k(0);
 #pragma unroll 1
       for (int u = 0; u < n_union && ok; ++u) {
-        if constexpr (PT) {
-          do_v(u);
-          do_k(u + 1);
-        } else {
-          do_k(u + 1);
-          do_v(u);
-        }
+        do_k(u + 1);
+        do_v(u);
       }
     }
     __syncwarp();
@@ -404,8 +358,9 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_off + kSCol + t * 128;
     const uint32_t o_addr = tmem_base + lane_off + kOCol + t * 128;
-    uint8_t* my_p = p_s + t * kPBytes;
+    uint8_t* my_p = p_s + t * kPBytes + r * 128;
     const int n_tiles = tr.hi - tr.lo;
+    const int n_other = t == 0 ? (two ? tr1.hi - tr1.lo : 0) : tr0.hi - tr0.lo;   // KV tiles of the other query tile
     float m = -INFINITY, l = 0.f;
     int hi_pos = ctx - 1;
     if (p.causal) hi_pos = min(hi_pos, q_pos);
@@ -414,14 +369,9 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 
     for (int it = 0; it < n_tiles; ++it) {
       const int kv0 = (tr.lo + it) * kKVTile;
-#ifdef NKB_PF_TRACE
-      const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && quad == 0;
-#endif
-      PF_MARK(t, it, 0);
       bool ok = pf_wait(&ctrl->s_full[t], uint32_t(it) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
       tc_fence_after();
-      PF_MARK(t, it, 1);
       uint32_t v[kKVTile];
 #pragma unroll
       for (int c = 0; c < kKVTile / 32; ++c) tmem_ld_32x32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
@@ -429,7 +379,6 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctrl->s_empty[t]);   // the scores are in registers: S_t may be overwritten
-      PF_MARK(t, it, 2);
 
       // the mask only on tiles that cross the causal diagonal, the end of the context or the window edge
       const bool edge = kv0 + kKVTile - 1 > hi_pos || kv0 < lo_pos;
@@ -449,14 +398,13 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= p.scale_log2;
 
-      bool p_free = PT || it == 0;     // P_t's shared buffer may be overwritten
+      bool p_free = it == 0;     // the P_t buffer may be overwritten (P V of the previous tile has finished)
       if (it == 0) {
         m = mx;
       } else {
         const bool grow = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
-        const bool rescale = __any_sync(0xffffffffu, grow);
-        if (rescale) {
-          // O_t holds the previous tile's contribution
+        if (__any_sync(0xffffffffu, grow)) {
+          // O_t holds all of the previous tile's contribution
           ok = pf_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
           if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
           p_free = true;
@@ -476,10 +424,8 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           if (grow) m = mx;
         }
       }
-      PF_MARK(t, it, 3);
       const float base = (m == -INFINITY) ? 0.f : m;
-      const float nbase = -base;
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nb2 = make_float2(nbase, nbase);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nb2 = make_float2(-base, -base);
       float2 sum2[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) sum2[i] = make_float2(0.f, 0.f);
@@ -494,49 +440,45 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           pk[i] = pack_bf16x2(e.x, e.y);
         }
       };
-      auto store_chunk = [&](int c32, const uint32_t (&pk)[16]) {
-        if constexpr (PT) {
-          tmem_st_32x16(s_addr + c32 * 16, pk);
-        } else {
+      // 32 tokens = four 16-byte chunks of the row, swizzled like a TMA 128-byte-swizzle load places them
+      auto store_chunk = [&](int c, const uint32_t (&pk)[16]) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            // 16-byte chunk of the row, swizzled like a TMA 128-byte-swizzle load would place it
-            const int c8 = c32 * 4 + q;
-            uint8_t* dst = my_p + (c8 >> 3) * kHalf + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
-            *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-          }
-        }
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(my_p + (c >> 1) * kHalf + ((((c & 1) * 4 + q) ^ (r & 7)) << 4)) =
+              make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
       };
-      {
-        // The first half of the row is computed before the previous tile's P_t must have been read: that wait
-        // (P V of the previous tile has finished) then rarely finds the barrier pending.
-        uint32_t pk0[16], pk1[16];
-        exp_chunk(0, pk0);
-        exp_chunk(1, pk1);
-        if (!p_free) {
-          ok = pf_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
-          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        }
-        store_chunk(0, pk0);
-        store_chunk(1, pk1);
-#pragma unroll
-        for (int c32 = 2; c32 < kKVTile / 32; ++c32) {
-          uint32_t pk[16];
-          exp_chunk(c32, pk);
-          store_chunk(c32, pk);
-        }
+      // P_t's buffer is free once P V of the previous tile has finished
+      if (!p_free) {
+        ok = pf_wait(&ctrl->o_full[t], uint32_t(it - 1) & 1u, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
       }
-      if constexpr (PT) tmem_st_wait();
+      // The exponentials of the two query tiles take turns.  The warps of tile 0 and tile 1 that own the same TMEM
+      // lanes share a scheduler and its special-function unit, which 128 exponentials per row keep busy for about
+      // as long as the rest of an iteration takes; left alone the two tiles fall into step (they share the K/V
+      // ring), both compute exponentials at half speed and then both wait.  Alternating lets one tile use the unit
+      // at full speed while the other loads its scores, takes the maximum and publishes P.
+      // Order: tile 0 (it), tile 1 (it), tile 0 (it + 1), ...; a tile that has run out of KV tiles is not waited for.
+      if (t == 0 ? (it >= 1 && it - 1 < n_other) : (it < n_other)) {
+        ok = pf_wait(&ctrl->turn[t][quad], uint32_t(t == 0 ? it - 1 : it) & 1u, abort_flag, p.status, ERR_WAIT_SOFTMAX);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+      }
+#pragma unroll
+      for (int c = 0; c < kKVTile / 32; ++c) {
+        uint32_t pk[16];
+        exp_chunk(c, pk);
+        store_chunk(c, pk);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctrl->turn[1 - t][quad]);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctrl->p_full[t]);
       {
         const float2 s01 = fadd2(sum2[0], sum2[1]), s23 = fadd2(sum2[2], sum2[3]);
         const float2 s4 = fadd2(s01, s23);
         l += s4.x + s4.y;
       }
-      if constexpr (!PT) fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctrl->p_full[t]);
-      PF_MARK(t, it, 4);
     }
     // ---- epilogue: O_t / l to global memory
     if (tr.rows > 0) {
@@ -592,34 +534,27 @@ flash_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   }
 }
 
-template <int D, bool PT>
+template <int D>
 static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const PrefillParams& p, int batch, int max_q_len, cudaStream_t s) {
   constexpr int NH = D / 64;
-  constexpr int stages = PT ? kKVStagesTmemP : kKVStagesSmemP;
-  constexpr int smem = NH * 16384 * (2 + stages) + (PT ? 0 : 2 * 2 * 16384) + int(sizeof(PrefillCtrl)) + 1024 + 64;
+  constexpr int smem = NH * 16384 * (2 + kKVStages) + 2 * 2 * 16384 + int(sizeof(PrefillCtrl)) + 1024 + 64;
   static bool attr_set[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
   if (!attr_set[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(flash_attn_prefill_kernel<D, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(flash_attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
     attr_set[dev] = true;
   }
   dim3 grid((max_q_len + kQPair - 1) / kQPair, p.nq, batch);
-  return launch_pdl(flash_attn_prefill_kernel<D, PT>, grid, dim3(kPfThreads), size_t(smem), s, tq, tk, tv, p);
+  return launch_pdl(flash_attn_prefill_kernel<D>, grid, dim3(kPfThreads), size_t(smem), s, tq, tk, tv, p);
 }
 
 }  // namespace nkb
 
 using namespace nkb;
-
-#ifdef NKB_PF_TRACE
-extern "C" int nkb_prefill_trace(long long* host_out) {
-  return int(cudaMemcpyFromSymbol(host_out, nkb::g_pf_trace, sizeof(long long) * 4 * 64 * 8));
-}
-#endif
 
 extern "C" int nkb_flash_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                       const int* q_start, const int* q_lens, const int* context_lens, void* out,
@@ -655,16 +590,7 @@ extern "C" int nkb_flash_attn_prefill(const void* q, const void* k_cache, const 
     if (encode_tmap_bf16(&tv, v_cache, 4, dims, strides, box)) return -4;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  static const bool p_smem = [] {
-    const char* e = getenv("NKIPY_B200_PREFILL_P");
-    return e && e[0] == 's';
-  }();
-  if (p_smem) {
-    if (head_dim == 128) return launch_prefill<128, false>(tq, tk, tv, p, batch, max_q_len, s);
-    if (head_dim == 64) return launch_prefill<64, false>(tq, tk, tv, p, batch, max_q_len, s);
-    return -2;
-  }
-  if (head_dim == 128) return launch_prefill<128, true>(tq, tk, tv, p, batch, max_q_len, s);
-  if (head_dim == 64) return launch_prefill<64, true>(tq, tk, tv, p, batch, max_q_len, s);
+  if (head_dim == 128) return launch_prefill<128>(tq, tk, tv, p, batch, max_q_len, s);
+  if (head_dim == 64) return launch_prefill<64>(tq, tk, tv, p, batch, max_q_len, s);
   return -2;
 }
