@@ -50,7 +50,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(base);
   uint8_t* tiles = base + 1024;
-  const int warp = threadIdx.x >> 5;
+  const int warp = warp_idx_uniform();
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();        // 0 = issues the MMAs
   const int stages = args.stages;
@@ -122,43 +122,44 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
   } else if (warp == 1 && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer (first CTA of the pair)
+    // One elected thread runs the whole loop alone: the tensor pipe queues only a few MMAs, so warp votes,
+    // reconvergence and descriptor arithmetic between two k-blocks are time in which it drains.
     constexpr uint32_t idesc = make_idesc_bf16(256, k2TileN, 0, 0);
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool alive = true;
-    for (int w = pair; w < total_work && alive; w += npairs) {
-      bool ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
-      if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-      tc_fence_after();
-      const uint32_t d0 = tmem_base + uint32_t(acc * k2TileN);
-      for (int kb = 0; kb < args.kb_total; ++kb) {
-        ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(tiles + stage * k2StageBytes);
-          const uint64_t da = make_smem_desc_sw128(a_addr, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(a_addr + kATileBytes, 0, 1024);
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      const uint64_t d_tiles = make_smem_desc_sw128(smem_u32(tiles), 0, 1024);
+      const uint64_t d_hi = d_tiles & 0xffffffff00000000ull;
+      const uint32_t a_lo0 = uint32_t(d_tiles);
+      const uint32_t empty0 = map_to_cta(&ctrl->empty[0], 0), empty1 = map_to_cta(&ctrl->empty[0], 1);
+      bool ok = true;
+      for (int w = pair; w < total_work && ok; w += npairs) {
+        ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
+        if (!ok) break;
+        const uint32_t d0 = tmem_base + uint32_t(acc * k2TileN);
+        for (int kb = 0; kb < args.kb_total; ++kb) {
+          ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + uint32_t(stage) * uint32_t(k2StageBytes >> 4);
+          const uint64_t da = d_hi | a_lo, db = d_hi | (a_lo + uint32_t(kATileBytes >> 4));
 #pragma unroll
           for (int k = 0; k < kBlockK / 16; ++k)
             umma_f16_pair(d0, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          umma_commit_pair(map_to_cta(&ctrl->empty[stage], 0));
-          umma_commit_pair(map_to_cta(&ctrl->empty[stage], 1));
+          umma_commit_pair(empty0 + uint32_t(stage) * 8u);
+          umma_commit_pair(empty1 + uint32_t(stage) * 8u);
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
-        __syncwarp();
-        if (++stage == stages) { stage = 0; phase ^= 1u; }
-      }
-      if (!alive) break;
-      if (lane == 0) {
+        if (!ok) break;
         umma_commit_pair(map_to_cta(&ctrl->tfull[acc], 0));
         umma_commit_pair(map_to_cta(&ctrl->tfull[acc], 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
       }
-      __syncwarp();
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
     }
+    __syncwarp();
   } else if (warp >= 2) {
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
