@@ -139,11 +139,28 @@ class Heartbeat:
             return None
         return float(v.decode() if isinstance(v, (bytes, bytearray)) else v)
 
+    def has_left(self, rank: int) -> bool:
+        """True once `rank` has announced its departure with `stop()`."""
+        key = f"left/{rank}"
+        check = getattr(self.store, "check", None)
+        try:
+            if check is not None:                 # TCPStore: `get` would block on a missing key
+                return bool(check([key]))
+            self.store.get(key)
+            return True
+        except Exception:
+            return False
+
     def dead_ranks(self, timeout_s: float = 1.0) -> List[int]:
+        """Ranks that announced their departure or whose last beat is older than `timeout_s`.  The announcement
+        makes a clean departure visible at once, whatever the beat interval and the scheduler did."""
         now = time.time()
         dead = []
         for r in range(self.world_size):
             if r == self.rank:
+                continue
+            if self.has_left(r):
+                dead.append(r)
                 continue
             t = self.last_seen(r)
             if t is None or now - t > timeout_s:
@@ -151,9 +168,13 @@ class Heartbeat:
         return dead
 
     def stop(self):
-        """Stop beating (what a leaving rank does between steps)."""
+        """Stop beating and announce the departure (what a leaving rank does between steps)."""
         self._stop.set()
         self._thread.join(timeout=1.0)
+        try:
+            self.store.set(f"left/{self.rank}", "1")
+        except Exception:
+            pass
 
 
 # ----------------------------------------------------------------------------- fault injection (host only)

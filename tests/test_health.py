@@ -159,8 +159,8 @@ def _leave_worker(rank, world, port, hb_port, q):
     try:
         for step in range(6):
             plan.before_step(rank, step)                       # rank 1 leaves before step 3, nothing in flight
-            time.sleep(0.4)                                    # host work between steps
-            dead = hb.dead_ranks(timeout_s=0.3)
+            time.sleep(1.0)                                    # host work between steps, well above the time-out
+            dead = hb.dead_ranks(timeout_s=0.3)                # and the leaving rank announces itself in stop()
             if dead:                                           # learnt on the host, before the next launch
                 q.put((rank, "peer-left", dead, steps_done))
                 return
@@ -323,3 +323,30 @@ def test_recover_rebuilds_fused_tp_after_a_rank_left():
     all-reduce + RMSNorm step is right again on both."""
     rec = _run_recovery(use_gpu=True)
     assert set(rec) == {0, 1} and all(e[2] < 2e-2 for e in rec.values()), rec
+
+
+def test_departure_is_announced_and_seen_at_once():
+    """A rank that stops its heartbeat writes an explicit key; its peer lists it as gone without waiting for the
+    beat to age, and a rank that merely beats late is not listed before the time-out."""
+    class DictStore:
+        def __init__(self):
+            self.d = {}
+
+        def set(self, k, v):
+            self.d[k] = v
+
+        def get(self, k):
+            return self.d[k]
+
+    store = DictStore()
+    a = Heartbeat(store, 0, 2, interval_s=0.02)
+    b = Heartbeat(store, 1, 2, interval_s=0.02)
+    try:
+        assert a.dead_ranks(timeout_s=5.0) == []
+        assert not a.has_left(1)
+        b.stop()
+        assert a.has_left(1)
+        assert a.dead_ranks(timeout_s=5.0) == [1]            # far inside the time-out
+        assert b.dead_ranks(timeout_s=5.0) == []             # rank 0 still beats
+    finally:
+        a.stop()
