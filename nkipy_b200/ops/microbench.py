@@ -410,7 +410,7 @@ def main(argv=None):
     ap.add_argument("--splits", type=int, default=0, help="override the split-K factor of the gemm-decode-* cases")
     ap.add_argument("--kv-splits", type=int, default=0, help="split-KV factor of attn-decode (0 = heuristic)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count of the gemm-decode-* cases")
-    ap.add_argument("--impl", default="fixup", choices=["fixup", "cluster", "splitk"],
+    ap.add_argument("--impl", default="splitk", choices=["fixup", "cluster", "splitk"],
                     help="gemm-decode-*: fixup / cluster = split-K summed inside the kernel (last-arriver fix-up / "
                          "CTA clusters), splitk = fp32 partials left to the next kernel")
     ap.add_argument("--batch", type=int, default=0, help="attn-prefill: sequences (default 8)")
