@@ -23,9 +23,20 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
         return None
 
     def create_module(self, spec):
-        return importlib.import_module(_REAL + spec.name[len(_ALIAS):])
+        module = importlib.import_module(_REAL + spec.name[len(_ALIAS):])
+        self._own_spec = getattr(self, "_own_spec", {})
+        self._own_spec[spec.name] = (module.__spec__, getattr(module, "__loader__", None))
+        return module
 
     def exec_module(self, module):
+        # the import machinery has just stamped the alias spec on the shared module object: give it its own
+        # back, or its relative imports would see a package name that differs from its spec's parent
+        for name, (own, loader) in list(getattr(self, "_own_spec", {}).items()):
+            if getattr(module, "__spec__", None) is not None and module.__spec__.name == name:
+                module.__spec__ = own
+                if loader is not None:
+                    module.__loader__ = loader
+                del self._own_spec[name]
         return None
 
 
