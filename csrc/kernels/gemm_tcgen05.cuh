@@ -142,7 +142,7 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  const int warp = warp_idx_uniform();
+  const int warp = PUSH ? int(threadIdx.x >> 5) : warp_idx_uniform();
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) sync.mark(0);
   const int a_tiles = (args.gated == 1) ? 2 : 1;
@@ -293,55 +293,108 @@ __device__ __forceinline__ bool gemm_bf16_body(const CUtensorMap& tmA, const CUt
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    // One elected thread runs the whole loop alone: the tensor pipe queues only a few MMAs, so warp votes,
-    // reconvergence and descriptor arithmetic between two k-blocks are time in which it drains.
-    constexpr uint32_t idesc = make_idesc_bf16(kTileRows, BN, 0, 0);
-    if (elect_one()) {
+    if constexpr (PUSH) {
+      // The kernels with the fused-collective epilogue keep the issue loop they were validated with across
+      // ranks (the whole warp loops and votes, lane 0 issues); the plain kernels use the single-thread loop below.
+      constexpr uint32_t idesc = make_idesc_bf16(kTileRows, BN, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      const uint64_t d_tiles = make_smem_desc_sw128(smem_u32(tiles), 0, 1024);
-      const uint64_t d_hi = d_tiles & 0xffffffff00000000ull;
-      const uint32_t a_lo0 = uint32_t(d_tiles);
-      bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      bool alive = true;
+      for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
         const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
         if (!wi.valid) continue;
         const int sp = wi.sp;
         const int kb0 = sp * args.kb_per_split;
         const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
-        ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
-        if (!ok) break;
+        bool ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        tc_fence_after();
         const uint32_t d0 = tmem_base + uint32_t(acc * acc_cols);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
-          if (!ok) break;
-          if (kb == kb0 && w == int(blockIdx.x)) sync.mark(3);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          if (lane == 0 && kb == kb0 && w == int(blockIdx.x)) sync.mark(3);
           tc_fence_after();
-          const uint32_t a_lo = a_lo0 + uint32_t(stage) * uint32_t(stage_bytes >> 4);
-          const uint32_t b_lo = a_lo + uint32_t(a_tiles) * uint32_t(kATileBytes >> 4);
-          const uint64_t da = d_hi | a_lo, db = d_hi | b_lo;
-          const uint64_t da1 = d_hi | (a_lo + uint32_t(kATileBytes >> 4)), db1 = d_hi | (b_lo + uint32_t(kBTileBytes >> 4));
-#pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k) {
-            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            const uint64_t koff = uint64_t(k * 2);  // 16 bf16 = 32 bytes, >>4
-            umma_f16(d0, da + koff, db + koff, idesc, accum);
-            if (args.gated == 1) umma_f16(d0 + BN, da1 + koff, db + koff, idesc, accum);
-            if (args.gated == 2) umma_f16(d0 + BN, da + koff, db1 + koff, idesc, accum);
+          if (lane == 0) {
+            const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
+            const uint32_t b_addr = a_addr + a_tiles * kATileBytes;
+            const uint64_t da = make_smem_desc_sw128(a_addr, 0, 1024);
+            const uint64_t db = make_smem_desc_sw128(b_addr, 0, 1024);
+            const uint64_t da1 = make_smem_desc_sw128(a_addr + kATileBytes, 0, 1024);
+            const uint64_t db1 = make_smem_desc_sw128(b_addr + kBTileBytes, 0, 1024);
+  #pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k) {
+              const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+              const uint64_t koff = uint64_t(k * 2);  // 16 bf16 = 32 bytes, >>4
+              umma_f16(d0, da + koff, db + koff, idesc, accum);
+              if (args.gated == 1) umma_f16(d0 + BN, da1 + koff, db + koff, idesc, accum);
+              if (args.gated == 2) umma_f16(d0 + BN, da + koff, db1 + koff, idesc, accum);
+            }
+            umma_commit(&ctrl->empty[stage]);
           }
-          umma_commit(&ctrl->empty[stage]);
+          __syncwarp();
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
-        umma_commit(&ctrl->tfull[acc]);
-        if (w == int(blockIdx.x)) sync.mark(4);
+        if (!alive) break;
+        if (lane == 0) umma_commit(&ctrl->tfull[acc]);
+        if (lane == 0 && w == int(blockIdx.x)) sync.mark(4);
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+    } else {
+      // One elected thread runs the whole loop alone: the tensor pipe queues only a few MMAs, so warp votes,
+      // reconvergence and descriptor arithmetic between two k-blocks are time in which it drains.
+      constexpr uint32_t idesc = make_idesc_bf16(kTileRows, BN, 0, 0);
+      if (elect_one()) {
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const uint64_t d_tiles = make_smem_desc_sw128(smem_u32(tiles), 0, 1024);
+        const uint64_t d_hi = d_tiles & 0xffffffff00000000ull;
+        const uint32_t a_lo0 = uint32_t(d_tiles);
+        bool ok = true;
+        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+          const WorkItem wi = decode_work<BN, GROUPED>(args, grp, w);
+          if (!wi.valid) continue;
+          const int sp = wi.sp;
+          const int kb0 = sp * args.kb_per_split;
+          const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
+          ok = mbar_wait(&ctrl->tempty[acc], acc_phase ^ 1u, abort_flag, args.status, ERR_WAIT_TMEM_EMPTY);
+          if (!ok) break;
+          const uint32_t d0 = tmem_base + uint32_t(acc * acc_cols);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            ok = mbar_wait(&ctrl->full[stage], phase, abort_flag, args.status, ERR_WAIT_SMEM_FULL);
+            if (!ok) break;
+            if (kb == kb0 && w == int(blockIdx.x)) sync.mark(3);
+            tc_fence_after();
+            const uint32_t a_lo = a_lo0 + uint32_t(stage) * uint32_t(stage_bytes >> 4);
+            const uint32_t b_lo = a_lo + uint32_t(a_tiles) * uint32_t(kATileBytes >> 4);
+            const uint64_t da = d_hi | a_lo, db = d_hi | b_lo;
+            const uint64_t da1 = d_hi | (a_lo + uint32_t(kATileBytes >> 4)), db1 = d_hi | (b_lo + uint32_t(kBTileBytes >> 4));
+  #pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k) {
+              const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+              const uint64_t koff = uint64_t(k * 2);  // 16 bf16 = 32 bytes, >>4
+              umma_f16(d0, da + koff, db + koff, idesc, accum);
+              if (args.gated == 1) umma_f16(d0 + BN, da1 + koff, db + koff, idesc, accum);
+              if (args.gated == 2) umma_f16(d0 + BN, da + koff, db1 + koff, idesc, accum);
+            }
+            umma_commit(&ctrl->empty[stage]);
+            if (++stage == stages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          umma_commit(&ctrl->tfull[acc]);
+          if (w == int(blockIdx.x)) sync.mark(4);
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+      }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may touch
