@@ -5,5 +5,6 @@ examples/models/gpt_oss/kernels/."""
 from .attention import attention_block
 from .moe import moe_ffn
 from .transformer_layer import decode_layer, prefill_layer
+from .verify import accept, verify_tokens
 
-__all__ = ["attention_block", "moe_ffn", "prefill_layer", "decode_layer"]
+__all__ = ["attention_block", "moe_ffn", "prefill_layer", "decode_layer", "verify_tokens", "accept"]

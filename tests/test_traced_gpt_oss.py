@@ -112,3 +112,26 @@ def test_traced_layers_lower_to_cuda_that_compiles_for_sm_100a(tmp_path):
                             os.path.join(ROOT, "csrc", "kernels"), "-o", str(tmp_path / f"{name}.cubin"), str(src)],
                            capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_verify_kernel_and_acceptance():
+    """The speculative-decoding verification as a kernel function: greedy target tokens at K + 1 positions, direct
+    and traced, and the host-side acceptance rule (longest matching prefix plus the target's own token)."""
+    from gpt_oss_kernels import accept, verify_tokens
+
+    rng = np.random.default_rng(5)
+    B, S, H, V = 3, 4, 32, 97
+    h = rng.standard_normal((B, S, H)).astype(np.float32)
+    norm = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    head = rng.standard_normal((H, V)).astype(np.float32)
+    got = verify_tokens(h, norm, head, 1e-5)
+    hn = h / np.sqrt((h * h).mean(-1, keepdims=True) + 1e-5) * norm
+    want = np.argmax(hn @ head, axis=-1)
+    assert got.dtype == np.int32 and np.array_equal(got, want)
+    g = trace(verify_tokens).specialize(h, norm, head, norm_eps=1e-5)
+    assert np.array_equal(np.asarray(evaluate(g, [h, norm, head])[0]), want)
+    target = np.array([[5, 6, 7, 8], [5, 6, 7, 8], [1, 2, 3, 4]])
+    drafts = np.array([[5, 6, 7], [5, 9, 7], [0, 2, 3]])
+    n, out = accept(drafts, target)
+    assert n.tolist() == [3, 1, 0]
+    assert out == [[5, 6, 7, 8], [5, 6], [1]]
