@@ -130,6 +130,11 @@ def test_verify_kernel_and_acceptance():
     assert got.dtype == np.int32 and np.array_equal(got, want)
     g = trace(verify_tokens).specialize(h, norm, head, norm_eps=1e-5)
     assert np.array_equal(np.asarray(evaluate(g, [h, norm, head])[0]), want)
+    # vocabulary-parallel form: in one process the gather replicates this rank's winners, rank 0 wins every tie,
+    # so the global id is the local one -- the reshapes, the winner selection and the id arithmetic all run
+    assert np.array_equal(verify_tokens(h, norm, head, 1e-5, world_size=2), want)
+    g2 = trace(verify_tokens).specialize(h, norm, head, norm_eps=1e-5, world_size=2)
+    assert any(n.opcode == "all_gather" for n in g2.nodes)
     target = np.array([[5, 6, 7, 8], [5, 6, 7, 8], [1, 2, 3, 4]])
     drafts = np.array([[5, 6, 7], [5, 9, 7], [0, 2, 3]])
     n, out = accept(drafts, target)
