@@ -248,7 +248,7 @@ class TransformerLM:
                     qkv = ops.linear(normed, lw.qkv, splits=self.split_qkv)
                 else:
                     qkv = ops.linear(normed, lw.qkv)
-                if (ops.FUSED_ROPE_ATTN and q_len == 1 and qkv.dtype == torch.float32 and qkv.is_cuda
+                if (ops.fused_rope_attn_enabled(self.tp.world_size) and q_len == 1 and qkv.dtype == torch.float32 and qkv.is_cuda
                         and self.d in (64, 128) and self.nq // self.nkv <= 16):
                     # RoPE and the cache append run inside the attention kernel: one launch less per layer
                     q = None

@@ -830,8 +830,16 @@ def paged_attn_decode(
 
 
 # Decode attention reads the fused QKV projection's split-K partials itself (bias, QK-norm, RoPE and the cache
-# append included) instead of running after a separate RoPE + append launch.  "0" restores the two launches.
-FUSED_ROPE_ATTN = os.environ.get("NKIPY_B200_FUSED_ROPE_ATTN", "1") != "0"
+# append included) instead of running after a separate RoPE + append launch.  "1" = always, "0" = never, "auto"
+# (default) = on one rank only: the fusion is time-neutral inside the CUDA graph and its multi-rank runs have not
+# been re-validated.
+FUSED_ROPE_ATTN = os.environ.get("NKIPY_B200_FUSED_ROPE_ATTN", "auto")
+
+
+def fused_rope_attn_enabled(world_size: int) -> bool:
+    if FUSED_ROPE_ATTN == "auto":
+        return world_size == 1
+    return FUSED_ROPE_ATTN != "0"
 
 
 def rope_attn_decode(
