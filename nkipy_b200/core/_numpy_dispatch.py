@@ -64,6 +64,8 @@ def register_all_numpy_apis() -> None:
         np.concatenate: ops.concatenate, np.split: ops.split, np.copy: ops.copy, np.repeat: ops.repeat,
         np.squeeze: ops.squeeze, np.pad: ops.pad, np.swapaxes: ops.swapaxes, np.stack: ops.stack, np.diff: ops.diff,
         np.flip: ops.flip, np.tile: ops.tile, np.roll: ops.roll, np.ravel: lambda x: ops.reshape(x, (-1,)),
+        np.sort: lambda x, axis=-1, kind=None: ops.sort(x, axis=axis),
+        np.argsort: lambda x, axis=-1, kind=None: ops.argsort(x, axis=axis),
         # creation
         np.zeros_like: ops.zeros_like, np.ones_like: ops.ones_like, np.empty_like: ops.empty_like,
         np.full_like: ops.full_like, np.tril: ops.tril, np.triu: ops.triu, np.diag: ops.diag,

@@ -39,7 +39,7 @@ _NAMES = [
     "reshape", "transpose", "expand_dims", "concatenate", "split", "copy", "repeat", "broadcast_to", "copyto",
     "astype", "squeeze", "pad", "swapaxes", "stack", "diff", "flip", "tile", "roll",
     # nn
-    "softmax", "topk", "rms_norm",
+    "softmax", "topk", "rms_norm", "sort", "argsort",
     # conv
     "conv2d", "conv3d",
     # indexing
@@ -453,6 +453,31 @@ def _trace(x, offset=0, axis1=0, axis2=1, dtype=None):
     sel = where(mask if get_backend() == "cpu" else constant(mask), xt, 0)
     out = _f("sum")(_f("sum")(sel, axis=-1), axis=-1)
     return astype(out, dtype) if dtype is not None else out
+
+
+def _sorted_last_axis(x, axis, descending):
+    nd = len(x.shape)
+    if axis is None:
+        x, axis, nd = reshape(x, (-1,)), 0, 1
+    axis = axis % nd
+    if axis != nd - 1:
+        x = swapaxes(x, axis, nd - 1)
+    vals, idx = topk(x, x.shape[-1], axis=-1, is_ascend=not descending)
+    if axis != nd - 1:
+        vals, idx = swapaxes(vals, axis, nd - 1), swapaxes(idx, axis, nd - 1)
+    return vals, idx
+
+
+@sort.composed_impl
+def _sort(x, axis=-1, descending=False):
+    """Sorted copy along `axis` (None = flattened): a full-length top-k, so it lowers to the same kernel."""
+    return _sorted_last_axis(x, axis, descending)[0]
+
+
+@argsort.composed_impl
+def _argsort(x, axis=-1, descending=False):
+    """Indices that sort `x` along `axis` (int32; ties keep their original order like NumPy's stable sort)."""
+    return astype(_sorted_last_axis(x, axis, descending)[1], np.int32)
 
 
 @diff.composed_impl

@@ -104,6 +104,11 @@ CASES = {
     "take_numpy_index": (lambda x: np.take(x, np.array([2, 0, 3]), axis=0), [A]),
     "take_scalar": (lambda x: np.take(x, 1, axis=1), [A]),
     "take_along_axis": (lambda x, i: np.take_along_axis(x, i, axis=-1), [A, np.argsort(A, axis=-1).astype(np.int32)]),
+    "sort_last_axis": (lambda x: np.sort(x, axis=-1), [A]),
+    "sort_axis0": (lambda x: np.sort(x, axis=0), [A]),
+    "sort_flattened": (lambda x: np.sort(x, axis=None), [A]),
+    "argsort_middle_axis": (lambda x: np.argsort(x, axis=1), [C3]),
+    "argsort_then_gather": (lambda x: np.take_along_axis(x, np.argsort(x, axis=-1), axis=-1), [A]),
     "take_along_axis_constant": (lambda x: np.take_along_axis(x, np.array([[0], [2], [5], [1]]), axis=-1), [A]),
     # integer and bitwise
     "bitwise_and_or_xor": (lambda a, b: (a & b) | (a ^ b), [I32, I32[::-1].copy()]),
