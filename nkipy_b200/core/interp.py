@@ -266,7 +266,12 @@ def _eval_node(n: Node, ins: List[np.ndarray], world: int = 1) -> List[np.ndarra
     if op == "reduce_scatter":
         x = ins[0]
         part = np.split(x, n_ranks, axis=a["dim"])[0]
-        return [(_compute(part) * n_ranks).astype(odt) if a.get("op", "add") == "add" else part.copy()]
+        kind = a.get("op", "add")
+        if kind == "add":
+            return [(_compute(part) * n_ranks).astype(odt)]
+        if kind == "multiply":
+            return [np.power(_compute(part), n_ranks).astype(odt)]
+        return [part.copy()]
     if op == "all_to_all":
         parts = np.split(ins[0], n_ranks, axis=a["split_dim"])
         return [np.concatenate([parts[0]] * n_ranks, axis=a["concat_dim"])]

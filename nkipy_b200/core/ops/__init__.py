@@ -253,7 +253,11 @@ def _all_reduce_cpu(data, replica_groups, reduce_op=np.add, **kw):
 def _reduce_scatter_cpu(data, reduce_scatter_dim, replica_groups, reduce_op=np.add, **kw):
     n = len(replica_groups[0])
     part = np.split(np.asarray(data), n, axis=reduce_scatter_dim)[0]
-    return part * n if reduce_op is np.add else part.copy()
+    if reduce_op is np.add:
+        return part * n
+    if reduce_op is np.multiply:
+        return part ** n
+    return part.copy()
 
 
 @_cpu("all_to_all")
