@@ -43,6 +43,6 @@ class HLOTraceContext:
 
 def get_hlo_context() -> HLOTraceContext:
     ctx = get_context()
-    if ctx is None or ctx.backend_name != "hlo":
+    if ctx is None or ctx.backend_name not in ("hlo", "nkigen"):      # both trace the same tensor IR
         raise RuntimeError("no IR trace context is active")
     return ctx

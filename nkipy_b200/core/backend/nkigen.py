@@ -18,6 +18,8 @@ NkiGenTensor = Value
 class NkiGenTraceContext(HLOTraceContext):
     """Trace context whose knobs are kept (`honours_knobs`) for the native compiler."""
 
+    backend_name = "nkigen"
+
     def __init__(self, module: Optional[Graph] = None):
         super().__init__(module)
         self.honours_knobs = True

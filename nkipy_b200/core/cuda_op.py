@@ -90,11 +90,3 @@ def cuda_custom_op(name: str, source: str, entry: str, output_specs: Sequence[Tu
         dtype_from_name(d) if isinstance(d, str) else np.dtype(d)
     return CudaCustomOp(name, source, entry, [(tuple(s), d) for s, d in output_specs], tuple(grid), tuple(block), smem,
                         reference, dict(aliases or {}), has_collectives)
-
-
-# names of the reference's API, for code written against it
-nki_custom_op = cuda_custom_op
-NKICustomOp = CudaCustomOp
-wrap_nki_kernel = cuda_custom_op
-NKICustomOpHandle = CudaCustomOp     # what a wrapped kernel call returns in the reference is the op object itself here
-NKIOp = CudaCustomOp

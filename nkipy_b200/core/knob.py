@@ -28,7 +28,7 @@ def knob(tensor, partition_dim: Optional[int] = None, mem_space: Optional[str] =
     ctx = get_context()
     hints = getattr(ctx, "knobs", None)
     if hints is None or not getattr(ctx, "honours_knobs", False):
-        warnings.warn("knob() hints only take effect with the 'nkigen' (native pass pipeline) backend", stacklevel=2)
+        warnings.warn("knob() is only effective with backend='nkigen' (the native pass pipeline); ignored here", stacklevel=2)
         return tensor
     hints[tensor.backend_tensor.id] = {
         "partition_dim": partition_dim, "mem_space": MEM_SPACES.get(mem_space) if mem_space else None,

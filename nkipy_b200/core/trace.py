@@ -87,7 +87,7 @@ class NKIPyKernel:
         bound.apply_defaults()
         graph = Graph(self.func.__name__)
         ctx = HLOTraceContext(graph)
-        ctx.backend_name = "hlo"
+        ctx.backend_name = "nkigen" if self.backend == "nkigen" else "hlo"      # what get_backend() reports meanwhile
         if self.backend == "nkigen":
             ctx.honours_knobs = True
             ctx.knobs = {}

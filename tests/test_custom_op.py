@@ -12,6 +12,7 @@ from nkipy_b200.compiler.codegen import generate
 from nkipy_b200.core.compile import trace
 from nkipy_b200.core.cuda_op import CudaCustomOp, cuda_custom_op
 from nkipy_b200.core.interp import evaluate
+from utils import check, trace_kernel
 
 AXPY = '''extern "C" __global__ void axpy_kernel(const float* x, const float* y, float* out, int n) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -123,3 +124,126 @@ def test_generated_program_contains_the_source_and_compiles(tmp_path):
     r = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-cubin", "-o",
                         str(tmp_path / "k.cubin"), str(src)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-1500:]
+
+
+# ------------------------------------------------------------------ the cross-backend handle and the shape-pinned form
+def _double_builder(input_specs, output_specs, factor=2.0):
+    n = int(np.prod(input_specs[0][0]))
+    return {"source": f'extern "C" __global__ void scale_kernel(const float* x, float* y) '
+                      f'{{ int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < {n}) y[i] = {factor}f * x[i]; }}',
+            "entry": "scale_kernel", "grid": ((n + 255) // 256,), "block": (256,)}
+
+
+def test_handle_needs_a_kernel_or_a_builder_and_specs_for_the_builder():
+    from nkipy_b200.core.nki_op import nki_custom_op
+
+    with pytest.raises(ValueError, match="At least one"):
+        nki_custom_op()
+    with pytest.raises(ValueError, match="input_specs and output_specs"):
+        nki_custom_op(kernel_builder=_double_builder)
+    with pytest.raises(TypeError, match="nki_kernel must be"):
+        nki_custom_op(nki_kernel=lambda x: x)
+    with pytest.raises(TypeError, match="unknown argument"):
+        nki_custom_op(kernel_builder=_double_builder, input_specs=[((8,), "f32")], output_specs=[((8,), "f32")], tile=4)
+    with pytest.raises((ValueError, KeyError, TypeError)):
+        nki_custom_op(kernel_builder=_double_builder, input_specs=[((8,), "f33")], output_specs=[((8,), "f32")])
+
+
+def test_handle_without_a_reference_raises_on_numpy_arrays_and_traces_fine():
+    from nkipy_b200.core.nki_op import nki_custom_op
+
+    op = nki_custom_op(kernel_builder=_double_builder, input_specs=[((8,), "f32")], output_specs=[((8,), "f32")])
+    with pytest.raises(RuntimeError, match="not supported on backend 'cpu'"):
+        op(np.ones(8, np.float32))
+    g = trace_kernel(lambda x: op(x), np.ones(8, np.float32))
+    node = next(n for n in g.nodes if n.opcode == "custom_call")
+    assert node.attrs["entry"] == "scale_kernel" and node.attrs["grid"] == [1, 1, 1] and node.attrs["block"] == [256, 1, 1]
+    assert "2.0f * x[i]" in node.attrs["source"]
+
+
+@pytest.mark.parametrize("backend", ["hlo", "nkigen"])
+def test_handle_picks_the_form_the_backend_prefers_and_falls_back(backend):
+    from nkipy_b200.core.nki_op import nki_custom_op
+    from nkipy_b200.core.trace import NKIPyKernel
+
+    written = cuda_custom_op(name="written", source=_double_builder([((8,), "f32")], None)["source"], entry="scale_kernel",
+                             output_specs=[((8,), "f32")], reference=lambda x: 2 * x)
+    both = nki_custom_op(nki_kernel=written, kernel_builder=_double_builder, input_specs=[((8,), "f32")],
+                         output_specs=[((8,), "f32")], name="built", reference=lambda x: 2 * x)
+    g = NKIPyKernel(lambda x: both(x), backend).specialize(np.ones(8, np.float32))
+    g = getattr(g, "graph", g)
+    target = next(n for n in g.nodes if n.opcode == "custom_call").attrs["target"]
+    assert target == ("written" if backend == "hlo" else "built")
+    only_written = nki_custom_op(nki_kernel=written)
+    only_built = nki_custom_op(kernel_builder=_double_builder, input_specs=[((8,), "f32")], output_specs=[((8,), "f32")],
+                               name="built")
+    for op, want in ((only_written, "written"), (only_built, "built")):
+        g = NKIPyKernel(lambda x: op(x), backend).specialize(np.ones(8, np.float32))
+        g = getattr(g, "graph", g)
+        assert next(n for n in g.nodes if n.opcode == "custom_call").attrs["target"] == want
+    np.testing.assert_array_equal(both(np.ones(8, np.float32)), np.full(8, 2, np.float32))
+
+
+def test_handle_checks_operands_against_its_specs():
+    from nkipy_b200.core.nki_op import nki_custom_op
+
+    op = nki_custom_op(kernel_builder=_double_builder, input_specs=[((8,), "f32")], output_specs=[((8,), "f32")],
+                       reference=lambda x: 2 * x)
+    with pytest.raises(ValueError, match="takes 1 operand"):
+        op(np.ones(8, np.float32), np.ones(8, np.float32))
+    with pytest.raises(ValueError, match="built for f32"):
+        op(np.ones(9, np.float32))
+    with pytest.raises(ValueError, match="built for f32"):
+        op(np.ones(8, np.float16))
+    with pytest.raises(ValueError, match="built for f32"):
+        trace_kernel(lambda x: op(x), np.ones((2, 8), np.float32))
+
+
+def test_builder_is_called_once_and_gets_its_keyword_arguments():
+    from nkipy_b200.core.nki_op import nki_custom_op
+
+    calls = []
+
+    def builder(input_specs, output_specs, factor):
+        calls.append(factor)
+        return _double_builder(input_specs, output_specs, factor)
+
+    op = nki_custom_op(kernel_builder=builder, input_specs=[((8,), "f32")], output_specs=[((8,), "f32")],
+                       builder_kwargs={"factor": 3.0}, reference=lambda x: 3 * x)
+    x = np.arange(8, dtype=np.float32)
+    g = trace(lambda a: op(op(a))).specialize(x)
+    assert calls == [3.0]
+    assert sum(n.opcode == "custom_call" for n in g.nodes) == 2
+    np.testing.assert_array_equal(evaluate(g, [x])[0], 9 * x)
+    np.testing.assert_array_equal(op(op(x)), 9 * x)
+
+
+def test_wrapped_kernel_is_pinned_to_its_example_operands():
+    from nkipy_b200.core.nki_op import NKICustomOp, wrap_nki_kernel
+
+    written = cuda_custom_op(name="written", source="", entry="k", output_specs=[((4, 4), "f32")], grid=(1,), block=(16,),
+                             reference=lambda a, b: a + b)
+    op = wrap_nki_kernel(written, [np.ones((4, 4), np.float32), np.ones((4, 4), np.float32)], grid=(2, 2))
+    assert isinstance(op, NKICustomOp)
+    assert op.config["grid"] == [2, 2] and op.config["block"] == [16] and op.config["input_specs"] == [((4, 4), "f32")] * 2
+    assert written.grid == (1,)                                   # the wrapped kernel itself is left alone
+    np.testing.assert_array_equal(op(np.ones((4, 4), np.float32), np.ones((4, 4), np.float32)), np.full((4, 4), 2.0))
+    with pytest.raises(ValueError, match="operand 1"):
+        op(np.ones((4, 4), np.float32), np.ones((4, 5), np.float32))
+    with pytest.raises(TypeError):
+        wrap_nki_kernel(lambda a: a, [np.ones(4, np.float32)])
+
+
+def test_decorator_form_of_the_nkigen_front_end():
+    from nkipy_b200.nkigen.custom_op import custom_op
+
+    @custom_op(input_specs=[((8,), "f32")], output_specs=[((8,), "f32")], reference=lambda x: 2 * x)
+    def scale_kernel(input_specs, output_specs):
+        return _double_builder(input_specs, output_specs)["source"]
+
+    x = np.arange(8, dtype=np.float32)
+    g = trace(lambda a: scale_kernel(a) + 1.0).specialize(x)
+    np.testing.assert_array_equal(evaluate(g, [x])[0], 2 * x + 1)
+    np.testing.assert_array_equal(scale_kernel(x) + 1.0, 2 * x + 1)
+    node = next(n for n in g.nodes if n.opcode == "custom_call")
+    assert node.attrs["target"] == "scale_kernel" and node.attrs["entry"] == "scale_kernel"
