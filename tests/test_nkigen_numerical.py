@@ -88,6 +88,21 @@ KERNELS = {
     "feed_forward": (_ffn, [f32(8, 16), f32(16, 64, scale=0.3), f32(32, 16, scale=0.3)]),
     "layer": (lambda x, w, wgu, wd: x + _ffn(_rmsnorm(x, w), wgu, wd), [f32(8, 16), f32(16), f32(16, 64, scale=0.3),
                                                                        f32(32, 16, scale=0.3)]),
+    # comparisons, selection, logic
+    "equal": (lambda a, b: np.equal(a, b), [np.array([[1, 2], [3, 4]], np.float32), np.array([[1, 0], [3, 5]], np.float32)]),
+    "greater": (lambda a, b: np.greater(a, b), [f32(8, 16), f32(8, 16)]),
+    "less_scalar": (lambda a: np.less(a, 0.25), [f32(8, 16)]),
+    "logical_not": (lambda a: np.logical_not(a > 0.0), [f32(8, 16)]),
+    "bitwise_and": (lambda a, b: np.bitwise_and(a, b), [R.integers(0, 255, (8, 16)).astype(np.int32),
+                                                        R.integers(0, 255, (8, 16)).astype(np.int32)]),
+    "where_same_type": (lambda c, a, b: np.where(c > 0.0, a, b), [f32(8, 16), f32(8, 16), f32(8, 16)]),
+    "where_scalar_branch": (lambda a: np.where(a > 0.5, a, 0.0), [f32(8, 16)]),
+    "clip": (lambda a: np.clip(a, -0.5, 0.5), [f32(8, 16)]),
+    # more shape ops
+    "squeeze": (lambda a: np.squeeze(a, axis=1) * 2.0, [f32(8, 1, 16)]),
+    "swapaxes": (lambda a: np.swapaxes(a, 0, 2) + 1.0, [f32(2, 8, 4)]),
+    "stack": (lambda a, b: np.stack([a, b], axis=1), [f32(8, 16), f32(8, 16)]),
+    "expand_then_broadcast": (lambda a, b: np.expand_dims(a, 1) * b, [f32(8, 16), f32(4, 16)]),
     # loops
     "fori_loop": (_loop, [f32(8, 8, scale=0.5), f32(8, 8, scale=0.5)]),
 }
