@@ -39,17 +39,18 @@ class SpikeTensor:
 
     @classmethod
     def from_numpy(cls, array: np.ndarray, name: Optional[str] = None, core_id: int = 0) -> "SpikeTensor":
+        shape = np.shape(array)                      # ascontiguousarray turns a 0-d array into shape (1,)
         array = np.ascontiguousarray(array)
-        t = cls.empty(array.shape, array.dtype, name, core_id)
+        t = cls.empty(shape, array.dtype, name, core_id)
         if array.nbytes:
             get_spike_singleton().tensor_write(t.tensor_ref, array.view(np.uint8).reshape(-1), 0)
         return t
 
     def numpy(self) -> np.ndarray:
-        out = np.empty(self.shape, dtype=self.dtype)
-        if out.nbytes:
-            get_spike_singleton().tensor_read_to_buffer(self.tensor_ref, out.view(np.uint8).reshape(-1), 0)
-        return out
+        flat = np.empty(int(np.prod(self.shape, dtype=np.int64)), dtype=self.dtype)    # 1-d: a 0-d array has no byte view
+        if flat.nbytes:
+            get_spike_singleton().tensor_read_to_buffer(self.tensor_ref, flat.view(np.uint8), 0)
+        return flat.reshape(self.shape)
 
     def write_from_numpy(self, array: np.ndarray) -> None:
         """Overwrite the contents in place (no reallocation); sizes must match."""
