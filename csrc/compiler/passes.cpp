@@ -204,25 +204,156 @@ static void canonicalize_reshape(Graph& g, const PassOptions&) {
   dce(g);
 }
 
-static void simplify_linalg(Graph& g, const PassOptions&) {
-  for (Node* n : g.nodes) {
-    if (n->dead || n->opcode != "transpose") continue;
-    auto perm = ints(n->attrs.at("perm"));
-    Node* p = n->inputs[0]->producer;
-    if (p && p->opcode == "transpose") {
-      auto inner = ints(p->attrs.at("perm"));
-      std::vector<long long> composed(perm.size());
-      for (size_t i = 0; i < perm.size(); ++i) composed[i] = inner[size_t(perm[i])];
-      perm = composed;
-      n->inputs[0] = p->inputs[0];
-      n->attrs.set("perm", int_array(perm));
-    }
-    bool identity = true;
-    for (size_t i = 0; i < perm.size(); ++i) identity = identity && perm[i] == (long long)i;
-    if (identity) forward(g, n, n->inputs[0]);
+// ---- simplify-linalg: compositions of data-movement operations become one operation, and data movement that moves
+// nothing becomes a reshape (a view).  Patterns return true when they rewrote `n`.
+static bool compose_transposes(Graph& g, Node* n) {
+  if (n->opcode != "transpose") return false;
+  auto perm = ints(n->attrs.at("perm"));
+  bool changed = false;
+  Node* p = n->inputs[0]->producer;
+  if (p && p->opcode == "transpose") {
+    auto inner = ints(p->attrs.at("perm"));
+    std::vector<long long> composed(perm.size());
+    for (size_t i = 0; i < perm.size(); ++i) composed[i] = inner[size_t(perm[i])];
+    perm = composed;
+    n->inputs[0] = p->inputs[0];
+    n->attrs.set("perm", int_array(perm));
+    changed = true;
   }
-  g.sweep();
-  dce(g);
+  bool identity = true;
+  for (size_t i = 0; i < perm.size(); ++i) identity = identity && perm[i] == (long long)i;
+  if (identity) return forward(g, n, n->inputs[0]), true;
+  return changed;
+}
+
+// a transpose that keeps the order of all dimensions larger than one moves no element
+static bool transpose_of_unit_dims(Graph&, Node* n) {
+  if (n->opcode != "transpose") return false;
+  auto perm = ints(n->attrs.at("perm"));
+  const auto& in = n->inputs[0]->shape;
+  long long last = -1;
+  for (long long d : perm) {
+    if (in[size_t(d)] == 1) continue;
+    if (d < last) return false;
+    last = d;
+  }
+  n->opcode = "reshape";
+  Json attrs = Json::make_object();
+  attrs.set("shape", int_array(n->outputs[0]->shape));
+  for (const auto& kv : n->attrs.obj)
+    if (!kv.first.empty() && kv.first[0] == '_') attrs.set(kv.first, kv.second);
+  n->attrs = attrs;
+  return true;
+}
+
+// sum / max / min / prod over dimensions of extent one is a reshape
+static bool reduce_of_unit_dims(Graph&, Node* n) {
+  if (n->opcode != "reduce") return false;
+  const std::string kind = n->attrs.at("kind").as_string();
+  if (kind != "sum" && kind != "max" && kind != "min" && kind != "prod") return false;
+  if (n->inputs[0]->dtype != n->outputs[0]->dtype) return false;
+  for (long long a : ints(n->attrs.at("axes")))
+    if (n->inputs[0]->shape[size_t(a)] != 1) return false;
+  n->opcode = "reshape";
+  Json attrs = Json::make_object();
+  attrs.set("shape", int_array(n->outputs[0]->shape));
+  n->attrs = attrs;
+  return true;
+}
+
+static bool compose_slices(Graph&, Node* n) {
+  if (n->opcode != "slice") return false;
+  Node* p = n->inputs[0]->producer;
+  if (!p || p->opcode != "slice") return false;
+  auto s1 = ints(p->attrs.at("start")), t1 = ints(p->attrs.at("stride"));
+  auto s2 = ints(n->attrs.at("start")), t2 = ints(n->attrs.at("stride"));
+  const auto& out = n->outputs[0]->shape;
+  std::vector<long long> start(s1.size()), stride(s1.size()), limit(s1.size());
+  for (size_t i = 0; i < s1.size(); ++i) {
+    start[i] = s1[i] + s2[i] * t1[i];
+    stride[i] = t1[i] * t2[i];
+    limit[i] = out[i] == 0 ? start[i] : start[i] + (out[i] - 1) * stride[i] + 1;
+  }
+  n->inputs[0] = p->inputs[0];
+  n->attrs.set("start", int_array(start));
+  n->attrs.set("stride", int_array(stride));
+  n->attrs.set("limit", int_array(limit));
+  return true;
+}
+
+// a slice that takes everything
+static bool full_slice(Graph& g, Node* n) {
+  if (n->opcode != "slice" || n->inputs[0]->shape != n->outputs[0]->shape) return false;
+  for (long long t : ints(n->attrs.at("stride")))
+    if (t != 1) return false;
+  return forward(g, n, n->inputs[0]), true;
+}
+
+static bool compose_broadcasts(Graph&, Node* n) {
+  if (n->opcode != "broadcast") return false;
+  Node* p = n->inputs[0]->producer;
+  if (!p || p->opcode != "broadcast") return false;
+  auto inner = ints(p->attrs.at("dims")), outer = ints(n->attrs.at("dims"));
+  std::vector<long long> dims(inner.size());
+  for (size_t i = 0; i < inner.size(); ++i) dims[i] = outer[size_t(inner[i])];
+  n->inputs[0] = p->inputs[0];
+  n->attrs.set("dims", int_array(dims));
+  return true;
+}
+
+// reshape / transpose / slice of a broadcast scalar is a broadcast of that scalar
+static bool view_of_splat(Graph&, Node* n) {
+  if (n->opcode != "reshape" && n->opcode != "transpose" && n->opcode != "slice") return false;
+  Node* p = n->inputs[0]->producer;
+  if (!p || p->opcode != "broadcast" || !p->inputs[0]->shape.empty()) return false;
+  n->opcode = "broadcast";
+  n->inputs[0] = p->inputs[0];
+  Json attrs = Json::make_object();
+  attrs.set("dims", Json::make_array());
+  attrs.set("shape", int_array(n->outputs[0]->shape));
+  n->attrs = attrs;
+  return true;
+}
+
+// concat(concat(a, b), c) along one axis is concat(a, b, c) when nothing else reads the inner result
+static bool flatten_concats(Graph& g, Node* n) {
+  if (n->opcode != "concat") return false;
+  const long long axis = n->attrs.at("axis").as_int();
+  auto uses = g.use_counts();
+  std::vector<Value*> flat;
+  bool changed = false;
+  for (Value* v : n->inputs) {
+    Node* p = v->producer;
+    if (p && p->opcode == "concat" && p->attrs.at("axis").as_int() == axis && uses[v] == 1 && !g.is_result(v)) {
+      flat.insert(flat.end(), p->inputs.begin(), p->inputs.end());
+      changed = true;
+    } else {
+      flat.push_back(v);
+    }
+  }
+  if (changed) n->inputs = flat;
+  return changed;
+}
+
+static void simplify_linalg(Graph& g, const PassOptions&) {
+  using Pattern = bool (*)(Graph&, Node*);
+  static const Pattern patterns[] = {compose_transposes, transpose_of_unit_dims, reduce_of_unit_dims, compose_slices,
+                                     full_slice,         compose_broadcasts,     view_of_splat,       flatten_concats};
+  for (int round = 0; round < 8; ++round) {
+    bool changed = false;
+    std::vector<Node*> snapshot = g.nodes;
+    for (Node* n : snapshot) {
+      if (n->dead) continue;
+      for (Pattern p : patterns)
+        if (p(g, n)) {
+          changed = true;
+          break;
+        }
+    }
+    g.sweep();
+    dce(g);
+    if (!changed) break;
+  }
 }
 
 static void eliminate_uninitialized_copies(Graph& g, const PassOptions&) {
@@ -272,23 +403,181 @@ static void cse(Graph& g, const PassOptions&) {
   g.sweep();
 }
 
-static void canonicalize(Graph& g, const PassOptions&) {
-  for (Node* n : g.nodes) {
-    if (n->dead) continue;
-    double c;
-    if (n->opcode == "mul") {
-      if (splat_f64(n->inputs[1], c) && c == 1.0) forward(g, n, n->inputs[0]);
-      else if (splat_f64(n->inputs[0], c) && c == 1.0) forward(g, n, n->inputs[1]);
-    } else if (n->opcode == "sub" || n->opcode == "add") {
-      if (splat_f64(n->inputs[1], c) && c == 0.0) forward(g, n, n->inputs[0]);
-    } else if (n->opcode == "div") {
-      if (splat_f64(n->inputs[1], c) && c == 1.0) forward(g, n, n->inputs[0]);
-    } else if (n->opcode == "convert") {
-      if (n->inputs[0]->dtype == n->outputs[0]->dtype) forward(g, n, n->inputs[0]);
-    }
+// ---- canonicalize: local rewrites that keep every result value (the one exception, the sign of a zero produced by
+// x + 0, is noted at its pattern).  Each pattern returns true when it rewrote `n`.
+// A conversion T -> U -> T gives back the input when every T value is exactly representable in U.
+static bool widens_losslessly(const std::string& from, const std::string& to) {
+  static const std::map<std::string, std::set<std::string>> wider = {
+      {"f16", {"f32", "f64"}}, {"bf16", {"f32", "f64"}}, {"f32", {"f64"}},
+      {"i8", {"i16", "i32", "i64", "f32", "f64"}}, {"u8", {"i16", "u16", "i32", "u32", "i64", "f16", "f32", "f64"}},
+      {"i16", {"i32", "i64", "f32", "f64"}}, {"u16", {"i32", "u32", "i64", "f32", "f64"}}, {"i32", {"i64", "f64"}},
+      {"u32", {"i64", "f64"}}, {"pred", {"i8", "u8", "i16", "i32", "i64", "f16", "bf16", "f32", "f64"}}};
+  auto it = wider.find(from);
+  return it != wider.end() && it->second.count(to) > 0;
+}
+
+static bool same_value_operands(const Node* n) { return n->inputs.size() == 2 && n->inputs[0] == n->inputs[1]; }
+
+// x * 1, 1 * x, x + 0, 0 + x, x - 0, x / 1, x ** 1
+static bool fold_identity_operand(Graph& g, Node* n) {
+  double c;
+  const std::string& op = n->opcode;
+  if (n->inputs.size() != 2) return false;
+  const bool rhs = splat_f64(n->inputs[1], c);
+  const double rc = c;
+  const bool lhs = splat_f64(n->inputs[0], c);
+  const double lc = c;
+  // the other operand must already have the result's type and shape: a forward may not change either
+  auto fits = [&](Value* v) { return v->dtype == n->outputs[0]->dtype && v->shape == n->outputs[0]->shape; };
+  if (op == "mul") {
+    if (rhs && rc == 1.0 && fits(n->inputs[0])) return forward(g, n, n->inputs[0]), true;
+    if (lhs && lc == 1.0 && fits(n->inputs[1])) return forward(g, n, n->inputs[1]), true;
+  } else if (op == "add") {
+    // for x = -0 the sum is +0 and the forwarded value -0; every other x is unchanged
+    if (rhs && rc == 0.0 && fits(n->inputs[0])) return forward(g, n, n->inputs[0]), true;
+    if (lhs && lc == 0.0 && fits(n->inputs[1])) return forward(g, n, n->inputs[1]), true;
+  } else if (op == "sub") {
+    if (rhs && rc == 0.0 && fits(n->inputs[0])) return forward(g, n, n->inputs[0]), true;
+  } else if (op == "div" || op == "pow") {
+    if (rhs && rc == 1.0 && fits(n->inputs[0])) return forward(g, n, n->inputs[0]), true;
   }
-  g.sweep();
-  dce(g);
+  return false;
+}
+
+// max(x, x), min(x, x), and(x, x), or(x, x), select(c, x, x)
+static bool fold_idempotent(Graph& g, Node* n) {
+  const std::string& op = n->opcode;
+  if ((op == "max" || op == "min" || op == "and" || op == "or") && same_value_operands(n))
+    return forward(g, n, n->inputs[0]), true;
+  if (op == "select" && n->inputs.size() == 3 && n->inputs[1] == n->inputs[2] &&
+      n->inputs[1]->shape == n->outputs[0]->shape)
+    return forward(g, n, n->inputs[1]), true;
+  return false;
+}
+
+// neg(neg(x)), not(not(x)), abs(abs(x)) -> abs(x), abs(neg(x)) -> abs(x)
+static bool fold_involution(Graph& g, Node* n) {
+  if (n->inputs.size() != 1) return false;
+  Node* p = n->inputs[0]->producer;
+  if (!p) return false;
+  if ((n->opcode == "neg" && p->opcode == "neg") || (n->opcode == "not" && p->opcode == "not"))
+    return forward(g, n, p->inputs[0]), true;
+  if (n->opcode == "abs" && p->opcode == "abs") return forward(g, n, n->inputs[0]), true;
+  if (n->opcode == "abs" && p->opcode == "neg") {
+    n->inputs[0] = p->inputs[0];
+    return true;
+  }
+  return false;
+}
+
+// convert to the same type; convert(convert(x : T) : U) : T with U holding every T value; convert chains
+// T -> U -> V with T -> U lossless collapse to T -> V
+static bool fold_convert(Graph& g, Node* n) {
+  if (n->opcode != "convert") return false;
+  if (n->inputs[0]->dtype == n->outputs[0]->dtype) return forward(g, n, n->inputs[0]), true;
+  Node* p = n->inputs[0]->producer;
+  if (!p || p->opcode != "convert") return false;
+  const std::string& t = p->inputs[0]->dtype;
+  const std::string& u = p->outputs[0]->dtype;
+  if (!widens_losslessly(t, u)) return false;
+  if (t == n->outputs[0]->dtype) return forward(g, n, p->inputs[0]), true;
+  n->inputs[0] = p->inputs[0];
+  return true;
+}
+
+// x / 2^k -> x * 2^-k for f32: both are the correctly rounded value of the same real number
+static bool fold_power_of_two_divisor(Graph& g, Node* n) {
+  double c;
+  if (n->opcode != "div" || n->outputs[0]->dtype != "f32" || !splat_f64(n->inputs[1], c)) return false;
+  int e = 0;
+  const double m = std::frexp(std::fabs(c), &e);
+  if (c == 0.0 || !std::isfinite(c) || m != 0.5 || e < -100 || e > 100) return false;
+  Value* r = make_f32_splat(g, n, float(1.0 / c), n->outputs[0]->shape, n->loc);
+  n->opcode = "mul";
+  n->inputs[1] = r;
+  return true;
+}
+
+// an elementwise operation whose operands are all splats of f32 scalars is a splat itself
+static bool fold_splat_arithmetic(Graph& g, Node* n) {
+  if (n->outputs.size() != 1 || n->outputs[0]->dtype != "f32") return false;
+  const std::string& op = n->opcode;
+  double a, b = 0;
+  float r;
+  if (n->inputs.size() == 2 && n->inputs[0]->dtype == "f32" && n->inputs[1]->dtype == "f32" &&
+      splat_f64(n->inputs[0], a) && splat_f64(n->inputs[1], b)) {
+    const float x = float(a), y = float(b);
+    if (op == "add") r = x + y;
+    else if (op == "sub") r = x - y;
+    else if (op == "mul") r = x * y;
+    else if (op == "div") r = x / y;
+    else if (op == "max") r = std::fmax(x, y);
+    else if (op == "min") r = std::fmin(x, y);
+    else return false;
+    if (std::isnan(x) || std::isnan(y)) return false;          // max / min of NaN differ between libraries
+  } else if (n->inputs.size() == 1 && n->inputs[0]->dtype == "f32" && splat_f64(n->inputs[0], a)) {
+    const float x = float(a);
+    if (op == "neg") r = -x;
+    else if (op == "abs") r = std::fabs(x);
+    else if (op == "sqrt" && x >= 0) r = std::sqrt(x);          // correctly rounded everywhere
+    else return false;
+  } else {
+    return false;
+  }
+  Value* v = make_f32_splat(g, n, r, n->outputs[0]->shape, n->loc);
+  return forward(g, n, v), true;
+}
+
+// broadcast that changes nothing
+static bool fold_trivial_broadcast(Graph& g, Node* n) {
+  if (n->opcode != "broadcast" || n->inputs[0]->shape != n->outputs[0]->shape) return false;
+  return forward(g, n, n->inputs[0]), true;
+}
+
+// a constant tensor whose elements are all equal is stored as one scalar and broadcast
+static bool fold_splat_storage(Graph& g, Node* n) {
+  std::vector<uint8_t> b;
+  if (n->opcode != "constant" || n->outputs[0]->shape.empty() || n->outputs[0]->size() < 2 || !constant_bytes(n, b))
+    return false;
+  const std::string dt = n->outputs[0]->dtype;
+  const size_t w = dtype_bytes(dt);
+  if (w == 0 || b.size() != size_t(n->outputs[0]->size()) * w) return false;
+  for (size_t i = w; i < b.size(); ++i)
+    if (b[i] != b[i % w]) return false;
+  Json t = Json::make_object();
+  t.set("__tensor__", Json::make_str(dt));
+  t.set("shape", Json::make_array());
+  t.set("data", Json::make_str(b64_encode(std::vector<uint8_t>(b.begin(), b.begin() + long(w)))));
+  Json attrs = Json::make_object();
+  attrs.set("value", t);
+  Node* c = g.insert_node(n, "constant", {}, attrs, {{dt, {}}}, n->loc);
+  Json battrs = Json::make_object();
+  battrs.set("shape", int_array(n->outputs[0]->shape));
+  battrs.set("dims", Json::make_array());
+  Node* bc = g.insert_node(n, "broadcast", {c->outputs[0]}, battrs, {{dt, n->outputs[0]->shape}}, n->loc);
+  return forward(g, n, bc->outputs[0]), true;
+}
+
+static void canonicalize(Graph& g, const PassOptions&) {
+  using Pattern = bool (*)(Graph&, Node*);
+  static const Pattern patterns[] = {fold_identity_operand, fold_idempotent,           fold_involution,
+                                     fold_convert,          fold_power_of_two_divisor, fold_splat_arithmetic,
+                                     fold_trivial_broadcast, fold_splat_storage};
+  for (int round = 0; round < 8; ++round) {          // rewrites expose one another; graphs settle in two or three
+    bool changed = false;
+    std::vector<Node*> snapshot = g.nodes;             // patterns insert constants while we walk
+    for (Node* n : snapshot) {
+      if (n->dead) continue;
+      for (Pattern p : patterns)
+        if (p(g, n)) {
+          changed = true;
+          break;
+        }
+    }
+    g.sweep();
+    dce(g);
+    if (!changed) break;
+  }
 }
 
 // ---------------------------------------------------------------------------- layout group
