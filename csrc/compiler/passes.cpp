@@ -610,7 +610,9 @@ static long long pick_tn(long long n) {
 static void infer_layout(Graph& g, const PassOptions&) {
   auto uses = g.use_counts();
   for (Node* n : g.nodes) {
-    const Json* knob = n->attrs.has("_knob") ? &n->attrs.at("_knob") : nullptr;
+    // a copy: setting attributes below may move the node's attribute storage
+    const Json knob_copy = n->attrs.has("_knob") ? n->attrs.at("_knob") : Json::make_object();
+    const Json* knob = n->attrs.has("_knob") ? &knob_copy : nullptr;
     if (n->opcode == "dot") {
       DotDims d = dot_dims(n);
       std::vector<long long> tile = {std::min<long long>(d.m, 128), std::min<long long>(pick_tn(d.n), 256),
@@ -632,8 +634,9 @@ static void infer_layout(Graph& g, const PassOptions&) {
       for (Value* v : n->inputs)
         if (v->producer && v->producer->attrs.has("_tile") && v->shape == n->outputs[0]->shape) src = v->producer;
       if (src) {
-        auto t = ints(src->attrs.at("_tile"));
-        n->attrs.set("_tile", int_array({t[0], t[1]}));
+        auto t = ints(src->attrs.at("_tile"));            // [m, n, k] of a dot, or one entry per dimension
+        if (t.size() > 2) t.resize(2);
+        n->attrs.set("_tile", int_array(t));
         n->attrs.set("_mem", Json::make_str("Register"));
       } else {
         const auto& s = n->outputs[0]->shape;

@@ -52,6 +52,20 @@ def build(force: bool = False):
     return module_path(), opt_path()
 
 
+def build_sanitized(out_dir) -> Path:
+    """The command-line driver built with AddressSanitizer and UndefinedBehaviorSanitizer (aborting on the first
+    finding), for running the pass pipeline over test IR on the host.  The reference has no sanitizer configuration;
+    device-side sanitizers are not available for this code base, so the host-side C++ is checked this way."""
+    out = Path(out_dir) / "nkipy-b200-opt-san"
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-fsanitize=address,undefined", "-fno-sanitize-recover=all",
+           "-fno-omit-frame-pointer", str(SRC_DIR / "ir.cpp"), str(SRC_DIR / "passes.cpp"), str(SRC_DIR / "opt_main.cpp"),
+           "-o", str(out)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the sanitized driver failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    return out
+
+
 def opt_main(argv=None) -> int:
     """Console entry `nkipy-b200-opt`: builds the native driver if needed and runs it with the given arguments
     (same role as the reference's `nkigen-opt`, nkigen/tools/nkigen-opt/nkigen-opt.cpp)."""
