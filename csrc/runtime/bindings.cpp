@@ -23,7 +23,10 @@ PYBIND11_MODULE(_spike, m) {
     try {
       if (p) std::rethrow_exception(p);
     } catch (const CudaError& e) {
-      PyErr_SetString(ex_cuda.ptr(), e.what());
+      // the driver's status code travels with the exception (`e.code`), as the vendor code does in the reference
+      py::object exc = py::reinterpret_borrow<py::object>(ex_cuda.ptr())(e.what());
+      exc.attr("code") = e.code();
+      PyErr_SetObject(ex_cuda.ptr(), exc.ptr());
     } catch (const SpikeError& e) {
       PyErr_SetString(ex_spike.ptr(), e.what());
     } catch (const SpikeRuntimeError& e) {

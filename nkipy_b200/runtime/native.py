@@ -48,5 +48,36 @@ def build(force: bool = False) -> Path:
     return out
 
 
+def build_sanitized(out_dir) -> Path:
+    """The runtime module built with AddressSanitizer and UndefinedBehaviorSanitizer, for tests that drive it on the
+    host against a stand-in driver library.  A process that imports it must preload the sanitizer runtime
+    (`sanitizer_preload()`), because the interpreter itself is not instrumented."""
+    import pybind11
+
+    out = Path(out_dir) / module_path().name
+    cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
+           "-fsanitize=address,undefined", "-fno-sanitize-recover=all", "-fno-omit-frame-pointer",
+           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{cuda_inc}",
+           *[str(s) for s in sorted(SRC_DIR.glob("*.cpp"))], "-o", str(out), "-ldl", "-lpthread"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the sanitized runtime failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    return out
+
+
+def sanitizer_preload() -> str:
+    """Value for LD_PRELOAD: the shared AddressSanitizer runtime of the host compiler, followed by the C++ runtime
+    library (the interpreter does not link it, and the sanitizer must find `__cxa_throw` when it starts)."""
+    paths = []
+    for lib in ("libasan.so", "libstdc++.so.6"):
+        res = subprocess.run(["g++", f"-print-file-name={lib}"], capture_output=True, text=True)
+        path = res.stdout.strip()
+        if not os.path.isabs(path):
+            return ""
+        paths.append(os.path.realpath(path))
+    return " ".join(paths)
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))

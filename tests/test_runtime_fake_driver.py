@@ -1,0 +1,441 @@
+"""The C++ device runtime on a machine without a GPU: `tests/fake_cuda/fake_libcuda.cpp` (device memory = host memory,
+launches and copies written to a log, error codes injected by name) is built as libcuda.so.1 and put first on the
+library path of a child process that drives the runtime through its Python bindings.
+
+Covers what the reference checks through its bindings in tests/unit/test_spike_cpp_api.py (tensor life cycle, slices,
+bounds, use after free, models and executes, error types with preserved driver codes, close) plus the launch list a
+loaded module issues and host-side failure injection: the failing driver call is a fake that returns an error code."""
+import json
+import os
+import shutil
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="no host compiler")
+
+
+@pytest.fixture(scope="module")
+def fake_lib(tmp_path_factory):
+    d = tmp_path_factory.mktemp("fake_cuda")
+    cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
+    if not os.path.exists(os.path.join(cuda_inc, "cuda.h")):
+        pytest.skip("CUDA headers not installed")
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-shared", "-fPIC", "-Wall", f"-I{cuda_inc}",
+           os.path.join(ROOT, "tests", "fake_cuda", "fake_libcuda.cpp"), "-o", str(d / "libcuda.so.1")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    return d
+
+
+@pytest.fixture(scope="module")
+def compiled(tmp_path_factory):
+    """A real compiled module (cubin + plan) of a small kernel: the fake driver ignores the code, the runtime reads the plan."""
+    if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        pytest.skip("nvcc not installed")
+    from nkipy_b200.core.compile import compile_to_neff, trace
+
+    def kernel(a, b):
+        return np.tanh(a @ b) + 1.0, np.sum(a, axis=0)
+
+    out = tmp_path_factory.mktemp("module")
+    k = trace(kernel)
+    k.specialize(np.zeros((8, 16), np.float32), np.zeros((16, 4), np.float32))
+    path = compile_to_neff(k, str(out), "k.cubin")
+    plan = json.loads(open(os.path.splitext(path)[0] + ".json").read())
+    return path, plan
+
+
+@pytest.fixture(scope="module")
+def sanitized_module(tmp_path_factory):
+    from nkipy_b200.runtime import native
+
+    preload = native.sanitizer_preload()
+    if not preload or not all(os.path.exists(p) for p in preload.split()):
+        pytest.skip("no shared AddressSanitizer runtime")
+    return native.build_sanitized(tmp_path_factory.mktemp("san_runtime")), preload
+
+
+@pytest.fixture(params=["plain", "sanitized"])
+def fake_dir(request, fake_lib):
+    """The directory of the fake driver; in the `sanitized` variant the child process also loads the runtime module
+    built with AddressSanitizer + UndefinedBehaviorSanitizer (any finding aborts the child, which fails the test)."""
+    if request.param == "plain":
+        return FakeEnv(fake_lib, None, None)
+    so, preload = request.getfixturevalue("sanitized_module")
+    return FakeEnv(fake_lib, so, preload)
+
+
+class FakeEnv:
+    def __init__(self, lib_dir, san_module, preload):
+        self.lib_dir, self.san_module, self.preload = lib_dir, san_module, preload
+
+
+_SAN_PREAMBLE = """
+import importlib.util
+_spec = importlib.util.spec_from_file_location("nkipy_b200.spike._spike", %r)
+_mod = importlib.util.module_from_spec(_spec); _spec.loader.exec_module(_mod)
+sys.modules["nkipy_b200.spike._spike"] = _mod
+"""
+
+
+def run_child(fake, body, env=None, log=None):
+    code = "import sys\nsys.path.insert(0, %r)\nimport numpy as np\n" % ROOT
+    e = dict(os.environ)
+    if fake.san_module is not None:
+        code += _SAN_PREAMBLE % str(fake.san_module)
+        e["LD_PRELOAD"] = fake.preload
+        e["ASAN_OPTIONS"] = "detect_leaks=0:abort_on_error=0:exitcode=99"      # the interpreter's own leaks are not ours
+    code += textwrap.dedent(body)
+    fake_dir = fake.lib_dir
+    e["LD_LIBRARY_PATH"] = str(fake_dir) + os.pathsep + e.get("LD_LIBRARY_PATH", "")
+    e.pop("CUDA_VISIBLE_DEVICES", None)
+    if log is not None:
+        e["FAKE_CUDA_LOG"] = str(log)
+    e.update(env or {})
+    res = subprocess.run([sys.executable, "-W", "ignore", "-c", code], capture_output=True, text=True, timeout=300, env=e)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+def test_device_discovery_and_properties(fake_dir):
+    out = run_child(fake_dir, """
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import get_spike_singleton
+        assert "torch" not in sys.modules
+        print(spike.visible_device_count())
+        rt = get_spike_singleton()
+        print(rt.device_name, rt.sm_count, rt.total_memory >> 30, rt.device_ordinal, rt.is_closed)
+    """, env={"FAKE_CUDA_DEVICES": "4"})
+    assert out.split() == ["4", "Fake", "B200", "#0", "148", "180", "0", "False"]
+
+
+def test_no_devices_is_reported_not_raised(fake_dir):
+    out = run_child(fake_dir, """
+        from nkipy_b200 import spike
+        print(spike.visible_device_count())
+        try:
+            spike.get_spike_singleton()
+        except spike.SpikeError as e:
+            print("error:", e)
+    """, env={"FAKE_CUDA_DEVICES": "0"})
+    assert out.startswith("0\n") and "out of range" in out
+
+
+def test_tensor_life_cycle(fake_dir, tmp_path):
+    log = tmp_path / "log.txt"
+    run_child(fake_dir, """
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import SpikeTensor, get_spike_singleton
+        rt = get_spike_singleton()
+        a = np.arange(64, dtype=np.float32).reshape(8, 8)
+        t = SpikeTensor.from_numpy(a, "whole")
+        assert t.tensor_ref.size == 256 and t.tensor_ref.name == "whole" and t.va != 0 and not t.tensor_ref.is_freed
+        np.testing.assert_array_equal(t.numpy(), a)
+        # a byte-range view shares the allocation
+        rows = t.slice_bytes(2 * 32, (2, 8), name="rows")
+        np.testing.assert_array_equal(rows.numpy(), a[2:4])
+        rows.write_from_numpy(np.zeros((2, 8), np.float32))
+        want = a.copy(); want[2:4] = 0
+        np.testing.assert_array_equal(t.numpy(), want)
+        assert rows.va == t.va + 64
+        # bounds
+        for bad in (lambda: t.slice_bytes(250, (4,), np.float32), lambda: rt.tensor_write(t.tensor_ref, np.zeros(8, np.uint8), 252),
+                    lambda: rt.tensor_read_to_buffer(t.tensor_ref, np.zeros(300, np.uint8), 0)):
+            try:
+                bad()
+            except spike.SpikeError as e:
+                assert "exceeds" in str(e)
+            else:
+                raise AssertionError("no error")
+        # free: the view dies with its parent, later use is an error, a second free is not
+        t.free()
+        assert t.tensor_ref.is_freed and rows.tensor_ref.is_freed
+        for bad in (t.numpy, rows.numpy, lambda: t.slice_bytes(0, (1,), np.float32)):
+            try:
+                bad()
+            except spike.SpikeError as e:
+                assert "freed" in str(e)
+            else:
+                raise AssertionError("no error")
+        t.free()
+        # zero-size tensors
+        z = SpikeTensor.from_numpy(np.zeros((0, 4), np.float32))
+        assert z.numpy().shape == (0, 4)
+    """, log=log)
+    text = log.read_text()
+    assert "bad_free" not in text and "out_of_bounds" not in text          # the runtime's own checks came first
+
+
+def test_module_load_execute_and_launch_list(fake_dir, compiled, tmp_path):
+    path, plan = compiled
+    log = tmp_path / "log.txt"
+    out = run_child(fake_dir, f"""
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import SpikeModel, SpikeTensor, get_spike_singleton
+        m = SpikeModel.load_from_neff({path!r}, name="k")
+        ref = m.model_ref
+        print(ref.num_launches, ref.is_collective, ref.rank_id, ref.world_size, ref.unloaded)
+        print(sorted((n, tuple(t.shape), t.dtype) for n, t in m.input_info.items()), m.input_order)
+        print(sorted((n, tuple(t.shape), t.dtype) for n, t in m.output_info.items()), m.output_order)
+        a = SpikeTensor.from_numpy(np.ones((8, 16), np.float32), "a")
+        b = SpikeTensor.from_numpy(np.ones((16, 4), np.float32), "b")
+        outs = m({{"a": a, "b": b}})
+        print(sorted((k, v.shape) for k, v in outs.items()))
+        # missing, extra and wrongly sized tensors are rejected before anything is launched
+        for bad in ({{"a": a}}, {{"a": a, "b": b, "c": b}}, {{"a": b, "b": a}}):
+            try:
+                m(bad)
+            except (ValueError, spike.SpikeError) as e:
+                print("rejected")
+        a.free()
+        try:
+            m({{"a": a, "b": b}})
+        except (ValueError, spike.SpikeError) as e:
+            print("freed input rejected")
+        m.unload()
+        print(ref.unloaded)
+    """, log=log)
+    lines = out.strip().splitlines()
+    assert lines[0] == f"{len(plan['launches'])} False 0 1 False"
+    assert "('a', (8, 16), 'f32')" in lines[1] and "('b', (16, 4), 'f32')" in lines[1]
+    assert "(8, 4)" in lines[3] and "(16,)" in lines[3]
+    assert lines.count("rejected") == 3 and "freed input rejected" in lines and lines[-1] == "True"
+    launches = [ln for ln in log.read_text().splitlines() if ln.startswith("launch ")]
+    assert len(launches) == len(plan["launches"])                            # one execute went through; the rejected ones launched nothing
+    for ln, want in zip(launches, plan["launches"]):
+        assert ln.split()[1] == want["kernel"]
+        assert f"grid={','.join(map(str, want['grid']))}" in ln and f"block={','.join(map(str, want['block']))}" in ln
+    assert "module_load id=1" in log.read_text() and "module_unload id=1" in log.read_text()
+
+
+def test_benchmark_uses_device_events(fake_dir, compiled):
+    path, plan = compiled
+    out = run_child(fake_dir, f"""
+        from nkipy_b200.spike import SpikeModel, SpikeTensor
+        m = SpikeModel.load_from_neff({path!r}, name="k")
+        a = SpikeTensor.from_numpy(np.ones((8, 16), np.float32), "a")
+        b = SpikeTensor.from_numpy(np.ones((16, 4), np.float32), "b")
+        r = m.benchmark({{"a": a, "b": b}}, warmup_iterations=2, benchmark_iterations=5, mode="device")
+        print(r.iterations, r.warmup_iterations, round(r.mean_ms, 3), round(r.min_ms, 3), round(r.max_ms, 3))
+    """, env={"FAKE_CUDA_EVENT_MS": "0.5"})
+    per_execute = f"{0.5 * len(plan['launches']):.1f}"            # one event pair per launch, 0.5 ms each from the fake
+    assert out.split() == ["5", "2", per_execute, per_execute, per_execute]
+
+
+@pytest.mark.parametrize("call,code,name", [("cuLaunchKernel", 719, "CUDA_ERROR_LAUNCH_FAILED"),
+                                            ("cuLaunchKernel", 702, "CUDA_ERROR_LAUNCH_TIMEOUT"),
+                                            ("cuStreamSynchronize", 700, "CUDA_ERROR_ILLEGAL_ADDRESS"),
+                                            ("cuModuleLoadData", 2, "CUDA_ERROR_OUT_OF_MEMORY")])
+def test_a_failing_driver_call_surfaces_with_its_code_and_leaves_the_runtime_usable(fake_dir, compiled, call, code, name):
+    path, _ = compiled
+    out = run_child(fake_dir, f"""
+        import os
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import SpikeModel, SpikeTensor
+        a = SpikeTensor.from_numpy(np.ones((8, 16), np.float32), "a")
+        b = SpikeTensor.from_numpy(np.ones((16, 4), np.float32), "b")
+        os.environ["FAKE_CUDA_FAIL"] = "{call}:{code}:1"            # the first call of that function fails
+        try:
+            m = SpikeModel.load_from_neff({path!r}, name="k")
+            m({{"a": a, "b": b}})
+            print("no error")
+        except spike.NrtError as e:
+            print("code", e.code, "|", e)
+            assert isinstance(e, spike.SpikeRuntimeError)
+        os.environ.pop("FAKE_CUDA_FAIL")
+        m = SpikeModel.load_from_neff({path!r}, name="k2")                 # the runtime still works afterwards
+        outs = m({{"a": a, "b": b}})
+        print("recovered", len(outs))
+    """)
+    assert "no error" not in out
+    assert f"code {code} |" in out and name in out and f"({code})" in out
+    assert "recovered 2" in out
+
+
+def test_allocation_failure_is_a_typed_error(fake_dir):
+    out = run_child(fake_dir, """
+        import os
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import SpikeTensor, get_spike_singleton
+        get_spike_singleton()
+        os.environ["FAKE_CUDA_FAIL"] = "cuMemAlloc_v2:2"
+        try:
+            SpikeTensor.empty((1024,), np.float32)
+        except spike.CudaError as e:
+            print("oom:", e.code, e)
+        os.environ.pop("FAKE_CUDA_FAIL")
+        print(SpikeTensor.empty((1024,), np.float32).nbytes)
+    """)
+    assert "CUDA_ERROR_OUT_OF_MEMORY (2)" in out and out.strip().endswith("4096")
+
+
+def test_close_and_reset(fake_dir, tmp_path):
+    log = tmp_path / "log.txt"
+    out = run_child(fake_dir, """
+        import warnings
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import SpikeTensor, get_spike_singleton
+        rt = get_spike_singleton()
+        t = SpikeTensor.from_numpy(np.ones(4, np.float32))
+        try:
+            spike.configure(visible_cores=[0])
+        except RuntimeError as e:
+            print("configure refused")
+        with warnings.catch_warnings(record=True):
+            warnings.simplefilter("always")
+            spike.reset()
+        print(rt.is_closed, t.tensor_ref.is_freed)
+        try:
+            t.numpy()
+        except spike.SpikeError:
+            print("stale tensor rejected")
+        rt2 = get_spike_singleton()
+        print(rt2 is not rt, rt2.is_closed)
+        print(SpikeTensor.from_numpy(np.full(4, 3.0, np.float32)).numpy().sum())
+    """, log=log)
+    assert out.split("\n")[:5] == ["configure refused", "True True", "stale tensor rejected", "True False", "12.0"]
+    assert log.read_text().count("ctx_release") == 2                         # once at reset, once at exit
+
+
+def test_system_trace_session(fake_dir, compiled):
+    path, _ = compiled
+    out = run_child(fake_dir, f"""
+        import json
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import SpikeModel, SpikeTensor
+        m = SpikeModel.load_from_neff({path!r}, name="k")
+        a = SpikeTensor.from_numpy(np.ones((8, 16), np.float32), "a")
+        b = SpikeTensor.from_numpy(np.ones((16, 4), np.float32), "b")
+        with spike.SystemTraceSession() as s:
+            for _ in range(3):
+                m({{"a": a, "b": b}})
+            ev = json.loads(s.fetch_events_json())["events"]
+        kinds = [(e["event_type"], e["phase"]) for e in ev]
+        print(kinds.count(("kernel_exec", "start")), kinds.count(("kernel_exec", "stop")))
+        print(len(json.loads(s.fetch_events_json())["events"]))                # the ring was consumed
+    """)
+    assert out.split() == ["3", "3", "0"]
+
+
+# ------------------------------------------------------------------ symmetric memory on the fake driver's VMM emulation
+def test_symmetric_buffers_alias_across_ranks_and_release_everything(fake_dir, tmp_path):
+    log = tmp_path / "log.txt"
+    out = run_child(fake_dir, """
+        import ctypes, os
+        from nkipy_b200.spike.spike_singleton import _native
+        S = _native()
+        assert S.SymmetricBuffer.supported(0) and S.SymmetricBuffer.multicast_supported(1)
+        bufs = [S.SymmetricBuffer(r, 1000) for r in range(3)]
+        print(sorted({b.size for b in bufs}), [b.device_ordinal for b in bufs])
+        fds = [b.export_fd() for b in bufs]
+        for r, b in enumerate(bufs):
+            for p, fd in enumerate(fds):
+                if p != r:
+                    b.import_peer(p, fd)
+            b.zero()
+        for fd in fds:
+            os.close(fd)
+        # what rank r writes through its mapping of rank p's memory, rank p reads in its own
+        for r, b in enumerate(bufs):
+            for p in range(3):
+                if p != r:
+                    ctypes.memmove(b.peer_ptr(p) + 64 * r, b"from%d" % r, 5)
+        for p, b in enumerate(bufs):
+            got = [ctypes.string_at(b.local_ptr + 64 * r, 5) for r in range(3) if r != p]
+            assert got == [b"from%d" % r for r in range(3) if r != p], got
+            assert b.peer_ptr(p) == 0 and len({b.peer_ptr(q) for q in range(3) if q != p} | {b.local_ptr}) == 3
+        # multicast object: created by rank 0, imported by the others, every device added before anyone binds
+        m = bufs[0].multicast_create(3)
+        for b in bufs[1:]:
+            b.multicast_import(m)
+        os.close(m)
+        for b in bufs:
+            b.multicast_add_device()
+        for b in bufs:
+            b.multicast_bind()
+        print([b.has_multicast for b in bufs], all(b.multicast_ptr for b in bufs))
+        for b in bufs:
+            b.close()
+            b.close()                                   # idempotent
+        print([b.closed for b in bufs])
+    """, env={"FAKE_CUDA_DEVICES": "3"}, log=log)
+    assert out.splitlines() == ["[2097152] [0, 1, 2]", "[True, True, True] True", "[True, True, True]"]
+    text = log.read_text()
+    assert text.count("mem_create") == 3 and text.count("multicast_bind") == 3 and text.count("multicast_unbind") == 3
+    assert text.strip().splitlines()[-1] == "mem_release live_handles=0"
+    for bad in ("bad_release", "bad_unmap", "bad_unbind", "bad_address_free", "address_free_while_mapped"):
+        assert bad not in text
+
+
+def test_symmetric_buffer_misuse_and_driver_failures(fake_dir, tmp_path):
+    log = tmp_path / "log.txt"
+    out = run_child(fake_dir, """
+        import os
+        from nkipy_b200 import spike
+        from nkipy_b200.spike.spike_singleton import _native
+        S = _native()
+        a = S.SymmetricBuffer(0, 4096)
+        def expect(fn, *types):
+            try:
+                fn()
+            except types as e:
+                return type(e).__name__
+            return "no error"
+        r, w = os.pipe()
+        print(expect(lambda: a.import_peer(1, w), spike.SpikeRuntimeError))       # not an allocation handle
+        os.close(r); os.close(w)
+        print(expect(lambda: a.import_peer(0, a.export_fd()), spike.SpikeRuntimeError, ValueError))   # mapping one's own allocation a second time is allowed
+        print(expect(lambda: S.SymmetricBuffer(7, 4096), spike.SpikeRuntimeError))  # no such device
+        os.environ["FAKE_CUDA_FAIL"] = "cuMemMap:2"
+        print(expect(lambda: S.SymmetricBuffer(1, 4096), spike.CudaError))
+        os.environ["FAKE_CUDA_FAIL"] = "cuMemSetAccess:1"
+        print(expect(lambda: S.SymmetricBuffer(1, 4096), spike.CudaError))
+        os.environ.pop("FAKE_CUDA_FAIL")
+        b = S.SymmetricBuffer(1, 4096)                                            # and afterwards it works
+        a.close(); b.close()
+        print(expect(lambda: a.export_fd(), spike.SpikeRuntimeError))             # closed
+    """, env={"FAKE_CUDA_DEVICES": "2"}, log=log)
+    lines = out.splitlines()
+    assert lines == ["CudaError", "no error", "CudaError", "CudaError", "CudaError", "SpikeError"]
+    text = log.read_text()
+    # the constructors that failed half way gave back what they had taken
+    assert "address_free_while_mapped" not in text and "bad_unmap" not in text and "bad_release" not in text
+    assert text.strip().splitlines()[-1] == "mem_release live_handles=0"
+
+
+def test_descriptors_cross_processes(fake_lib, tmp_path):
+    """Two processes, one buffer each; the descriptors travel over a Unix socket pair with SCM_RIGHTS, and a write by
+    one process through its mapping of the other's memory is read by the owner."""
+    body = """
+        import ctypes, os, socket, sys, time
+        from nkipy_b200.spike.spike_singleton import _native
+        S = _native()
+        rank = int(sys.argv[1]); sock = socket.socket(fileno=int(sys.argv[2]))
+        buf = S.SymmetricBuffer(rank, 8192); buf.zero()
+        fd = buf.export_fd()
+        socket.send_fds(sock, [b"fd"], [fd]); os.close(fd)
+        _, fds, _, _ = socket.recv_fds(sock, 16, 1)
+        buf.import_peer(1 - rank, fds[0]); os.close(fds[0])
+        ctypes.memmove(buf.peer_ptr(1 - rank) + 128, b"written by rank %d" % rank, 17)
+        sock.sendall(b"done"); assert sock.recv(4) == b"done"                  # both have written
+        print(ctypes.string_at(buf.local_ptr + 128, 17).decode())
+        sock.sendall(b"read"); assert sock.recv(4) == b"read"                  # both have read: safe to unmap
+        buf.close()
+    """
+    import socket
+
+    a, b = socket.socketpair(socket.AF_UNIX, socket.SOCK_STREAM)
+    code = "import sys\nsys.path.insert(0, %r)\n" % ROOT + textwrap.dedent(body)
+    env = dict(os.environ, LD_LIBRARY_PATH=str(fake_lib), FAKE_CUDA_DEVICES="2")
+    env.pop("CUDA_VISIBLE_DEVICES", None)
+    procs = [subprocess.Popen([sys.executable, "-W", "ignore", "-c", code, str(r), str(s.fileno())], env=env, pass_fds=[s.fileno()],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r, s in ((0, a), (1, b))]
+    outs = [p.communicate(timeout=120) for p in procs]
+    a.close(); b.close()
+    assert [p.returncode for p in procs] == [0, 0], outs
+    assert outs[0][0].strip() == "written by rank 1" and outs[1][0].strip() == "written by rank 0"
