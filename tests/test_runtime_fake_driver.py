@@ -439,3 +439,70 @@ def test_descriptors_cross_processes(fake_lib, tmp_path):
     a.close(); b.close()
     assert [p.returncode for p in procs] == [0, 0], outs
     assert outs[0][0].strip() == "written by rank 1" and outs[1][0].strip() == "written by rank 0"
+
+
+# ------------------------------------------------------------------ modules with collectives
+@pytest.fixture(scope="module")
+def compiled_cc(tmp_path_factory):
+    if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        pytest.skip("nvcc not installed")
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_segmented_cc import _data, make_kernel
+
+    from nkipy_b200.core.compile import compile_to_neff, trace
+
+    paths = {}
+    for world in (1, 2):
+        x, w = _data(0)
+        k = trace(make_kernel(world))
+        k.specialize(x, w)
+        out = tmp_path_factory.mktemp(f"cc{world}")
+        paths[world] = compile_to_neff(k, str(out), "k.cubin")
+    return paths
+
+
+def test_collective_module_load_rules(fake_dir, compiled_cc, tmp_path):
+    log = tmp_path / "log.txt"
+    out = run_child(fake_dir, f"""
+        from nkipy_b200 import spike
+        from nkipy_b200.spike import get_spike_singleton, SpikeTensor
+        rt = get_spike_singleton()
+        def expect(fn):
+            try:
+                fn()
+            except spike.SpikeRuntimeError as e:
+                return str(e)
+            return "no error"
+        one, two = {compiled_cc[1]!r}, {compiled_cc[2]!r}
+        # traced for one rank: the module brings its own workspace and runs alone
+        m1 = rt.load_model(one, 0, False, 0, 1)
+        print(m1.has_collectives, m1.collective_world, m1.workspace_bytes > 0)
+        print(expect(lambda: m1.set_collective_workspace([1])))                   # already set at load
+        # traced for two ranks: needs a collective load of the same world
+        print(expect(lambda: rt.load_model(two, 0, False, 0, 1)))
+        print(expect(lambda: rt.load_model(two, 0, True, 0, 4)))
+        print(expect(lambda: rt.load_model(two, 0, True, 2, 2)))
+        m2 = rt.load_model(two, 0, True, 1, 2)
+        print(m2.is_collective, m2.rank_id, m2.world_size, m2.collective_world)
+        info = rt.get_tensor_info(m2)
+        ins = {{n: SpikeTensor.empty(tuple(t.shape), np.float32, n).tensor_ref for n, t in dict(info.inputs).items()}}
+        outs = {{n: SpikeTensor.empty(tuple(t.shape), np.float32, n).tensor_ref for n, t in dict(info.outputs).items()}}
+        print(expect(lambda: rt.execute(m2, ins, outs, "", False)))               # no peer table yet
+        print(expect(lambda: m2.set_collective_workspace([4096])))                # one entry for two ranks
+        ws = [SpikeTensor.empty((m2.workspace_bytes,), np.uint8, f"ws{{r}}") for r in range(2)]
+        m2.set_collective_workspace([w.va for w in ws])
+        print(expect(lambda: m2.set_collective_workspace([w.va for w in ws])))    # only once
+        rt.execute(m2, ins, outs, "", False)
+        print("executed", m2.num_launches)
+    """, log=log)
+    lines = out.splitlines()
+    assert lines[0] == "True 1 True" and "already set" in lines[1]
+    assert "load it with cc_enabled and world_size 2" in lines[2] and "world_size 2" in lines[3]
+    assert "rank_id < world_size" in lines[4]
+    assert lines[5] == "True 1 2 2"
+    assert "set_collective_workspace" in lines[6] and "needs 2 entries" in lines[7] and "already set" in lines[8]
+    assert lines[9].startswith("executed ")
+    launched = [ln.split()[1] for ln in log.read_text().splitlines() if ln.startswith("launch ")]
+    assert len(launched) == int(lines[9].split()[1])
+    kinds = {k.split("_", 1)[1] for k in launched}
+    assert {"cc_push", "cc_all_reduce", "cc_all_gather", "cc_reduce_scatter", "cc_all_to_all"} <= kinds
