@@ -506,3 +506,70 @@ def test_collective_module_load_rules(fake_dir, compiled_cc, tmp_path):
     assert len(launched) == int(lines[9].split()[1])
     kinds = {k.split("_", 1)[1] for k in launched}
     assert {"cc_push", "cc_all_reduce", "cc_all_gather", "cc_reduce_scatter", "cc_all_to_all"} <= kinds
+
+
+# ------------------------------------------------------------------ the spike-run command line, end to end
+def _cli(fake_lib, args, env=None, cwd=None):
+    e = dict(os.environ, LD_LIBRARY_PATH=str(fake_lib), PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    e.pop("CUDA_VISIBLE_DEVICES", None)
+    e.update(env or {})
+    return subprocess.run([sys.executable, "-W", "ignore", "-m", "nkipy_b200.spike.cli", *args], capture_output=True,
+                          text=True, timeout=300, env=e, cwd=cwd)
+
+
+def test_cli_single_core_run_benchmark_and_trace(fake_lib, compiled, tmp_path):
+    path, plan = compiled
+    a = np.ones((8, 16), np.float32)
+    np.save(tmp_path / "a.npy", a)
+    log = tmp_path / "log.txt"
+    res = _cli(fake_lib, [path, "-i", f"a={tmp_path / 'a.npy'}", "--output-dir", str(tmp_path / "out")],
+               env={"FAKE_CUDA_LOG": str(log)})
+    assert res.returncode == 0, res.stderr[-2000:]
+    produced = sorted(os.listdir(tmp_path / "out"))
+    assert len(produced) == 2 and all(p.endswith(".npy") for p in produced)        # b was not given: zeros
+    shapes = sorted(np.load(tmp_path / "out" / p).shape for p in produced)
+    assert shapes == [(8, 4), (16,)]
+    assert sum(ln.startswith("launch ") for ln in log.read_text().splitlines()) == len(plan["launches"])
+    # without an output directory the results are summarised on stdout
+    res = _cli(fake_lib, [path])
+    assert res.returncode == 0 and res.stdout.count("[core 0]") == 2 and "shape=(8, 4)" in res.stdout
+    # benchmark: warm-up + iterations executes, the statistics come from device events
+    log.write_text("")
+    res = _cli(fake_lib, [path, "--benchmark", "--warmup", "2", "--iterations", "3"],
+               env={"FAKE_CUDA_LOG": str(log), "FAKE_CUDA_EVENT_MS": "0.125"})
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "over 3 iterations (2 warm-up)" in res.stdout and f"mean {0.125 * len(plan['launches']):.4f} ms" in res.stdout
+    assert sum(ln.startswith("launch ") for ln in log.read_text().splitlines()) == 5 * len(plan["launches"])
+    # trace file
+    res = _cli(fake_lib, [path, "--save-trace", "--ntff-name", str(tmp_path / "trace.json")])
+    assert res.returncode == 0, res.stderr[-2000:]
+    trace_doc = json.loads((tmp_path / "trace.json").read_text())
+    assert trace_doc and json.dumps(trace_doc).count(plan["launches"][0]["kernel"]) >= 1
+
+
+def test_cli_rejects_bad_inputs(fake_lib, compiled, tmp_path):
+    path, _ = compiled
+    np.save(tmp_path / "wrong.npy", np.ones((3, 3), np.float32))
+    res = _cli(fake_lib, [path, "-i", f"a={tmp_path / 'wrong.npy'}"])
+    assert res.returncode != 0 and "expected shape (8, 16)" in res.stderr
+    res = _cli(fake_lib, [path, "-i", "a"])
+    assert res.returncode != 0 and "expected name=path.npy" in res.stderr
+    res = _cli(fake_lib, [str(tmp_path / "missing.cubin")])
+    assert res.returncode != 0
+    res = _cli(fake_lib, [path, "--cc-enabled", "--rank-id", "3", "--world-size", "2"])
+    assert res.returncode != 0 and "--rank-id" in res.stderr
+
+
+def test_cli_multi_core_expands_rank_in_input_names(fake_lib, compiled, tmp_path):
+    path, _ = compiled
+    for r in range(2):
+        np.save(tmp_path / f"a_{r}.npy", np.full((8, 16), float(r + 1), np.float32))
+    log = tmp_path / "log.txt"
+    res = _cli(fake_lib, [path, "--num-cores", "2", "-i", f"a={tmp_path}/a_{{rank}}.npy", "--output-dir", str(tmp_path / "out")],
+               env={"FAKE_CUDA_DEVICES": "2", "FAKE_CUDA_LOG": str(log)})
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert sorted(os.listdir(tmp_path / "out")) == ["core_0", "core_1"]
+    assert all(len(os.listdir(tmp_path / "out" / f"core_{r}")) == 2 for r in range(2))
+    # more cores than devices
+    res = _cli(fake_lib, [path, "--num-cores", "2"], env={"FAKE_CUDA_DEVICES": "1"})
+    assert res.returncode != 0
