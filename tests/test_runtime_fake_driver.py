@@ -80,6 +80,8 @@ import importlib.util
 _spec = importlib.util.spec_from_file_location("nkipy_b200.spike._spike", %r)
 _mod = importlib.util.module_from_spec(_spec); _spec.loader.exec_module(_mod)
 sys.modules["nkipy_b200.spike._spike"] = _mod
+import os as _os
+_os.environ.pop("LD_PRELOAD", None)          # it has done its work here; compilers started from this process must not inherit it
 """
 
 
@@ -573,3 +575,75 @@ def test_cli_multi_core_expands_rank_in_input_names(fake_lib, compiled, tmp_path
     # more cores than devices
     res = _cli(fake_lib, [path, "--num-cores", "2"], env={"FAKE_CUDA_DEVICES": "1"})
     assert res.returncode != 0
+
+
+# ------------------------------------------------------------------ one-shot execution and the kernel cache
+def test_jit_and_one_shot_execution_flow(fake_dir, tmp_path):
+    """Trace -> compile -> load -> run -> read back, as the reference's tests/integration/test_execute.py does on a
+    device.  The stand-in driver computes nothing, so the checks are on shapes, dtypes, names, write-back and files."""
+    out = run_child(fake_dir, f"""
+        import os
+        from nkipy_b200.runtime import baremetal_jit, baremetal_run_traced_kernel, BaremetalExecutor, CompiledKernel
+        from nkipy_b200.core.compile import trace, compile_to_neff
+
+        def kernel(a, b):
+            return np.tanh(a @ b), a.sum(axis=0)
+
+        a, b = np.ones((8, 16), np.float32), np.ones((16, 4), np.float32)
+        assert [x.shape for x in kernel(a, b)] == [(8, 4), (16,)]                  # direct mode needs no device
+        o = baremetal_jit(kernel)(a, b)
+        print([x.shape for x in o], [str(x.dtype) for x in o])
+        o = baremetal_jit(kernel)(a.astype(np.float64), b.astype(np.float64))      # wide inputs are narrowed
+        print([str(x.dtype) for x in o])
+        print(baremetal_jit(lambda x: x[:, :0] * 2.0)(a).shape)                    # an empty result never reaches the device
+
+        def update(cache, v):
+            cache[2:4] = v
+            return np.sum(cache, axis=0)
+
+        cache = np.arange(128, dtype=np.float32).reshape(8, 16)
+        r = baremetal_run_traced_kernel(update, cache, np.ones((2, 16), np.float32), artifacts_dir={str(tmp_path)!r},
+                                        save_trace=True)
+        print(r.shape, cache.shape, str(cache.dtype))                               # the mutated input is read back from the device
+        print(sorted(f for f in os.listdir({str(tmp_path)!r}) if f.endswith(".json"))[:3])
+
+        k = trace(kernel); k.specialize(a, b)
+        ck = CompiledKernel(k, compile_to_neff(k, {str(tmp_path / 'ck')!r}, "k.cubin"))
+        with BaremetalExecutor() as ex:
+            r = ex.run(ck, a, b)
+            st = ex.benchmark(ck, a, b, warmup_iterations=1, benchmark_iterations=4)
+        print([x.shape for x in r], st.iterations, st.warmup_iterations)
+    """)
+    lines = out.splitlines()
+    assert lines[0] == "[(8, 4), (16,)] ['float32', 'float32']" and lines[1] == "['float32', 'float32']"
+    assert lines[2] == "(8, 0)"
+    assert lines[3] == "(16,) (8, 16) float32"
+    assert any("trace" in f for f in eval(lines[4]))
+    assert lines[5] == "[(8, 4), (16,)] 4 1"
+
+
+def test_kernel_cache_in_memory_and_on_disk(fake_dir, tmp_path):
+    build = str(tmp_path / "build")
+    body = f"""
+        from nkipy_b200.runtime import DeviceKernel, device_kernel as DK
+        def mm(a, b):
+            return a @ b
+        a, b = np.ones((8, 16), np.float32), np.ones((16, 4), np.float32)
+        if sys.argv[-1] == "second":
+            def refuse(*args, **kw):
+                raise AssertionError("compiled again although the artifact is on disk")
+            DK.compile_to_neff = refuse
+        k1 = DeviceKernel.compile_and_load(mm, a, b, name="mm", build_dir={build!r})
+        k2 = DeviceKernel.compile_and_load(mm, a, b, name="mm", build_dir={build!r})
+        k3 = DeviceKernel.compile_and_load(mm, a[:4], b, name="mm", build_dir={build!r}) if sys.argv[-1] != "second" else None
+        print(k1 is k2, k3 is not k1 if k3 is not None else "-", k1.neff_path.startswith({build!r}))
+    """
+    log = tmp_path / "log.txt"
+    out = run_child(fake_dir, body, log=log)
+    assert out.split() == ["True", "True", "True"]
+    assert log.read_text().count("module_load") == 2                               # two shapes, each loaded once
+    # a new process finds the artifact on disk
+    code_env = {"FAKE_CUDA_LOG": str(log)}
+    log.write_text("")
+    out = run_child(fake_dir, body.replace('sys.argv[-1]', '"second"'), env=code_env)
+    assert out.split() == ["True", "-", "True"] and log.read_text().count("module_load") == 1
