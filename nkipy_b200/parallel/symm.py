@@ -124,12 +124,18 @@ class SymmetricMemory:
         else:
             self._init_ipc()
 
+    def _device_sync(self) -> None:
+        """Wait for this process's device work; a group without a CUDA device (host-side tests) has none."""
+        dev = self.tp.device
+        if dev is not None and getattr(dev, "type", "cuda") == "cuda":
+            torch.cuda.synchronize()
+
     # ------------------------------------------------------------------ VMM + multicast
     def _init_vmm(self, rt, dev_index: int, want_mc: bool) -> None:
         import os
 
         tp = self.tp
-        torch.cuda.synchronize()
+        self._device_sync()
         buf = rt.SymmetricBuffer(dev_index, self.nbytes)
         self._buf = buf
         buf.zero()
@@ -213,7 +219,7 @@ class SymmetricMemory:
         if self._closed:
             return
         self._closed = True
-        torch.cuda.synchronize()
+        self._device_sync()
         if self.backend == "vmm":
             self._buf.close()
             return
@@ -226,7 +232,7 @@ class SymmetricMemory:
         if self._closed:
             return
         self._closed = True
-        torch.cuda.synchronize()
+        self._device_sync()
         self.tp.barrier()
         if self.backend == "vmm":
             self._buf.close()

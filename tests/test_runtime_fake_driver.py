@@ -647,3 +647,51 @@ def test_kernel_cache_in_memory_and_on_disk(fake_dir, tmp_path):
     log.write_text("")
     out = run_child(fake_dir, body.replace('sys.argv[-1]', '"second"'), env=code_env)
     assert out.split() == ["True", "-", "True"] and log.read_text().count("module_load") == 1
+
+
+def test_symmetric_memory_bootstrap_over_gloo_ranks(fake_lib, tmp_path):
+    """`parallel.symm.SymmetricMemory` end to end on two host processes: gloo for the barriers, Unix sockets for the
+    descriptors, the C++ `SymmetricBuffer` on the stand-in driver for the mappings, a multicast object on top; then the
+    collective close, and on a second buffer the one-sided `abandon()` of the recovery path."""
+    body = """
+        import ctypes, datetime, os, sys
+        import torch, torch.distributed as dist
+        rank, world, port = int(sys.argv[1]), 2, sys.argv[2]
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=60))
+        from nkipy_b200.parallel.comm import TPGroup
+        from nkipy_b200.parallel.symm import SymmetricMemory
+        tp = TPGroup(rank, world, dist.group.WORLD, torch.device("cpu"))
+        mem = SymmetricMemory(tp, 1 << 16, multicast=True)
+        assert mem.backend == "vmm" and len(mem.ptrs) == 2 and mem.ptrs[rank] == mem.local_ptr and mem.mc_ptr != 0
+        ctypes.memmove(mem.ptrs[1 - rank] + 256, b"rank %d was here" % rank, 15)
+        tp.barrier()
+        print(ctypes.string_at(mem.local_ptr + 256, 15).decode())
+        mem.close(); mem.close()
+        second = SymmetricMemory(tp, 4096, multicast=False)
+        assert second.mc_ptr == 0
+        tp.barrier()
+        second.abandon()                       # no barrier inside: either rank may go first
+        print("closed")
+        dist.destroy_process_group()
+    """
+    import socket
+
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    code = "import sys\nsys.path.insert(0, %r)\n" % ROOT + textwrap.dedent(body)
+    logs = [tmp_path / f"log{r}.txt" for r in range(2)]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, LD_LIBRARY_PATH=str(fake_lib), FAKE_CUDA_DEVICES="2", FAKE_CUDA_LOG=str(logs[r]),
+                   NKIPY_B200_NVLS="1")
+        env.pop("CUDA_VISIBLE_DEVICES", None)
+        procs.append(subprocess.Popen([sys.executable, "-W", "ignore", "-c", code, str(r), str(port)], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=240) for p in procs]
+    assert [p.returncode for p in procs] == [0, 0], outs
+    assert outs[0][0].split("\n")[:2] == ["rank 1 was here", "closed"] and outs[1][0].split("\n")[:2] == ["rank 0 was here", "closed"]
+    for log in logs:
+        text = log.read_text()
+        assert text.count("multicast_bind") == 1 and text.count("multicast_unbind") == 1
+        assert "mem_release live_handles=0" in text.splitlines()[-1]
+        assert not any(bad in text for bad in ("bad_release", "bad_unmap", "bad_unbind", "address_free_while_mapped"))
