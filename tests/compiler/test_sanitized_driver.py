@@ -132,3 +132,41 @@ def test_the_numerical_suite_kernels_are_clean_too(san):
         res = _run(san, text, "--pipeline")
         assert res.returncode == 0 and "Sanitizer" not in res.stderr and "runtime error" not in res.stderr, \
             (name, res.stderr[-3000:])
+
+
+def test_the_spec_kernels_are_clean_and_keep_their_results(san):
+    """Every specification kernel under tests/kernels, traced on its default inputs, goes through the sanitized
+    pipeline; the lowered graph still evaluates to what direct mode gives."""
+    import copy
+    import glob
+    import importlib
+    import os
+
+    from utils import trace_kernel
+
+    from nkipy_b200.core.interp import evaluate
+    from nkipy_b200.core.ir import Graph
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    n = 0
+    for path in sorted(glob.glob(os.path.join(here, "..", "kernels", "*.py"))):
+        stem = os.path.splitext(os.path.basename(path))[0]
+        if stem == "__init__":
+            continue
+        specs = getattr(importlib.import_module(f"kernels.{stem}"), "kernel_specs", None) or []
+        for spec in specs if isinstance(specs, list) else [specs]:
+            if not spec.is_pure_numpy:
+                continue
+            inputs = spec.default_inputs(np.random.default_rng(0))
+            g = trace_kernel(spec.function, *copy.deepcopy(inputs))
+            res = _run(san, g.to_text(), "--pipeline")
+            assert res.returncode == 0 and "Sanitizer" not in res.stderr and "runtime error" not in res.stderr, \
+                (stem, spec.function.__name__, res.stderr[-3000:])
+            arrays = [np.asarray(a) for a in inputs if isinstance(a, np.ndarray)]
+            got = evaluate(Graph.from_text(res.stdout), [a.astype(p.dtype) for a, p in zip(arrays, g.params)])
+            want = spec.function(*copy.deepcopy(inputs))
+            want = list(want) if isinstance(want, (tuple, list)) else [want]
+            for o, e in zip(got, want):
+                np.testing.assert_allclose(np.asarray(o, np.float64), np.asarray(e, np.float64), rtol=2e-3, atol=2e-3)
+            n += 1
+    assert n >= 12
