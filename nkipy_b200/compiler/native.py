@@ -33,22 +33,42 @@ def build(force: bool = False):
     stamp = h.hexdigest()[:16]
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     stamp_file = BUILD_DIR / "stamp"
-    if (not force and module_path().exists() and opt_path().exists() and stamp_file.exists()
-            and stamp_file.read_text() == stamp):
+    def fresh() -> bool:
+        return (module_path().exists() and opt_path().exists() and stamp_file.exists()
+                and stamp_file.read_text() == stamp)
+
+    if not force and fresh():
         return module_path(), opt_path()
+    import fcntl
+    import os
+
     lib = [str(SRC_DIR / "ir.cpp"), str(SRC_DIR / "passes.cpp")]
     common = ["g++", "-O2", "-std=c++17", "-Wall", "-fPIC"]
-    cmds = [
-        common + ["-shared", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
-                  f"-I{sysconfig.get_paths()['include']}", *lib, str(SRC_DIR / "bindings.cpp"), "-o",
-                  str(module_path())],
-        common + [*lib, str(SRC_DIR / "opt_main.cpp"), "-o", str(opt_path())],
-    ]
-    for cmd in cmds:
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"building the native compiler failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
-    stamp_file.write_text(stamp)
+    # one process builds while others wait; outputs are written under temporary names and moved into place
+    with open(BUILD_DIR / "lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and fresh():
+                return module_path(), opt_path()
+            tmp_mod = module_path().with_name(module_path().name + f".tmp{os.getpid()}")
+            tmp_opt = opt_path().with_name(opt_path().name + f".tmp{os.getpid()}")
+            cmds = [
+                common + ["-shared", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
+                          f"-I{sysconfig.get_paths()['include']}", *lib, str(SRC_DIR / "bindings.cpp"), "-o", str(tmp_mod)],
+                common + [*lib, str(SRC_DIR / "opt_main.cpp"), "-o", str(tmp_opt)],
+            ]
+            for cmd in cmds:
+                res = subprocess.run(cmd, capture_output=True, text=True)
+                if res.returncode != 0:
+                    for t in (tmp_mod, tmp_opt):
+                        if t.exists():
+                            t.unlink()
+                    raise RuntimeError(f"building the native compiler failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+            os.replace(tmp_mod, module_path())
+            os.replace(tmp_opt, opt_path())
+            stamp_file.write_text(stamp)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return module_path(), opt_path()
 
 

@@ -35,16 +35,35 @@ def build(force: bool = False) -> Path:
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     stamp_file = BUILD_DIR / "stamp"
     out = module_path()
-    if not force and out.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
+
+    def fresh() -> bool:
+        return out.exists() and stamp_file.exists() and stamp_file.read_text() == stamp
+
+    if not force and fresh():
         return out
-    cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
-    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
-           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{cuda_inc}",
-           *[str(s) for s in srcs], "-o", str(out), "-ldl", "-lpthread"]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"building the device runtime failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
-    stamp_file.write_text(stamp)
+    import fcntl
+
+    # several rank processes may get here at once: one builds, the others wait and find it done; the module is
+    # linked under a temporary name and moved into place, so nobody ever maps a half-written file
+    with open(BUILD_DIR / "lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and fresh():
+                return out
+            cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
+            tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+            cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
+                   f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{cuda_inc}",
+                   *[str(s) for s in srcs], "-o", str(tmp), "-ldl", "-lpthread"]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                if tmp.exists():
+                    tmp.unlink()
+                raise RuntimeError(f"building the device runtime failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+            os.replace(tmp, out)
+            stamp_file.write_text(stamp)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return out
 
 
