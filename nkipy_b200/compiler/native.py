@@ -72,17 +72,30 @@ def build(force: bool = False):
     return module_path(), opt_path()
 
 
-def build_sanitized(out_dir) -> Path:
+def _source_digest() -> str:
+    h = hashlib.sha256()
+    for d in sorted(SRC_DIR.glob("*.cpp")) + sorted(SRC_DIR.glob("*.h")) + [ROOT / "csrc" / "runtime" / "json.h"]:
+        h.update(d.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def build_sanitized(out_dir=None) -> Path:
     """The command-line driver built with AddressSanitizer and UndefinedBehaviorSanitizer (aborting on the first
     finding), for running the pass pipeline over test IR on the host.  The reference has no sanitizer configuration;
     device-side sanitizers are not available for this code base, so the host-side C++ is checked this way."""
-    out = Path(out_dir) / "nkipy-b200-opt-san"
+    out_dir = Path(out_dir) if out_dir is not None else BUILD_DIR / "sanitized"      # kept between runs: the build takes a while
+    out_dir.mkdir(parents=True, exist_ok=True)
+    out = out_dir / "nkipy-b200-opt-san"
+    stamp, stamp_file = _source_digest(), out_dir / "stamp"
+    if out.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
+        return out
     cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-fsanitize=address,undefined", "-fno-sanitize-recover=all",
            "-fno-omit-frame-pointer", str(SRC_DIR / "ir.cpp"), str(SRC_DIR / "passes.cpp"), str(SRC_DIR / "opt_main.cpp"),
            "-o", str(out)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"building the sanitized driver failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    stamp_file.write_text(stamp)
     return out
 
 

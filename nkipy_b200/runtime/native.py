@@ -67,13 +67,25 @@ def build(force: bool = False) -> Path:
     return out
 
 
-def build_sanitized(out_dir) -> Path:
+def _source_digest() -> str:
+    h = hashlib.sha256()
+    for d in sorted(SRC_DIR.glob("*.cpp")) + sorted(SRC_DIR.glob("*.h")) + [ROOT / "csrc" / "kernels" / "gemm_args.h"]:
+        h.update(d.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def build_sanitized(out_dir=None) -> Path:
     """The runtime module built with AddressSanitizer and UndefinedBehaviorSanitizer, for tests that drive it on the
     host against a stand-in driver library.  A process that imports it must preload the sanitizer runtime
     (`sanitizer_preload()`), because the interpreter itself is not instrumented."""
     import pybind11
 
-    out = Path(out_dir) / module_path().name
+    out_dir = Path(out_dir) if out_dir is not None else BUILD_DIR / "sanitized"      # kept between runs: the build takes a while
+    out_dir.mkdir(parents=True, exist_ok=True)
+    out = out_dir / module_path().name
+    stamp, stamp_file = _source_digest(), out_dir / "stamp"
+    if out.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
+        return out
     cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
     cmd = ["g++", "-O1", "-g", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
            "-fsanitize=address,undefined", "-fno-sanitize-recover=all", "-fno-omit-frame-pointer",
@@ -82,6 +94,7 @@ def build_sanitized(out_dir) -> Path:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"building the sanitized runtime failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    stamp_file.write_text(stamp)
     return out
 
 

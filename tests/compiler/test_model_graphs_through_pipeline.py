@@ -91,7 +91,7 @@ def test_lowered_model_graphs_keep_their_results(graphs):
 @pytest.mark.skipif(shutil.which("g++") is None, reason="no host compiler")
 def test_model_graphs_are_clean_under_the_sanitizers(graphs, tmp_path):
     try:
-        san = native.build_sanitized(tmp_path)
+        san = native.build_sanitized()
     except RuntimeError as e:
         if "sanitize" in str(e) or "asan" in str(e):
             pytest.skip("sanitizer runtime not installed")

@@ -15,9 +15,9 @@ pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="no host com
 
 
 @pytest.fixture(scope="module")
-def san(tmp_path_factory):
+def san():
     try:
-        return native.build_sanitized(tmp_path_factory.mktemp("san"))
+        return native.build_sanitized()
     except RuntimeError as e:                                   # a toolchain without the sanitizer runtimes
         if "sanitize" in str(e) or "asan" in str(e):
             pytest.skip("sanitizer runtime not installed")

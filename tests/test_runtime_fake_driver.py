@@ -57,7 +57,7 @@ def sanitized_module(tmp_path_factory):
     preload = native.sanitizer_preload()
     if not preload or not all(os.path.exists(p) for p in preload.split()):
         pytest.skip("no shared AddressSanitizer runtime")
-    return native.build_sanitized(tmp_path_factory.mktemp("san_runtime")), preload
+    return native.build_sanitized(), preload
 
 
 @pytest.fixture(params=["plain", "sanitized"])
