@@ -695,3 +695,27 @@ def test_symmetric_memory_bootstrap_over_gloo_ranks(fake_lib, tmp_path):
         assert text.count("multicast_bind") == 1 and text.count("multicast_unbind") == 1
         assert "mem_release live_handles=0" in text.splitlines()[-1]
         assert not any(bad in text for bad in ("bad_release", "bad_unmap", "bad_unbind", "address_free_while_mapped"))
+
+
+def test_profiler_adapter_logs_each_execute_on_rank_zero_only(fake_lib, compiled, tmp_path):
+    path, _ = compiled
+    fake = FakeEnv(fake_lib, None, None)
+    out = run_child(fake, f"""
+        import os
+        from nkipy_b200.spike import SpikeProfiler, SpikeTensor, get_spike_singleton
+        rt = get_spike_singleton()
+        m = rt.load_model({path!r}, 0, False, 0, 1)
+        info = rt.get_tensor_info(m)
+        ins = {{n: SpikeTensor.empty(tuple(t.shape), np.float32, n).tensor_ref for n, t in dict(info.inputs).items()}}
+        outs = {{n: SpikeTensor.empty(tuple(t.shape), np.float32, n).tensor_ref for n, t in dict(info.outputs).items()}}
+        for rank in (0, 1):
+            prof = SpikeProfiler(rt, log_dir={str(tmp_path)!r}, rank=rank)
+            prof.execute(m, ins, outs)
+            prof.execute(m, ins, outs)
+            assert prof.sm_count == rt.sm_count                    # everything else is passed through
+        print(sorted(os.listdir({str(tmp_path)!r})), os.getpid())
+    """)
+    files, pid = out.strip().rsplit(" ", 1)
+    assert "debug_rank_0.txt" in files and "debug_rank_1.txt" not in files
+    text = (tmp_path / "debug_rank_0.txt").read_text()
+    assert text.count(f"PID {pid}\n") == 2 and text.count("SOURCE ") == 2 and text.count(f"({path})") == 2
